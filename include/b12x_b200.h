@@ -1,0 +1,113 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the b12x block-scaled GEMM hot path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches on that
+ * stream, returns 0 on success or a negative B12X_B200_ERR_* code, and never allocates,
+ * synchronises or throws. Pointers must be device pointers the caller has validated; the
+ * functions re-check only what a wrong value would turn into a device fault (alignment,
+ * divisibility, null). Tensors are row-major and dense unless a leading dimension is given.
+ *
+ * Scale-factor ("MMA") layout used by all entry points: 512-byte atoms that cover 128 rows x
+ * 4 scale columns, atom order [row_tile][col_tile] with col_tile = ceil(scale_cols / 4) atoms
+ * per row tile, byte in atom = (r % 32) * 16 + ((r / 32) % 4) * 4 + (c % 4). This is the
+ * layout the reference stores (b12x/_lib/utils.py:384-407, b12x/_lib/intrinsics.py:62-93).
+ *
+ * Citations name the reference interface each function stands in for, as
+ * path:line inside the b12x source tree.
+ */
+#ifndef B12X_B200_H_
+#define B12X_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b12x_b200_stream_t;
+
+enum {
+  B12X_B200_OK = 0,
+  B12X_B200_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad enum, bad size               */
+  B12X_B200_ERR_ALIGNMENT = -2,        /* pointer / leading dimension not 16-byte aligned */
+  B12X_B200_ERR_UNSUPPORTED = -3,      /* shape or option outside what the kernels cover  */
+  B12X_B200_ERR_CUDA = -4,             /* a CUDA runtime / driver call failed             */
+  B12X_B200_ERR_NO_DEVICE_CODE = -5    /* the device is not compute capability 10.x       */
+};
+
+/* Operand recipes. */
+enum {
+  B12X_B200_KIND_MXFP8 = 0, /* E4M3 codes, UE8M0 scale per 32 elements of K              */
+  B12X_B200_KIND_NVFP4 = 1  /* packed E2M1 codes, UE4M3 (E4M3) scale per 16 elements     */
+};
+
+/* Element types of dense tensors. */
+enum {
+  B12X_B200_BF16 = 0,
+  B12X_B200_FP16 = 1,
+  B12X_B200_FP32 = 2
+};
+
+/* Library identification: "b12x_b200 <version> sm_100a". */
+const char* b12x_b200_version(void);
+
+/* Last CUDA error text seen by this library on the calling thread ("" if none). */
+const char* b12x_b200_last_error(void);
+
+/*
+ * Block-scaled GEMM  C[M,N] = cvt(alpha * (A . SFA) (B . SFB)^T).
+ * Replaces dense_gemm / b12x::dense_gemm_launch for the NVFP4 and MXFP8 recipes with L = 1
+ * (b12x/_lib/dense_gemm.py:7068-7098, 6335-6373; device kernel :1459-4157).
+ *
+ *   a      [M, K] codes (K bytes per row for MXFP8, K/2 bytes for NVFP4), K-major
+ *   b      [N, K] codes, same packing
+ *   sfa    scale atoms of A: ceil(M/128) x ceil(K / (4*vec)) atoms, vec = 32 / 16
+ *   sfb    scale atoms of B: ceil(N/128) x the same
+ *   c      [M, ldc] output of c_dtype
+ *   alpha  device FP32 scalar read by the kernel at run time, or NULL for 1
+ *   block_n 0 = choose, else one of 32, 64, 128, 192, 224, 256
+ *   sm_count 0 = all SMs of the current device
+ *   status device int32 the kernel raises to a non-zero KernelStatus when a bounded wait
+ *          ran out; may be NULL
+ */
+int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const void* b,
+                               const void* sfb, void* c, int c_dtype, const float* alpha,
+                               int64_t m, int64_t n, int64_t k, int64_t ldc, int block_n,
+                               int sm_count, int* status, b12x_b200_stream_t stream);
+
+/*
+ * MXFP8 row quantizer. Replaces quantize_mxfp8_rows_cute
+ * (b12x/_lib/quant/mxfp8_rows.py:398-434; kernel :88-269), numerics of
+ * quantize_mxfp8_rows_torch (b12x/gemm/_shared/wo_mxfp8.py:1884-1918).
+ *
+ *   src        [M, ld_src] BF16 or FP16, K % 32 == 0
+ *   values     [M, K] E4M3 bytes
+ *   scale_rows [M, K/32] UE8M0 bytes, may be NULL
+ *   scale_mma  atoms for ceil(M/128) x ceil(K/128); may be NULL. Bytes of rows >= M and of
+ *              scale columns >= K/32 inside those atoms are set to 127.
+ */
+int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src, void* values,
+                                  void* scale_rows, void* scale_mma, int64_t m, int64_t k,
+                                  b12x_b200_stream_t stream);
+
+/*
+ * NVFP4 row quantizer. Replaces Bf16ToFp4TmaKernel / compile_bf16_to_fp4_tma(...).launch
+ * (b12x/quantization/nvfp4/_kernel.py:250-518, _impl.py:117-224), numerics of
+ * quantize_grouped_nvfp4_torch (b12x/_lib/intrinsics.py:149-193). Unlike the reference
+ * kernel M need not be a multiple of 128.
+ *
+ *   src          [M, ld_src] BF16 or FP16, K % 16 == 0 and K % 32 == 0 for packed rows
+ *   global_scale device FP32 scalar (448 * 6 / amax of the tensor), read at run time
+ *   packed       [M, K/2] bytes, low nibble = even k
+ *   scale_mma    atoms for ceil(M/128) x ceil(K/64); bytes of rows >= M and of scale
+ *                columns >= K/16 inside those atoms are set to 0.
+ */
+int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int64_t ld_src,
+                                  const float* global_scale, void* packed, void* scale_mma,
+                                  int64_t m, int64_t k, b12x_b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B12X_B200_H_ */

@@ -1,0 +1,91 @@
+"""ctypes binding of the C-ABI library ``_b12x_b200.so`` (declared in include/b12x_b200.h).
+
+The library is built in-tree by :mod:`sparkinfer_b200.build`. There is no fallback: if the
+shared object is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from threading import Lock
+
+_LIB_NAME = "_b12x_b200.so"
+_LOCK = Lock()
+_LIB: ctypes.CDLL | None = None
+
+KIND_MXFP8 = 0
+KIND_NVFP4 = 1
+DT_BF16 = 0
+DT_FP16 = 1
+DT_FP32 = 2
+
+_c_void_p = ctypes.c_void_p
+_c_int = ctypes.c_int
+_c_i64 = ctypes.c_int64
+
+# name -> (restype, argtypes); one entry per function declared in include/b12x_b200.h.
+SIGNATURES = {
+    "b12x_b200_version": (ctypes.c_char_p, []),
+    "b12x_b200_last_error": (ctypes.c_char_p, []),
+    "b12x_b200_gemm_blockscaled": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_void_p],
+    ),
+    "b12x_b200_quantize_mxfp8_rows": (
+        _c_int,
+        [_c_void_p, _c_int, _c_i64, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_void_p],
+    ),
+    "b12x_b200_quantize_nvfp4_rows": (
+        _c_int,
+        [_c_void_p, _c_int, _c_i64, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_void_p],
+    ),
+}
+
+
+class NativeLibraryError(RuntimeError):
+    """The CUDA extension is missing, failed to load, or a call returned an error."""
+
+
+def library_path() -> Path:
+    override = os.environ.get("B12X_B200_LIBRARY")
+    return Path(override) if override else Path(__file__).resolve().parent / _LIB_NAME
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared object once and declare every prototype."""
+    global _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = library_path()
+        if not path.exists():
+            raise NativeLibraryError(
+                f"{path} not found: build it with `python -m sparkinfer_b200.build` "
+                "(there is no CPU or PyTorch fallback for these ops)"
+            )
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as exc:  # pragma: no cover - depends on the machine
+            raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _LIB = lib
+        return lib
+
+
+def last_error() -> str:
+    return load().b12x_b200_last_error().decode("utf-8", "replace")
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeLibraryError(f"{what} failed with code {code}: {last_error()}")
+
+
+def version() -> str:
+    return load().b12x_b200_version().decode()

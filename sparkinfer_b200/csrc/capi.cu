@@ -1,0 +1,285 @@
+// Host side of the C ABI: argument checks, TMA descriptor encoding, tile choice, launches.
+#include "../../include/b12x_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gemm_blockscaled.cuh"
+#include "quantize.cuh"
+
+namespace b12x_b200 {
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int fail_cuda(cudaError_t err, const char* what) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(err));
+  return B12X_B200_ERR_CUDA;
+}
+
+int fail(int code, const char* what) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s", what);
+  return code;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime so the library carries no link-time
+// dependency on libcuda (it must load on machines without a driver).
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// K-major byte matrix [rows, row_bytes] -> boxes of 128 bytes x box_rows, 128-byte swizzle.
+int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                     uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed (%d)", int(r));
+    return B12X_B200_ERR_CUDA;
+  }
+  return B12X_B200_OK;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+};
+
+int device_info(DeviceInfo* out) {
+  static DeviceInfo cache[64];
+  static bool have[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 0 || dev >= 64) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "device index out of range");
+  if (!have[dev]) {
+    err = cudaDeviceGetAttribute(&cache[dev].sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaDeviceGetAttribute");
+    err = cudaDeviceGetAttribute(&cache[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaDeviceGetAttribute");
+    have[dev] = true;
+  }
+  *out = cache[dev];
+  return B12X_B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Tile width: fewest (waves x per-tile cost). The per-tile cost model is the bytes one k-step
+// pulls through shared memory, (128 + BN) rows of 128 bytes, which tracks both the MMA time
+// (proportional to BN) and the operand traffic.
+int choose_block_n(int64_t m, int64_t n, int sms) {
+  static const int candidates[] = {256, 224, 192, 128, 64, 32};
+  const int64_t tiles_m = (m + 127) / 128;
+  int best = 128;
+  double best_cost = 1e300;
+  for (int bn : candidates) {
+    const int64_t tiles = tiles_m * ((n + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double cost = double(waves) * (128 + bn);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <int KIND, int BN>
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int grid,
+                cudaStream_t stream) {
+  using T = GemmTile<KIND, BN>;
+  // The large dynamic shared memory opt-in is per device: set it the first time each device
+  // launches this instantiation.
+  static bool set_for[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set_for[dev]) {
+    const cudaError_t attr_err =
+        cudaFuncSetAttribute(gemm_blockscaled_kernel<KIND, BN>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+    if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    set_for[dev] = true;
+  }
+  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled launch");
+  return B12X_B200_OK;
+}
+
+template <int KIND>
+int dispatch_block_n(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                     const GemmParams& p, int grid, cudaStream_t stream) {
+  switch (bn) {
+    case 32: return launch_gemm<KIND, 32>(map_a, map_b, p, grid, stream);
+    case 64: return launch_gemm<KIND, 64>(map_a, map_b, p, grid, stream);
+    case 128: return launch_gemm<KIND, 128>(map_a, map_b, p, grid, stream);
+    case 192: return launch_gemm<KIND, 192>(map_a, map_b, p, grid, stream);
+    case 224: return launch_gemm<KIND, 224>(map_a, map_b, p, grid, stream);
+    case 256: return launch_gemm<KIND, 256>(map_a, map_b, p, grid, stream);
+    default: return fail(B12X_B200_ERR_INVALID_ARGUMENT, "block_n must be 32/64/128/192/224/256");
+  }
+}
+
+}  // namespace
+}  // namespace b12x_b200
+
+using namespace b12x_b200;
+
+extern "C" const char* b12x_b200_version(void) { return "b12x_b200 0.1.0 sm_100a"; }
+
+extern "C" const char* b12x_b200_last_error(void) { return g_last_error; }
+
+extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const void* b,
+                                          const void* sfb, void* c, int c_dtype,
+                                          const float* alpha, int64_t m, int64_t n, int64_t k,
+                                          int64_t ldc, int block_n, int sm_count, int* status,
+                                          b12x_b200_stream_t stream) {
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
+  if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
+  if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (m == 0 || n == 0) return B12X_B200_OK;
+  if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
+  if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
+  const int64_t row_bytes = (kind == B12X_B200_KIND_MXFP8) ? k : k / 2;
+  if (row_bytes % 16 != 0) return fail(B12X_B200_ERR_ALIGNMENT, "operand rows must be 16-byte multiples");
+  if (!aligned16(a) || !aligned16(b) || !aligned16(sfa) || !aligned16(sfb))
+    return fail(B12X_B200_ERR_ALIGNMENT, "operand and scale pointers must be 16-byte aligned");
+
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  const int bn = block_n > 0 ? block_n : choose_block_n(m, n, sms);
+
+  CUtensorMap map_a, map_b;
+  rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(row_bytes), 128);
+  if (rc != B12X_B200_OK) return rc;
+  rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(row_bytes), uint32_t(bn));
+  if (rc != B12X_B200_OK) return rc;
+
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.c = c;
+  p.alpha = alpha;
+  p.status = status;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.ldc = int(ldc);
+  p.out_dtype = c_dtype;
+  p.tiles_m = int((m + 127) / 128);
+  p.tiles_n = int((n + bn - 1) / bn);
+  p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
+  p.group_m = 16;
+  const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+  const int grid = int(tiles < sms ? tiles : sms);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == B12X_B200_KIND_MXFP8) return dispatch_block_n<kMxfp8>(bn, map_a, map_b, p, grid, s);
+  return dispatch_block_n<kNvfp4>(bn, map_a, map_b, p, grid, s);
+}
+
+extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src,
+                                             void* values, void* scale_rows, void* scale_mma,
+                                             int64_t m, int64_t k, b12x_b200_stream_t stream) {
+  if (src_dtype != B12X_B200_BF16 && src_dtype != B12X_B200_FP16)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "source must be BF16 or FP16");
+  if (m < 0 || k <= 0 || m > INT32_MAX - 128 || k > INT32_MAX - 128)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad size");
+  if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
+  if (m == 0) return B12X_B200_OK;
+  if (!src || !values) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ld_src < k || ld_src % 8 != 0 || !aligned16(src) || !aligned16(values))
+    return fail(B12X_B200_ERR_ALIGNMENT, "source rows and values must be 16-byte aligned");
+  const int k_atoms = int((k + 127) / 128);
+  const int rows_cover = scale_mma ? int((m + 127) / 128) * 128 : int(m);
+  const int k_cover = scale_mma ? k_atoms * 128 : int(k);
+  const int64_t threads = int64_t(rows_cover) * (k_cover / 16);
+  const int64_t blocks = (threads + 255) / 256;
+  if (blocks > INT32_MAX) return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (src_dtype == B12X_B200_BF16)
+    quantize_mxfp8_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(src), ld_src, static_cast<uint8_t*>(values),
+        static_cast<uint8_t*>(scale_rows), static_cast<uint8_t*>(scale_mma), int(m), int(k),
+        rows_cover, k_cover, k_atoms);
+  else
+    quantize_mxfp8_rows_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(
+        static_cast<const __half*>(src), ld_src, static_cast<uint8_t*>(values),
+        static_cast<uint8_t*>(scale_rows), static_cast<uint8_t*>(scale_mma), int(m), int(k),
+        rows_cover, k_cover, k_atoms);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "quantize_mxfp8_rows launch");
+  return B12X_B200_OK;
+}
+
+extern "C" int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int64_t ld_src,
+                                             const float* global_scale, void* packed,
+                                             void* scale_mma, int64_t m, int64_t k,
+                                             b12x_b200_stream_t stream) {
+  if (src_dtype != B12X_B200_BF16 && src_dtype != B12X_B200_FP16)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "source must be BF16 or FP16");
+  if (m < 0 || k <= 0 || m > INT32_MAX - 128 || k > INT32_MAX - 128)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad size");
+  if (k % 16 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 16");
+  if (m == 0) return B12X_B200_OK;
+  if (!src || !packed || !scale_mma || !global_scale)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ld_src < k || ld_src % 8 != 0 || !aligned16(src) || (reinterpret_cast<uintptr_t>(packed) & 7))
+    return fail(B12X_B200_ERR_ALIGNMENT, "source rows must be 16-byte and packed 8-byte aligned");
+  const int k_atoms = int((k + 63) / 64);
+  const int rows_cover = int((m + 127) / 128) * 128;
+  const int k_cover = k_atoms * 64;
+  const int64_t threads = int64_t(rows_cover) * (k_cover / 16);
+  const int64_t blocks = (threads + 255) / 256;
+  if (blocks > INT32_MAX) return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (src_dtype == B12X_B200_BF16)
+    quantize_nvfp4_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(src), ld_src, global_scale,
+        static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scale_mma), int(m), int(k),
+        rows_cover, k_cover, k_atoms);
+  else
+    quantize_nvfp4_rows_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(
+        static_cast<const __half*>(src), ld_src, global_scale, static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(scale_mma), int(m), int(k), rows_cover, k_cover, k_atoms);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "quantize_nvfp4_rows launch");
+  return B12X_B200_OK;
+}

@@ -1,0 +1,335 @@
+// Persistent, warp-specialised block-scaled GEMM for sm_100a:
+//
+//     C[M,N] = cvt(alpha * sum_k (A[M,K] . SFA) (B[N,K] . SFB)^T)
+//
+// A and B are K-major. Two operand recipes share one kernel template:
+//   kMxfp8 : E4M3 codes, one UE8M0 scale per 32 elements of K  (tcgen05 kind::mxf8f6f4)
+//   kNvfp4 : packed E2M1 codes (low nibble = even k), one UE4M3 scale per 16 elements
+//            (tcgen05 kind::mxf4nvf4, scale_vec::4X)
+// Scale factors live in global memory as 512-byte atoms covering 128 rows x 4 scale columns,
+// atom order [row_tile][k_tile], byte (r%32)*16 + ((r/32)%4)*4 + (kb%4) inside an atom. That is
+// byte for byte the chunk tcgen05.cp moves from shared to tensor memory, so the atoms are
+// streamed with plain bulk copies and never re-arranged.
+//
+// Roles inside one CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2..5 = epilogue (TMEM -> registers -> global). Accumulators sit in TMEM, double
+// buffered when 2*BN plus the scale columns fit in the 512 columns, so the epilogue of tile i
+// overlaps the main loop of tile i+1. One stage of the shared-memory ring holds 128 bytes of K
+// for 128 rows of A and BN rows of B plus that slice's scale atoms.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace b12x_b200 {
+
+enum OperandKind : int { kMxfp8 = 0, kNvfp4 = 1 };
+enum OutDtype : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
+
+template <int KIND, int BN>
+struct GemmTile {
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 in [32,256]");
+  static constexpr int BM = 128;
+  static constexpr int kRowBytes = 128;                       // bytes of K per stage and row
+  static constexpr int kMmasPerStage = 4;                     // 32 bytes of K per instruction
+  static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
+  static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
+  static constexpr int kSfVec = (KIND == kMxfp8) ? 32 : 16;
+  static constexpr int kElemsPerAtom = kSfVec * 4;            // K covered by one scale atom
+  static constexpr int kKAtoms = kElemsPerStage / kElemsPerAtom;  // 1 (MXFP8) or 4 (NVFP4)
+  // Row atoms of SFB a tile can touch: tiles that are not multiples of 128 start inside an atom.
+  static constexpr int kSfbRowAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 96 + 127) / 128;
+  static constexpr int kABytes = BM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kSfaBytes = kKAtoms * 512;
+  static constexpr int kSfbBytes = kSfbRowAtoms * kKAtoms * 512;
+  static constexpr int kStageBytes =
+      ((kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024) * 1024;
+  static constexpr int kSfaCols = kKAtoms * 4;
+  static constexpr int kSfbCols = kSfbRowAtoms * kKAtoms * 4;
+  static constexpr int kAccStages = (2 * BN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
+  static constexpr int kSfaCol0 = kAccStages * BN;
+  static constexpr int kSfbCol0 = kSfaCol0 + kSfaCols;
+  static_assert(kSfbCol0 + kSfbCols <= 512, "tensor memory overflow");
+  static constexpr int kMaxSmem = 227 * 1024;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kStagesRaw = (kMaxSmem - kBarrierBytes - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+};
+
+struct GemmParams {
+  const uint8_t* sfa;    // scale atoms of A: [ceil(M/128)][k_atoms][512]
+  const uint8_t* sfb;    // scale atoms of B: [ceil(N/128)][k_atoms][512]
+  void* c;               // [M, ldc] row-major
+  const float* alpha;    // device scalar, may be null (= 1)
+  int* status;           // device status word, may be null
+  int m, n, k;           // K in elements
+  int ldc;               // elements
+  int out_dtype;         // OutDtype
+  int tiles_m, tiles_n;
+  int k_atoms_total;     // scale atoms along K in global memory
+  int group_m;           // tile-order grouping along M (L2 reuse)
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
+                                            int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
+  const int in_group = tile - g * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Writes 32 consecutive output columns of one row. `vals` already carry alpha.
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col0,
+                                                const float (&vals)[32]) {
+  if (row >= p.m || col0 >= p.n) return;
+  const size_t base = static_cast<size_t>(row) * p.ldc + col0;
+  const bool full = (col0 + 32 <= p.n);
+  if (p.out_dtype == kOutFp32) {
+    float* out = static_cast<float*>(p.c) + base;
+    if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(out)[i] =
+            make_float4(vals[4 * i], vals[4 * i + 1], vals[4 * i + 2], vals[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.n) out[i] = vals[i];
+    }
+    return;
+  }
+  uint16_t* out = static_cast<uint16_t*>(p.c) + base;
+  uint32_t packed[16];
+  if (p.out_dtype == kOutBf16) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) packed[i] = pack_bf16x2(vals[2 * i], vals[2 * i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) packed[i] = pack_f16x2(vals[2 * i], vals[2 * i + 1]);
+  }
+  if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<uint4*>(out)[i] =
+          make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < p.n)
+        out[i] = static_cast<uint16_t>((i & 1) ? (packed[i >> 1] >> 16) : (packed[i >> 1] & 0xFFFF));
+  }
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
+                        const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using T = GemmTile<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled operand tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_area = smem + T::kStages * T::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + T::kStages;
+  uint64_t* acc_full_bar = empty_bar + T::kStages;
+  uint64_t* acc_empty_bar = acc_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_tiles = (p.k + T::kElemsPerStage - 1) / T::kElemsPerStage;
+  const int n_row_atoms_b = (p.n + 127) / 128;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        const int m0 = tm * T::BM;
+        const int n0 = tn * BN;
+        const int sfb_atom0 = n0 / 128;
+        const int sfb_atoms =
+            min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            *abort_flag = 1;
+            if (p.status) atomicMax(p.status, kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + stage * T::kStageBytes;
+          const int katom0 = kt * T::kKAtoms;
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+          mbar_arrive_expect_tx(&full_bar[stage],
+                                T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
+          tma_load_2d(st, &map_a, &full_bar[stage], kt * T::kRowBytes, m0);
+          tma_load_2d(st + T::kABytes, &map_b, &full_bar[stage], kt * T::kRowBytes, n0);
+          bulk_load(st + T::kABytes + T::kBBytes,
+                    p.sfa + (static_cast<size_t>(tm) * p.k_atoms_total + katom0) * 512, sf_bytes,
+                    &full_bar[stage]);
+          for (int ra = 0; ra < sfb_atoms; ++ra)
+            bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
+                      p.sfb + (static_cast<size_t>(sfb_atom0 + ra) * p.k_atoms_total + katom0) * 512,
+                      sf_bytes, &full_bar[stage]);
+          if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_base = make_idesc_block_scaled(
+          128, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        const int n0 = tn * BN;
+        const int sfb_atom0 = n0 / 128;
+        const int sfb_atoms =
+            min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
+        const uint32_t sfb_col_shift = static_cast<uint32_t>((n0 % 128) / 32);
+        const int acc = iter % T::kAccStages;
+        const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+        if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status) atomicMax(p.status, kStatusMmaTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_taddr = tmem_base + acc * BN;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            *abort_flag = 1;
+            if (p.status) atomicMax(p.status, kStatusMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t st = smem_addr_u32(smem + stage * T::kStageBytes);
+          const int k0 = kt * T::kElemsPerStage;
+          const int mmas = min(T::kMmasPerStage, (p.k - k0 + T::kElemsPerMma - 1) / T::kElemsPerMma);
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - kt * T::kKAtoms);
+          const uint32_t sfa_smem = st + T::kABytes + T::kBBytes;
+          const uint32_t sfb_smem = sfa_smem + T::kSfaBytes;
+          for (int ka = 0; ka < katoms; ++ka) {
+            tc_copy_sf_atom(tmem_base + T::kSfaCol0 + ka * 4, make_sf_chunk_desc(sfa_smem + ka * 512));
+            for (int ra = 0; ra < sfb_atoms; ++ra)
+              tc_copy_sf_atom(tmem_base + T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
+                              make_sf_chunk_desc(sfb_smem + (ra * T::kKAtoms + ka) * 512));
+          }
+          const uint64_t adesc = make_kmajor_sw128_desc(st);
+          const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
+          for (int j = 0; j < mmas; ++j) {
+            const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+            // 32 bytes of K per instruction: +2 in the (address >> 4) field.
+            if (KIND == kMxfp8) {
+              tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                          idesc_with_sf_ids(idesc_base, j, j), accumulate,
+                          tmem_base + T::kSfaCol0, tmem_base + T::kSfbCol0 + sfb_col_shift);
+            } else {
+              tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
+                          tmem_base + T::kSfaCol0 + j * 4,
+                          tmem_base + T::kSfbCol0 + j * T::kSfbRowAtoms * 4 + sfb_col_shift);
+            }
+          }
+          tc_commit(&empty_bar[stage]);
+          if (kt == k_tiles - 1) tc_commit(&acc_full_bar[acc]);
+          if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quarter = warp & 3;  // TMEM lanes this warp may read
+    const float alpha = p.alpha ? *p.alpha : 1.0f;
+    int iter = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int acc = iter % T::kAccStages;
+      const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+      if (!mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag)) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tm * T::BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tmem_load_32cols(taddr + c * 32, raw);
+        tmem_load_wait();
+        float vals[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
+        store_row_chunk(p, row, tn * BN + c * 32, vals);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b12x_b200
