@@ -65,7 +65,7 @@ const char* b12x_b200_last_error(void);
  *   sfb    scale atoms of B: ceil(N/128) x the same
  *   c      [M, ldc] output of c_dtype
  *   alpha  device FP32 scalar read by the kernel at run time, or NULL for 1
- *   block_n 0 = choose, else one of 32, 64, 128, 192, 224, 256
+ *   block_n 0 = choose, else one of 64, 128, 192, 256
  *   sm_count 0 = all SMs of the current device
  *   status device int32 the kernel raises to a non-zero KernelStatus when a bounded wait
  *          ran out; may be NULL

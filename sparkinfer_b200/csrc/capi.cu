@@ -98,7 +98,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // pulls through shared memory, (128 + BN) rows of 128 bytes, which tracks both the MMA time
 // (proportional to BN) and the operand traffic.
 int choose_block_n(int64_t m, int64_t n, int sms) {
-  static const int candidates[] = {256, 224, 192, 128, 64, 32};
+  static const int candidates[] = {256, 192, 128, 64};
   const int64_t tiles_m = (m + 127) / 128;
   int best = 128;
   double best_cost = 1e300;
@@ -140,13 +140,11 @@ template <int KIND>
 int dispatch_block_n(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b,
                      const GemmParams& p, int grid, cudaStream_t stream) {
   switch (bn) {
-    case 32: return launch_gemm<KIND, 32>(map_a, map_b, p, grid, stream);
     case 64: return launch_gemm<KIND, 64>(map_a, map_b, p, grid, stream);
     case 128: return launch_gemm<KIND, 128>(map_a, map_b, p, grid, stream);
     case 192: return launch_gemm<KIND, 192>(map_a, map_b, p, grid, stream);
-    case 224: return launch_gemm<KIND, 224>(map_a, map_b, p, grid, stream);
     case 256: return launch_gemm<KIND, 256>(map_a, map_b, p, grid, stream);
-    default: return fail(B12X_B200_ERR_INVALID_ARGUMENT, "block_n must be 32/64/128/192/224/256");
+    default: return fail(B12X_B200_ERR_INVALID_ARGUMENT, "block_n must be 64, 128, 192 or 256");
   }
 }
 

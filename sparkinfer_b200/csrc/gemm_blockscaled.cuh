@@ -27,7 +27,9 @@ enum OutDtype : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
 
 template <int KIND, int BN>
 struct GemmTile {
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 in [32,256]");
+  // Tiles start on 64-row boundaries of B: the MMA accepts a scale-factor address shifted by two
+  // TMEM columns (64 rows) but faults on an odd column shift, so 32-row granularity is out.
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be a multiple of 64 in [64,256]");
   static constexpr int BM = 128;
   static constexpr int kRowBytes = 128;                       // bytes of K per stage and row
   static constexpr int kMmasPerStage = 4;                     // 32 bytes of K per instruction
@@ -37,7 +39,7 @@ struct GemmTile {
   static constexpr int kElemsPerAtom = kSfVec * 4;            // K covered by one scale atom
   static constexpr int kKAtoms = kElemsPerStage / kElemsPerAtom;  // 1 (MXFP8) or 4 (NVFP4)
   // Row atoms of SFB a tile can touch: tiles that are not multiples of 128 start inside an atom.
-  static constexpr int kSfbRowAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 96 + 127) / 128;
+  static constexpr int kSfbRowAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
   static constexpr int kABytes = BM * kRowBytes;
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kSfaBytes = kKAtoms * 512;
