@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -130,7 +131,9 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmPa
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
-  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, p);
+  GemmParams q = p;
+  q.num_stages = (p.num_stages >= 2 && p.num_stages <= T::kStages) ? p.num_stages : T::kStages;
+  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, q);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled launch");
   return B12X_B200_OK;
@@ -206,6 +209,12 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   p.tiles_n = int((n + bn - 1) / bn);
   p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
   p.group_m = 16;
+  p.num_stages = 0;  // filled per instantiation
+  p.debug_flags = 0;
+  if (const char* e = getenv("B12X_B200_DEBUG_FLAGS")) p.debug_flags = atoi(e);
+  if (const char* e = getenv("B12X_B200_STAGES")) p.num_stages = atoi(e);
+  p.prof = nullptr;
+  if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -72,6 +72,10 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int k_atoms_total;     // scale atoms along K in global memory
   int group_m;           // tile-order grouping along M (L2 reuse)
+  int num_stages;        // shared-memory ring depth actually used (<= GemmTile::kStages)
+  int debug_flags;       // bring-up switches: 1 = no MMA issue, 2 = no loads, 4 = no scale copies,
+                         // 8 = no global stores
+  long long* prof;       // optional cycle counters written by CTA 0 (bring-up only)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
@@ -179,137 +183,197 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // The CTA owns all 512 columns (one CTA per SM), so the allocation starts at column 0 and
+  // every TMEM address below is a compile-time constant. Anything else is reported and the
+  // CTA leaves without touching tensor memory.
   const uint32_t tmem_base = *tmem_slot;
+  if (tmem_base != 0) {
+    if (threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    return;
+  }
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int k_tiles = (p.k + T::kElemsPerStage - 1) / T::kElemsPerStage;
   const int n_row_atoms_b = (p.n + 127) / 128;
+  const uint32_t smem_u32 = smem_addr_u32(smem);
 
+  // All lanes of the producer and MMA warps walk their loops together (waits included) and one
+  // elected lane issues: the loop state stays warp-uniform, which keeps descriptor arithmetic
+  // on the uniform datapath instead of costing a register shuffle per tcgen05 operand.
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-        const int m0 = tm * T::BM;
-        const int n0 = tn * BN;
-        const int sfb_atom0 = n0 / 128;
-        const int sfb_atoms =
-            min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
-        for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
-            *abort_flag = 1;
-            if (p.status) atomicMax(p.status, kStatusProducerTimeout);
-            ok = false;
-            break;
-          }
-          uint8_t* st = smem + stage * T::kStageBytes;
-          const int katom0 = kt * T::kKAtoms;
-          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
-          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-          mbar_arrive_expect_tx(&full_bar[stage],
-                                T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
-          tma_load_2d(st, &map_a, &full_bar[stage], kt * T::kRowBytes, m0);
-          tma_load_2d(st + T::kABytes, &map_b, &full_bar[stage], kt * T::kRowBytes, n0);
-          bulk_load(st + T::kABytes + T::kBBytes,
-                    p.sfa + (static_cast<size_t>(tm) * p.k_atoms_total + katom0) * 512, sf_bytes,
-                    &full_bar[stage]);
-          for (int ra = 0; ra < sfb_atoms; ++ra)
-            bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
-                      p.sfb + (static_cast<size_t>(sfb_atom0 + ra) * p.k_atoms_total + katom0) * 512,
-                      sf_bytes, &full_bar[stage]);
-          if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    long long prof_wait = 0;
+    const long long prof_begin = clock64();
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int m0 = tm * T::BM;
+      const int n0 = tn * BN;
+      const int sfb_atom0 = n0 / 128;
+      const int sfb_atoms = min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
+      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(tm) * p.k_atoms_total * 512;
+      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const long long t0 = clock64();
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
         }
+        prof_wait += clock64() - t0;
+        if (elect_one()) {
+          uint8_t* st = smem + stage * T::kStageBytes;
+          uint64_t* bar = &full_bar[stage];
+          if (p.debug_flags & 2) {
+            mbar_arrive(bar);
+          } else {
+            const int katom0 = kt * T::kKAtoms;
+            const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+            const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+            mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
+            tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
+            tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0);
+            bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
+                      sf_bytes, bar);
+            for (int ra = 0; ra < sfb_atoms; ++ra)
+              bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
+                        sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
+                        sf_bytes, bar);
+          }
+        }
+        __syncwarp();
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       }
+    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) {
+      p.prof[0] = clock64() - prof_begin;
+      p.prof[1] = prof_wait;
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_base = make_idesc_block_scaled(
-          128, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
-      int stage = 0;
-      uint32_t phase = 0;
-      int iter = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
-        int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-        const int n0 = tn * BN;
-        const int sfb_atom0 = n0 / 128;
-        const int sfb_atoms =
-            min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
-        const uint32_t sfb_col_shift = static_cast<uint32_t>((n0 % 128) / 32);
-        const int acc = iter % T::kAccStages;
-        const uint32_t acc_phase = (iter / T::kAccStages) & 1;
-        if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+    constexpr uint32_t idesc_base = make_idesc_block_scaled(
+        128, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    int stage = 0;
+    uint32_t phase = 0;
+    int iter = 0;
+    bool ok = true;
+    long long prof_wait_full = 0, prof_wait_acc = 0, prof_issue = 0;
+    const long long prof_begin = clock64();
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const uint32_t sfb_col_shift = static_cast<uint32_t>(((tn * BN) % 128) / 32);
+      const int acc = iter % T::kAccStages;
+      const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+      const long long ta = clock64();
+      if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+        break;
+      }
+      prof_wait_acc += clock64() - ta;
+      tc_fence_after_sync();
+      const uint32_t d_taddr = acc * BN;
+      const uint32_t sfb_taddr = T::kSfbCol0 + sfb_col_shift;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const long long tf = clock64();
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
           *abort_flag = 1;
-          if (p.status) atomicMax(p.status, kStatusMmaTimeout);
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          ok = false;
           break;
         }
+        const long long ti = clock64();
+        prof_wait_full += ti - tf;
         tc_fence_after_sync();
-        const uint32_t d_taddr = tmem_base + acc * BN;
-        for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
-            *abort_flag = 1;
-            if (p.status) atomicMax(p.status, kStatusMmaTimeout);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t st = smem_addr_u32(smem + stage * T::kStageBytes);
-          const int k0 = kt * T::kElemsPerStage;
-          const int mmas = min(T::kMmasPerStage, (p.k - k0 + T::kElemsPerMma - 1) / T::kElemsPerMma);
-          const int katoms = min(T::kKAtoms, p.k_atoms_total - kt * T::kKAtoms);
-          const uint32_t sfa_smem = st + T::kABytes + T::kBBytes;
-          const uint32_t sfb_smem = sfa_smem + T::kSfaBytes;
-          for (int ka = 0; ka < katoms; ++ka) {
-            tc_copy_sf_atom(tmem_base + T::kSfaCol0 + ka * 4, make_sf_chunk_desc(sfa_smem + ka * 512));
-            for (int ra = 0; ra < sfb_atoms; ++ra)
-              tc_copy_sf_atom(tmem_base + T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
-                              make_sf_chunk_desc(sfb_smem + (ra * T::kKAtoms + ka) * 512));
+        const uint32_t st = smem_u32 + stage * T::kStageBytes;
+        const int mmas = min(T::kMmasPerStage,
+                             (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
+        if (elect_one()) {
+          // Scale atoms of this stage -> TMEM. Every atom slot of the stage is copied; slots the
+          // producer did not fill (edge of N or K) only feed masked columns or skipped MMAs.
+          if (!(p.debug_flags & 4)) {
+            const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
+#pragma unroll
+            for (int ka = 0; ka < T::kKAtoms; ++ka) {
+              tc_copy_sf_atom(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
+#pragma unroll
+              for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
+                tc_copy_sf_atom(T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
+                                sf_desc + ((T::kSfaBytes + (ra * T::kKAtoms + ka) * 512) >> 4));
+            }
           }
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
-          for (int j = 0; j < mmas; ++j) {
-            const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+          if (!(p.debug_flags & 1)) {
             // 32 bytes of K per instruction: +2 in the (address >> 4) field.
-            if (KIND == kMxfp8) {
-              tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
-                          idesc_with_sf_ids(idesc_base, j, j), accumulate,
-                          tmem_base + T::kSfaCol0, tmem_base + T::kSfbCol0 + sfb_col_shift);
+            if (mmas == T::kMmasPerStage) {
+#pragma unroll
+              for (int j = 0; j < T::kMmasPerStage; ++j) {
+                const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+                if (KIND == kMxfp8)
+                  tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
+                              sfb_taddr);
+                else
+                  tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
+                              T::kSfaCol0 + j * 4, sfb_taddr + j * T::kSfbRowAtoms * 4);
+              }
             } else {
-              tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
-                          tmem_base + T::kSfaCol0 + j * 4,
-                          tmem_base + T::kSfbCol0 + j * T::kSfbRowAtoms * 4 + sfb_col_shift);
+              for (int j = 0; j < mmas; ++j) {
+                const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+                if (KIND == kMxfp8)
+                  tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
+                              sfb_taddr);
+                else
+                  tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
+                              T::kSfaCol0 + j * 4, sfb_taddr + j * T::kSfbRowAtoms * 4);
+              }
             }
           }
           tc_commit(&empty_bar[stage]);
           if (kt == k_tiles - 1) tc_commit(&acc_full_bar[acc]);
-          if (++stage == T::kStages) { stage = 0; phase ^= 1; }
         }
+        __syncwarp();
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
+        prof_issue += clock64() - ti;
       }
+    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) {
+      p.prof[2] = clock64() - prof_begin;
+      p.prof[3] = prof_wait_full;
+      p.prof[4] = prof_wait_acc;
+      p.prof[5] = prof_issue;
     }
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // TMEM lanes this warp may read
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     int iter = 0;
+    long long prof_wait = 0;
+    const long long prof_begin = clock64();
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+      const long long tw = clock64();
       if (!mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag)) {
         *abort_flag = 1;
         if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
         break;
       }
+      prof_wait += clock64() - tw;
       tc_fence_after_sync();
       const int row = tm * T::BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t raw[32];
@@ -318,11 +382,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
-        store_row_chunk(p, row, tn * BN + c * 32, vals);
+        if (!(p.debug_flags & 8)) store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+    }
+    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
+      p.prof[6] = clock64() - prof_begin;
+      p.prof[7] = prof_wait;
     }
   }
 
@@ -330,7 +398,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(0, 512);
   }
 }
 

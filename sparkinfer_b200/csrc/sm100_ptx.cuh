@@ -21,6 +21,7 @@ enum KernelStatus : int {
   kStatusMmaTimeout = 2,        // MMA issuer waited too long for a full stage / free accumulator
   kStatusEpilogueTimeout = 3,   // epilogue waited too long for a finished accumulator
   kStatusReduceTimeout = 4,     // split-K reduction waited too long for its peers
+  kStatusTmemLayout = 5,        // tensor memory was not handed out from column 0
 };
 
 // Polls allowed on one mbarrier phase before a wait gives up. Legitimate waits on this
