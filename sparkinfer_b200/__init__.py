@@ -1,0 +1,116 @@
+"""B200-native implementation of the b12x block-scaled GEMM hot path.
+
+Ops live at ``sparkinfer_b200.<group>.<op>`` with the reference's grammar
+(b12x/__init__.py:7-11, 41-62): planned ops ``Caps -> plan() -> bind() -> run()``, one-shot
+ops as plain functions. Importing this package (or an op package) imports neither torch nor
+the CUDA library; entry points resolve lazily on first attribute access.
+
+    from sparkinfer_b200.gemm import blockscaled, mxfp8_linear, block_fp8_linear
+    from sparkinfer_b200.quantization import nvfp4, mxfp8
+
+:func:`install_as_b12x` additionally exposes the package under the name ``b12x`` so code
+written against the reference's import paths for these ops runs unchanged.
+"""
+
+from __future__ import annotations
+
+import importlib
+import sys
+from typing import Any
+
+from ._lib.meta import OpMeta, Provenance
+from ._lib.runtime_control import (
+    KernelResolutionFrozenError,
+    compilation_frozen,
+    freeze_compilation,
+    freeze_kernel_resolution,
+    kernel_resolution_frozen,
+    unfreeze_compilation,
+    unfreeze_kernel_resolution,
+)
+
+__version__ = "0.1.0"
+
+# group -> op names; one directory per op, checked by tests/test_registry.py.
+_OPS: dict[str, tuple[str, ...]] = {
+    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear"),
+    "quantization": ("nvfp4", "mxfp8"),
+}
+
+
+def list_ops() -> list[OpMeta]:
+    """META of every op, in registry order."""
+    return [
+        importlib.import_module(f"{__name__}.{group}.{name}").META
+        for group, names in _OPS.items()
+        for name in names
+    ]
+
+
+def find_op(qualname: str) -> OpMeta:
+    """META of ``"group.name"``; ``KeyError`` when unknown."""
+    group, _, name = qualname.partition(".")
+    if name not in _OPS.get(group, ()):
+        raise KeyError(f"unknown op {qualname!r}")
+    return importlib.import_module(f"{__name__}.{group}.{name}").META
+
+
+def clear_all_caches() -> None:
+    """Drop host-side caches (alpha scalars, small-M quantization scratch, status buffers).
+    Kernels are compiled ahead of time, so there is no compile cache to clear."""
+    dense = sys.modules.get(f"{__name__}._lib.dense_gemm")
+    if dense is not None:
+        dense._ALPHA_ONE_CACHE.clear()
+        dense._FUSED_QUANT_SCRATCH.clear()
+    launch = sys.modules.get(f"{__name__}._lib.launch")
+    if launch is not None:
+        launch._STATUS.clear()
+
+
+def install_as_b12x() -> None:
+    """Alias this package (and its sub-packages as they load) to the name ``b12x``."""
+    import importlib.abc
+    import importlib.util
+
+    if isinstance(sys.modules.get("b12x"), type(sys)) and sys.modules["b12x"] is not sys.modules[__name__]:
+        raise RuntimeError("a different 'b12x' package is already imported")
+    sys.modules["b12x"] = sys.modules[__name__]
+
+    class _Alias(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+        def find_spec(self, fullname, path=None, target=None):
+            if fullname == "b12x" or fullname.startswith("b12x."):
+                real = __name__ + fullname[len("b12x"):]
+                try:
+                    module = importlib.import_module(real)
+                except ImportError:
+                    return None
+                sys.modules[fullname] = module
+                return importlib.util.spec_from_loader(fullname, self, origin=real)
+            return None
+
+        def create_module(self, spec):
+            return sys.modules[spec.name]
+
+        def exec_module(self, module):
+            return None
+
+    if not any(type(f).__name__ == "_Alias" for f in sys.meta_path):
+        sys.meta_path.insert(0, _Alias())
+
+
+__all__ = [
+    "OpMeta", "Provenance", "list_ops", "find_op", "clear_all_caches", "install_as_b12x",
+    "KernelResolutionFrozenError", "freeze_kernel_resolution", "unfreeze_kernel_resolution",
+    "kernel_resolution_frozen", "freeze_compilation", "unfreeze_compilation",
+    "compilation_frozen", "ScratchBufferSpec",
+]
+
+
+def __getattr__(name: str) -> Any:
+    if name == "ScratchBufferSpec":  # needs torch; resolved lazily
+        from ._lib.scratch import ScratchBufferSpec
+
+        return ScratchBufferSpec
+    if name in _OPS:
+        return importlib.import_module(f"{__name__}.{name}")
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -1,0 +1,375 @@
+"""Dense block-scaled GEMM entry points: ``C = cvt(alpha * (A . SFA) @ (B . SFB)^T)``.
+
+Drop-in for the reference's ``dense_gemm`` / ``dense_gemm_fused_quant_a`` and the torch
+custom ops ``b12x::dense_gemm_launch`` / ``b12x::dense_gemm_launch_functional``
+(b12x/_lib/dense_gemm.py:7068-7777, 6897-7051, 6335-6373, 6494-6532). Same names, argument
+meaning and host-side errors; the device work is the sm_100a tcgen05 kernel behind the C
+ABI. Tuning keywords of the reference's SM120 kernel (``load_path``, ``swap_ab``,
+``cluster_shape_mn``, ``sfb_k_replicated``, the policy booleans of the custom ops) are
+accepted and ignored; ``mma_tiler_mn[1]`` selects the tile width when it is one the kernel
+has (64/128/192/256).
+
+Operand contract (same as the reference): ``lhs = (A[M, Kp, L], SFA)``, ``rhs = (B[N, Kp, L],
+SFB)``, K-major, ``Kp = K/2`` bytes for ``float4_e2m1fn`` (two codes per byte, low nibble
+first) or ``K`` for ``float8_e4m3fn``; the scale tensors are the 6-D MMA views
+``(32, 4, row_tiles, 4, k_tiles, L)`` over dense atom storage. Output is ``[M, N, L]`` backed by
+physical ``[L, M, N]`` storage.
+"""
+
+from __future__ import annotations
+
+import os
+import logging
+import time
+from typing import Literal, Optional, Tuple
+
+import torch
+
+from .. import _native
+from . import launch
+from .launch import cuda_stream_to_int
+from .layout import mma_view_is_canonical
+
+logger = logging.getLogger(__name__)
+_B12X_TIMING = os.getenv("B12X_TIMING", "0") == "1"
+_B12X_TIMING_THRESHOLD_MS = float(os.getenv("B12X_TIMING_THRESHOLD_MS", "0"))
+
+_DENSE_LOAD_PATHS = ("tma", "cpasync")
+_AB_DTYPES = ("float4_e2m1fn", "float8_e4m3fn")
+_MXFP6_AB_DTYPES = ("float6_e3m2fn", "float6_e2m3fn")
+_C_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
+_KERNEL_BLOCK_N = (64, 128, 192, 256)
+_ALPHA_ONE_CACHE: dict[tuple[str, int | None], torch.Tensor] = {}
+_FUSED_QUANT_SCRATCH: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def get_num_sm(device: torch.device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def _cached_alpha_one(device: torch.device | str) -> torch.Tensor:
+    """Per-device FP32 one, so the default-alpha path allocates only on first use."""
+    resolved = torch.device(device)
+    if resolved.type == "cuda" and resolved.index is None:
+        resolved = torch.device("cuda", torch.cuda.current_device())
+    key = (resolved.type, resolved.index)
+    alpha = _ALPHA_ONE_CACHE.get(key)
+    if alpha is None:
+        alpha = torch.ones((1,), dtype=torch.float32, device=resolved)
+        _ALPHA_ONE_CACHE[key] = alpha
+    return alpha
+
+
+def _empty_dense_gemm_output(m: int, n: int, l: int, *, dtype: torch.dtype,
+                             device: torch.device | str) -> torch.Tensor:
+    """``[M, N, L]`` output in the layout the kernel writes: physical ``[L, M, N]``."""
+    if l > 1:
+        return torch.empty((l, m, n), dtype=dtype, device=device).as_strided(
+            (m, n, l), (n, 1, m * n))
+    return torch.empty((m, n, l), dtype=dtype, device=device)
+
+
+def _kind_of(ab_dtype: str, sf_dtype: str, sf_vec_size: int) -> int:
+    if ab_dtype == "float4_e2m1fn":
+        if sf_dtype == "float8_e4m3fn" and sf_vec_size == 16:
+            return _native.KIND_NVFP4
+        raise ValueError(
+            "float4_e2m1fn operands are supported as NVFP4 only (sf_dtype='float8_e4m3fn', "
+            f"sf_vec_size=16); got sf_dtype={sf_dtype!r}, sf_vec_size={sf_vec_size}")
+    if sf_dtype == "float8_e8m0fnu" and sf_vec_size == 32:
+        return _native.KIND_MXFP8
+    raise ValueError(
+        "float8_e4m3fn operands need sf_dtype='float8_e8m0fnu' with sf_vec_size=32 "
+        f"(or block_fp8=True); got sf_dtype={sf_dtype!r}, sf_vec_size={sf_vec_size}")
+
+
+def _check_operand(name: str, t: torch.Tensor, rows: int, row_bytes: int, l: int) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be on CUDA")
+    if t.element_size() != 1:
+        raise TypeError(f"{name} must hold one byte per element, got {t.dtype}")
+    if tuple(t.shape) != (rows, row_bytes, l):
+        raise ValueError(f"{name} must have shape {(rows, row_bytes, l)}, got {tuple(t.shape)}")
+    want = (row_bytes, 1, rows * row_bytes)
+    if any(t.shape[i] > 1 and t.stride(i) != want[i] for i in range(3)):
+        raise ValueError(
+            f"{name} must be K-major over physical [L, rows, K] storage (strides {want}), "
+            f"got {t.stride()}")
+    if t.data_ptr() % 16 != 0 or row_bytes % 16 != 0:
+        raise ValueError(f"{name} rows must be 16-byte aligned")
+
+
+def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int, ab_dtype: str,
+                            sf_dtype: str, sf_vec_size: int, mma_tile_n: int, sm_count: int,
+                            alpha_is_one: bool, stream_int: Optional[int]) -> None:
+    kind = _kind_of(ab_dtype, sf_dtype, sf_vec_size)
+    m = int(a.shape[0])
+    row_bytes = k // 2 if kind == _native.KIND_NVFP4 else k
+    _check_operand("A", a, m, row_bytes, l)
+    _check_operand("B", b, n, row_bytes, l)
+    if not mma_view_is_canonical(sfa, m, k, sf_vec_size, l):
+        raise ValueError("SFA must be the (32,4,m_tiles,4,k_tiles,L) view over dense atom storage")
+    if not mma_view_is_canonical(sfb, n, k, sf_vec_size, l):
+        raise ValueError("SFB must be the (32,4,n_tiles,4,k_tiles,L) view over dense atom storage")
+    if tuple(c.shape) != (m, n, l):
+        raise ValueError(f"out must have shape {(m, n, l)}, got {tuple(c.shape)}")
+    if c.stride(1) != 1 or (l > 1 and c.stride(2) != m * n) or (m > 1 and c.stride(0) < n):
+        raise ValueError(f"out must be backed by physical [L, M, N] storage, got strides {c.stride()}")
+    if alpha is not None and (alpha.dtype != torch.float32 or alpha.numel() != 1):
+        raise ValueError("alpha must be a float32 tensor with one element")
+    if m == 0 or n == 0:
+        return
+    block_n = mma_tile_n if mma_tile_n in _KERNEL_BLOCK_N else 0
+    k_tiles = -(-(-(-k // sf_vec_size)) // 4)
+    sfa_group = (-(-m // 128)) * k_tiles * 512
+    sfb_group = (-(-n // 128)) * k_tiles * 512
+    sfa_flat = sfa.view(torch.uint8) if sfa.dtype != torch.uint8 else sfa
+    sfb_flat = sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb
+    sfa_base = torch.as_strided(sfa_flat, (l * sfa_group,), (1,))
+    sfb_base = torch.as_strided(sfb_flat, (l * sfb_group,), (1,))
+    ldc = c.stride(0) if m > 1 else n
+    for g in range(l):
+        launch.gemm_blockscaled(
+            kind, a.select(2, g), sfa_base[g * sfa_group:], b.select(2, g),
+            sfb_base[g * sfb_group:], c.select(2, g), None if alpha_is_one else alpha,
+            m, n, k, ldc=ldc, block_n=block_n, sm_count=sm_count, stream_int=stream_int)
+
+
+@torch.library.custom_op("b12x::dense_gemm_launch", mutates_args=("c_tensor_gpu",))
+def _dense_gemm_launch_op(
+    a_tensor_gpu: torch.Tensor, b_tensor_gpu: torch.Tensor, sfa_tensor_gpu: torch.Tensor,
+    sfb_tensor_gpu: torch.Tensor, c_tensor_gpu: torch.Tensor, alpha_tensor_gpu: torch.Tensor,
+    n: int, k: int, l: int, c_l: int, ab_dtype: str, sf_dtype: str, c_dtype: str,
+    alpha_dtype: str, sf_vec_size: int, mma_k: int, tile_k: int, mma_tile_m: int,
+    mma_tile_n: int, cluster_shape_m: int, cluster_shape_n: int, sm_count: int,
+    single_work_tile_per_cta: bool, direct_one_m_tile_scheduler: bool, use_m1_non_tma: bool,
+    split_k_slices: int, split_k_atomic_bf16: bool, large_m_unroll: bool, load_path: str,
+    swap_ab: bool, sfb_k_reuse: bool, alpha_is_one: bool, stream_int: Optional[int],
+) -> None:
+    _dense_gemm_launch_flat(
+        a_tensor_gpu, b_tensor_gpu, sfa_tensor_gpu, sfb_tensor_gpu, c_tensor_gpu,
+        alpha_tensor_gpu, n=n, k=k, l=l, ab_dtype=ab_dtype, sf_dtype=sf_dtype,
+        sf_vec_size=sf_vec_size, mma_tile_n=mma_tile_n, sm_count=sm_count,
+        alpha_is_one=alpha_is_one, stream_int=stream_int)
+
+
+@_dense_gemm_launch_op.register_fake
+def _dense_gemm_launch_fake(*args, **kwargs) -> None:
+    return None
+
+
+@torch.library.custom_op("b12x::dense_gemm_launch_functional", mutates_args=())
+def _dense_gemm_launch_functional_op(
+    a_tensor_gpu: torch.Tensor, b_tensor_gpu: torch.Tensor, sfa_tensor_gpu: torch.Tensor,
+    sfb_tensor_gpu: torch.Tensor, alpha_tensor_gpu: torch.Tensor, n: int, k: int, l: int,
+    kernel_c_l: int, ab_dtype: str, sf_dtype: str, c_dtype: str, kernel_c_dtype: str,
+    alpha_dtype: str, sf_vec_size: int, mma_k: int, tile_k: int, mma_tile_m: int,
+    mma_tile_n: int, cluster_shape_m: int, cluster_shape_n: int, sm_count: int,
+    single_work_tile_per_cta: bool, direct_one_m_tile_scheduler: bool, use_m1_non_tma: bool,
+    split_k_slices: int, split_k_atomic_bf16: bool, large_m_unroll: bool, load_path: str,
+    swap_ab: bool, sfb_k_reuse: bool, alpha_is_one: bool, stream_int: Optional[int],
+) -> torch.Tensor:
+    m = int(a_tensor_gpu.shape[0])
+    out = _empty_dense_gemm_output(m, n, l, dtype=_C_DTYPES[c_dtype], device=a_tensor_gpu.device)
+    _dense_gemm_launch_flat(
+        a_tensor_gpu, b_tensor_gpu, sfa_tensor_gpu, sfb_tensor_gpu, out, alpha_tensor_gpu,
+        n=n, k=k, l=l, ab_dtype=ab_dtype, sf_dtype=sf_dtype, sf_vec_size=sf_vec_size,
+        mma_tile_n=mma_tile_n, sm_count=sm_count, alpha_is_one=alpha_is_one,
+        stream_int=stream_int)
+    return out
+
+
+@_dense_gemm_launch_functional_op.register_fake
+def _dense_gemm_launch_functional_fake(
+    a_tensor_gpu, b_tensor_gpu, sfa_tensor_gpu, sfb_tensor_gpu, alpha_tensor_gpu, n, k, l,
+    kernel_c_l, ab_dtype, sf_dtype, c_dtype, *rest,
+) -> torch.Tensor:
+    return _empty_dense_gemm_output(a_tensor_gpu.shape[0], n, l, dtype=_C_DTYPES[c_dtype],
+                                    device=a_tensor_gpu.device)
+
+
+def _select_default_mma_tiler_mn(m: int, n: int, sm_count: int) -> Tuple[int, int]:
+    """Tile the kernel would pick for (m, n) on ``sm_count`` SMs: 128 rows by the width with
+    the fewest waves x per-tile cost (same model as the C side)."""
+    best, best_cost = 128, None
+    tiles_m = -(-m // 128)
+    for bn in (256, 192, 128, 64):
+        waves = -(-(tiles_m * -(-n // bn)) // max(sm_count, 1))
+        cost = waves * (128 + bn)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return (128, best)
+
+
+def dense_gemm(
+    lhs: Tuple[torch.Tensor, torch.Tensor],
+    rhs: Tuple[torch.Tensor, torch.Tensor],
+    out: Optional[torch.Tensor] = None,
+    *,
+    ab_dtype: str,
+    sf_dtype: str,
+    c_dtype: str,
+    sf_vec_size: int,
+    sm_count: Optional[int] = None,
+    mma_tiler_mn: Optional[Tuple[int, int]] = None,
+    cluster_shape_mn: Tuple[int, int] = (1, 1),
+    alpha: Optional[torch.Tensor] = None,
+    alpha_dtype: Optional[str] = None,
+    expected_m: Optional[int] = None,
+    load_path: Optional[Literal["tma", "cpasync"]] = None,
+    swap_ab: Optional[bool] = None,
+    sfb_k_replicated: bool = False,
+    rhs_values_tiled: Optional[torch.Tensor] = None,
+    _quantized_c: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+    stream: object = None,
+    a_preexpanded: bool = False,
+    b_preexpanded: bool = False,
+    b_packed: bool = False,
+    a_fmt: Optional[str] = None,
+    b_fmt: Optional[str] = None,
+    x_bf16: Optional[torch.Tensor] = None,
+    w_gscale: Optional[torch.Tensor] = None,
+    plain_fp8: bool = False,
+    block_fp8: bool = False,
+) -> torch.Tensor:
+    """Dense block-scaled GEMM for one batch stack; see the module docstring for layouts.
+
+    ``expected_m`` is a regime hint in the reference; the sm_100a kernel chooses its tile from
+    the live shape, so the hint is accepted and unused. ``alpha`` is a device FP32 scalar
+    read by the kernel at run time (CUDA-graph replays see updated values).
+    """
+    a_torch, sfa_torch = lhs
+    b_torch, sfb_torch = rhs
+    if load_path is not None and load_path not in _DENSE_LOAD_PATHS:
+        raise ValueError(
+            f"dense_gemm load_path must be one of {_DENSE_LOAD_PATHS}, got {load_path!r}")
+    if b_packed and b_preexpanded:
+        raise ValueError("b_packed and b_preexpanded are mutually exclusive")
+    if ab_dtype in _MXFP6_AB_DTYPES:
+        raise NotImplementedError("MX-FP6 operands are outside the block-scaled GEMM path built here")
+    if ab_dtype not in _AB_DTYPES:
+        raise TypeError(f"dense_gemm unsupported ab_dtype: {ab_dtype}")
+    if (a_preexpanded or b_preexpanded or b_packed or a_fmt is not None or b_fmt is not None
+            or x_bf16 is not None or w_gscale is not None):
+        raise ValueError(
+            "a_preexpanded/b_preexpanded/a_fmt/b_fmt/x_bf16/w_gscale are only "
+            f"supported with an MX-FP6 ab_dtype, got ab_dtype={ab_dtype!r}")
+    if rhs_values_tiled is not None or _quantized_c is not None:
+        raise NotImplementedError("tile-major RHS and quantized-C outputs are not part of this path")
+    if c_dtype not in _C_DTYPES:
+        raise KeyError(f"unsupported c_dtype string: {c_dtype!r}")
+
+    m, k, l = a_torch.shape
+    n = b_torch.shape[0]
+    if ab_dtype == "float4_e2m1fn":
+        k *= 2
+        mma_k = 64
+    else:
+        mma_k = 32
+    if sm_count is None:
+        sm_count = get_num_sm(a_torch.device)
+    if block_fp8:
+        from .block_fp8_gemm import block_fp8_gemm
+
+        return block_fp8_gemm(a_torch, sfa_torch, b_torch, sfb_torch, out, c_dtype=c_dtype,
+                              sf_dtype=sf_dtype, sf_vec_size=sf_vec_size, alpha=alpha,
+                              load_path=load_path, swap_ab=swap_ab,
+                              sfb_k_replicated=sfb_k_replicated, sm_count=sm_count,
+                              stream=stream)
+    if plain_fp8:
+        raise NotImplementedError("plain_fp8 (per-tensor FP8) is not part of this path")
+    _kind_of(ab_dtype, sf_dtype, sf_vec_size)
+    if mma_tiler_mn is None:
+        mma_tiler_mn = _select_default_mma_tiler_mn(m, n, sm_count)
+    if alpha_dtype is None:
+        alpha_dtype = "float32" if alpha is None else str(alpha.dtype).split(".")[-1]
+    alpha_is_one = alpha is None
+    if alpha is None:
+        alpha = _cached_alpha_one(a_torch.device)
+    stream_int = cuda_stream_to_int(stream)
+    op_tail = (
+        alpha_dtype, sf_vec_size, mma_k, sf_vec_size * 8 if ab_dtype == "float4_e2m1fn" else 128,
+        int(mma_tiler_mn[0]), int(mma_tiler_mn[1]), int(cluster_shape_mn[0]),
+        int(cluster_shape_mn[1]), int(sm_count), False, False, False, 1, False, False,
+        load_path or "tma", bool(swap_ab), bool(sfb_k_replicated), alpha_is_one, stream_int,
+    )
+    t0 = time.perf_counter() if _B12X_TIMING else 0.0
+    if out is None:
+        out = torch.ops.b12x.dense_gemm_launch_functional(
+            a_torch, b_torch, sfa_torch, sfb_torch, alpha, n, k, l, l, ab_dtype, sf_dtype,
+            c_dtype, c_dtype, *op_tail)
+    else:
+        if out.dtype != _C_DTYPES[c_dtype]:
+            raise ValueError(f"out dtype {out.dtype} does not match c_dtype={c_dtype!r}")
+        torch.ops.b12x.dense_gemm_launch(
+            a_torch, b_torch, sfa_torch, sfb_torch, out, alpha, n, k, l, l, ab_dtype, sf_dtype,
+            c_dtype, *op_tail)
+    if _B12X_TIMING:
+        ms = (time.perf_counter() - t0) * 1000.0
+        if ms >= _B12X_TIMING_THRESHOLD_MS:
+            logger.warning("b12x_dense_gemm timing m=%d n=%d k=%d l=%d enqueue=%.3fms",
+                           m, n, k, l, ms)
+    return out
+
+
+def dense_gemm_fused_quant_a(
+    source: torch.Tensor,
+    b: torch.Tensor,
+    sfb: torch.Tensor,
+    *,
+    out: Optional[torch.Tensor] = None,
+    expected_m: Optional[int] = None,
+    sfb_k_replicated: bool = False,
+    rhs_values_tiled: Optional[torch.Tensor] = None,
+    a_inner_span: int = 0,
+    mma_tiler_mn: Optional[Tuple[int, int]] = None,
+    _atomic_output_precleared: bool = False,
+    stream: object = None,
+) -> torch.Tensor:
+    """Small-M BF16 activations -> MXFP8 GEMM (b12x/_lib/dense_gemm.py:6897-7051).
+
+    The activation rows are quantized to E4M3 + UE8M0/32 by the row quantizer into a
+    per-device scratch that is created on the first call for a given K (so a warm-up call
+    must precede CUDA-graph capture, as for every op here), then the MXFP8 GEMM runs on the
+    same stream. Results equal ``quantize_rows`` followed by ``mm``.
+    """
+    if source.dtype != torch.bfloat16:
+        raise ValueError("fused MXFP8 activation quantization requires BF16 A")
+    if int(a_inner_span) != 0 or rhs_values_tiled is not None:
+        raise NotImplementedError("L-blocked A and tile-major RHS belong to the WO projection path")
+    if source.ndim != 2 or not source.is_contiguous():
+        raise ValueError("fused MXFP8 activation quantization requires contiguous BF16 [M,K]")
+    m, k = map(int, source.shape)
+    if m < 1 or m > 8 or k % 128 != 0:
+        raise ValueError(
+            f"fused MXFP8 activation quantization requires 1<=M<=8 and K%128=0, got M={m}, K={k}")
+    if b.ndim != 3 or int(b.shape[1]) != k or int(b.shape[2]) != 1:
+        raise ValueError(f"B must have shape [N,{k},1], got {tuple(b.shape)}")
+    n = int(b.shape[0])
+    if out is None:
+        if _atomic_output_precleared:
+            raise ValueError("a precleared fused-quant output must be caller-owned")
+        out = torch.empty((m, n, 1), dtype=torch.bfloat16, device=source.device)
+    if out.shape != (m, n, 1) or out.dtype != torch.bfloat16:
+        raise ValueError(
+            f"out must be BF16 with shape {(m, n, 1)}, got {out.dtype} {tuple(out.shape)}")
+    dev_index = source.device.index if source.device.index is not None else torch.cuda.current_device()
+    key = (dev_index, 8, k)
+    scratch = _FUSED_QUANT_SCRATCH.get(key)
+    if scratch is None:
+        values = torch.empty((8, k), dtype=torch.uint8, device=source.device)
+        scale_mma = torch.full(((k // 128) * 512,), 127, dtype=torch.uint8, device=source.device)
+        scratch = (values, scale_mma)
+        _FUSED_QUANT_SCRATCH[key] = scratch
+    values, scale_mma = scratch
+    stream_int = cuda_stream_to_int(stream)
+    launch.quantize_mxfp8_rows(source, values, None, scale_mma, stream_int=stream_int)
+    launch.gemm_blockscaled(
+        _native.KIND_MXFP8, values, scale_mma, b.select(2, 0),
+        sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb, out.select(2, 0), None,
+        m, n, k, ldc=n, block_n=(mma_tiler_mn[1] if mma_tiler_mn and mma_tiler_mn[1] in _KERNEL_BLOCK_N else 0),
+        stream_int=stream_int)
+    return out
+
+
+__all__ = ["dense_gemm", "dense_gemm_fused_quant_a", "get_num_sm"]

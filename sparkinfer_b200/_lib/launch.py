@@ -1,0 +1,125 @@
+"""torch tensors -> C-ABI calls. Every public op funnels through these few functions.
+
+They validate what the C ABI cannot (device, dtype, contiguity), pick the stream, and pass
+raw pointers. Nothing here computes on tensors: if the CUDA library is missing the import
+of :mod:`sparkinfer_b200._native` raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from threading import Lock
+
+import torch
+
+from .. import _native
+
+_STATUS_LOCK = Lock()
+_STATUS: dict[int, torch.Tensor] = {}
+
+_DTYPE_CODE = {torch.bfloat16: _native.DT_BF16, torch.float16: _native.DT_FP16,
+               torch.float32: _native.DT_FP32}
+
+KERNEL_STATUS_TEXT = {
+    1: "TMA producer timed out waiting for a free pipeline stage",
+    2: "MMA issuer timed out waiting for operands or a free accumulator",
+    3: "epilogue timed out waiting for a finished accumulator",
+    4: "split-K reduction timed out waiting for its peers",
+    5: "tensor memory was not allocated from column 0",
+}
+
+
+def cuda_stream_to_int(stream: object | None) -> int | None:
+    """Raw CUDA stream handle of ``stream`` (object with ``.cuda_stream`` or int); ``None``
+    stays ``None`` and means torch's current stream (b12x/_lib/utils.py:184-204)."""
+    if stream is None:
+        return None
+    handle = getattr(stream, "cuda_stream", None)
+    return int(handle) if handle is not None else int(stream)
+
+
+def _stream_ptr(stream_int: int | None, device: torch.device) -> ctypes.c_void_p:
+    if stream_int is None:
+        stream_int = torch.cuda.current_stream(device).cuda_stream
+    return ctypes.c_void_p(int(stream_int))
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    """Per-device int32[4] the kernels raise when a bounded wait runs out. Allocated once, on
+    first use (call an op once before CUDA-graph capture, as with any warm-up)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    with _STATUS_LOCK:
+        buf = _STATUS.get(index)
+        if buf is None:
+            buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+            _STATUS[index] = buf
+        return buf
+
+
+def check_kernel_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    buf = status_buffer(device)
+    code = int(buf[0].item())
+    if code != 0:
+        buf.zero_()
+        raise RuntimeError(f"b12x kernel status {code}: {KERNEL_STATUS_TEXT.get(code, 'unknown')}")
+
+
+def _require_cuda(name: str, t: torch.Tensor) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be on CUDA")
+
+
+def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
+                     sfb: torch.Tensor, c: torch.Tensor, alpha: torch.Tensor | None,
+                     m: int, n: int, k: int, *, ldc: int | None = None, block_n: int = 0,
+                     sm_count: int = 0, stream_int: int | None = None) -> None:
+    """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)`` for one group. ``a``/``b`` are row
+    pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom."""
+    for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
+        _require_cuda(name, t)
+    if c.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported output dtype {c.dtype}")
+    dev = a.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_gemm_blockscaled(
+            kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+            _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
+            m, n, k, ldc if ldc is not None else n, block_n, sm_count,
+            status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_blockscaled")
+
+
+def quantize_mxfp8_rows(src: torch.Tensor, values: torch.Tensor, scale_rows: torch.Tensor | None,
+                        scale_mma: torch.Tensor | None, *, stream_int: int | None = None) -> None:
+    _require_cuda("source", src)
+    m, k = src.shape
+    dev = src.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_quantize_mxfp8_rows(
+            src.data_ptr(), _DTYPE_CODE[src.dtype], src.stride(0), values.data_ptr(),
+            scale_rows.data_ptr() if scale_rows is not None else None,
+            scale_mma.data_ptr() if scale_mma is not None else None, m, k,
+            _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_quantize_mxfp8_rows")
+
+
+def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: torch.Tensor,
+                        scale_mma: torch.Tensor, *, stream_int: int | None = None) -> None:
+    _require_cuda("source", src)
+    m, k = src.shape
+    dev = src.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_quantize_nvfp4_rows(
+            src.data_ptr(), _DTYPE_CODE[src.dtype], src.stride(0), global_scale.data_ptr(),
+            packed.data_ptr(), scale_mma.data_ptr(), m, k, _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_quantize_nvfp4_rows")
+
+
+__all__ = [
+    "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled",
+    "quantize_mxfp8_rows", "quantize_nvfp4_rows", "KERNEL_STATUS_TEXT",
+]

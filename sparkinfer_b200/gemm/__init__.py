@@ -1,0 +1,1 @@
+"""GEMM op group: ``blockscaled``, ``mxfp8_linear``, ``block_fp8_linear``."""

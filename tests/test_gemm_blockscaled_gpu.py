@@ -1,0 +1,259 @@
+"""Block-scaled GEMM on the GPU against the CPU oracle (dequantize to FP32, matmul).
+
+Modelled on the reference's tests/gemm/test_blockscaled.py:90-220, test_gemm_stack.py:210-312
+and test_cute_migration_gemm_corpus.py:78-139: NVFP4 and MXFP8 operands built by the (oracle)
+reference quantizers, BF16/FP16/FP32 outputs, grouped batches with their own scales,
+caller-owned outputs, CUDA-graph replay, a device alpha read at run time; plus decode shapes,
+ragged edges, every tile width, and full-size configurations checked on sampled rows and
+through linearity in alpha.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, bf16_bits_to_f32, seeded_bf16
+from oracle import blockscaled_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+NVFP4 = dict(ab_dtype="float4_e2m1fn", sf_dtype="float8_e4m3fn", sf_vec_size=16)
+MXFP8 = dict(ab_dtype="float8_e4m3fn", sf_dtype="float8_e8m0fnu", sf_vec_size=32)
+
+
+def _alpha(gsa, gsb):
+    from gpu_util import DEV
+
+    return torch.tensor([1.0 / (float(gsa) * float(gsb))], dtype=torch.float32, device=DEV)
+
+
+@pytest.mark.parametrize("m,n,k,c_dtype,tile_n", [
+    (128, 128, 128, "bfloat16", None), (256, 512, 128, "bfloat16", None),
+    (512, 256, 256, "bfloat16", None), (128, 128, 128, "float16", None),
+    (32, 128, 128, "bfloat16", None), (1, 512, 512, "bfloat16", None),
+    (4, 512, 512, "bfloat16", 64), (16, 512, 1024, "bfloat16", 128),
+    (64, 768, 512, "bfloat16", 192), (130, 72, 384, "bfloat16", None),
+    (300, 504, 640, "float32", 192), (256, 1024, 2048, "bfloat16", 256),
+    (128, 200, 192, "bfloat16", 64),
+])
+def test_mm_nvfp4_matches_oracle(m, n, k, c_dtype, tile_n):
+    from gpu_util import assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(m * 7 + k, (m, k), 0.25))
+    rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(n * 11 + k, (n, k), 0.02))
+    out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype=c_dtype,
+                         mma_tiler_mn=(128, tile_n) if tile_n else None, **NVFP4)
+    torch.cuda.synchronize()
+    assert out.shape == (m, n, 1)
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T, out_dtype=out.dtype)
+
+
+@pytest.mark.parametrize("m,n,k,c_dtype,tile_n", [
+    (128, 128, 128, "bfloat16", None), (7, 32, 128, "bfloat16", None),
+    (3, 40, 256, "bfloat16", None), (64, 1024, 512, "bfloat16", 128),
+    (256, 512, 384, "float16", 64), (129, 256, 256, "bfloat16", None),
+    (8, 4096, 4096, "bfloat16", None), (300, 504, 640, "float32", 192),
+    (512, 1024, 1024, "bfloat16", 256),
+])
+def test_mm_mxfp8_matches_oracle(m, n, k, c_dtype, tile_n):
+    from gpu_util import assert_gemm_close, mxfp8_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    lhs, a_deq = mxfp8_operand(seeded_bf16(m * 5 + k, (m, k), 0.25))
+    rhs, b_deq = mxfp8_operand(seeded_bf16(n * 13 + k, (n, k), 1.0 / 32))
+    out = blockscaled.mm(lhs, rhs, c_dtype=c_dtype,
+                         mma_tiler_mn=(128, tile_n) if tile_n else None, expected_m=m, **MXFP8)
+    torch.cuda.synchronize()
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T, out_dtype=out.dtype)
+
+
+def test_mm_nvfp4_matches_reference_fixture():
+    """Operands and FP32 result produced by the reference's own torch code."""
+    from gpu_util import assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    g = np.load(GOLDEN / "gemm_ref.npz")
+    a = torch.from_numpy(g["nv_a"].view(np.int16)).view(torch.bfloat16)
+    b = torch.from_numpy(g["nv_b"].view(np.int16)).view(torch.bfloat16)
+    lhs, gsa, _ = nvfp4_operand(a, g["nv_gsa"][0])
+    rhs, gsb, _ = nvfp4_operand(b, g["nv_gsb"][0])
+    out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype="float32", **NVFP4)
+    assert_gemm_close(out[:, :, 0], g["nv_out"], out_dtype=torch.float32)
+
+
+def test_mm_equals_bf16_of_dequantized_matmul_on_tiny_shape():
+    """tests/gemm/test_cute_migration_gemm_corpus.py:78-139: M=32, N=128, K=128, the kernel
+    output equals the BF16 rounding of the dequantized product up to the accumulation order."""
+    from gpu_util import nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 32, 128, 128
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(1, (m, k), 0.25))
+    rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(2, (n, k), 0.25))
+    out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype="bfloat16", **NVFP4)
+    ref = O.bf16_round(a_deq @ b_deq.T)
+    got = out[:, :, 0].float().cpu().numpy()
+    ulp = np.abs(ref) * 2.0 ** -7 + 1e-30
+    assert (np.abs(got - ref) <= ulp).all()
+    assert (got == ref).mean() > 0.98
+
+
+def test_mm_grouped_batches_use_their_own_scales():
+    """L = 3 MXFP8 groups, each scaled differently (tests/gemm/test_blockscaled.py:128-175)."""
+    from gpu_util import DEV, assert_gemm_close, to_dev
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k, groups = 64, 256, 256, 3
+    mult = [1.0, 4.0, 0.5]
+    a_vals, a_sw, b_vals, b_sw, refs = [], [], [], [], []
+    for g in range(groups):
+        a = seeded_bf16(50 + g, (m, k), 0.25 * mult[g]).float().numpy()
+        b = seeded_bf16(60 + g, (n, k), 0.03 / mult[g]).float().numpy()
+        av, asr = O.quantize_mxfp8_rows(a)
+        bv, bsr = O.quantize_mxfp8_rows(b)
+        a_vals.append(av); b_vals.append(bv)
+        a_sw.append(O.swizzle_scales(asr, 127)); b_sw.append(O.swizzle_scales(bsr, 127))
+        refs.append(O.dequantize_mxfp8(av, asr) @ O.dequantize_mxfp8(bv, bsr).T)
+    a_t = to_dev(np.stack(a_vals)).view(torch.float8_e4m3fn).as_strided((m, k, groups), (k, 1, m * k))
+    b_t = to_dev(np.stack(b_vals)).view(torch.float8_e4m3fn).as_strided((n, k, groups), (k, 1, n * k))
+    sfa = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(a_sw)), m, k, groups, 32)
+    sfb = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(b_sw)), n, k, groups, 32)
+    out = blockscaled.mm((a_t, sfa), (b_t, sfb), c_dtype="bfloat16", **MXFP8)
+    assert out.shape == (m, n, groups) and out.stride() == (n, 1, m * n)
+    for g in range(groups):
+        assert_gemm_close(out[:, :, g], refs[g])
+
+
+def test_mm_writes_caller_output_and_replays_under_cuda_graph():
+    """out= given: no allocation, capture after warm-up, three bit-identical replays, and a
+    device alpha changed between replays is honoured (tests/gemm/test_blockscaled.py:178-220,
+    tests/gemm/test_gemm_stack.py:167-190)."""
+    from gpu_util import DEV, assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 128, 256, 256
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(5, (m, k), 0.25))
+    rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(6, (n, k), 0.02))
+    alpha = _alpha(gsa, gsb)
+    out = torch.zeros((m, n, 1), dtype=torch.bfloat16, device=DEV)
+    ret = blockscaled.mm(lhs, rhs, out, alpha=alpha, c_dtype="bfloat16", **NVFP4)
+    torch.cuda.synchronize()
+    assert ret.data_ptr() == out.data_ptr()
+    eager = out.clone()
+    ref = a_deq @ b_deq.T
+    assert_gemm_close(eager[:, :, 0], ref)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        blockscaled.mm(lhs, rhs, out, alpha=alpha, c_dtype="bfloat16", **NVFP4)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    alpha.mul_(2.0)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out.float(), eager.float() * 2.0)  # power-of-two alpha: exact
+
+
+def test_mm_row_strided_output_view():
+    from gpu_util import DEV, assert_gemm_close, mxfp8_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 128, 128, 256
+    lhs, a_deq = mxfp8_operand(seeded_bf16(8, (m, k), 0.25))
+    rhs, b_deq = mxfp8_operand(seeded_bf16(9, (n, k), 0.03))
+    wide = torch.full((m, 2 * n), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = wide[:, :n].unsqueeze(-1)
+    blockscaled.mm(lhs, rhs, out, c_dtype="bfloat16", **MXFP8)
+    torch.cuda.synchronize()
+    assert_gemm_close(wide[:, :n], a_deq @ b_deq.T)
+    assert (wide[:, n:] == 7.0).all()
+
+
+def test_mm_fused_quant_a_equals_quantize_then_mm():
+    from gpu_util import assert_gemm_close, mxfp8_operand
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 5, 512, 512
+    x = seeded_bf16(15, (m, k), 0.25)
+    rhs, b_deq = mxfp8_operand(seeded_bf16(16, (n, k), 0.03))
+    _, a_deq = mxfp8_operand(x)
+    out = blockscaled.mm_fused_quant_a(x.to(DEV), rhs[0], rhs[1])
+    torch.cuda.synchronize()
+    assert out.shape == (m, n, 1) and out.dtype == torch.bfloat16
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
+    with pytest.raises(ValueError, match="1<=M<=8"):
+        blockscaled.mm_fused_quant_a(seeded_bf16(1, (9, k)).to(DEV), rhs[0], rhs[1])
+
+
+@pytest.mark.parametrize("recipe", ["mxfp8_prefill", "nvfp4_row_parallel_shard"])
+def test_full_size_configurations_on_sampled_rows(recipe):
+    """Full-size operands (the MXFP8 prefill GEMM 8192 x 7168 x 7168 and one 1/8 K-shard of the
+    row-parallel NVFP4 GEMM, 4096 x 7168 x 2304): quantized on the GPU by the row quantizers,
+    multiplied by the GEMM, and compared with the oracle on a sample of rows; then linearity
+    in alpha over the whole output."""
+    from gpu_util import DEV
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200._lib.mxfp8_rows import empty_mxfp8_rows_for_dense_gemm, quantize_mxfp8_rows
+    from sparkinfer_b200.gemm import blockscaled
+    from sparkinfer_b200.quantization import nvfp4
+
+    if recipe == "mxfp8_prefill":
+        m, n, k = 8192, 7168, 7168
+    else:
+        m, n, k = 4096, 7168, 2304
+    x = seeded_bf16(42 + 2000, (m, k)).to(DEV)
+    w = seeded_bf16(42 + 2001, (n, k), 0.02).to(DEV)
+    rows = np.r_[0:16, m // 2:m // 2 + 16, m - 16:m]
+    cols = np.r_[0:64, n - 64:n]
+    if recipe == "mxfp8_prefill":
+        xq = empty_mxfp8_rows_for_dense_gemm(m, k, device=DEV)
+        wq = empty_mxfp8_rows_for_dense_gemm(n, k, device=DEV)
+        quantize_mxfp8_rows(x, xq.values, xq.scale_rows, xq.scale_mma)
+        quantize_mxfp8_rows(w, wq.values, wq.scale_rows, wq.scale_mma)
+        lhs = (xq.values.view(m, k, 1), xq.scale_mma)
+        rhs = (wq.values.view(n, k, 1), wq.scale_mma)
+        alpha = torch.ones(1, device=DEV)
+        kw = MXFP8
+        a_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(x[rows].float().cpu().numpy()))
+        b_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(w[cols].float().cpu().numpy()))
+    else:
+        gsx = O.nvfp4_global_scale(x.float().cpu().numpy())
+        gsw = O.nvfp4_global_scale(w.float().cpu().numpy())
+        ops = []
+        for t, gs, r in ((x, gsx, m), (w, gsw, n)):
+            plan = nvfp4.plan(r, k)
+            outs = nvfp4.allocate_outputs(plan, device=DEV)
+            nvfp4.run(plan=plan, x=t, global_scale=torch.tensor([gs], device=DEV), outputs=outs)
+            ops.append((outs.packed_a_view, outs.scale_mma_view(r, k)))
+        lhs, rhs = ops
+        alpha = _alpha(gsx, gsw)
+        kw = NVFP4
+        pa, sa = O.quantize_nvfp4_rows(x[rows].float().cpu().numpy(), gsx)
+        pb, sb = O.quantize_nvfp4_rows(w[cols].float().cpu().numpy(), gsw)
+        a_deq, b_deq = O.dequantize_nvfp4(pa, sa, gsx), O.dequantize_nvfp4(pb, sb, gsw)
+    out = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **kw)
+    torch.cuda.synchronize()
+    got = out[:, :, 0][torch.from_numpy(rows).to(DEV)][:, torch.from_numpy(cols).to(DEV)]
+    ref = a_deq @ b_deq.T
+    err = np.abs(got.float().cpu().numpy() - ref).max()
+    assert err <= 1e-2 * np.abs(ref).max()
+    assert err <= (2.0 ** -8 + 2.0 ** -16) * np.abs(ref).max()
+    alpha2 = alpha * 4.0
+    out2 = blockscaled.mm(lhs, rhs, alpha=alpha2, c_dtype="bfloat16", **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(out2.float(), out.float() * 4.0)
+    assert not torch.isnan(out.float()).any()
+
+
+def test_no_kernel_reported_a_timed_out_wait():
+    from gpu_util import DEV
+    from sparkinfer_b200._lib.launch import check_kernel_status
+
+    check_kernel_status(DEV)

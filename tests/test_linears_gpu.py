@@ -1,0 +1,139 @@
+"""mxfp8_linear and block_fp8_linear on the GPU against the oracle composition
+"quantize rows -> dequantize -> FP32 matmul" (the reference's tests/gemm/test_mxfp8_linear.py
+:77-116 and tests/gemm/test_block_fp8_linear.py:50-114)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import seeded_bf16
+from oracle import blockscaled_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _modelopt_weight(seed, n, k, scale=1.0 / 8):
+    """ModelOpt-style MXFP8 weight built by the oracle quantizer: (values e4m3, scales u8)."""
+    from gpu_util import to_dev
+
+    w = seeded_bf16(seed, (n, k), scale).float().numpy()
+    values, scale_rows = O.quantize_mxfp8_rows(w)
+    return to_dev(values).view(torch.float8_e4m3fn), to_dev(scale_rows), O.dequantize_mxfp8(values, scale_rows)
+
+
+def _quantized_activation_reference(x: torch.Tensor, padded_k: int) -> np.ndarray:
+    xf = np.zeros((x.shape[0], padded_k), dtype=np.float32)
+    xf[:, : x.shape[1]] = x.float().numpy()
+    return O.dequantize_mxfp8(*O.quantize_mxfp8_rows(xf))
+
+
+@pytest.mark.parametrize("tokens,k,n", [(7, 128, 32), (3, 160, 40), (129, 256, 256), (16, 4096, 512)])
+def test_mxfp8_linear_matches_quantized_reference(tokens, k, n):
+    from gpu_util import DEV, assert_gemm_close
+    from sparkinfer_b200.gemm import mxfp8_linear
+
+    x = seeded_bf16(tokens + k, (tokens, k), 0.25)
+    w_values, w_scale, w_deq = _modelopt_weight(n + k, n, k)
+    packed = mxfp8_linear.pack_weight(w_values, w_scale)
+    padded_k = -(-k // 128) * 128
+    assert packed.in_features == k and packed.padded_in_features == padded_k
+    assert packed.weight.values.shape == (n, padded_k)
+    assert packed.weight.scale_rows.shape == (1, n, padded_k // 32)
+    assert torch.equal(packed.weight.scale_rows.view(torch.uint8)[0, :, : k // 32], w_scale)
+    assert (packed.weight.scale_rows.view(torch.uint8)[0, :, k // 32:] == 127).all()
+    out = mxfp8_linear.mm(x.to(DEV), packed)
+    torch.cuda.synchronize()
+    assert out.shape == (tokens, n) and out.dtype == torch.bfloat16
+    w_pad = np.zeros((n, padded_k), dtype=np.float32)
+    w_pad[:, :k] = w_deq
+    assert_gemm_close(out, _quantized_activation_reference(x, padded_k) @ w_pad.T)
+
+
+def test_mxfp8_linear_bias_leading_dims_and_empty():
+    from gpu_util import DEV, assert_gemm_close
+    from sparkinfer_b200.gemm import mxfp8_linear
+
+    k, n = 256, 128
+    w_values, w_scale, w_deq = _modelopt_weight(3, n, k)
+    packed = mxfp8_linear.pack_weight(w_values, w_scale)
+    x = seeded_bf16(4, (2, 5, k), 0.25)
+    bias = seeded_bf16(5, (n,)).to(DEV)
+    out = mxfp8_linear.mm(x.to(DEV), packed, bias=bias)
+    assert out.shape == (2, 5, n)
+    ref = _quantized_activation_reference(x.reshape(10, k), k) @ w_deq.T
+    plain = mxfp8_linear.mm(x.to(DEV), packed)
+    assert_gemm_close(plain.reshape(10, n), ref)
+    assert torch.equal(out, plain + bias)
+    assert mxfp8_linear.mm(torch.empty((0, k), dtype=torch.bfloat16, device=DEV), packed).shape == (0, n)
+    with pytest.raises(ValueError, match="does not match"):
+        mxfp8_linear.mm(torch.zeros((2, 128), dtype=torch.bfloat16, device=DEV), packed)
+    with pytest.raises(TypeError):
+        mxfp8_linear.mm(x.to(DEV), object())
+
+
+def _block_fp8_checkpoint(seed, n, k):
+    """DeepSeek-style weight: E4M3 codes + FP32 128x128 scales (amax / 448)."""
+    from gpu_util import to_dev
+
+    w = seeded_bf16(seed, (n, k), 0.05).float().numpy()
+    codes, scales = O.quantize_block_fp8(w, 128, 128)
+    return to_dev(codes).view(torch.float8_e4m3fn), to_dev(scales), codes, scales
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 9, 200])
+def test_block_fp8_linear_plan_bind_run(tokens):
+    from gpu_util import DEV, assert_gemm_close
+    from sparkinfer_b200._lib.mxfp8_rows import empty_dense_gemm_mnl_view
+    from sparkinfer_b200.gemm import block_fp8_linear as bfl
+
+    k, n = 512, 384
+    w_codes, w_scales, codes_np, scales_np = _block_fp8_checkpoint(21, n, k)
+    weight = bfl.pack_weight(w_codes, w_scales)
+    assert weight.in_features == k and weight.out_features == n
+    # The packed weight keeps the information of the checkpoint: its dequantized rows are the
+    # re-quantization of codes * scale onto power-of-two block scales.
+    w_rec = O.e4m3_decode(codes_np).reshape(n // 128, 128, k // 128, 128) * scales_np[:, None, :, None]
+    w_deq = O.dequantize_mxfp8(weight.weight.values.view(torch.uint8).cpu().numpy(),
+                               weight.weight.scale_rows.view(torch.uint8)[0].cpu().numpy())
+    assert np.abs(w_deq - w_rec.reshape(n, k)).max() <= 2.0 ** -4 * np.abs(w_rec).max()
+    byte = weight.weight.scale_rows.view(torch.uint8)[0].cpu().numpy()
+    assert (byte.reshape(n // 128, 128, k // 128, 4) == byte.reshape(n // 128, 128, k // 128, 4)[:, :1, :, :1]).all()
+
+    x = seeded_bf16(22 + tokens, (tokens, k), 0.25)
+    plan = bfl.plan(bfl.Caps(device=DEV, max_tokens=256, in_features=k, out_features=n))
+    spec = plan.scratch_specs()[0]
+    scratch = torch.empty(spec.shape, dtype=spec.dtype, device=spec.device)
+    output = empty_dense_gemm_mnl_view(tokens, n, 1, device=DEV, dtype=torch.bfloat16)
+    binding = bfl.bind(plan, scratch=scratch, source=x.to(DEV), packed_weight=weight, output=output)
+    y = bfl.run(binding=binding)
+    torch.cuda.synchronize()
+    assert y.shape == (tokens, n) and y.data_ptr() == output.data_ptr()
+    ref = _quantized_activation_reference(x, k) @ w_deq.T
+    assert_gemm_close(y, ref)
+    # one-shot form gives the same bits
+    y2 = bfl.run(x.to(DEV), weight)
+    assert torch.equal(y2, y)
+    # bound path under CUDA-graph capture (tests/gemm/test_block_fp8_linear.py:70-114)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        binding.run()
+    output.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(output[:, :, 0], y2)
+
+
+def test_block_fp8_quantize_input_and_prewarm():
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import block_fp8_linear as bfl
+
+    x = seeded_bf16(31, (20, 256), 0.25)
+    xq = bfl.quantize_input(x.to(DEV))
+    ref_values, ref_rows = O.quantize_mxfp8_rows(x.float().numpy())
+    assert np.array_equal(xq.values.view(torch.uint8).cpu().numpy(), ref_values)
+    assert np.array_equal(xq.scale_rows.view(torch.uint8)[0].cpu().numpy(), ref_rows)
+    assert xq.scale_mma.shape == (32, 4, 1, 4, 2, 1)
+    w_codes, w_scales, _, _ = _block_fp8_checkpoint(32, 128, 256)
+    bfl.prewarm(bfl.pack_weight(w_codes, w_scales), [1, 4, 0, 4])
