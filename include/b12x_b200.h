@@ -76,6 +76,21 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
                                int sm_count, int* status, b12x_b200_stream_t stream);
 
 /*
+ * Block-FP8 GEMM with compact FP32 scales,
+ *   C[M,N] = cvt(alpha * sum_kb (A[:,kb] B[:,kb]^T) * sfa[m,kb] * sfb[n/128,kb]).
+ * Replaces dense_gemm(..., block_fp8=True, sf_dtype="float32", sf_vec_size=128)
+ * (b12x/_lib/dense_gemm.py:7137-7139, 7190-7224, kernel :1314-1348, 2290-2348).
+ *
+ *   a   [M, K] E4M3, K-major      sfa [M, K/128] FP32, contiguous
+ *   b   [N, K] E4M3, K-major      sfb [N/128, K/128] FP32, contiguous
+ *   N and K must be multiples of 128. Other arguments as for b12x_b200_gemm_blockscaled.
+ */
+int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const void* b, const float* sfb,
+                             void* c, int c_dtype, const float* alpha, int64_t m, int64_t n,
+                             int64_t k, int64_t ldc, int sm_count, int* status,
+                             b12x_b200_stream_t stream);
+
+/*
  * MXFP8 row quantizer. Replaces quantize_mxfp8_rows_cute
  * (b12x/_lib/quant/mxfp8_rows.py:398-434; kernel :88-269), numerics of
  * quantize_mxfp8_rows_torch (b12x/gemm/_shared/wo_mxfp8.py:1884-1918).

@@ -93,6 +93,23 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     _native.check(rc, "b12x_b200_gemm_blockscaled")
 
 
+def gemm_block_fp8(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: torch.Tensor,
+                   c: torch.Tensor, alpha: torch.Tensor | None, m: int, n: int, k: int, *,
+                   ldc: int | None = None, sm_count: int = 0,
+                   stream_int: int | None = None) -> None:
+    """E4M3 operands with FP32 scales ``sfa [M, K/128]`` / ``sfb [N/128, K/128]``."""
+    for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
+        _require_cuda(name, t)
+    dev = a.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_gemm_block_fp8(
+            a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+            _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None, m, n, k,
+            ldc if ldc is not None else n, sm_count, status_buffer(dev).data_ptr(),
+            _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_block_fp8")
+
+
 def quantize_mxfp8_rows(src: torch.Tensor, values: torch.Tensor, scale_rows: torch.Tensor | None,
                         scale_mma: torch.Tensor | None, *, stream_int: int | None = None) -> None:
     _require_cuda("source", src)
@@ -121,5 +138,5 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
 
 __all__ = [
     "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled",
-    "quantize_mxfp8_rows", "quantize_nvfp4_rows", "KERNEL_STATUS_TEXT",
+    "gemm_block_fp8", "quantize_mxfp8_rows", "quantize_nvfp4_rows", "KERNEL_STATUS_TEXT",
 ]

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "gemm_blockscaled.cuh"
+#include "gemm_block_fp8.cuh"
 #include "quantize.cuh"
 
 namespace b12x_b200 {
@@ -288,5 +289,67 @@ extern "C" int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int
         static_cast<uint8_t*>(scale_mma), int(m), int(k), rows_cover, k_cover, k_atoms);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "quantize_nvfp4_rows launch");
+  return B12X_B200_OK;
+}
+
+extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const void* b,
+                                        const float* sfb, void* c, int c_dtype,
+                                        const float* alpha, int64_t m, int64_t n, int64_t k,
+                                        int64_t ldc, int sm_count, int* status,
+                                        b12x_b200_stream_t stream) {
+  if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
+  if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (n % 128 != 0 || k % 128 != 0)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "block-FP8 GEMM needs N and K divisible by 128");
+  if (m == 0 || n == 0) return B12X_B200_OK;
+  if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  if (!aligned16(a) || !aligned16(b) || (reinterpret_cast<uintptr_t>(sfa) & 3) ||
+      (reinterpret_cast<uintptr_t>(sfb) & 3))
+    return fail(B12X_B200_ERR_ALIGNMENT, "operands must be 16-byte and scales 4-byte aligned");
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+
+  CUtensorMap map_a, map_b;
+  rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(k), BlockFp8Tile::BM);
+  if (rc != B12X_B200_OK) return rc;
+  rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(k), BlockFp8Tile::BN);
+  if (rc != B12X_B200_OK) return rc;
+
+  BlockFp8Params p;
+  p.sfa = sfa;
+  p.sfb = sfb;
+  p.c = c;
+  p.alpha = alpha;
+  p.status = status;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.ldc = int(ldc);
+  p.out_dtype = c_dtype;
+  p.tiles_m = int((m + BlockFp8Tile::BM - 1) / BlockFp8Tile::BM);
+  p.tiles_n = int((n + BlockFp8Tile::BN - 1) / BlockFp8Tile::BN);
+  p.group_m = 16;
+  const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+  const int grid = int(tiles < sms ? tiles : sms);
+  static bool set_for[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set_for[dev]) {
+    const cudaError_t attr_err =
+        cudaFuncSetAttribute(gemm_block_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             BlockFp8Tile::kSmemBytes);
+    if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    set_for[dev] = true;
+  }
+  gemm_block_fp8_kernel<<<grid, BlockFp8Tile::kThreads, BlockFp8Tile::kSmemBytes,
+                          reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "gemm_block_fp8 launch");
   return B12X_B200_OK;
 }

@@ -1,0 +1,222 @@
+// Block-FP8 GEMM with compact FP32 scales (DeepSeek-V3 style) for sm_100a:
+//
+//     C[M,N] = cvt(alpha * sum_kb (A[:, kb] B[:, kb]^T) * sfa[m, kb] * sfb[n/128, kb])
+//
+// A [M,K] and B [N,K] are E4M3, K-major; sfa is [M, K/128] FP32 (one scale per row and 128
+// columns), sfb is [N/128, K/128] FP32 (one per 128x128 block). FP32 scales cannot ride on the
+// block-scaled MMA (it takes power-of-two or E4M3 scale bytes), so every 128-wide k-block is
+// multiplied unscaled (tcgen05 kind::f8f6f4, four K=32 instructions) into a TMEM buffer and
+// promoted into FP32 register accumulators with one FMA per element.
+//
+// One CTA (320 threads) owns a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer,
+// warps 2..9 = promotion/epilogue (two warps per 32-lane TMEM quarter, each taking 128 of the
+// 256 columns = exactly one 128-column scale block). The two 256-column TMEM buffers fill all
+// 512 columns, so the MMA of k-block i+1 overlaps the promotion of k-block i.
+#pragma once
+
+#include "gemm_blockscaled.cuh"
+
+namespace b12x_b200 {
+
+struct BlockFp8Tile {
+  static constexpr int BM = 128;
+  static constexpr int BN = 256;
+  static constexpr int kABytes = BM * 128;
+  static constexpr int kBBytes = BN * 128;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 4;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static constexpr int kEpilogueWarps = 8;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+};
+
+struct BlockFp8Params {
+  const float* sfa;   // [M, K/128]
+  const float* sfb;   // [ceil(N/128), K/128]
+  void* c;
+  const float* alpha;
+  int* status;
+  int m, n, k, ldc, out_dtype;
+  int tiles_m, tiles_n, group_m;
+};
+
+__global__ void __launch_bounds__(BlockFp8Tile::kThreads, 1)
+gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
+                      const __grid_constant__ CUtensorMap map_b, const BlockFp8Params p) {
+  using T = BlockFp8Tile;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + T::kStages * T::kStageBytes);
+  uint64_t* empty_bar = full_bar + T::kStages;
+  uint64_t* part_full_bar = empty_bar + T::kStages;
+  uint64_t* part_empty_bar = part_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&part_full_bar[b], 1);
+      mbar_init(&part_empty_bar[b], T::kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tmem_base != 0) {  // the CTA owns the whole TMEM, so the base is column 0
+    if (threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    return;
+  }
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_blocks = p.k / 128;
+  const uint32_t smem_u32 = smem_addr_u32(smem);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          uint8_t* st = smem + stage * T::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], T::kStageBytes);
+          tma_load_2d(st, &map_a, &full_bar[stage], kb * 128, tm * T::BM);
+          tma_load_2d(st + T::kABytes, &map_b, &full_bar[stage], kb * 128, tn * T::BN);
+        }
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    constexpr uint32_t idesc = make_idesc_f8(128, T::BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const uint32_t buf = it & 1;
+        if (!mbar_wait_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag) ||
+            !mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t st = smem_u32 + stage * T::kStageBytes;
+        if (elect_one()) {
+          const uint64_t adesc = make_kmajor_sw128_desc(st);
+          const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tc_mma_f8(buf * T::BN, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
+          tc_commit(&empty_bar[stage]);
+          tc_commit(&part_full_bar[buf]);
+        }
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------- promotion + epilogue -------------------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
+    const float alpha = p.alpha ? *p.alpha : 1.0f;
+    const int kb_total = k_blocks;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int row = tm * T::BM + quarter * 32 + lane;
+      const int col0 = tn * T::BN + half * 128;
+      const bool row_ok = row < p.m;
+      const bool col_ok = col0 < p.n;
+      const float* sfa_row = p.sfa + static_cast<size_t>(row_ok ? row : 0) * kb_total;
+      const float* sfb_row = p.sfb + static_cast<size_t>(col_ok ? col0 / 128 : 0) * kb_total;
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const uint32_t buf = it & 1;
+        // Scales of this k-block are fetched before the wait so their latency hides behind it.
+        const float scale = __fmul_rn(row_ok ? __ldg(sfa_row + kb) : 0.0f,
+                                      col_ok ? __ldg(sfb_row + kb) : 0.0f);
+        if (!mbar_wait_bounded(&part_full_bar[buf], (it >> 1) & 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t taddr =
+            (static_cast<uint32_t>(quarter * 32) << 16) + buf * T::BN + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t raw[32];
+          tmem_load_32cols(taddr + c * 32, raw);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[c * 32 + i] = fmaf(__uint_as_float(raw[i]), scale, acc[c * 32 + i]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&part_empty_bar[buf]);
+      }
+      if (!ok) break;
+      GemmParams gp;
+      gp.c = p.c;
+      gp.m = p.m;
+      gp.n = p.n;
+      gp.ldc = p.ldc;
+      gp.out_dtype = p.out_dtype;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float vals[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[i] = acc[c * 32 + i] * alpha;
+        store_row_chunk(gp, row, col0 + c * 32, vals);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(0, 512);
+  }
+}
+
+}  // namespace b12x_b200

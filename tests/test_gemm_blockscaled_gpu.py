@@ -257,3 +257,86 @@ def test_no_kernel_reported_a_timed_out_wait():
     from sparkinfer_b200._lib.launch import check_kernel_status
 
     check_kernel_status(DEV)
+
+
+# --------------------------------------------------------------------------------------
+# block_fp8=True: E4M3 operands with compact FP32 scales (1x128 activations, 128x128 weights)
+# --------------------------------------------------------------------------------------
+BLOCK_FP8 = dict(ab_dtype="float8_e4m3fn", sf_dtype="float32", sf_vec_size=128, block_fp8=True)
+
+
+def _block_fp8_operands(seed, m, n, k):
+    from gpu_util import to_dev
+
+    a = seeded_bf16(seed, (m, k)).float().numpy()
+    b = seeded_bf16(seed + 1, (n, k)).float().numpy()
+    a_codes, a_scale = O.quantize_block_fp8(a, 1)
+    b_codes, b_scale = O.quantize_block_fp8(b, 128)
+    lhs = (to_dev(a_codes).view(torch.float8_e4m3fn).view(m, k, 1), to_dev(a_scale))
+    rhs = (to_dev(b_codes).view(torch.float8_e4m3fn).view(n, k, 1), to_dev(b_scale))
+    return lhs, rhs, O.gemm_block_fp8(a_codes, a_scale, b_codes, b_scale)
+
+
+@pytest.mark.parametrize("m,n,k,c_dtype", [
+    (1, 128, 256, "bfloat16"), (8, 256, 256, "bfloat16"), (64, 128, 512, "bfloat16"),
+    (129, 256, 256, "bfloat16"), (2, 4096, 4096, "bfloat16"), (300, 384, 1024, "float32"),
+    (512, 1152, 768, "float16"),
+])
+def test_mm_block_fp8_matches_oracle(m, n, k, c_dtype):
+    """tests/gemm/test_gemm_stack.py:139-165: rtol 2e-2 / atol 2e-3 and cosine >= 0.9999
+    against the dequantized FP32 product; the tighter bound of assert_gemm_close holds too."""
+    from gpu_util import assert_gemm_close
+    from sparkinfer_b200.gemm import blockscaled
+
+    lhs, rhs, ref = _block_fp8_operands(m + n + k, m, n, k)
+    out = blockscaled.mm(lhs, rhs, c_dtype=c_dtype, **BLOCK_FP8)
+    torch.cuda.synchronize()
+    got = out[:, :, 0].float().cpu().numpy()
+    assert np.allclose(got, ref, rtol=2e-2, atol=2e-3 * np.abs(ref).max())
+    cos = float((got * ref).sum() / np.sqrt((got * got).sum() * (ref * ref).sum()))
+    assert cos >= 0.9999
+    assert_gemm_close(out[:, :, 0], ref, out_dtype=out.dtype)
+
+
+def test_mm_block_fp8_matches_reference_fixture_and_rereads_live_scales():
+    """Operands and result from the reference's _block_fp8_reference restated with torch ops;
+    then a CUDA-graph replay after changing a scale in place
+    (tests/gemm/test_gemm_stack.py:167-190)."""
+    from gpu_util import DEV, assert_gemm_close, to_dev
+    from sparkinfer_b200.gemm import blockscaled
+
+    g = np.load(GOLDEN / "gemm_ref.npz")
+    m, k = g["bf8_a"].shape
+    n = g["bf8_b"].shape[0]
+    sa, sb = to_dev(g["bf8_sa"]), to_dev(g["bf8_sb"])
+    lhs = (to_dev(g["bf8_a"]).view(torch.float8_e4m3fn).view(m, k, 1), sa)
+    rhs = (to_dev(g["bf8_b"]).view(torch.float8_e4m3fn).view(n, k, 1), sb)
+    out = torch.empty((m, n, 1), dtype=torch.float32, device=DEV)
+    blockscaled.mm(lhs, rhs, out, c_dtype="float32", **BLOCK_FP8)
+    torch.cuda.synchronize()
+    assert_gemm_close(out[:, :, 0], g["bf8_out"], out_dtype=torch.float32)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        blockscaled.mm(lhs, rhs, out, c_dtype="float32", **BLOCK_FP8)
+    sb[0, :] *= 2.0
+    graph.replay()
+    torch.cuda.synchronize()
+    ref = O.gemm_block_fp8(g["bf8_a"], g["bf8_sa"], g["bf8_b"], sb.cpu().numpy())
+    assert_gemm_close(out[:, :, 0], ref, out_dtype=torch.float32)
+
+
+def test_mm_block_fp8_rejects_bad_scales():
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import blockscaled
+
+    a = torch.zeros((4, 256, 1), dtype=torch.float8_e4m3fn, device=DEV)
+    b = torch.zeros((128, 256, 1), dtype=torch.float8_e4m3fn, device=DEV)
+    sa = torch.ones((4, 2), device=DEV)
+    sb = torch.ones((1, 2), device=DEV)
+    with pytest.raises(ValueError, match="block_fp8 requires"):
+        blockscaled.mm((a, sa[:, :1]), (b, sb), c_dtype="bfloat16", **BLOCK_FP8)
+    with pytest.raises(ValueError, match="block_fp8 requires"):
+        blockscaled.mm((a, sa), (b, sb), c_dtype="bfloat16", ab_dtype="float8_e4m3fn",
+                       sf_dtype="float8_e8m0fnu", sf_vec_size=128, block_fp8=True)
+    with pytest.raises(ValueError, match="unswapped"):
+        blockscaled.mm((a, sa), (b, sb), c_dtype="bfloat16", swap_ab=True, **BLOCK_FP8)
