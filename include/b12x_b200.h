@@ -76,6 +76,29 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
                                int sm_count, int* status, b12x_b200_stream_t stream);
 
 /*
+ * Decode-shape (1 <= M <= 128) variant of b12x_b200_gemm_blockscaled: the weight matrix is
+ * streamed once, split evenly over all SMs along N and K (stream-K), and partial sums meet in
+ * a caller-owned FP32 workspace. Stands in for the reference's small-M split-K policy and its
+ * partial-sum reduction (b12x/_lib/dense_gemm.py:412-426, 174-206, 2685-2800), which the
+ * reference has for FP8 operands only.
+ *
+ *   x, sf_x    activations [M, K] codes and their scale atoms (1 row tile)
+ *   w, sf_w    weights [N, K] codes and their scale atoms
+ *   workspace  at least b12x_b200_gemm_smallm_workspace_bytes(...) bytes, 16-byte aligned.
+ *              Its first 64 KiB hold per-tile counters that must be zero before the first
+ *              launch that uses the buffer (zero the buffer once); each launch leaves them
+ *              zero, so one buffer serves any sequence of shapes. Launches that share a
+ *              workspace must not overlap on the device.
+ */
+int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
+                                              int sm_count);
+int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x, const void* w,
+                                      const void* sf_w, void* c, int c_dtype, const float* alpha,
+                                      int64_t m, int64_t n, int64_t k, int64_t ldc,
+                                      void* workspace, int64_t workspace_bytes, int sm_count,
+                                      int* status, b12x_b200_stream_t stream);
+
+/*
  * Block-FP8 GEMM with compact FP32 scales,
  *   C[M,N] = cvt(alpha * sum_kb (A[:,kb] B[:,kb]^T) * sfa[m,kb] * sfb[n/128,kb]).
  * Replaces dense_gemm(..., block_fp8=True, sf_dtype="float32", sf_vec_size=128)

@@ -65,6 +65,7 @@ def clear_all_caches() -> None:
     launch = sys.modules.get(f"{__name__}._lib.launch")
     if launch is not None:
         launch._STATUS.clear()
+        launch._WORKSPACE.clear()
 
 
 def install_as_b12x() -> None:

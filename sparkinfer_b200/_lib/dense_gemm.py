@@ -280,7 +280,10 @@ def dense_gemm(
         raise NotImplementedError("plain_fp8 (per-tensor FP8) is not part of this path")
     _kind_of(ab_dtype, sf_dtype, sf_vec_size)
     if mma_tiler_mn is None:
-        mma_tiler_mn = _select_default_mma_tiler_mn(m, n, sm_count)
+        # Tile width 0 in the op arguments means "the launcher chooses": the persistent tiled
+        # kernel picks its width from the live shape and decode shapes go to the
+        # weight-streaming kernel. A caller-supplied tile forces the tiled kernel.
+        mma_tiler_mn = (128, 0)
     if alpha_dtype is None:
         alpha_dtype = "float32" if alpha is None else str(alpha.dtype).split(".")[-1]
     alpha_is_one = alpha is None

@@ -16,9 +16,15 @@ from .. import _native
 
 _STATUS_LOCK = Lock()
 _STATUS: dict[int, torch.Tensor] = {}
+_WORKSPACE: dict[int, torch.Tensor] = {}
+SMALL_M_MAX = 128
 
 _DTYPE_CODE = {torch.bfloat16: _native.DT_BF16, torch.float16: _native.DT_FP16,
                torch.float32: _native.DT_FP32}
+
+import os as _os
+
+_SMALL_M_DISABLED = _os.getenv("B12X_B200_DISABLE_SMALL_M", "0") == "1"
 
 KERNEL_STATUS_TEXT = {
     1: "TMA producer timed out waiting for a free pipeline stage",
@@ -73,17 +79,53 @@ def _require_cuda(name: str, t: torch.Tensor) -> None:
         raise ValueError(f"{name} must be on CUDA")
 
 
+def smallm_workspace(kind: int, m: int, n: int, k: int, device: torch.device,
+                     sm_count: int = 0) -> torch.Tensor:
+    """Per-device scratch of the decode-shape kernel (FP32 partial tiles + per-tile counters).
+    Created zeroed and grown on demand, so the first call for a larger shape allocates (warm up
+    before CUDA-graph capture). Every launch leaves the counters zero, and launches on one
+    device share the buffer, so they must not overlap on the GPU (same stream, or ordered)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(index):
+        need = int(_native.load().b12x_b200_gemm_smallm_workspace_bytes(kind, m, n, k, sm_count))
+    if need < 0:
+        raise _native.NativeLibraryError(f"no decode-shape plan for M={m}, N={n}, K={k}")
+    with _STATUS_LOCK:
+        buf = _WORKSPACE.get(index)
+        if buf is None or buf.numel() < need:
+            buf = torch.zeros(max(need, 1 << 20), dtype=torch.uint8,
+                              device=torch.device("cuda", index))
+            _WORKSPACE[index] = buf
+        return buf
+
+
 def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
                      sfb: torch.Tensor, c: torch.Tensor, alpha: torch.Tensor | None,
                      m: int, n: int, k: int, *, ldc: int | None = None, block_n: int = 0,
-                     sm_count: int = 0, stream_int: int | None = None) -> None:
+                     sm_count: int = 0, stream_int: int | None = None,
+                     small_m: bool | None = None) -> None:
     """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)`` for one group. ``a``/``b`` are row
-    pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom."""
+    pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom.
+
+    Decode shapes (M <= 128, unless ``small_m=False`` or a tile width is forced) go to the
+    weight-streaming stream-K kernel, everything else to the persistent tiled kernel."""
     for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
         _require_cuda(name, t)
     if c.dtype not in _DTYPE_CODE:
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = a.device
+    if small_m is None:
+        small_m = m <= SMALL_M_MAX and block_n == 0 and not _SMALL_M_DISABLED
+    if small_m and 0 < m <= SMALL_M_MAX and n > 0:
+        work = smallm_workspace(kind, m, n, k, dev, sm_count)
+        with torch.cuda.device(dev):
+            rc = _native.load().b12x_b200_gemm_blockscaled_smallm(
+                kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+                _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
+                m, n, k, ldc if ldc is not None else n, work.data_ptr(), work.numel(), sm_count,
+                status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+        _native.check(rc, "b12x_b200_gemm_blockscaled_smallm")
+        return
     with torch.cuda.device(dev):
         rc = _native.load().b12x_b200_gemm_blockscaled(
             kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),

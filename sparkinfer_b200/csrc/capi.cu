@@ -11,6 +11,7 @@
 
 #include "gemm_blockscaled.cuh"
 #include "gemm_block_fp8.cuh"
+#include "gemm_smallm.cuh"
 #include "quantize.cuh"
 
 namespace b12x_b200 {
@@ -352,4 +353,160 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_block_fp8 launch");
   return B12X_B200_OK;
+}
+
+namespace {
+
+// The workspace starts with a fixed-size block of per-tile counters, so the counters of every
+// shape live at the same offsets and stay zero between launches of different shapes.
+constexpr size_t kSmallMCounterBytes = 64 * 1024;
+
+struct SmallMPlan {
+  int m_pad, tiles, k_tiles, k_atoms, grid, max_segments, stages, stage_bytes;
+  size_t partial_bytes, total_bytes;
+};
+
+// Geometry of the decode-shape kernel for (kind, m, n, k) on `sms` SMs.
+int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* out) {
+  if (m < 1 || m > 128) return fail(B12X_B200_ERR_UNSUPPORTED, "decode kernel needs 1 <= M <= 128");
+  const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
+  const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
+  SmallMPlan pl;
+  pl.m_pad = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+  pl.tiles = int((n + 127) / 128);
+  pl.k_tiles = int((k + elems_per_stage - 1) / elems_per_stage);
+  pl.k_atoms = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
+  const int64_t units = int64_t(pl.tiles) * pl.k_tiles;
+  if (units >= (int64_t(1) << 31)) return fail(B12X_B200_ERR_UNSUPPORTED, "problem too large for the decode kernel");
+  // Grid: with no more tiles than SMs, a whole number of CTAs per tile (capped by the k-tiles a
+  // tile has) keeps every CTA range inside one tile, so a tile that gets a single CTA needs no
+  // partial sums at all; with more tiles than SMs one CTA per SM streams an equal share.
+  if (pl.tiles <= sms) {
+    int per_tile = sms / pl.tiles;
+    if (per_tile > pl.k_tiles) per_tile = pl.k_tiles;
+    pl.grid = pl.tiles * per_tile;
+  } else {
+    pl.grid = sms;
+  }
+  const int64_t units_per_cta = units / pl.grid;  // >= 1
+  int64_t seg = (pl.k_tiles + units_per_cta - 1) / units_per_cta + 1;
+  if (seg > pl.grid) seg = pl.grid;
+  pl.max_segments = int(seg);
+  pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
+                                                  : SmallMTile<kNvfp4>::stage_bytes(pl.m_pad);
+  int stages = (227 * 1024 - 2048) / pl.stage_bytes;
+  if (stages > SmallMTile<kMxfp8>::kMaxStages) stages = SmallMTile<kMxfp8>::kMaxStages;
+  pl.stages = stages;
+  pl.partial_bytes = size_t(pl.tiles) * pl.max_segments * pl.m_pad * 128 * sizeof(float);
+  if (size_t(pl.tiles) * sizeof(int) > kSmallMCounterBytes)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "N too large for the decode kernel's counter block");
+  pl.total_bytes = kSmallMCounterBytes + pl.partial_bytes;
+  *out = pl;
+  return B12X_B200_OK;
+}
+
+template <int KIND>
+int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
+                  int grid, int smem_bytes, cudaStream_t stream) {
+  static bool set_for[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set_for[dev]) {
+    const cudaError_t attr_err = cudaFuncSetAttribute(
+        gemm_smallm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    set_for[dev] = true;
+  }
+  gemm_smallm_kernel<KIND><<<grid, 192, smem_bytes, stream>>>(map_w, map_x, p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
+  return B12X_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
+                                                         int sm_count) {
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (n <= 0 || k <= 0) return -1;
+  DeviceInfo info;
+  int sms = sm_count;
+  if (sms <= 0) {
+    if (device_info(&info) != B12X_B200_OK) return -1;
+    sms = info.sm_count;
+  }
+  SmallMPlan pl;
+  if (plan_smallm(kind, m, n, k, sms, &pl) != B12X_B200_OK) return -1;
+  return int64_t(pl.total_bytes);
+}
+
+extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
+                                                 const void* w, const void* sf_w, void* c,
+                                                 int c_dtype, const float* alpha, int64_t m,
+                                                 int64_t n, int64_t k, int64_t ldc,
+                                                 void* workspace, int64_t workspace_bytes,
+                                                 int sm_count, int* status,
+                                                 b12x_b200_stream_t stream) {
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
+  if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
+  if (n < 0 || k <= 0 || n > INT32_MAX || k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (m == 0 || n == 0) return B12X_B200_OK;
+  if (!x || !w || !sf_x || !sf_w || !c || !workspace)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
+  const int64_t row_bytes = (kind == B12X_B200_KIND_MXFP8) ? k : k / 2;
+  if (row_bytes % 16 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(sf_x) ||
+      !aligned16(sf_w) || !aligned16(workspace))
+    return fail(B12X_B200_ERR_ALIGNMENT, "operands, scales and workspace must be 16-byte aligned");
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  SmallMPlan pl;
+  rc = plan_smallm(kind, m, n, k, sms, &pl);
+  if (rc != B12X_B200_OK) return rc;
+  if (workspace_bytes < int64_t(pl.total_bytes))
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "workspace smaller than b12x_b200_gemm_smallm_workspace_bytes");
+
+  CUtensorMap map_w, map_x;
+  rc = make_operand_map(&map_w, w, uint64_t(n), uint64_t(row_bytes), 128);
+  if (rc != B12X_B200_OK) return rc;
+  rc = make_operand_map(&map_x, x, uint64_t(m), uint64_t(row_bytes), uint32_t(pl.m_pad));
+  if (rc != B12X_B200_OK) return rc;
+
+  SmallMParams p;
+  p.sf_w = static_cast<const uint8_t*>(sf_w);
+  p.sf_x = static_cast<const uint8_t*>(sf_x);
+  p.c = c;
+  p.alpha = alpha;
+  p.status = status;
+  p.counters = static_cast<int*>(workspace);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSmallMCounterBytes);
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  p.ldc = int(ldc);
+  p.out_dtype = c_dtype;
+  p.m_pad = pl.m_pad;
+  p.tiles = pl.tiles;
+  p.k_tiles = pl.k_tiles;
+  p.k_atoms_total = pl.k_atoms;
+  p.max_segments = pl.max_segments;
+  p.num_stages = pl.stages;
+  p.stage_bytes = pl.stage_bytes;
+  p.debug_flags = 0;
+  if (const char* e = getenv("B12X_B200_DEBUG_FLAGS")) p.debug_flags = atoi(e);
+  if (const char* e = getenv("B12X_B200_STAGES")) { int st = atoi(e); if (st >= 2 && st < p.num_stages) p.num_stages = st; }
+  p.prof = nullptr;
+  if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
+  const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == B12X_B200_KIND_MXFP8)
+    return launch_smallm<kMxfp8>(map_w, map_x, p, pl.grid, smem_bytes, s);
+  return launch_smallm<kNvfp4>(map_w, map_x, p, pl.grid, smem_bytes, s);
 }

@@ -1,0 +1,370 @@
+// Weight-streaming block-scaled GEMM for decode shapes (M <= 128) on sm_100a.
+//
+// With a handful of activation rows the GEMM is a pure stream of the weight matrix: what
+// matters is that every SM pulls an equal share of the weight bytes with enough of them in
+// flight. The roles of the operands are swapped relative to the large-M kernel: 128 weight
+// rows fill the M side of the tcgen05 MMA, the (padded) activation rows are its N side, so no
+// shared memory or tensor-core time is spent on padding rows.
+//
+// Work is cut stream-K style. A unit is (weight tile of 128 rows, k-tile of 128 bytes of K);
+// units are numbered tile-major and CTA c of G takes units [c*U/G, (c+1)*U/G), i.e. every
+// CTA streams the same number of bytes (+-1 unit) whatever N is. A CTA range covers a run of
+// segments, one per tile it touches. A segment that spans its whole tile is converted and
+// stored directly. Otherwise the FP32 partial goes to scratch slot (tile, segment index) and
+// a per-tile counter is bumped; the CTA that brings the counter to the segment count adds the
+// slots in segment order (deterministic) and stores the tile, then resets the counter. Nobody
+// waits on another CTA.
+//
+// Scratch ("workspace") layout: a 64 KiB block of per-tile int32 counters, then
+// [tiles][max_segments][m_pad][128] FP32 partials. Counters must be zero before the first
+// launch; every launch leaves them zero again, whatever the shape.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_blockscaled.cuh"
+
+namespace b12x_b200 {
+
+struct SmallMParams {
+  const uint8_t* sf_w;     // weight scale atoms   [ceil(N/128)][k_atoms][512]
+  const uint8_t* sf_x;     // activation scale atoms [1][k_atoms][512] (rows >= M unused)
+  void* c;                 // [M, ldc]
+  const float* alpha;
+  int* status;
+  float* partials;         // scratch, see above
+  int* counters;
+  int m, n, k, ldc, out_dtype;
+  int m_pad;               // MMA N: 16, 32, 64 or 128
+  int tiles;               // ceil(N / 128)
+  int k_tiles;             // ceil(K / elems per stage)
+  int k_atoms_total;
+  int max_segments;        // scratch slots per tile
+  int num_stages;
+  int stage_bytes;
+  long long* prof;         // optional cycle counters of CTA 0 (bring-up only)
+  int debug_flags;         // bring-up: 1 = no MMA / scale copies, 2 = no loads
+};
+
+template <int KIND>
+struct SmallMTile {
+  static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
+  static constexpr int kElemsPerStage = kElemsPerMma * 4;
+  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : 4;
+  static constexpr int kWBytes = 128 * 128;
+  static constexpr int kSfBytes = kKAtoms * 512;
+  // Stage = weights | weight scales | activation scales | activation rows (m_pad * 128 B).
+  static constexpr int kXOffset = kWBytes + 2 * kSfBytes;
+  static constexpr int kSfwCol0 = 256;                 // after two accumulators of <= 128 cols
+  static constexpr int kSfxCol0 = kSfwCol0 + kKAtoms * 4;
+  static constexpr int kMaxStages = 10;
+  __host__ __device__ static constexpr int stage_bytes(int m_pad) {
+    return ((kXOffset + m_pad * 128 + 1023) / 1024) * 1024;
+  }
+};
+
+// CTA that owns unit u when units are split as begin_c = c * U / G.
+__device__ __forceinline__ int owner_of_unit(int u, int units, int ctas) {
+  return static_cast<int>(((static_cast<long long>(u) + 1) * ctas - 1) / units);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(192, 1)
+gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
+  using T = SmallMTile<KIND>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.num_stages * p.stage_bytes);
+  uint64_t* empty_bar = full_bar + T::kMaxStages;
+  uint64_t* acc_full_bar = empty_bar + T::kMaxStages;
+  uint64_t* acc_empty_bar = acc_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.num_stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tmem_base != 0) {
+    if (threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    return;
+  }
+
+  // Unit arithmetic is 32-bit in the loops (the host rejects tiles * k_tiles >= 2^31); the
+  // range ends use 64-bit products once.
+  const int units = p.tiles * p.k_tiles;
+  const int u_begin = static_cast<int>(static_cast<long long>(units) * blockIdx.x / gridDim.x);
+  const int u_end = static_cast<int>(static_cast<long long>(units) * (blockIdx.x + 1) / gridDim.x);
+  const uint32_t smem_u32 = smem_addr_u32(smem);
+  const uint32_t x_bytes = static_cast<uint32_t>(p.m_pad) * 128u;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    const long long pt0 = clock64();
+    int tile = u_begin / p.k_tiles;
+    int kt = u_begin - tile * p.k_tiles;
+    for (int u = u_begin; u < u_end; ++u) {
+      if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+        break;
+      }
+      if (elect_one()) {
+        uint8_t* st = smem + stage * p.stage_bytes;
+        uint64_t* bar = &full_bar[stage];
+        const int katom0 = kt * T::kKAtoms;
+        const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+        const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+        if (p.debug_flags & 2) {
+          mbar_arrive(bar);
+        } else {
+        mbar_arrive_expect_tx(bar, T::kWBytes + x_bytes + 2 * sf_bytes);
+        tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
+        tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
+        bulk_load(st + T::kWBytes,
+                  p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512, sf_bytes,
+                  bar);
+        bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
+                  sf_bytes, bar);
+        }
+      }
+      __syncwarp();
+      if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
+      if (++kt == p.k_tiles) { kt = 0; ++tile; }
+    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) p.prof[0] = clock64() - pt0;
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc_base = make_idesc_block_scaled(
+        128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    int stage = 0;
+    uint32_t phase = 0;
+    int seg = 0;
+    bool ok = true;
+    int u = u_begin;
+    const long long mt0 = clock64();
+    long long m_wait_full = 0;
+    while (u < u_end && ok) {
+      const int tile = u / p.k_tiles;
+      const int tile_end = (tile + 1) * p.k_tiles;
+      const int seg_end = tile_end < u_end ? tile_end : u_end;
+      int kt = u - tile * p.k_tiles;
+      const int acc = seg & 1;
+      if (!mbar_wait_bounded(&acc_empty_bar[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_taddr = acc * 128;
+      bool first = true;
+      for (; u < seg_end; ++u, ++kt) {
+        const long long tw = clock64();
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        m_wait_full += clock64() - tw;
+        tc_fence_after_sync();
+        const uint32_t st = smem_u32 + stage * p.stage_bytes;
+        const int mmas = min(4, (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
+        if (elect_one()) {
+          const uint64_t sf_desc = make_sf_chunk_desc(st + T::kWBytes);
+#pragma unroll
+          for (int ka = 0; ka < ((p.debug_flags & 1) ? 0 : T::kKAtoms); ++ka) {
+            tc_copy_sf_atom(T::kSfwCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
+            tc_copy_sf_atom(T::kSfxCol0 + ka * 4, sf_desc + ((T::kSfBytes + ka * 512) >> 4));
+          }
+          const uint64_t wdesc = make_kmajor_sw128_desc(st);
+          const uint64_t xdesc = make_kmajor_sw128_desc(st + T::kXOffset);
+          for (int j = 0; j < ((p.debug_flags & 1) ? 0 : mmas); ++j) {
+            const uint32_t accumulate = (first && j == 0) ? 0u : 1u;
+            if (KIND == kMxfp8)
+              tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
+                          idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfwCol0,
+                          T::kSfxCol0);
+            else
+              tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
+                          T::kSfwCol0 + j * 4, T::kSfxCol0 + j * 4);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (u + 1 == seg_end) tc_commit(&acc_full_bar[acc]);
+        }
+        __syncwarp();
+        first = false;
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
+      }
+      ++seg;
+    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) {
+      p.prof[1] = clock64() - mt0;
+      p.prof[2] = m_wait_full;
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quarter = warp & 3;
+    const int n_local = quarter * 32 + lane;          // weight row inside the tile
+    const float alpha = p.alpha ? *p.alpha : 1.0f;
+    const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
+    int seg = 0;
+    int u = u_begin;
+    const long long et0 = clock64();
+    long long e_wait = 0, e_drain = 0, e_publish = 0, e_reduce = 0;
+    while (u < u_end) {
+      const long long ew0 = clock64();
+      const int tile = u / p.k_tiles;
+      const int tile_begin = tile * p.k_tiles;
+      const int tile_end = tile_begin + p.k_tiles;
+      const int seg_end = tile_end < u_end ? tile_end : u_end;
+      const bool whole = (u == tile_begin) && (seg_end == tile_end);
+      const int acc = seg & 1;
+      // The four epilogue warps meet at barriers further down, so they leave together or not
+      // at all: the outcome of the wait is AND-reduced across them first.
+      if (!epilogue_bar_and(mbar_wait_bounded(&acc_full_bar[acc], (seg >> 1) & 1, abort_flag))) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const long long ew1 = clock64();
+      e_wait += ew1 - ew0;
+      const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * 128;
+      const int n_global = tile * 128 + n_local;
+      const bool n_ok = n_global < p.n;
+      int first_cta = 0, segments = 1, slot = 0;
+      if (!whole) {
+        first_cta = owner_of_unit(tile_begin, units, gridDim.x);
+        segments = owner_of_unit(tile_end - 1, units, gridDim.x) - first_cta + 1;
+        slot = static_cast<int>(blockIdx.x) - first_cta;
+      }
+      float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
+      for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+        uint32_t raw[16];
+        tmem_load_16cols(taddr + c0, raw);
+        tmem_load_wait();
+        if (whole) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int mrow = c0 + i;
+            if (n_ok && mrow < p.m) {
+              const float v = __uint_as_float(raw[i]) * alpha;
+              const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+              if (p.out_dtype == kOutBf16)
+                static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
+              else if (p.out_dtype == kOutFp16)
+                static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
+              else
+                static_cast<float*>(p.c)[idx] = v;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            my_slot[static_cast<size_t>(c0 + i) * 128 + n_local] = __uint_as_float(raw[i]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      const long long ew2 = clock64();
+      e_drain += ew2 - ew1;
+
+      if (!whole) {
+        // Publish the partial, count the arrival, and let the last arriver finish the tile.
+        __threadfence();
+        epilogue_bar_sync();
+        if (warp == 2 && lane == 0) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (prev == segments - 1) ? 1 : 0;
+          if (prev == segments - 1) p.counters[tile] = 0;
+        }
+        epilogue_bar_sync();
+        const long long ew3 = clock64();
+        e_publish += ew3 - ew2;
+        if (*last_flag) {
+          __threadfence();
+          const float* tile_slots = p.partials + static_cast<size_t>(tile) * p.max_segments * slot_floats;
+          // Eight rows at a time so that 8 x segments loads are in flight per thread.
+          for (int m0 = 0; m0 < p.m; m0 += 8) {
+            float sum[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+            for (int s = 0; s < segments; ++s) {
+              const float* src = tile_slots + s * slot_floats + static_cast<size_t>(m0) * 128 + n_local;
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = (m0 + i < p.m) ? __ldcg(src + i * 128) : 0.0f;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) sum[i] += v[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int mrow = m0 + i;
+              if (n_ok && mrow < p.m) {
+                const float v = sum[i] * alpha;
+                const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+                if (p.out_dtype == kOutBf16)
+                  static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
+                else if (p.out_dtype == kOutFp16)
+                  static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
+                else
+                  static_cast<float*>(p.c)[idx] = v;
+              }
+            }
+          }
+        }
+        epilogue_bar_sync();
+        e_reduce += clock64() - ew3;
+      }
+      u = seg_end;
+      ++seg;
+    }
+    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
+      p.prof[3] = clock64() - et0;
+      p.prof[4] = e_wait;
+      p.prof[5] = e_drain;
+      p.prof[6] = e_publish;
+      p.prof[7] = e_reduce;
+      p.prof[8] = seg;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(0, 512);
+  }
+}
+
+}  // namespace b12x_b200

@@ -99,6 +99,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Barrier 1 over the 128 epilogue threads, AND-reducing a predicate: lets the four epilogue
+// warps agree on "everyone's wait succeeded" before any of them enters a barrier the others
+// might never reach.
+__device__ __forceinline__ bool epilogue_bar_and(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "barrier.cta.red.and.pred p, 1, 128, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
+__device__ __forceinline__ void epilogue_bar_sync() {
+  asm volatile("barrier.cta.sync 1, 128;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------------------
 // TMA: tiled tensor loads (never multicast), plain bulk loads, tiled stores
 // ----------------------------------------------------------------------------------------
