@@ -99,6 +99,40 @@ int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
                                       int* status, b12x_b200_stream_t stream);
 
 /*
+ * b12x_b200_gemm_blockscaled_smallm for callers that cannot allocate device memory. It has no
+ * counterpart in the reference.
+ *
+ * Some callers of a decode GEMM are not in a position to call cudaMalloc (or a framework
+ * allocator) for the workspace above: a serving process that gave all device memory to its own
+ * pool at start-up and runs with a fixed budget, a plugin called from a thread that is in the
+ * middle of a CUDA stream capture (where an allocation fails or invalidates the capture), a
+ * small C host that links this library and nothing else. For them this entry point keeps the
+ * workspace inside the library: a fixed 4 MiB + 64 KiB array in device memory, present on every
+ * GPU that loads the library until the process exits. The function allocates nothing and calls
+ * no allocating routine; inputs and outputs are still the caller's.
+ *
+ *   - Shapes whose workspace need (b12x_b200_gemm_smallm_workspace_bytes) exceeds
+ *     b12x_b200_gemm_smallm_noalloc_capacity_bytes() are refused with
+ *     B12X_B200_ERR_UNSUPPORTED and a message naming both sizes. M <= 16 with N <= 16384 always
+ *     fits; larger M fits for smaller N.
+ *   - The first call on each device looks up the device address of the built-in array (with
+ *     that device current). Make that first call outside any stream capture, e.g. as the
+ *     warm-up call.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents:
+ *     every call first clears the per-tile counters on the given stream. Two calls that can
+ *     run on the GPU at the same time (different streams without ordering) race on it; keep
+ *     them on one stream or order them with events.
+ *
+ * Arguments as for b12x_b200_gemm_blockscaled_smallm, minus the workspace.
+ */
+int64_t b12x_b200_gemm_smallm_noalloc_capacity_bytes(void);
+int b12x_b200_gemm_blockscaled_smallm_noalloc(int kind, const void* x, const void* sf_x,
+                                              const void* w, const void* sf_w, void* c,
+                                              int c_dtype, const float* alpha, int64_t m,
+                                              int64_t n, int64_t k, int64_t ldc, int sm_count,
+                                              int* status, b12x_b200_stream_t stream);
+
+/*
  * Block-FP8 GEMM with compact FP32 scales,
  *   C[M,N] = cvt(alpha * sum_kb (A[:,kb] B[:,kb]^T) * sfa[m,kb] * sfb[n/128,kb]).
  * Replaces dense_gemm(..., block_fp8=True, sf_dtype="float32", sf_vec_size=128)

@@ -510,3 +510,77 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
     return launch_smallm<kMxfp8>(map_w, map_x, p, pl.grid, smem_bytes, s);
   return launch_smallm<kNvfp4>(map_w, map_x, p, pl.grid, smem_bytes, s);
 }
+
+// ----------------------------------------------------------------------------------------
+// Decode-shape GEMM for callers that cannot allocate device memory
+// ----------------------------------------------------------------------------------------
+namespace {
+
+// Scratch of the allocation-free entry point: the 64 KiB counter block plus 4 MiB of FP32
+// partial tiles. It is part of the library image, so every GPU that loads the library keeps
+// these bytes for the life of the process.
+constexpr size_t kNoAllocScratchBytes = kSmallMCounterBytes + (size_t(4) << 20);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of g_noalloc_scratch per device. In host code the array's name is only a
+// handle for the runtime, not a device pointer, so the address is looked up once per device.
+void* g_noalloc_scratch_ptr[64] = {};
+std::mutex g_noalloc_mu;
+
+}  // namespace
+
+extern "C" int64_t b12x_b200_gemm_smallm_noalloc_capacity_bytes(void) {
+  return int64_t(kNoAllocScratchBytes);
+}
+
+extern "C" int b12x_b200_gemm_blockscaled_smallm_noalloc(int kind, const void* x, const void* sf_x,
+                                                         const void* w, const void* sf_w, void* c,
+                                                         int c_dtype, const float* alpha,
+                                                         int64_t m, int64_t n, int64_t k,
+                                                         int64_t ldc, int sm_count, int* status,
+                                                         b12x_b200_stream_t stream) {
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
+  if (m == 0 || n == 0) return B12X_B200_OK;
+  if (n < 0 || k <= 0) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "device index out of range");
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  SmallMPlan pl;
+  rc = plan_smallm(kind, m, n, k, sms, &pl);
+  if (rc != B12X_B200_OK) return rc;
+  if (pl.total_bytes > kNoAllocScratchBytes) {
+    snprintf(g_last_error, sizeof(g_last_error),
+             "M=%lld N=%lld K=%lld needs %zu bytes of scratch; the built-in scratch of the "
+             "allocation-free entry point holds %zu",
+             static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k),
+             pl.total_bytes, kNoAllocScratchBytes);
+    return B12X_B200_ERR_UNSUPPORTED;
+  }
+  void* scratch = nullptr;
+  {
+    // First call on this device: resolve the device address of the static array (the device
+    // must be current, which it is: it is the one cudaGetDevice just reported).
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_scratch_ptr[dev]) {
+      void* ptr = nullptr;
+      err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress(g_noalloc_scratch)");
+      g_noalloc_scratch_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_scratch_ptr[dev];
+  }
+  // The array keeps whatever the previous call left. Only the per-tile counters have to start
+  // at zero; partial slots are fully written before they are read.
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  err = cudaMemsetAsync(scratch, 0, size_t(pl.tiles) * sizeof(int), s);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaMemsetAsync(counters)");
+  return b12x_b200_gemm_blockscaled_smallm(kind, x, sf_x, w, sf_w, c, c_dtype, alpha, m, n, k, ldc,
+                                           scratch, int64_t(kNoAllocScratchBytes), sm_count,
+                                           status, stream);
+}
