@@ -11,6 +11,7 @@
 
 #include "gemm_blockscaled.cuh"
 #include "gemm_block_fp8.cuh"
+#include "gemm_blockscaled_pair.cuh"
 #include "gemm_smallm.cuh"
 #include "quantize.cuh"
 
@@ -70,6 +71,27 @@ int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return B12X_B200_OK;
 }
 
+// Row-major 2-byte matrix [rows, cols] with row pitch `ld` elements -> boxes of 64 columns
+// (128 bytes) x 128 rows, 128-byte swizzle; used for TMA stores of BF16/FP16 outputs.
+int make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                    uint64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
+         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(C) failed (%d)", int(r));
+    return B12X_B200_ERR_CUDA;
+  }
+  return B12X_B200_OK;
+}
+
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -118,8 +140,8 @@ int choose_block_n(int64_t m, int64_t n, int sms) {
 }
 
 template <int KIND, int BN>
-int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int grid,
-                cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                const GemmParams& p, int grid, cudaStream_t stream) {
   using T = GemmTile<KIND, BN>;
   // The large dynamic shared memory opt-in is per device: set it the first time each device
   // launches this instantiation.
@@ -135,20 +157,55 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmPa
   }
   GemmParams q = p;
   q.num_stages = (p.num_stages >= 2 && p.num_stages <= T::kStages) ? p.num_stages : T::kStages;
-  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, q);
+  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, map_c, q);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled launch");
   return B12X_B200_OK;
 }
 
+// CTA-pair kernel: clusters of two CTAs, one 256 x BN tile per pair.
+template <int KIND, int BN>
+int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                     const GemmParams& p, int pairs, cudaStream_t stream) {
+  using T = PairTile<KIND, BN>;
+  static bool set_for[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set_for[dev]) {
+    const cudaError_t attr_err =
+        cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, BN>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+    if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    set_for[dev] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = T::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t err =
+      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN>, map_a, map_b, map_c, p);
+  if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled_pair launch");
+  return B12X_B200_OK;
+}
+
 template <int KIND>
 int dispatch_block_n(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                     const GemmParams& p, int grid, cudaStream_t stream) {
+                     const CUtensorMap& map_c, const GemmParams& p, int grid,
+                     cudaStream_t stream) {
   switch (bn) {
-    case 64: return launch_gemm<KIND, 64>(map_a, map_b, p, grid, stream);
-    case 128: return launch_gemm<KIND, 128>(map_a, map_b, p, grid, stream);
-    case 192: return launch_gemm<KIND, 192>(map_a, map_b, p, grid, stream);
-    case 256: return launch_gemm<KIND, 256>(map_a, map_b, p, grid, stream);
+    case 64: return launch_gemm<KIND, 64>(map_a, map_b, map_c, p, grid, stream);
+    case 128: return launch_gemm<KIND, 128>(map_a, map_b, map_c, p, grid, stream);
+    case 192: return launch_gemm<KIND, 192>(map_a, map_b, map_c, p, grid, stream);
+    case 256: return launch_gemm<KIND, 256>(map_a, map_b, map_c, p, grid, stream);
     default: return fail(B12X_B200_ERR_INVALID_ARGUMENT, "block_n must be 64, 128, 192 or 256");
   }
 }
@@ -190,10 +247,17 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
   const int bn = block_n > 0 ? block_n : choose_block_n(m, n, sms);
 
+  // Large problems (at least one full wave of 256 x 256 pair tiles) go to the CTA-pair kernel
+  // unless a tile width was forced.
+  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  bool use_pair = (block_n == 0) && (sms >= 2) && (pair_tiles >= sms / 2);
+  if (const char* e = getenv("B12X_B200_PAIR")) use_pair = (block_n == 0) && (sms >= 2) && atoi(e) != 0;
+
   CUtensorMap map_a, map_b;
   rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(row_bytes), 128);
   if (rc != B12X_B200_OK) return rc;
-  rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(row_bytes), uint32_t(bn));
+  rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(row_bytes),
+                        use_pair ? 128u : uint32_t(bn));
   if (rc != B12X_B200_OK) return rc;
 
   GemmParams p;
@@ -220,8 +284,29 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (kind == B12X_B200_KIND_MXFP8) return dispatch_block_n<kMxfp8>(bn, map_a, map_b, p, grid, s);
-  return dispatch_block_n<kNvfp4>(bn, map_a, map_b, p, grid, s);
+  // Output through TMA when rows of C are 16-byte aligned 2-byte values; otherwise the
+  // epilogue stores straight from registers.
+  CUtensorMap map_c;
+  memset(&map_c, 0, sizeof(map_c));
+  p.use_tma_store = 0;
+  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0 &&
+      !getenv("B12X_B200_DIRECT_STORE")) {
+    rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
+    if (rc != B12X_B200_OK) return rc;
+    p.use_tma_store = 1;
+  }
+  if (use_pair) {
+    p.tiles_m = int((m + 255) / 256);
+    p.tiles_n = int((n + 255) / 256);
+    p.group_m = 8;
+    const int pairs = int(pair_tiles < sms / 2 ? pair_tiles : sms / 2);
+    if (kind == B12X_B200_KIND_MXFP8)
+      return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, pairs, s);
+    return launch_gemm_pair<kNvfp4, 256>(map_a, map_b, map_c, p, pairs, s);
+  }
+  if (kind == B12X_B200_KIND_MXFP8)
+    return dispatch_block_n<kMxfp8>(bn, map_a, map_b, map_c, p, grid, s);
+  return dispatch_block_n<kNvfp4>(bn, map_a, map_b, map_c, p, grid, s);
 }
 
 extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src,

@@ -54,10 +54,13 @@ struct GemmTile {
   static_assert(kSfbCol0 + kSfbCols <= 512, "tensor memory overflow");
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kStagesRaw = (kMaxSmem - kBarrierBytes - 1024) / kStageBytes;
+  // Output staging for the TMA-store epilogue: 128 rows x 128 columns of 2-byte values, as two
+  // 128-byte-swizzled sub-tiles of 64 columns; wider tiles go through it in passes.
+  static constexpr int kCStageBytes = 128 * 128 * 2;
+  static constexpr int kStagesRaw = (kMaxSmem - kBarrierBytes - 1024 - kCStageBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static_assert(kStages >= 2, "not enough shared memory for a pipeline");
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kCStageBytes + kBarrierBytes + 1024;
 };
 
 struct GemmParams {
@@ -73,6 +76,7 @@ struct GemmParams {
   int k_atoms_total;     // scale atoms along K in global memory
   int group_m;           // tile-order grouping along M (L2 reuse)
   int num_stages;        // shared-memory ring depth actually used (<= GemmTile::kStages)
+  int use_tma_store;     // 2-byte outputs with 16-byte aligned rows: stage in smem, TMA store
   int debug_flags;       // bring-up switches: 1 = no MMA issue, 2 = no loads, 4 = no scale copies,
                          // 8 = no global stores
   long long* prof;       // optional cycle counters written by CTA 0 (bring-up only)
@@ -146,13 +150,15 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
 template <int KIND, int BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
-                        const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   using T = GemmTile<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled operand tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* bar_area = smem + T::kStages * T::kStageBytes;
+  uint8_t* c_stage = smem + T::kStages * T::kStageBytes;
+  uint8_t* bar_area = c_stage + T::kCStageBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
   uint64_t* empty_bar = full_bar + T::kStages;
   uint64_t* acc_full_bar = empty_bar + T::kStages;
@@ -178,6 +184,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (p.use_tma_store) tma_prefetch_desc(&map_c);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
@@ -236,15 +243,19 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
             const int katom0 = kt * T::kKAtoms;
             const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
             const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-            mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
+            const bool skip_sf = (p.debug_flags & 16) != 0;
+            mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes +
+                                           (skip_sf ? 0u : sf_bytes * (1 + sfb_atoms)));
             tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
             tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0);
+            if (!skip_sf) {
             bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
                       sf_bytes, bar);
             for (int ra = 0; ra < sfb_atoms; ++ra)
               bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
                         sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
                         sf_bytes, bar);
+            }
           }
         }
         __syncwarp();
@@ -358,6 +369,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     int iter = 0;
     long long prof_wait = 0;
+    bool store_pending = false;
     const long long prof_begin = clock64();
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
       int tm, tn;
@@ -365,15 +377,77 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       const long long tw = clock64();
-      if (!mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag)) {
+      // The epilogue warps meet at barriers in the TMA-store path, so they agree on the
+      // outcome of the wait before going on.
+      if (!epilogue_bar_and(mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag))) {
         *abort_flag = 1;
         if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
         break;
       }
       prof_wait += clock64() - tw;
       tc_fence_after_sync();
-      const int row = tm * T::BM + quarter * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = tm * T::BM + row_in_tile;
       const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (p.use_tma_store) {
+        // TMEM -> registers -> swizzled smem -> TMA store, 128 columns per pass. The
+        // accumulator is released as soon as its last column sits in shared memory, so the
+        // global write overlaps the next tile's main loop.
+        constexpr int kPasses = (BN + 127) / 128;
+        const bool store_thread = (threadIdx.x == 64);
+#pragma unroll 1
+        for (int pass = 0; pass < kPasses; ++pass) {
+          if (store_pending) {
+            if (store_thread) tma_store_wait_read<0>();
+            epilogue_bar_sync();
+            store_pending = false;
+          }
+          const int chunks = min(4, BN / 32 - pass * 4);
+#pragma unroll 1
+          for (int cc = 0; cc < chunks; ++cc) {
+            uint32_t raw[32];
+            tmem_load_32cols(taddr + pass * 128 + cc * 32, raw);
+            tmem_load_wait();
+            uint32_t packed[16];
+            if (p.out_dtype == kOutBf16) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                packed[i] = pack_bf16x2(__uint_as_float(raw[2 * i]) * alpha,
+                                        __uint_as_float(raw[2 * i + 1]) * alpha);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                packed[i] = pack_f16x2(__uint_as_float(raw[2 * i]) * alpha,
+                                       __uint_as_float(raw[2 * i + 1]) * alpha);
+            }
+            // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
+            // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
+            uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
+              *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
+                  packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            }
+          }
+          if (pass == kPasses - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+          }
+          fence_proxy_async_smem();
+          epilogue_bar_sync();
+          if (store_thread && !(p.debug_flags & 8)) {
+            for (int sub = 0; sub < (chunks + 1) / 2; ++sub) {
+              const int col = tn * BN + pass * 128 + sub * 64;
+              if (col < p.n) tma_store_2d(&map_c, c_stage + sub * (128 * 128), col, tm * T::BM);
+            }
+            tma_store_commit();
+          }
+          store_pending = true;
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t raw[32];
@@ -388,6 +462,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
     }
+    if (p.use_tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
     if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
       p.prof[6] = clock64() - prof_begin;
       p.prof[7] = prof_wait;

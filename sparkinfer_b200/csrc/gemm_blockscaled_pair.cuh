@@ -1,0 +1,366 @@
+// CTA-pair variant of the block-scaled GEMM (tcgen05 cta_group::2) for large M.
+//
+// Two CTAs of a cluster own one 256 x BN output tile. Each loads its own 128 rows of A and
+// only *half* of the B tile's rows; one tcgen05.mma issued by the leader multiplies the 256
+// rows against all BN columns, each CTA's tensor core reading both halves of B. Per CTA and
+// k-step that is 16 KiB + BN/2 * 128 B instead of 16 KiB + BN * 128 B, which is what the
+// single-CTA kernel was short of: its main loop waited on operand loads with only three stages
+// of 48 KiB fitting in shared memory. No load is multicast; every TMA writes the issuing CTA's
+// own shared memory and signals that CTA's own barrier.
+//
+// Hand-shake per stage s (all waits bounded):
+//   producer (each CTA)  : wait own empty[s] -> arm own full[s], issue own loads
+//   relay (peer, warp 1) : wait own full[s]  -> arrive on the leader's peer_full[s]
+//   issuer (leader, w 1) : wait own full[s] and peer_full[s] -> scale copies + 4 MMAs for the
+//                          pair -> tcgen05.commit to empty[s] of both CTAs (two commits)
+//   epilogue (each CTA)  : wait own acc_full (committed by the leader to both CTAs) -> drain own
+//                          128 rows from tensor memory -> arrive on the leader's acc_empty
+#pragma once
+
+#include "gemm_blockscaled.cuh"
+
+namespace b12x_b200 {
+
+template <int KIND, int BN>
+struct PairTile {
+  static_assert(BN == 128 || BN == 256, "pair tiles are 128 or 256 columns wide");
+  static constexpr int BM = 128;                               // rows per CTA (256 per pair)
+  static constexpr int kRowBytes = 128;
+  static constexpr int kMmasPerStage = 4;
+  static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
+  static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
+  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : 4;
+  static constexpr int kSfbRowAtoms = BN / 128;
+  static constexpr int kABytes = BM * kRowBytes;
+  static constexpr int kBBytes = (BN / 2) * kRowBytes;         // this CTA's half of B
+  static constexpr int kSfaBytes = kKAtoms * 512;
+  static constexpr int kSfbBytes = kSfbRowAtoms * kKAtoms * 512;
+  static constexpr int kStageBytes =
+      ((kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024) * 1024;
+  static constexpr int kSfaCols = kKAtoms * 4;
+  static constexpr int kSfbCols = kSfbRowAtoms * kKAtoms * 4;
+  static constexpr int kAccStages = (2 * BN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
+  static constexpr int kSfaCol0 = kAccStages * BN;
+  static constexpr int kSfbCol0 = kSfaCol0 + kSfaCols;
+  static constexpr int kCStageBytes = 128 * 128 * 2;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kStagesRaw =
+      (227 * 1024 - kBarrierBytes - 1024 - kCStageBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kCStageBytes + kBarrierBytes + 1024;
+};
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                             const __grid_constant__ CUtensorMap map_b,
+                             const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  using T = PairTile<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* c_stage = smem + T::kStages * T::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(c_stage + T::kCStageBytes);
+  uint64_t* peer_full_bar = full_bar + T::kStages;   // used in the leader only
+  uint64_t* empty_bar = peer_full_bar + T::kStages;
+  uint64_t* acc_full_bar = empty_bar + T::kStages;
+  uint64_t* acc_empty_bar = acc_full_bar + 2;        // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = (rank == 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&peer_full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (p.use_tma_store) tma_prefetch_desc(&map_c);
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool tmem_ok = (tmem_base == 0);
+  if (!tmem_ok && threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
+
+  // tiles_m counts 256-row pair tiles here.
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int k_tiles = (p.k + T::kElemsPerStage - 1) / T::kElemsPerStage;
+  const int m_row_atoms = (p.m + 127) / 128;
+  const int n_row_atoms = (p.n + 127) / 128;
+  const uint32_t smem_u32 = smem_addr_u32(smem);
+
+  if (!tmem_ok) {
+    // fall through to the common tear-down
+  } else if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int m0 = tm * 256 + static_cast<int>(rank) * 128;
+      const int n0 = tn * BN;
+      const int sfa_atom = tm * 2 + static_cast<int>(rank);
+      const bool sfa_ok = sfa_atom < m_row_atoms;
+      const int sfb_atom0 = n0 / 128;
+      const int sfb_atoms = min(T::kSfbRowAtoms, n_row_atoms - sfb_atom0);
+      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
+      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        if (!mbar_wait_bounded_cluster(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          uint8_t* st = smem + stage * T::kStageBytes;
+          uint64_t* bar = &full_bar[stage];
+          const int katom0 = kt * T::kKAtoms;
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes +
+                                         sf_bytes * ((sfa_ok ? 1 : 0) + sfb_atoms));
+          tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
+          tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes,
+                      n0 + static_cast<int>(rank) * (BN / 2));
+          if (sfa_ok)
+            bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
+                      sf_bytes, bar);
+          for (int ra = 0; ra < sfb_atoms; ++ra)
+            bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
+                      sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
+                      sf_bytes, bar);
+        }
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1 && !leader) {
+    // ------------------------------ relay (peer CTA) ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        if (elect_one())
+          mbar_arrive_cluster(map_to_cta(smem_addr_u32(&peer_full_bar[stage]), 0));
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA) ------------------------------
+    constexpr uint32_t idesc_base = make_idesc_block_scaled(
+        256, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    int stage = 0;
+    uint32_t phase = 0;
+    int iter = 0;
+    bool ok = true;
+    long long pf_local = 0, pf_peer = 0, pf_acc = 0, pf_issue = 0;
+    const long long pf_begin = clock64();
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++iter) {
+      const int acc = iter % T::kAccStages;
+      const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+      const long long ta = clock64();
+      if (!mbar_wait_bounded_cluster(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+        break;
+      }
+      pf_acc += clock64() - ta;
+      tc_fence_after_sync();
+      const uint32_t d_taddr = acc * BN;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const long long t0 = clock64();
+        const bool got_local = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
+        const long long t1 = clock64();
+        if (!got_local ||
+            !mbar_wait_bounded_cluster(&peer_full_bar[stage], phase, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        const long long t2 = clock64();
+        pf_local += t1 - t0;
+        pf_peer += t2 - t1;
+        tc_fence_after_sync();
+        const uint32_t st = smem_u32 + stage * T::kStageBytes;
+        const int mmas = min(T::kMmasPerStage,
+                             (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
+        if (elect_one()) {
+          const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
+#pragma unroll
+          for (int ka = 0; ka < T::kKAtoms; ++ka) {
+            tc_copy_sf_atom_pair(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
+#pragma unroll
+            for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
+              tc_copy_sf_atom_pair(T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
+                                   sf_desc + ((T::kSfaBytes + (ra * T::kKAtoms + ka) * 512) >> 4));
+          }
+          const uint64_t adesc = make_kmajor_sw128_desc(st);
+          const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
+          for (int j = 0; j < mmas; ++j) {
+            const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+            if (KIND == kMxfp8)
+              tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                               idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
+                               T::kSfbCol0);
+            else
+              tc_mma_nvf4_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
+                               T::kSfaCol0 + j * 4, T::kSfbCol0 + j * T::kSfbRowAtoms * 4);
+          }
+          // Free the stage in both CTAs; publish the accumulator to both after the last step.
+          const uint32_t empty_addr = smem_addr_u32(&empty_bar[stage]);
+          tc_commit_pair(empty_addr);
+          tc_commit_pair(map_to_cta(empty_addr, 1));
+          if (kt == k_tiles - 1) {
+            const uint32_t full_addr = smem_addr_u32(&acc_full_bar[acc]);
+            tc_commit_pair(full_addr);
+            tc_commit_pair(map_to_cta(full_addr, 1));
+          }
+        }
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+        pf_issue += clock64() - t2;
+      }
+    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) {
+      p.prof[2] = clock64() - pf_begin;
+      p.prof[3] = pf_local;
+      p.prof[4] = pf_acc;
+      p.prof[5] = pf_issue;
+      p.prof[6] = pf_peer;
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int quarter = warp & 3;
+    const float alpha = p.alpha ? *p.alpha : 1.0f;
+    int iter = 0;
+    bool store_pending = false;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++iter) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int acc = iter % T::kAccStages;
+      const uint32_t acc_phase = (iter / T::kAccStages) & 1;
+      if (!epilogue_bar_and(mbar_wait_bounded_cluster(&acc_full_bar[acc], acc_phase, abort_flag))) {
+        *abort_flag = 1;
+        if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row_in_tile = quarter * 32 + lane;
+      const int m0 = tm * 256 + static_cast<int>(rank) * 128;
+      const int row = m0 + row_in_tile;
+      const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      const uint32_t acc_empty_leader = map_to_cta(smem_addr_u32(&acc_empty_bar[acc]), 0);
+      if (p.use_tma_store) {
+        constexpr int kPasses = (BN + 127) / 128;
+        const bool store_thread = (threadIdx.x == 64);
+#pragma unroll 1
+        for (int pass = 0; pass < kPasses; ++pass) {
+          if (store_pending) {
+            if (store_thread) tma_store_wait_read<0>();
+            epilogue_bar_sync();
+            store_pending = false;
+          }
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t raw[32];
+            tmem_load_32cols(taddr + pass * 128 + cc * 32, raw);
+            tmem_load_wait();
+            uint32_t packed[16];
+            if (p.out_dtype == kOutBf16) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                packed[i] = pack_bf16x2(__uint_as_float(raw[2 * i]) * alpha,
+                                        __uint_as_float(raw[2 * i + 1]) * alpha);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                packed[i] = pack_f16x2(__uint_as_float(raw[2 * i]) * alpha,
+                                       __uint_as_float(raw[2 * i + 1]) * alpha);
+            }
+            uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
+              *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
+                  packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            }
+          }
+          if (pass == kPasses - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+          }
+          fence_proxy_async_smem();
+          epilogue_bar_sync();
+          if (store_thread) {
+            for (int sub = 0; sub < 2; ++sub) {
+              const int col = tn * BN + pass * 128 + sub * 64;
+              if (col < p.n && m0 < p.m) tma_store_2d(&map_c, c_stage + sub * (128 * 128), col, m0);
+            }
+            tma_store_commit();
+          }
+          store_pending = true;
+        }
+        continue;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tmem_load_32cols(taddr + c * 32, raw);
+        tmem_load_wait();
+        float vals[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
+        store_row_chunk(p, row, tn * BN + c * 32, vals);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+    }
+    if (p.use_tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
+  }
+
+  // Neither CTA may leave (or give back tensor memory) while the pair's tensor core can still
+  // read its shared memory or signal its barriers.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+}  // namespace b12x_b200

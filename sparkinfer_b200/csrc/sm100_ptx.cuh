@@ -297,6 +297,118 @@ __device__ __forceinline__ void tmem_load_wait() {
 }
 
 // ----------------------------------------------------------------------------------------
+// CTA pairs (cluster of two CTAs driving one tcgen05 instruction stream, cta_group::2)
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Shared-memory address of the same variable in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+// Arrive on an mbarrier that may live in the other CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  // Default (CTA-scope release) semantics: the arrival only forwards the completion of
+  // asynchronous copies, whose bytes the tensor core reads through the async proxy; a
+  // cluster-scope release here cost ~900 cycles per arrival.
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_addr_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait on a barrier that the other CTA of the pair (or the pair's tensor core) signals.
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity,
+                                                          volatile int* abort_flag) {
+  for (uint32_t polls = 0; polls < kMaxBarrierPolls; ++polls) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((polls & 1023u) == 1023u && *abort_flag != 0) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_addr_u32(smem_result)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+
+// Completion of all prior tcgen05 work of the pair -> one arrival on the mbarrier at
+// `cluster_addr` (own CTA or the peer).
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(cluster_addr)
+               : "memory");
+}
+
+// Scale atom copy executed in both CTAs of the pair: each reads its own shared memory at the
+// descriptor's offset and writes its own tensor memory.
+__device__ __forceinline__ void tc_copy_sf_atom_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc)
+               : "memory");
+}
+
+// 256-row MMA over the pair: rows 0..127 from the leader's A tile, 128..255 from the peer's;
+// each CTA holds half of the B tile's rows; D lands in each CTA's own tensor memory.
+__device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate,
+                                                 uint32_t sfa_taddr, uint32_t sfb_taddr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n"
+      ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_taddr),
+      "r"(sfb_taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate,
+                                                 uint32_t sfa_taddr, uint32_t sfb_taddr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n"
+      ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_taddr),
+      "r"(sfb_taddr)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------------------
 // Descriptors
 // ----------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit):

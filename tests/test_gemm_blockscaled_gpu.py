@@ -340,3 +340,27 @@ def test_mm_block_fp8_rejects_bad_scales():
                        sf_dtype="float8_e8m0fnu", sf_vec_size=128, block_fp8=True)
     with pytest.raises(ValueError, match="unswapped"):
         blockscaled.mm((a, sa), (b, sb), c_dtype="bfloat16", swap_ab=True, **BLOCK_FP8)
+
+
+@pytest.mark.parametrize("kind,m,n,k", [
+    ("nvfp4", 256, 256, 128), ("nvfp4", 300, 504, 640), ("nvfp4", 1024, 2048, 1024),
+    ("mxfp8", 256, 512, 256), ("mxfp8", 130, 264, 384), ("mxfp8", 768, 1280, 2048),
+])
+def test_cta_pair_kernel_matches_oracle(monkeypatch, kind, m, n, k):
+    """The cta_group::2 kernel (two CTAs per 256 x 256 tile) is chosen automatically only for
+    problems with a full wave of pair tiles; force it here on small and ragged shapes,
+    including ones whose second CTA lies entirely below the matrix."""
+    from gpu_util import assert_gemm_close, mxfp8_operand, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    monkeypatch.setenv("B12X_B200_PAIR", "1")
+    if kind == "nvfp4":
+        lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(m + 3 * k, (m, k), 0.25))
+        rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(n + 5 * k, (n, k), 0.02))
+        out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype="bfloat16", **NVFP4)
+    else:
+        lhs, a_deq = mxfp8_operand(seeded_bf16(m + 3 * k, (m, k), 0.25))
+        rhs, b_deq = mxfp8_operand(seeded_bf16(n + 5 * k, (n, k), 0.03))
+        out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **MXFP8)
+    torch.cuda.synchronize()
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
