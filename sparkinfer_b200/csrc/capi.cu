@@ -181,7 +181,7 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(2 * pairs), 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(224, 1, 1);
   cfg.dynamicSmemBytes = T::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -502,7 +502,7 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
-  gemm_smallm_kernel<KIND><<<grid, 192, smem_bytes, stream>>>(map_w, map_x, p);
+  gemm_smallm_kernel<KIND><<<grid, 224, smem_bytes, stream>>>(map_w, map_x, p);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;

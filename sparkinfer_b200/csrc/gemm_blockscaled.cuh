@@ -403,31 +403,36 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
             store_pending = false;
           }
           const int chunks = min(4, BN / 32 - pass * 4);
-#pragma unroll 1
-          for (int cc = 0; cc < chunks; ++cc) {
-            uint32_t raw[32];
-            tmem_load_32cols(taddr + pass * 128 + cc * 32, raw);
-            tmem_load_wait();
-            uint32_t packed[16];
-            if (p.out_dtype == kOutBf16) {
+          // The TMEM load of chunk cc+1 is in flight while chunk cc is converted and staged.
+          uint32_t raw[2][32];
+          tmem_load_32cols(taddr + pass * 128, raw[0]);
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                packed[i] = pack_bf16x2(__uint_as_float(raw[2 * i]) * alpha,
-                                        __uint_as_float(raw[2 * i + 1]) * alpha);
-            } else {
+          for (int cc = 0; cc < 4; ++cc) {
+            if (cc < chunks) {
+              tmem_load_wait();
+              if (cc + 1 < chunks) tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
+              const uint32_t(&cur)[32] = raw[cc & 1];
+              uint32_t packed[16];
+              if (p.out_dtype == kOutBf16) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                packed[i] = pack_f16x2(__uint_as_float(raw[2 * i]) * alpha,
-                                       __uint_as_float(raw[2 * i + 1]) * alpha);
-            }
-            // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
-            // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
-            uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
+                for (int i = 0; i < 16; ++i)
+                  packed[i] = pack_bf16x2(__uint_as_float(cur[2 * i]) * alpha,
+                                          __uint_as_float(cur[2 * i + 1]) * alpha);
+              } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
-              *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
-                  packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                for (int i = 0; i < 16; ++i)
+                  packed[i] = pack_f16x2(__uint_as_float(cur[2 * i]) * alpha,
+                                         __uint_as_float(cur[2 * i + 1]) * alpha);
+              }
+              // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
+              // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
+              uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
+                *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
+                    packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+              }
             }
           }
           if (pass == kPasses - 1) {

@@ -51,7 +51,7 @@ struct PairTile {
 };
 
 template <int KIND, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(224, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                              const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
@@ -75,7 +75,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], 2);  // operand producer + scale producer
       mbar_init(&peer_full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -137,14 +137,46 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
           uint8_t* st = smem + stage * T::kStageBytes;
           uint64_t* bar = &full_bar[stage];
-          const int katom0 = kt * T::kKAtoms;
-          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
-          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes +
-                                         sf_bytes * ((sfa_ok ? 1 : 0) + sfb_atoms));
+          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes);
           tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
           tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes,
                       n0 + static_cast<int>(rank) * (BN / 2));
+        }
+        __syncwarp();
+        if (++stage == T::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------- scale-factor producer (both CTAs) -------------------------
+    // A second producer warp so that the five copies of a stage are issued by two warps in
+    // parallel; both arrive on the stage's full barrier with their own byte counts.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int n0 = tn * BN;
+      const int sfa_atom = tm * 2 + static_cast<int>(rank);
+      const bool sfa_ok = sfa_atom < m_row_atoms;
+      const int sfb_atom0 = n0 / 128;
+      const int sfb_atoms = min(T::kSfbRowAtoms, n_row_atoms - sfb_atom0);
+      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
+      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        if (!mbar_wait_bounded_cluster(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          uint8_t* st = smem + stage * T::kStageBytes;
+          uint64_t* bar = &full_bar[stage];
+          const int katom0 = kt * T::kKAtoms;
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+          mbar_arrive_expect_tx(bar, sf_bytes * ((sfa_ok ? 1 : 0) + sfb_atoms));
           if (sfa_ok)
             bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
                       sf_bytes, bar);
@@ -219,7 +251,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
           const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
 #pragma unroll
-          for (int ka = 0; ka < T::kKAtoms; ++ka) {
+          for (int ka = 0; ka < ((p.debug_flags & 1) ? 0 : T::kKAtoms); ++ka) {
             tc_copy_sf_atom_pair(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
 #pragma unroll
             for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
@@ -228,7 +260,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
-          for (int j = 0; j < mmas; ++j) {
+          for (int j = 0; j < ((p.debug_flags & 1) ? 0 : mmas); ++j) {
             const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
             if (KIND == kMxfp8)
               tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
@@ -292,29 +324,36 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             epilogue_bar_sync();
             store_pending = false;
           }
-#pragma unroll 1
+          // The TMEM load of chunk cc+1 is in flight while chunk cc is converted and staged.
+          uint32_t raw[2][32];
+          tmem_load_32cols(taddr + pass * 128, raw[0]);
+#pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
-            uint32_t raw[32];
-            tmem_load_32cols(taddr + pass * 128 + cc * 32, raw);
-            tmem_load_wait();
-            uint32_t packed[16];
-            if (p.out_dtype == kOutBf16) {
+            if (cc < 4) {
+              tmem_load_wait();
+              if (cc + 1 < 4) tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
+              const uint32_t(&cur)[32] = raw[cc & 1];
+              uint32_t packed[16];
+              if (p.out_dtype == kOutBf16) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                packed[i] = pack_bf16x2(__uint_as_float(raw[2 * i]) * alpha,
-                                        __uint_as_float(raw[2 * i + 1]) * alpha);
-            } else {
+                for (int i = 0; i < 16; ++i)
+                  packed[i] = pack_bf16x2(__uint_as_float(cur[2 * i]) * alpha,
+                                          __uint_as_float(cur[2 * i + 1]) * alpha);
+              } else {
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                packed[i] = pack_f16x2(__uint_as_float(raw[2 * i]) * alpha,
-                                       __uint_as_float(raw[2 * i + 1]) * alpha);
-            }
-            uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
+                for (int i = 0; i < 16; ++i)
+                  packed[i] = pack_f16x2(__uint_as_float(cur[2 * i]) * alpha,
+                                         __uint_as_float(cur[2 * i + 1]) * alpha);
+              }
+              // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
+              // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
+              uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
-              *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
-                  packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+              for (int i = 0; i < 4; ++i) {
+                const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
+                *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
+                    packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+              }
             }
           }
           if (pass == kPasses - 1) {

@@ -70,7 +70,7 @@ __device__ __forceinline__ int owner_of_unit(int u, int units, int ctas) {
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(224, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
   using T = SmallMTile<KIND>;
@@ -90,7 +90,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], 2);  // weight producer + activation producer
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -124,8 +124,12 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
   const uint32_t smem_u32 = smem_addr_u32(smem);
   const uint32_t x_bytes = static_cast<uint32_t>(p.m_pad) * 128u;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp == 0 || warp == 6) {
+    // ------------------------------ TMA producers ------------------------------
+    // Two warps share the four copies of a unit so that a stage is armed in about half the
+    // time: warp 0 brings the weight tile and its scales, warp 6 the activation rows and
+    // theirs. Both arrive on the stage's full barrier with their own byte counts.
+    const bool weights = (warp == 0);
     int stage = 0;
     uint32_t phase = 0;
     const long long pt0 = clock64();
@@ -145,22 +149,24 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
         if (p.debug_flags & 2) {
           mbar_arrive(bar);
+        } else if (weights) {
+          mbar_arrive_expect_tx(bar, T::kWBytes + sf_bytes);
+          tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
+          bulk_load(st + T::kWBytes,
+                    p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512,
+                    sf_bytes, bar);
         } else {
-        mbar_arrive_expect_tx(bar, T::kWBytes + x_bytes + 2 * sf_bytes);
-        tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
-        tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
-        bulk_load(st + T::kWBytes,
-                  p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512, sf_bytes,
-                  bar);
-        bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
-                  sf_bytes, bar);
+          mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
+          tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
+          bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
+                    sf_bytes, bar);
         }
       }
       __syncwarp();
       if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       if (++kt == p.k_tiles) { kt = 0; ++tile; }
     }
-    if (p.prof && blockIdx.x == 0 && lane == 0) p.prof[0] = clock64() - pt0;
+    if (p.prof && blockIdx.x == 0 && lane == 0 && weights) p.prof[0] = clock64() - pt0;
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     const uint32_t idesc_base = make_idesc_block_scaled(
