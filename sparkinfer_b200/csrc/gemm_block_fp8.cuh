@@ -181,14 +181,16 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_fence_after_sync();
         const uint32_t taddr =
             (static_cast<uint32_t>(quarter * 32) << 16) + buf * T::BN + half * 128;
+        // Two TMEM loads in flight: chunk c+1 streams in while chunk c is promoted.
+        uint32_t raw[2][32];
+        tmem_load_32cols(taddr, raw[0]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t raw[32];
-          tmem_load_32cols(taddr + c * 32, raw);
           tmem_load_wait();
+          if (c + 1 < 4) tmem_load_32cols(taddr + (c + 1) * 32, raw[(c + 1) & 1]);
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            acc[c * 32 + i] = fmaf(__uint_as_float(raw[i]), scale, acc[c * 32 + i]);
+            acc[c * 32 + i] = fmaf(__uint_as_float(raw[c & 1][i]), scale, acc[c * 32 + i]);
         }
         tc_fence_before_sync();
         __syncwarp();
