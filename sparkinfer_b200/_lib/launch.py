@@ -17,7 +17,8 @@ from .. import _native
 _STATUS_LOCK = Lock()
 _STATUS: dict[int, torch.Tensor] = {}
 _WORKSPACE: dict[int, torch.Tensor] = {}
-SMALL_M_MAX = 128
+SMALL_M_MAX = 128        # largest M the decode kernel accepts
+SMALL_M_AUTO = 64        # largest M routed to it automatically
 
 _DTYPE_CODE = {torch.bfloat16: _native.DT_BF16, torch.float16: _native.DT_FP16,
                torch.float32: _native.DT_FP32}
@@ -115,7 +116,7 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = a.device
     if small_m is None:
-        small_m = m <= SMALL_M_MAX and block_n == 0 and not _SMALL_M_DISABLED
+        small_m = m <= SMALL_M_AUTO and block_n == 0 and not _SMALL_M_DISABLED
     if small_m and 0 < m <= SMALL_M_MAX and n > 0:
         work = smallm_workspace(kind, m, n, k, dev, sm_count)
         with torch.cuda.device(dev):

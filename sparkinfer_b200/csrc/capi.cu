@@ -502,7 +502,7 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
-  gemm_smallm_kernel<KIND><<<grid, 224, smem_bytes, stream>>>(map_w, map_x, p);
+  gemm_smallm_kernel<KIND><<<grid, 256, smem_bytes, stream>>>(map_w, map_x, p);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;
@@ -584,9 +584,8 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
   p.max_segments = pl.max_segments;
   p.num_stages = pl.stages;
   p.stage_bytes = pl.stage_bytes;
-  p.debug_flags = 0;
-  if (const char* e = getenv("B12X_B200_DEBUG_FLAGS")) p.debug_flags = atoi(e);
-  if (const char* e = getenv("B12X_B200_STAGES")) { int st = atoi(e); if (st >= 2 && st < p.num_stages) p.num_stages = st; }
+  p.issuers = (pl.m_pad <= 64) ? 2 : 1;
+  if (const char* e = getenv("B12X_B200_SMALLM_ISSUERS")) { if (atoi(e) == 1) p.issuers = 1; }
   p.prof = nullptr;
   if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
   const int smem_bytes = pl.stages * pl.stage_bytes + 2048;

@@ -8,10 +8,12 @@
 // multiplied unscaled (tcgen05 kind::f8f6f4, four K=32 instructions) into a TMEM buffer and
 // promoted into FP32 register accumulators with one FMA per element.
 //
-// One CTA (320 threads) owns a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer,
-// warps 2..9 = promotion/epilogue (two warps per 32-lane TMEM quarter, each taking 128 of the
-// 256 columns = exactly one 128-column scale block). The two 256-column TMEM buffers fill all
-// 512 columns, so the MMA of k-block i+1 overlaps the promotion of k-block i.
+// One CTA (576 threads) owns a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer,
+// warps 2..17 = promotion/epilogue (four warps per 32-lane TMEM quarter, each taking 64 of the
+// 256 columns, i.e. half of one 128-column scale block). Promotion is a chain of TMEM load ->
+// wait -> FMA per warp, so it is the number of warps per scheduler (four) that hides the load
+// latency. The two 256-column TMEM buffers fill all 512 columns, so the MMA of k-block i+1
+// overlaps the promotion of k-block i.
 #pragma once
 
 #include "gemm_blockscaled.cuh"
@@ -27,7 +29,8 @@ struct BlockFp8Tile {
   static constexpr int kStages = 4;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
-  static constexpr int kEpilogueWarps = 8;
+  static constexpr int kEpilogueWarps = 16;
+  static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 };
 
@@ -150,7 +153,8 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // ------------------------- promotion + epilogue -------------------------
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
+    const int group = (warp - 2) >> 2;  // which 64 of the tile's 256 columns
+    constexpr int kCols = T::kColsPerWarp;
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     const int kb_total = k_blocks;
     uint32_t it = 0;
@@ -159,14 +163,14 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int row = tm * T::BM + quarter * 32 + lane;
-      const int col0 = tn * T::BN + half * 128;
+      const int col0 = tn * T::BN + group * kCols;
       const bool row_ok = row < p.m;
       const bool col_ok = col0 < p.n;
       const float* sfa_row = p.sfa + static_cast<size_t>(row_ok ? row : 0) * kb_total;
       const float* sfb_row = p.sfb + static_cast<size_t>(col_ok ? col0 / 128 : 0) * kb_total;
-      float acc[128];
+      float acc[kCols];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+      for (int i = 0; i < kCols; ++i) acc[i] = 0.0f;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const uint32_t buf = it & 1;
         // Scales of this k-block are fetched before the wait so their latency hides behind it.
@@ -180,17 +184,17 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         tc_fence_after_sync();
         const uint32_t taddr =
-            (static_cast<uint32_t>(quarter * 32) << 16) + buf * T::BN + half * 128;
+            (static_cast<uint32_t>(quarter * 32) << 16) + buf * T::BN + group * kCols;
         // Two TMEM loads in flight: chunk c+1 streams in while chunk c is promoted.
-        uint32_t raw[2][32];
-        tmem_load_32cols(taddr, raw[0]);
+        uint32_t raw[2][16];
+        tmem_load_16cols(taddr, raw[0]);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kCols / 16; ++c) {
           tmem_load_wait();
-          if (c + 1 < 4) tmem_load_32cols(taddr + (c + 1) * 32, raw[(c + 1) & 1]);
+          if (c + 1 < kCols / 16) tmem_load_16cols(taddr + (c + 1) * 16, raw[(c + 1) & 1]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            acc[c * 32 + i] = fmaf(__uint_as_float(raw[c & 1][i]), scale, acc[c * 32 + i]);
+          for (int i = 0; i < 16; ++i)
+            acc[c * 16 + i] = fmaf(__uint_as_float(raw[c & 1][i]), scale, acc[c * 16 + i]);
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -204,7 +208,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
       gp.ldc = p.ldc;
       gp.out_dtype = p.out_dtype;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kCols / 32; ++c) {
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = acc[c * 32 + i] * alpha;

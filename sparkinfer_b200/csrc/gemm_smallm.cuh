@@ -15,6 +15,12 @@
 // slots in segment order (deterministic) and stores the tile, then resets the counter. Nobody
 // waits on another CTA.
 //
+// Issue rate, not bandwidth, is what limits one CTA: a unit costs about a dozen tcgen05
+// instructions (scale copies + MMAs) from a single thread. Two warps therefore issue, taking
+// alternate units of the CTA's range into accumulators of their own; the epilogue adds the two
+// (issuer 0 first, so the sum order is fixed). With 128 padded rows four accumulators do not fit
+// in TMEM next to the scales and the second issuer idles.
+//
 // Scratch ("workspace") layout: a 64 KiB block of per-tile int32 counters, then
 // [tiles][max_segments][m_pad][128] FP32 partials. Counters must be zero before the first
 // launch; every launch leaves them zero again, whatever the shape.
@@ -43,8 +49,8 @@ struct SmallMParams {
   int max_segments;        // scratch slots per tile
   int num_stages;
   int stage_bytes;
+  int issuers;             // 2 when four accumulators fit in TMEM (m_pad <= 64), else 1
   long long* prof;         // optional cycle counters of CTA 0 (bring-up only)
-  int debug_flags;         // bring-up: 1 = no MMA / scale copies, 2 = no loads
 };
 
 template <int KIND>
@@ -56,8 +62,10 @@ struct SmallMTile {
   static constexpr int kSfBytes = kKAtoms * 512;
   // Stage = weights | weight scales | activation scales | activation rows (m_pad * 128 B).
   static constexpr int kXOffset = kWBytes + 2 * kSfBytes;
-  static constexpr int kSfwCol0 = 256;                 // after two accumulators of <= 128 cols
-  static constexpr int kSfxCol0 = kSfwCol0 + kKAtoms * 4;
+  // TMEM columns: accumulator (segment parity a, issuer w) at (a * issuers + w) * m_pad, all
+  // below 256; then per issuer 16 columns of weight scales and 16 of activation scales.
+  static constexpr int kSfCol0 = 256;
+  static constexpr int kSfColsPerIssuer = 32;
   static constexpr int kMaxStages = 10;
   __host__ __device__ static constexpr int stage_bytes(int m_pad) {
     return ((kXOffset + m_pad * 128 + 1023) / 1024) * 1024;
@@ -70,7 +78,7 @@ __device__ __forceinline__ int owner_of_unit(int u, int units, int ctas) {
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(224, 1)
+__global__ void __launch_bounds__(256, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
   using T = SmallMTile<KIND>;
@@ -94,7 +102,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_full_bar[a], 2);  // one arrival per issuer warp
       mbar_init(&acc_empty_bar[a], 4);
     }
     *abort_flag = 0;
@@ -132,7 +140,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     const bool weights = (warp == 0);
     int stage = 0;
     uint32_t phase = 0;
-    const long long pt0 = clock64();
     int tile = u_begin / p.k_tiles;
     int kt = u_begin - tile * p.k_tiles;
     for (int u = u_begin; u < u_end; ++u) {
@@ -147,9 +154,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         const int katom0 = kt * T::kKAtoms;
         const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
         const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-        if (p.debug_flags & 2) {
-          mbar_arrive(bar);
-        } else if (weights) {
+        if (weights) {
           mbar_arrive_expect_tx(bar, T::kWBytes + sf_bytes);
           tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
           bulk_load(st + T::kWBytes,
@@ -166,18 +171,22 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       if (++kt == p.k_tiles) { kt = 0; ++tile; }
     }
-    if (p.prof && blockIdx.x == 0 && lane == 0 && weights) p.prof[0] = clock64() - pt0;
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp == 1 || warp == 7) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Unit number q of the CTA's range (q = u - u_begin) belongs to issuer q % issuers. Both
+    // warps walk every unit to keep the ring position; each arrives once per segment on the
+    // accumulator barrier, through a commit if it issued anything there, plainly otherwise.
+    const int me = (warp == 1) ? 0 : 1;
     const uint32_t idesc_base = make_idesc_block_scaled(
         128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    const uint32_t sfw_col = T::kSfCol0 + me * T::kSfColsPerIssuer;
+    const uint32_t sfx_col = sfw_col + 16;
     int stage = 0;
     uint32_t phase = 0;
     int seg = 0;
     bool ok = true;
     int u = u_begin;
     const long long mt0 = clock64();
-    long long m_wait_full = 0;
     while (u < u_end && ok) {
       const int tile = u / p.k_tiles;
       const int tile_end = (tile + 1) * p.k_tiles;
@@ -190,52 +199,52 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         break;
       }
       tc_fence_after_sync();
-      const uint32_t d_taddr = acc * 128;
+      const uint32_t d_taddr = static_cast<uint32_t>((acc * p.issuers + me) * p.m_pad);
       bool first = true;
       for (; u < seg_end; ++u, ++kt) {
-        const long long tw = clock64();
-        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
-          *abort_flag = 1;
-          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
-          ok = false;
-          break;
-        }
-        m_wait_full += clock64() - tw;
-        tc_fence_after_sync();
-        const uint32_t st = smem_u32 + stage * p.stage_bytes;
-        const int mmas = min(4, (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
-        if (elect_one()) {
-          const uint64_t sf_desc = make_sf_chunk_desc(st + T::kWBytes);
+        const bool mine = (p.issuers == 2) ? (((u - u_begin) & 1) == me) : (me == 0);
+        if (mine) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            *abort_flag = 1;
+            if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t st = smem_u32 + stage * p.stage_bytes;
+          const int mmas =
+              min(4, (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
+          if (elect_one()) {
+            const uint64_t sf_desc = make_sf_chunk_desc(st + T::kWBytes);
 #pragma unroll
-          for (int ka = 0; ka < ((p.debug_flags & 1) ? 0 : T::kKAtoms); ++ka) {
-            tc_copy_sf_atom(T::kSfwCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
-            tc_copy_sf_atom(T::kSfxCol0 + ka * 4, sf_desc + ((T::kSfBytes + ka * 512) >> 4));
+            for (int ka = 0; ka < T::kKAtoms; ++ka) {
+              tc_copy_sf_atom(sfw_col + ka * 4, sf_desc + ((ka * 512) >> 4));
+              tc_copy_sf_atom(sfx_col + ka * 4, sf_desc + ((T::kSfBytes + ka * 512) >> 4));
+            }
+            const uint64_t wdesc = make_kmajor_sw128_desc(st);
+            const uint64_t xdesc = make_kmajor_sw128_desc(st + T::kXOffset);
+            for (int j = 0; j < mmas; ++j) {
+              const uint32_t accumulate = (first && j == 0) ? 0u : 1u;
+              if (KIND == kMxfp8)
+                tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
+                            idesc_with_sf_ids(idesc_base, j, j), accumulate, sfw_col, sfx_col);
+              else
+                tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
+                            sfw_col + j * 4, sfx_col + j * 4);
+            }
+            tc_commit(&empty_bar[stage]);
+            // Last unit of this issuer in the segment: the next one of its parity is past the end.
+            if (u + p.issuers >= seg_end) tc_commit(&acc_full_bar[acc]);
           }
-          const uint64_t wdesc = make_kmajor_sw128_desc(st);
-          const uint64_t xdesc = make_kmajor_sw128_desc(st + T::kXOffset);
-          for (int j = 0; j < ((p.debug_flags & 1) ? 0 : mmas); ++j) {
-            const uint32_t accumulate = (first && j == 0) ? 0u : 1u;
-            if (KIND == kMxfp8)
-              tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
-                          idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfwCol0,
-                          T::kSfxCol0);
-            else
-              tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
-                          T::kSfwCol0 + j * 4, T::kSfxCol0 + j * 4);
-          }
-          tc_commit(&empty_bar[stage]);
-          if (u + 1 == seg_end) tc_commit(&acc_full_bar[acc]);
+          __syncwarp();
+          first = false;
         }
-        __syncwarp();
-        first = false;
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       }
+      if (ok && first && lane == 0) mbar_arrive(&acc_full_bar[acc]);  // nothing issued here
       ++seg;
     }
-    if (p.prof && blockIdx.x == 0 && lane == 0) {
-      p.prof[1] = clock64() - mt0;
-      p.prof[2] = m_wait_full;
-    }
+    if (p.prof && blockIdx.x == 0 && lane == 0) p.prof[1 + me * 8] = clock64() - mt0;
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;
@@ -244,10 +253,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
     int seg = 0;
     int u = u_begin;
-    const long long et0 = clock64();
-    long long e_wait = 0, e_drain = 0, e_publish = 0, e_reduce = 0;
     while (u < u_end) {
-      const long long ew0 = clock64();
       const int tile = u / p.k_tiles;
       const int tile_begin = tile * p.k_tiles;
       const int tile_end = tile_begin + p.k_tiles;
@@ -262,9 +268,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         break;
       }
       tc_fence_after_sync();
-      const long long ew1 = clock64();
-      e_wait += ew1 - ew0;
-      const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * 128;
+      // Which issuers hold a partial of this segment: both, unless it is a single unit.
+      const int first_issuer = (p.issuers == 2) ? ((u - u_begin) & 1) : 0;
+      const bool both = (p.issuers == 2) && (seg_end - u >= 2);
+      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t taddr0 =
+          lane_base + static_cast<uint32_t>((acc * p.issuers + (both ? 0 : first_issuer)) * p.m_pad);
+      const uint32_t taddr1 = lane_base + static_cast<uint32_t>((acc * p.issuers + 1) * p.m_pad);
       const int n_global = tile * 128 + n_local;
       const bool n_ok = n_global < p.n;
       int first_cta = 0, segments = 1, slot = 0;
@@ -276,8 +286,17 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
       for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
         uint32_t raw[16];
-        tmem_load_16cols(taddr + c0, raw);
-        tmem_load_wait();
+        tmem_load_16cols(taddr0 + c0, raw);
+        if (both) {
+          uint32_t other[16];
+          tmem_load_16cols(taddr1 + c0, other);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            raw[i] = __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(other[i])));
+        } else {
+          tmem_load_wait();
+        }
         if (whole) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -302,8 +321,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
-      const long long ew2 = clock64();
-      e_drain += ew2 - ew1;
 
       if (!whole) {
         // Publish the partial, count the arrival, and let the last arriver finish the tile.
@@ -315,8 +332,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           if (prev == segments - 1) p.counters[tile] = 0;
         }
         epilogue_bar_sync();
-        const long long ew3 = clock64();
-        e_publish += ew3 - ew2;
         if (*last_flag) {
           __threadfence();
           const float* tile_slots = p.partials + static_cast<size_t>(tile) * p.max_segments * slot_floats;
@@ -350,18 +365,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           }
         }
         epilogue_bar_sync();
-        e_reduce += clock64() - ew3;
       }
       u = seg_end;
       ++seg;
-    }
-    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
-      p.prof[3] = clock64() - et0;
-      p.prof[4] = e_wait;
-      p.prof[5] = e_drain;
-      p.prof[6] = e_publish;
-      p.prof[7] = e_reduce;
-      p.prof[8] = seg;
     }
   }
 
