@@ -324,9 +324,9 @@ extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int
   const int k_atoms = int((k + 127) / 128);
   const int rows_cover = scale_mma ? int((m + 127) / 128) * 128 : int(m);
   const int k_cover = scale_mma ? k_atoms * 128 : int(k);
-  const int64_t threads = int64_t(rows_cover) * (k_cover / 16);
-  const int64_t blocks = (threads + 255) / 256;
-  if (blocks > INT32_MAX) return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  if (quant_warps(rows_cover, k_cover) > INT32_MAX)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  const int64_t blocks = (quant_warps(rows_cover, k_cover) + 7) / 8;  // 8 warps per CTA
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (src_dtype == B12X_B200_BF16)
     quantize_mxfp8_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(
@@ -360,9 +360,9 @@ extern "C" int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int
   const int k_atoms = int((k + 63) / 64);
   const int rows_cover = int((m + 127) / 128) * 128;
   const int k_cover = k_atoms * 64;
-  const int64_t threads = int64_t(rows_cover) * (k_cover / 16);
-  const int64_t blocks = (threads + 255) / 256;
-  if (blocks > INT32_MAX) return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  if (quant_warps(rows_cover, k_cover) > INT32_MAX)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
+  const int64_t blocks = (quant_warps(rows_cover, k_cover) + 7) / 8;  // 8 warps per CTA
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (src_dtype == B12X_B200_BF16)
     quantize_nvfp4_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(

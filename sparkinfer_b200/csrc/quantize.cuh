@@ -7,7 +7,7 @@
 //                         supplied FP32 global scale (device scalar, read at run time).
 //
 // Both are pure streaming kernels (2 bytes read, ~1.03 / ~0.56 bytes written per element):
-// 16-byte loads, register amax, 8/16-byte stores. The arithmetic is IEEE round-to-nearest
+// coalesced 16-byte loads, amax in registers and shuffles, coalesced 8/4-byte stores. The arithmetic is IEEE round-to-nearest
 // throughout (true divisions, no approximations, no contraction) so the emitted bytes are
 // reproducible on a CPU.
 //
@@ -67,6 +67,15 @@ __device__ __forceinline__ uint4 ld_nc_16(const void* p) {
 // ceil(log2(v)) of a normal float is its exponent, plus one when the mantissa is non-zero.
 __device__ __forceinline__ uint32_t ue8m0_from_amax(float amax) {
   if (!(amax > 0.0f)) return 127u;
+  {
+    // 448 = 1.75 * 2^8, so for a quotient that stays normal the answer follows from amax's own
+    // fields: exponent - 8, plus one when the mantissa exceeds that of 1.75 (the rounded
+    // quotient has a non-zero mantissa exactly when the true one has, see the two neighbours of
+    // 1.75). Anything near the ends of the range takes the division below.
+    const uint32_t abits = __float_as_uint(amax);
+    const uint32_t aexp = abits >> 23;
+    if (aexp >= 10u && aexp < 255u) return aexp - 8u + (((abits & 0x007FFFFFu) > 0x00600000u) ? 1u : 0u);
+  }
   const float v = __fdiv_rn(amax, 448.0f);
   const uint32_t bits = __float_as_uint(v);
   const uint32_t exp = bits >> 23;
@@ -86,58 +95,72 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return lo | (hi << 16);
 }
 
-// One thread = 16 consecutive elements; two neighbouring lanes share one 32-element block.
-// The launch covers rows_cover x (k_cover / 16) threads: rows >= m and scale columns >= k/32
-// only receive the neutral scale byte 127 in the atom layout.
+// Work decomposition shared by both quantizers: one warp owns one chunk of kChunkElems
+// consecutive elements of one row and reads it with kLoadsPerLane 16-byte loads per lane, load j
+// covering elements [j*256 + lane*8, +8) of the chunk. Every load instruction of a warp thus
+// reads 512 contiguous bytes, all of a lane's loads are issued before the first use (64 bytes in
+// flight per thread), and a scale block (16 or 32 elements) spans 2 or 4 neighbouring lanes, so
+// its maximum is one or two shuffles away.
+constexpr int kQuantLoadsPerLane = 4;
+constexpr int kQuantChunkElems = kQuantLoadsPerLane * 256;
+
+__host__ __device__ inline int64_t quant_warps(int rows_cover, int k_cover) {
+  return static_cast<int64_t>(rows_cover) * ((k_cover + kQuantChunkElems - 1) / kQuantChunkElems);
+}
+
+// The launch covers rows_cover x k_cover elements: rows >= m and scale columns >= k/32 inside
+// the cover only receive the neutral scale byte 127 in the atom layout.
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ values,
                            uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma,
                            int m, int k, int rows_cover, int k_cover, int k_atoms) {
-  const int units_per_row = k_cover / 16;
-  const int64_t total = static_cast<int64_t>(rows_cover) * units_per_row;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const bool in_cover = idx < total;
-  const int row = in_cover ? static_cast<int>(idx / units_per_row) : 0;
-  const int unit = in_cover ? static_cast<int>(idx % units_per_row) : 0;
-  const int k0 = unit * 16;
-  const bool live = in_cover && row < m && k0 < k;
+  const int chunks_per_row = (k_cover + kQuantChunkElems - 1) / kQuantChunkElems;
+  // 32-bit on purpose (the host refuses covers with 2^31 or more warps): a 64-bit division per
+  // thread costs more instructions than the quantization itself.
+  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= static_cast<uint32_t>(rows_cover) * static_cast<uint32_t>(chunks_per_row))
+    return;  // whole warps leave
+  const int lane = threadIdx.x & 31;
+  const int row = static_cast<int>(warp_id / static_cast<uint32_t>(chunks_per_row));
+  const int chunk = static_cast<int>(warp_id - static_cast<uint32_t>(row) * chunks_per_row);
+  const int k_base = chunk * kQuantChunkElems + lane * 8;
+  const bool row_live = row < m;
+  const T* src_row = src + static_cast<int64_t>(row_live ? row : 0) * ld_src;
 
-  float x[16];
-  if (live) {
-    const T* p = src + static_cast<int64_t>(row) * ld_src + k0;
-    float a[8], b[8];
-    unpack8<T>(ld_nc_16(p), a);
-    unpack8<T>(ld_nc_16(p + 8), b);
+  uint4 raw[kQuantLoadsPerLane];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { x[i] = a[i]; x[8 + i] = b[i]; }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = 0.0f;
+  for (int j = 0; j < kQuantLoadsPerLane; ++j) {
+    const int k0 = k_base + j * 256;
+    raw[j] = (row_live && k0 < k) ? ld_nc_16(src_row + k0) : make_uint4(0, 0, 0, 0);
   }
-  float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-
-  const uint32_t byte = ue8m0_from_amax(amax);
-  const float inv = ue8m0_reciprocal(byte);
-  if (live) {
-    float y[16];
+  for (int j = 0; j < kQuantLoadsPerLane; ++j) {
+    const int k0 = k_base + j * 256;
+    const bool live = row_live && k0 < k;
+    float x[8];
+    unpack8<T>(raw[j], x);
+    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-      y[i] = fminf(fmaxf(__fmul_rn(x[i], inv), -448.0f), 448.0f);
-    uint4 out;
-    out.x = e4m3x4(y[0], y[1], y[2], y[3]);
-    out.y = e4m3x4(y[4], y[5], y[6], y[7]);
-    out.z = e4m3x4(y[8], y[9], y[10], y[11]);
-    out.w = e4m3x4(y[12], y[13], y[14], y[15]);
-    *reinterpret_cast<uint4*>(values + static_cast<int64_t>(row) * k + k0) = out;
-  }
-  if (in_cover && (unit & 1) == 0) {
-    const int kb = unit >> 1;
-    if (live && scale_rows) scale_rows[static_cast<int64_t>(row) * (k / 32) + kb] = byte;
-    if (scale_mma) scale_mma[sf_atom_offset(row, kb, k_atoms)] = live ? byte : 127u;
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t byte = ue8m0_from_amax(amax);
+    const float inv = ue8m0_reciprocal(byte);
+    if (live) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv);  // the conversion saturates at 448
+      uint2 out;
+      out.x = e4m3x4(y[0], y[1], y[2], y[3]);
+      out.y = e4m3x4(y[4], y[5], y[6], y[7]);
+      *reinterpret_cast<uint2*>(values + static_cast<int64_t>(row) * k + k0) = out;
+    }
+    if ((lane & 3) == 0 && k0 < k_cover) {
+      const int kb = k0 >> 5;
+      if (live && scale_rows) scale_rows[static_cast<int64_t>(row) * (k / 32) + kb] = byte;
+      if (scale_mma) scale_mma[sf_atom_offset(row, kb, k_atoms)] = live ? byte : 127u;
+    }
   }
 }
 
@@ -161,54 +184,84 @@ __device__ __forceinline__ uint32_t e2m1x8(const float* y) {
   return w & (0x77777777u | (nonzero << 3));
 }
 
-// One thread = one 16-element block. Rows >= m and scale columns >= k/16 inside the covered
-// area receive scale byte 0 (the atom layout's padding value for NVFP4).
+// Rows >= m and scale columns >= k/16 inside the covered area receive scale byte 0 (the atom
+// layout's padding value for NVFP4).
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
                            const float* __restrict__ global_scale, uint8_t* __restrict__ packed,
                            uint8_t* __restrict__ scale_mma, int m, int k, int rows_cover,
                            int k_cover, int k_atoms) {
-  const int units_per_row = k_cover / 16;
-  const int64_t total = static_cast<int64_t>(rows_cover) * units_per_row;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const int row = static_cast<int>(idx / units_per_row);
-  const int kb = static_cast<int>(idx % units_per_row);
-  const int k0 = kb * 16;
-  if (row >= m || k0 >= k) {
-    scale_mma[sf_atom_offset(row, kb, k_atoms)] = 0;
-    return;
+  const int chunks_per_row = (k_cover + kQuantChunkElems - 1) / kQuantChunkElems;
+  // 32-bit on purpose (the host refuses covers with 2^31 or more warps): a 64-bit division per
+  // thread costs more instructions than the quantization itself.
+  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= static_cast<uint32_t>(rows_cover) * static_cast<uint32_t>(chunks_per_row))
+    return;  // whole warps leave
+  const int lane = threadIdx.x & 31;
+  const int row = static_cast<int>(warp_id / static_cast<uint32_t>(chunks_per_row));
+  const int chunk = static_cast<int>(warp_id - static_cast<uint32_t>(row) * chunks_per_row);
+  const int k_base = chunk * kQuantChunkElems + lane * 8;
+  const bool row_live = row < m;
+  const T* src_row = src + static_cast<int64_t>(row_live ? row : 0) * ld_src;
+
+  uint4 raw[kQuantLoadsPerLane];
+#pragma unroll
+  for (int j = 0; j < kQuantLoadsPerLane; ++j) {
+    const int k0 = k_base + j * 256;
+    raw[j] = (row_live && k0 < k) ? ld_nc_16(src_row + k0) : make_uint4(0, 0, 0, 0);
   }
   const float gs = *global_scale;
-  const T* p = src + static_cast<int64_t>(row) * ld_src + k0;
-  float x[16];
-  {
-    float a[8], b[8];
-    unpack8<T>(ld_nc_16(p), a);
-    unpack8<T>(ld_nc_16(p + 8), b);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { x[i] = a[i]; x[8 + i] = b[i]; }
-  }
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
-
-  const float s = __fmul_rn(gs, __fdiv_rn(amax, 6.0f));
-  const uint32_t s_byte =
-      static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
-  const float s_q = e4m3_to_float(s_byte);
   const float r = (gs == 0.0f) ? 0.0f : __frcp_rn(gs);
-  const float t = __fmul_rn(s_q, r);
-  const float inv = (t == 0.0f) ? 0.0f : __frcp_rn(t);
-  float y[16];
+  // Block maxima: a block is the 16 elements of two neighbouring lanes.
+  float amax[kQuantLoadsPerLane];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) y[i] = fminf(fmaxf(__fmul_rn(x[i], inv), -6.0f), 6.0f);
-  uint2 out;
-  out.x = e2m1x8(y);
-  out.y = e2m1x8(y + 8);
-  *reinterpret_cast<uint2*>(packed + static_cast<int64_t>(row) * (k / 2) + k0 / 2) = out;
-  scale_mma[sf_atom_offset(row, kb, k_atoms)] = static_cast<uint8_t>(s_byte);
+  for (int j = 0; j < kQuantLoadsPerLane; ++j) {
+    float x[8];
+    unpack8<T>(raw[j], x);
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(x[i]));
+    amax[j] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+  }
+  // The scale arithmetic (two IEEE divisions and a round trip through E4M3) is the expensive
+  // part, so the two lanes of a block split it: the even lane does loads 0 and 1, the odd lane
+  // loads 2 and 3, and they swap the resulting multipliers.
+  const int odd = lane & 1;
+  float inv_mine[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int j = odd * 2 + h;
+    const float am = odd ? amax[2 + h] : amax[h];
+    const float s = __fmul_rn(gs, __fdiv_rn(am, 6.0f));
+    const uint32_t s_byte =
+        static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
+    const float t = __fmul_rn(e4m3_to_float(s_byte), r);
+    inv_mine[h] = (t == 0.0f) ? 0.0f : __frcp_rn(t);
+    const int kblk = (k_base - lane * 8 + j * 256 + (lane >> 1) * 16);  // first element of the block
+    if (kblk < k_cover)
+      scale_mma[sf_atom_offset(row, kblk >> 4, k_atoms)] =
+          (row_live && kblk < k) ? static_cast<uint8_t>(s_byte) : 0;
+  }
+  float inv[kQuantLoadsPerLane];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float theirs = __shfl_xor_sync(0xffffffffu, inv_mine[h], 1);
+    inv[h] = odd ? theirs : inv_mine[h];
+    inv[2 + h] = odd ? inv_mine[h] : theirs;
+  }
+#pragma unroll
+  for (int j = 0; j < kQuantLoadsPerLane; ++j) {
+    const int k0 = k_base + j * 256;
+    if (row_live && k0 < k) {
+      float x[8], y[8];
+      unpack8<T>(raw[j], x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv[j]);  // the conversion saturates at 6
+      *reinterpret_cast<uint32_t*>(packed + static_cast<int64_t>(row) * (k / 2) + k0 / 2) =
+          e2m1x8(y);
+    }
+  }
 }
 
 }  // namespace b12x_b200
