@@ -62,6 +62,27 @@ __device__ __forceinline__ uint4 ld_nc_16(const void* p) {
   return v;
 }
 
+// Largest magnitude of the eight 16-bit floats in `raw`, through the packed two-lane abs / max
+// instructions (exact: no rounding is involved in either).
+template <typename T>
+__device__ __forceinline__ float amax8(const uint4& raw);
+
+template <>
+__device__ __forceinline__ float amax8<__nv_bfloat16>(const uint4& raw) {
+  const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const __nv_bfloat162 a = __hmax2(__hmax2(__habs2(v[0]), __habs2(v[1])),
+                                   __hmax2(__habs2(v[2]), __habs2(v[3])));
+  return fmaxf(__low2float(a), __high2float(a));
+}
+
+template <>
+__device__ __forceinline__ float amax8<__half>(const uint4& raw) {
+  const __half2* v = reinterpret_cast<const __half2*>(&raw);
+  const __half2 a = __hmax2(__hmax2(__habs2(v[0]), __habs2(v[1])),
+                            __hmax2(__habs2(v[2]), __habs2(v[3])));
+  return fmaxf(__low2float(a), __high2float(a));
+}
+
 // UE8M0 byte for a block with maximum magnitude `amax`:
 //   127 + clamp(ceil(log2(amax / 448)), -127, 127), and 127 for an all-zero block.
 // ceil(log2(v)) of a normal float is its exponent, plus one when the mantissa is non-zero.
@@ -134,32 +155,34 @@ quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* _
     const int k0 = k_base + j * 256;
     raw[j] = (row_live && k0 < k) ? ld_nc_16(src_row + k0) : make_uint4(0, 0, 0, 0);
   }
+  // Addresses for load 0; load j adds a constant (256 codes, 8 scale columns = 2 atoms).
+  uint8_t* out_values = values + static_cast<int64_t>(row) * k + k_base;
+  const int kb0 = k_base >> 5;
+  uint8_t* out_rows = scale_rows ? scale_rows + static_cast<int64_t>(row) * (k >> 5) + kb0 : nullptr;
+  uint8_t* out_mma = scale_mma ? scale_mma + sf_atom_offset(row, kb0, k_atoms) : nullptr;
+  const bool scale_lane = (lane & 3) == 0;
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
     const int k0 = k_base + j * 256;
     const bool live = row_live && k0 < k;
-    float x[8];
-    unpack8<T>(raw[j], x);
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    float amax = amax8<T>(raw[j]);
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const uint32_t byte = ue8m0_from_amax(amax);
     const float inv = ue8m0_reciprocal(byte);
     if (live) {
-      float y[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv);  // the conversion saturates at 448
-      uint2 out;
-      out.x = e4m3x4(y[0], y[1], y[2], y[3]);
-      out.y = e4m3x4(y[4], y[5], y[6], y[7]);
-      *reinterpret_cast<uint2*>(values + static_cast<int64_t>(row) * k + k0) = out;
+      float x[8];
+      unpack8<T>(raw[j], x);
+      uint2 out;  // the conversion saturates at 448
+      out.x = e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv),
+                     __fmul_rn(x[3], inv));
+      out.y = e4m3x4(__fmul_rn(x[4], inv), __fmul_rn(x[5], inv), __fmul_rn(x[6], inv),
+                     __fmul_rn(x[7], inv));
+      *reinterpret_cast<uint2*>(out_values + j * 256) = out;
     }
-    if ((lane & 3) == 0 && k0 < k_cover) {
-      const int kb = k0 >> 5;
-      if (live && scale_rows) scale_rows[static_cast<int64_t>(row) * (k / 32) + kb] = byte;
-      if (scale_mma) scale_mma[sf_atom_offset(row, kb, k_atoms)] = live ? byte : 127u;
+    if (scale_lane && k0 < k_cover) {
+      if (live && out_rows) out_rows[j * 8] = byte;
+      if (out_mma) out_mma[j * 1024] = live ? byte : 127u;
     }
   }
 }
@@ -217,17 +240,15 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
   float amax[kQuantLoadsPerLane];
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
-    float x[8];
-    unpack8<T>(raw[j], x);
-    float a = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(x[i]));
+    const float a = amax8<T>(raw[j]);
     amax[j] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
   }
   // The scale arithmetic (two IEEE divisions and a round trip through E4M3) is the expensive
   // part, so the two lanes of a block split it: the even lane does loads 0 and 1, the odd lane
   // loads 2 and 3, and they swap the resulting multipliers.
   const int odd = lane & 1;
+  const int pair_k = chunk * kQuantChunkElems + (lane >> 1) * 16;  // the pair's block of load 0
+  uint8_t* out_mma = scale_mma + sf_atom_offset(row, pair_k >> 4, k_atoms);  // +4 atoms per load
   float inv_mine[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -238,11 +259,11 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
         static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
     const float t = __fmul_rn(e4m3_to_float(s_byte), r);
     inv_mine[h] = (t == 0.0f) ? 0.0f : __frcp_rn(t);
-    const int kblk = (k_base - lane * 8 + j * 256 + (lane >> 1) * 16);  // first element of the block
+    const int kblk = pair_k + j * 256;  // first element of the block
     if (kblk < k_cover)
-      scale_mma[sf_atom_offset(row, kblk >> 4, k_atoms)] =
-          (row_live && kblk < k) ? static_cast<uint8_t>(s_byte) : 0;
+      out_mma[j * 2048] = (row_live && kblk < k) ? static_cast<uint8_t>(s_byte) : 0;
   }
+  uint8_t* out_packed = packed + static_cast<int64_t>(row) * (k >> 1) + (k_base >> 1);
   float inv[kQuantLoadsPerLane];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -258,8 +279,7 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
       unpack8<T>(raw[j], x);
 #pragma unroll
       for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv[j]);  // the conversion saturates at 6
-      *reinterpret_cast<uint32_t*>(packed + static_cast<int64_t>(row) * (k / 2) + k0 / 2) =
-          e2m1x8(y);
+      *reinterpret_cast<uint32_t*>(out_packed + j * 128) = e2m1x8(y);
     }
   }
 }
