@@ -37,6 +37,18 @@ NOMINAL = {"hbm_gbs": 8000.0, "fp8_tflops": 4500.0, "fp4_tflops": 9000.0}
 DEFAULT_WORKLOAD = "cfg3_block_fp8_colpar"
 L2_FLUSH_BYTES = 256 << 20
 
+# DRAM bytes (read + write) of ONE launch of each workload's GEMM kernel on one GPU at the full
+# size, from `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` captures of
+# `python -m sparkinfer_b200.profile_case <op> M N K 3` (summaries under profiles/). Output
+# bytes still held in the 126 MB L2 when the kernel ends are not in the write figure.
+NCU_TRAFFIC_BYTES = {
+    "cfg0_nvfp4_128x4096x4096": 9_763_584 + 0,
+    "cfg1_nvfp4_decode_m16": 33_143_552 + 0,
+    "cfg2_mxfp8_prefill": 269_895_424 + 98_209_536,
+    "cfg3_block_fp8_colpar": 295_418_368 + 125_971_200,
+    "cfg4_nvfp4_rowpar": 205_942_016 + 43_922_176,
+}
+
 
 def measured_peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
@@ -535,19 +547,22 @@ def main() -> None:
     nominal_tensor = NOMINAL["fp4_tflops"] if w["kind"] == "nvfp4" else NOMINAL["fp8_tflops"]
     flops_local = 2.0 * w["m"] * step.n_local * step.k_local
     bytes_local = algorithmic_bytes(w, step.n_local, step.k_local)
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
     if w["bound"] == "tensor":
         achieved = flops_local / gemm_ms / 1e9
         roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak,
-                    "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": traffic,
                     "peak_source": f"{peaks['source']} BF16 cuBLAS burst x"
                                    f"{4 if w['kind'] == 'nvfp4' else 2} (no FP8/FP4 figure is measured)",
-                    "frac_of_nominal": achieved / nominal_tensor, "kernel_ms": gemm_ms}
+                    "frac_of_nominal": achieved / nominal_tensor, "kernel_ms": gemm_ms,
+                    "algorithmic_bytes": bytes_local}
     else:
         achieved = bytes_local / gemm_ms / 1e6
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                     "peak_source": f"{peaks['source']} copy bandwidth",
-                    "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "kernel_ms": gemm_ms}
+                    "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "kernel_ms": gemm_ms,
+                    "algorithmic_bytes": bytes_local}
 
     extra = {}
     if world == 1 and not args.no_extra:

@@ -448,6 +448,7 @@ constexpr size_t kSmallMCounterBytes = 64 * 1024;
 
 struct SmallMPlan {
   int m_pad, tiles, k_tiles, k_atoms, grid, max_segments, stages, stage_bytes;
+  int issuers, sf_col0, tmem_cols;
   size_t partial_bytes, total_bytes;
 };
 
@@ -479,8 +480,20 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   pl.max_segments = int(seg);
   pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
                                                   : SmallMTile<kNvfp4>::stage_bytes(pl.m_pad);
-  int stages = (227 * 1024 - 2048) / pl.stage_bytes;
+  // Up to 64 padded rows a CTA takes at most half of an SM (shared and tensor memory), so that
+  // the next decode GEMM in the stream can start beside it; 128 rows need all 512 columns.
+  pl.issuers = (pl.m_pad <= 32) ? 2 : 1;
+  pl.sf_col0 = 2 * pl.issuers * pl.m_pad;
+  const int cols = pl.sf_col0 + 2 * SmallMTile<kMxfp8>::kSfColsPerIssuer;
+  pl.tmem_cols = cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
+  const int smem_budget = (pl.tmem_cols <= 256) ? (227 * 1024) / 2 - 1024 : 227 * 1024;
+  int stages = (smem_budget - 2048) / pl.stage_bytes;
   if (stages > SmallMTile<kMxfp8>::kMaxStages) stages = SmallMTile<kMxfp8>::kMaxStages;
+  // With two issuing warps taking alternate units, a stage must always come back to the same
+  // warp: with an odd ring a warp would skip every other phase of a stage's barrier, and a
+  // parity wait cannot tell a phase from the one two before it.
+  if (pl.issuers == 2) stages &= ~1;
+  if (stages < 2) return fail(B12X_B200_ERR_UNSUPPORTED, "decode kernel stage does not fit");
   pl.stages = stages;
   pl.partial_bytes = size_t(pl.tiles) * pl.max_segments * pl.m_pad * 128 * sizeof(float);
   if (size_t(pl.tiles) * sizeof(int) > kSmallMCounterBytes)
@@ -500,10 +513,32 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
     const cudaError_t attr_err = cudaFuncSetAttribute(
         gemm_smallm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    // Largest shared-memory carve-out, so that two CTAs of ~112 KiB fit on one SM.
+    const cudaError_t carve_err = cudaFuncSetAttribute(
+        gemm_smallm_kernel<KIND>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        cudaSharedmemCarveoutMaxShared);
+    if (carve_err != cudaSuccess) return fail_cuda(carve_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
-  gemm_smallm_kernel<KIND><<<grid, 256, smem_bytes, stream>>>(map_w, map_x, p);
-  const cudaError_t err = cudaGetLastError();
+  // Programmatic stream serialization: this grid may start while the previous one in the stream
+  // is still running (if that one releases its dependents early, as this kernel does); the
+  // kernel itself waits for the predecessor before it touches anything the predecessor may own.
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(grid), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = size_t(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool overlap = []() {
+    const char* e = getenv("B12X_B200_DECODE_OVERLAP");
+    return !(e && atoi(e) == 0);
+  }();
+  cfg.numAttrs = overlap ? 1 : 0;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND>, map_w, map_x, p);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;
 }
@@ -584,8 +619,9 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
   p.max_segments = pl.max_segments;
   p.num_stages = pl.stages;
   p.stage_bytes = pl.stage_bytes;
-  p.issuers = (pl.m_pad <= 64) ? 2 : 1;
-  if (const char* e = getenv("B12X_B200_SMALLM_ISSUERS")) { if (atoi(e) == 1) p.issuers = 1; }
+  p.issuers = pl.issuers;
+  p.tmem_cols = pl.tmem_cols;
+  p.sf_col0 = pl.sf_col0;
   p.prof = nullptr;
   if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
   const int smem_bytes = pl.stages * pl.stage_bytes + 2048;

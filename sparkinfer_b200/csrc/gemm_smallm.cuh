@@ -21,6 +21,17 @@
 // (issuer 0 first, so the sum order is fixed). With 128 padded rows four accumulators do not fit
 // in TMEM next to the scales and the second issuer idles.
 //
+// Back-to-back launches overlap. A decode step is a chain of such GEMMs, each only a few
+// microseconds of streaming, and about as much again goes into fixed cost per launch: the gap
+// between dependent grids, the prologue, the ~2 us until the first weight bytes arrive, the
+// tail. So the kernel is built to run beside its predecessor: it takes at most half of an SM's
+// shared memory and (for up to 64 rows) half of its tensor memory, is launched with programmatic
+// stream serialization, and calls griddepcontrol.launch_dependents at once. The weight producer
+// starts streaming immediately (weights are not written by a predecessor that releases its
+// dependents early: only this kernel does that, and its output is never a weight operand); the
+// warps that read activations or write C, partials or counters wait for the predecessor to
+// finish (griddepcontrol.wait) first.
+//
 // Scratch ("workspace") layout: a 64 KiB block of per-tile int32 counters, then
 // [tiles][max_segments][m_pad][128] FP32 partials. Counters must be zero before the first
 // launch; every launch leaves them zero again, whatever the shape.
@@ -49,7 +60,9 @@ struct SmallMParams {
   int max_segments;        // scratch slots per tile
   int num_stages;
   int stage_bytes;
-  int issuers;             // 2 when four accumulators fit in TMEM (m_pad <= 64), else 1
+  int issuers;             // MMA-issuing warps in use (2 when four accumulators fit, else 1)
+  int tmem_cols;           // tensor memory to allocate: 128, 256 or 512 columns
+  int sf_col0;             // first scale column (after the accumulators)
   long long* prof;         // optional cycle counters of CTA 0 (bring-up only)
 };
 
@@ -62,9 +75,8 @@ struct SmallMTile {
   static constexpr int kSfBytes = kKAtoms * 512;
   // Stage = weights | weight scales | activation scales | activation rows (m_pad * 128 B).
   static constexpr int kXOffset = kWBytes + 2 * kSfBytes;
-  // TMEM columns: accumulator (segment parity a, issuer w) at (a * issuers + w) * m_pad, all
-  // below 256; then per issuer 16 columns of weight scales and 16 of activation scales.
-  static constexpr int kSfCol0 = 256;
+  // TMEM columns: accumulator (segment parity a, issuer w) at (a * issuers + w) * m_pad, then
+  // from SmallMParams::sf_col0 per issuer 16 columns of weight scales and 16 of activation scales.
   static constexpr int kSfColsPerIssuer = 32;
   static constexpr int kMaxStages = 10;
   __host__ __device__ static constexpr int stage_bytes(int m_pad) {
@@ -112,15 +124,19 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  // Let the next grid in the stream start its own prologue and weight stream now.
+  grid_launch_dependents();
+  if (warp == 1) tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // Column offset of this CTA's allocation (another CTA may hold the rest of the SM's tensor
+  // memory); the lane field must be zero.
   const uint32_t tmem_base = *tmem_slot;
-  if (tmem_base != 0) {
+  if ((tmem_base >> 16) != 0) {
     if (threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (warp == 1) tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
     return;
   }
 
@@ -138,6 +154,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     // time: warp 0 brings the weight tile and its scales, warp 6 the activation rows and
     // theirs. Both arrive on the stage's full barrier with their own byte counts.
     const bool weights = (warp == 0);
+    if (!weights) grid_dependency_wait();  // activations may come from the previous grid
     int stage = 0;
     uint32_t phase = 0;
     int tile = u_begin / p.k_tiles;
@@ -179,7 +196,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     const int me = (warp == 1) ? 0 : 1;
     const uint32_t idesc_base = make_idesc_block_scaled(
         128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
-    const uint32_t sfw_col = T::kSfCol0 + me * T::kSfColsPerIssuer;
+    const uint32_t sfw_col = tmem_base + p.sf_col0 + me * T::kSfColsPerIssuer;
     const uint32_t sfx_col = sfw_col + 16;
     int stage = 0;
     uint32_t phase = 0;
@@ -199,7 +216,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         break;
       }
       tc_fence_after_sync();
-      const uint32_t d_taddr = static_cast<uint32_t>((acc * p.issuers + me) * p.m_pad);
+      const uint32_t d_taddr = tmem_base + static_cast<uint32_t>((acc * p.issuers + me) * p.m_pad);
       bool first = true;
       for (; u < seg_end; ++u, ++kt) {
         const bool mine = (p.issuers == 2) ? (((u - u_begin) & 1) == me) : (me == 0);
@@ -247,6 +264,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     if (p.prof && blockIdx.x == 0 && lane == 0) p.prof[1 + me * 8] = clock64() - mt0;
   } else {
     // ------------------------------ epilogue ------------------------------
+    // alpha, C, the partial slots and the counters may be written or still read by the
+    // previous grid.
+    grid_dependency_wait();
     const int quarter = warp & 3;
     const int n_local = quarter * 32 + lane;          // weight row inside the tile
     const float alpha = p.alpha ? *p.alpha : 1.0f;
@@ -271,7 +291,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       // Which issuers hold a partial of this segment: both, unless it is a single unit.
       const int first_issuer = (p.issuers == 2) ? ((u - u_begin) & 1) : 0;
       const bool both = (p.issuers == 2) && (seg_end - u >= 2);
-      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t taddr0 =
           lane_base + static_cast<uint32_t>((acc * p.issuers + (both ? 0 : first_issuer)) * p.m_pad);
       const uint32_t taddr1 = lane_base + static_cast<uint32_t>((acc * p.issuers + 1) * p.m_pad);
@@ -373,9 +393,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 
   tc_fence_before_sync();
   __syncthreads();
+  drain_after_abort(abort_flag);
+  __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(0, 512);
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
 }
 

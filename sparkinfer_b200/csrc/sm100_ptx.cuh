@@ -50,6 +50,18 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Programmatic dependent launch. launch_dependents: the next grid in the stream (if it was
+// launched with programmatic stream serialization) may start once every CTA of this grid has
+// executed this or exited. wait: blocks until all grids this one depends on have completed and
+// their memory is visible; returns at once when there is no such dependency.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------------------
@@ -97,6 +109,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if ((polls & 1023u) == 1023u && *abort_flag != 0) return false;
   }
   return false;
+}
+
+// After a role gave up (abort flag set) copies of this CTA may still be in flight; give them a
+// bounded time to land before shared memory and tensor memory are released.
+__device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
+  if (*abort_flag == 0) return;
+  const long long start = clock64();
+  while (clock64() - start < 400000) {
+  }
 }
 
 // Barrier 1 over the 128 epilogue threads, AND-reducing a predicate: lets the four epilogue

@@ -364,3 +364,50 @@ def test_cta_pair_kernel_matches_oracle(monkeypatch, kind, m, n, k):
         out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **MXFP8)
     torch.cuda.synchronize()
     assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 4096, 2048), (16, 14336, 1024), (40, 2048, 4096)])
+def test_decode_gemm_chain_back_to_back_matches_separate_launches(m, n, k):
+    """Decode GEMMs launched back to back overlap on the device (each starts beside its
+    predecessor, shares the SMs' shared and tensor memory with it, and all share one scratch
+    buffer). A chain of six with different weights, eagerly and as a CUDA graph, must give bit
+    for bit what six synchronised launches give; the first of those is checked against the
+    oracle. Shapes cover whole tiles per CTA, split tiles (partial sums through scratch) and
+    the single-issuer layout (M > 32)."""
+    from gpu_util import assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(m + k, (m, k), 0.25))
+    weights = [nvfp4_operand(seeded_bf16(100 * r + n, (n, k), 0.02)) for r in range(6)]
+    alphas = [_alpha(gsa, w[1]) for w in weights]
+    separate = []
+    for (rhs, _, _), alpha in zip(weights, alphas):
+        separate.append(blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **NVFP4))
+        torch.cuda.synchronize()
+    assert_gemm_close(separate[0][:, :, 0], a_deq @ weights[0][2].T)
+
+    outs = [torch.empty_like(s) for s in separate]
+
+    def chain():
+        for (rhs, _, _), alpha, out in zip(weights, alphas, outs):
+            blockscaled.mm(lhs, rhs, out, alpha=alpha, c_dtype="bfloat16", **NVFP4)
+
+    for _ in range(3):
+        for out in outs:
+            out.zero_()
+        chain()
+        torch.cuda.synchronize()
+        for got, want in zip(outs, separate):
+            assert torch.equal(got, want)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain()
+    for _ in range(3):
+        for out in outs:
+            out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, want in zip(outs, separate):
+            assert torch.equal(got, want)
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(torch.device("cuda:0"))
