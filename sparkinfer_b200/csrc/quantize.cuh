@@ -110,10 +110,18 @@ __device__ __forceinline__ float ue8m0_reciprocal(uint32_t byte) {
                                       : ((254u - byte) << 23));
 }
 
+// Four floats -> four E4M3 bytes (element 0 in the lowest byte), saturating at +-448.
 __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
+  uint32_t out;
+  asm("{\n"
+      ".reg .b16 lo, hi;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n"
+      "mov.b32 %0, {lo, hi};\n"
+      "}\n"
+      : "=r"(out)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return out;
 }
 
 // Work decomposition shared by both quantizers: one warp owns one chunk of kChunkElems
@@ -121,7 +129,9 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
 // covering elements [j*256 + lane*8, +8) of the chunk. Every load instruction of a warp thus
 // reads 512 contiguous bytes, all of a lane's loads are issued before the first use (64 bytes in
 // flight per thread), and a scale block (16 or 32 elements) spans 2 or 4 neighbouring lanes, so
-// its maximum is one or two shuffles away.
+// its maximum is one or two shuffles away. A chunk that lies wholly inside the matrix (the
+// common case) runs a copy of the body without any bounds predicate: the kernels are bound by
+// instruction issue, not by memory, as soon as they carry per-element tests.
 constexpr int kQuantLoadsPerLane = 4;
 constexpr int kQuantChunkElems = kQuantLoadsPerLane * 256;
 
@@ -129,42 +139,49 @@ __host__ __device__ inline int64_t quant_warps(int rows_cover, int k_cover) {
   return static_cast<int64_t>(rows_cover) * ((k_cover + kQuantChunkElems - 1) / kQuantChunkElems);
 }
 
-// The launch covers rows_cover x k_cover elements: rows >= m and scale columns >= k/32 inside
-// the cover only receive the neutral scale byte 127 in the atom layout.
-template <typename T>
-__global__ void __launch_bounds__(256)
-quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ values,
-                           uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma,
-                           int m, int k, int rows_cover, int k_cover, int k_atoms) {
-  const int chunks_per_row = (k_cover + kQuantChunkElems - 1) / kQuantChunkElems;
-  // 32-bit on purpose (the host refuses covers with 2^31 or more warps): a 64-bit division per
-  // thread costs more instructions than the quantization itself.
-  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (warp_id >= static_cast<uint32_t>(rows_cover) * static_cast<uint32_t>(chunks_per_row))
-    return;  // whole warps leave
-  const int lane = threadIdx.x & 31;
-  const int row = static_cast<int>(warp_id / static_cast<uint32_t>(chunks_per_row));
-  const int chunk = static_cast<int>(warp_id - static_cast<uint32_t>(row) * chunks_per_row);
-  const int k_base = chunk * kQuantChunkElems + lane * 8;
-  const bool row_live = row < m;
-  const T* src_row = src + static_cast<int64_t>(row_live ? row : 0) * ld_src;
+struct QuantChunk {
+  int row, chunk, lane, k_base;  // k_base = first element of this lane's load 0
+};
 
+// 32-bit on purpose (the host refuses covers with 2^31 or more warps): a 64-bit division per
+// thread costs more instructions than the quantization itself. Returns false for surplus warps.
+__device__ __forceinline__ bool quant_chunk_of_warp(int rows_cover, int k_cover, QuantChunk& c) {
+  const uint32_t chunks_per_row =
+      static_cast<uint32_t>((k_cover + kQuantChunkElems - 1) / kQuantChunkElems);
+  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= static_cast<uint32_t>(rows_cover) * chunks_per_row) return false;
+  c.lane = threadIdx.x & 31;
+  c.row = static_cast<int>(warp_id / chunks_per_row);
+  c.chunk = static_cast<int>(warp_id - static_cast<uint32_t>(c.row) * chunks_per_row);
+  c.k_base = c.chunk * kQuantChunkElems + c.lane * 8;
+  return true;
+}
+
+template <typename T, bool kFull>
+__device__ __forceinline__ void quantize_mxfp8_chunk(const QuantChunk& c, const T* __restrict__ src,
+                                                     int64_t ld_src, uint8_t* __restrict__ values,
+                                                     uint8_t* __restrict__ scale_rows,
+                                                     uint8_t* __restrict__ scale_mma, int m, int k,
+                                                     int k_cover, int k_atoms) {
+  const bool row_live = kFull || c.row < m;
+  const T* src_row = src + static_cast<int64_t>(row_live ? c.row : 0) * ld_src + c.k_base;
   uint4 raw[kQuantLoadsPerLane];
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
-    const int k0 = k_base + j * 256;
-    raw[j] = (row_live && k0 < k) ? ld_nc_16(src_row + k0) : make_uint4(0, 0, 0, 0);
+    const bool live = kFull || (row_live && c.k_base + j * 256 < k);
+    raw[j] = live ? ld_nc_16(src_row + j * 256) : make_uint4(0, 0, 0, 0);
   }
   // Addresses for load 0; load j adds a constant (256 codes, 8 scale columns = 2 atoms).
-  uint8_t* out_values = values + static_cast<int64_t>(row) * k + k_base;
-  const int kb0 = k_base >> 5;
-  uint8_t* out_rows = scale_rows ? scale_rows + static_cast<int64_t>(row) * (k >> 5) + kb0 : nullptr;
-  uint8_t* out_mma = scale_mma ? scale_mma + sf_atom_offset(row, kb0, k_atoms) : nullptr;
-  const bool scale_lane = (lane & 3) == 0;
+  uint8_t* out_values = values + static_cast<int64_t>(c.row) * k + c.k_base;
+  const int kb0 = c.k_base >> 5;
+  uint8_t* out_rows =
+      scale_rows ? scale_rows + static_cast<int64_t>(c.row) * (k >> 5) + kb0 : nullptr;
+  uint8_t* out_mma = scale_mma ? scale_mma + sf_atom_offset(c.row, kb0, k_atoms) : nullptr;
+  const bool scale_lane = (c.lane & 3) == 0;
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
-    const int k0 = k_base + j * 256;
-    const bool live = row_live && k0 < k;
+    const int k0 = c.k_base + j * 256;
+    const bool live = kFull || (row_live && k0 < k);
     float amax = amax8<T>(raw[j]);
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
@@ -180,11 +197,28 @@ quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* _
                      __fmul_rn(x[7], inv));
       *reinterpret_cast<uint2*>(out_values + j * 256) = out;
     }
-    if (scale_lane && k0 < k_cover) {
-      if (live && out_rows) out_rows[j * 8] = byte;
-      if (out_mma) out_mma[j * 1024] = live ? byte : 127u;
+    if (scale_lane && (kFull || k0 < k_cover)) {
+      if (live && out_rows) out_rows[j * 8] = static_cast<uint8_t>(byte);
+      if (out_mma) out_mma[j * 1024] = live ? static_cast<uint8_t>(byte) : uint8_t(127);
     }
   }
+}
+
+// The launch covers rows_cover x k_cover elements: rows >= m and scale columns >= k/32 inside
+// the cover only receive the neutral scale byte 127 in the atom layout.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ values,
+                           uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma,
+                           int m, int k, int rows_cover, int k_cover, int k_atoms) {
+  QuantChunk c;
+  if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
+  if (c.row < m && (c.chunk + 1) * kQuantChunkElems <= k)
+    quantize_mxfp8_chunk<T, true>(c, src, ld_src, values, scale_rows, scale_mma, m, k, k_cover,
+                                  k_atoms);
+  else
+    quantize_mxfp8_chunk<T, false>(c, src, ld_src, values, scale_rows, scale_mma, m, k, k_cover,
+                                   k_atoms);
 }
 
 __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
@@ -192,49 +226,39 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 
-// Eight floats -> eight E2M1 nibbles (element 0 in the lowest nibble), negative zero folded
-// into zero.
+// Eight floats -> eight E2M1 nibbles (element 0 in the lowest nibble), saturating at +-6,
+// negative zero folded into zero.
 __device__ __forceinline__ uint32_t e2m1x8(const float* y) {
-  uint32_t w = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t b = __nv_cvt_float2_to_fp4x2(make_float2(y[2 * i], y[2 * i + 1]), __NV_E2M1,
-                                                cudaRoundNearest);
-    w |= (b & 0xFFu) << (8 * i);
-  }
+  uint32_t w;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}\n"
+      : "=r"(w)
+      : "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]), "f"(y[7]));
   const uint32_t mag = w & 0x77777777u;
   const uint32_t nonzero = (mag | (mag >> 1) | (mag >> 2)) & 0x11111111u;
   return w & (0x77777777u | (nonzero << 3));
 }
 
-// Rows >= m and scale columns >= k/16 inside the covered area receive scale byte 0 (the atom
-// layout's padding value for NVFP4).
-template <typename T>
-__global__ void __launch_bounds__(256)
-quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
-                           const float* __restrict__ global_scale, uint8_t* __restrict__ packed,
-                           uint8_t* __restrict__ scale_mma, int m, int k, int rows_cover,
-                           int k_cover, int k_atoms) {
-  const int chunks_per_row = (k_cover + kQuantChunkElems - 1) / kQuantChunkElems;
-  // 32-bit on purpose (the host refuses covers with 2^31 or more warps): a 64-bit division per
-  // thread costs more instructions than the quantization itself.
-  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (warp_id >= static_cast<uint32_t>(rows_cover) * static_cast<uint32_t>(chunks_per_row))
-    return;  // whole warps leave
-  const int lane = threadIdx.x & 31;
-  const int row = static_cast<int>(warp_id / static_cast<uint32_t>(chunks_per_row));
-  const int chunk = static_cast<int>(warp_id - static_cast<uint32_t>(row) * chunks_per_row);
-  const int k_base = chunk * kQuantChunkElems + lane * 8;
-  const bool row_live = row < m;
-  const T* src_row = src + static_cast<int64_t>(row_live ? row : 0) * ld_src;
-
+template <typename T, bool kFull>
+__device__ __forceinline__ void quantize_nvfp4_chunk(const QuantChunk& c, const T* __restrict__ src,
+                                                     int64_t ld_src, float gs,
+                                                     uint8_t* __restrict__ packed,
+                                                     uint8_t* __restrict__ scale_mma, int m, int k,
+                                                     int k_cover, int k_atoms) {
+  const bool row_live = kFull || c.row < m;
+  const T* src_row = src + static_cast<int64_t>(row_live ? c.row : 0) * ld_src + c.k_base;
   uint4 raw[kQuantLoadsPerLane];
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
-    const int k0 = k_base + j * 256;
-    raw[j] = (row_live && k0 < k) ? ld_nc_16(src_row + k0) : make_uint4(0, 0, 0, 0);
+    const bool live = kFull || (row_live && c.k_base + j * 256 < k);
+    raw[j] = live ? ld_nc_16(src_row + j * 256) : make_uint4(0, 0, 0, 0);
   }
-  const float gs = *global_scale;
   const float r = (gs == 0.0f) ? 0.0f : __frcp_rn(gs);
   // Block maxima: a block is the 16 elements of two neighbouring lanes.
   float amax[kQuantLoadsPerLane];
@@ -246,9 +270,9 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
   // The scale arithmetic (two IEEE divisions and a round trip through E4M3) is the expensive
   // part, so the two lanes of a block split it: the even lane does loads 0 and 1, the odd lane
   // loads 2 and 3, and they swap the resulting multipliers.
-  const int odd = lane & 1;
-  const int pair_k = chunk * kQuantChunkElems + (lane >> 1) * 16;  // the pair's block of load 0
-  uint8_t* out_mma = scale_mma + sf_atom_offset(row, pair_k >> 4, k_atoms);  // +4 atoms per load
+  const int odd = c.lane & 1;
+  const int pair_k = c.chunk * kQuantChunkElems + (c.lane >> 1) * 16;  // the pair's block of load 0
+  uint8_t* out_mma = scale_mma + sf_atom_offset(c.row, pair_k >> 4, k_atoms);  // +4 atoms per load
   float inv_mine[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -260,10 +284,10 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
     const float t = __fmul_rn(e4m3_to_float(s_byte), r);
     inv_mine[h] = (t == 0.0f) ? 0.0f : __frcp_rn(t);
     const int kblk = pair_k + j * 256;  // first element of the block
-    if (kblk < k_cover)
-      out_mma[j * 2048] = (row_live && kblk < k) ? static_cast<uint8_t>(s_byte) : 0;
+    if (kFull || kblk < k_cover)
+      out_mma[j * 2048] = (kFull || (row_live && kblk < k)) ? static_cast<uint8_t>(s_byte) : uint8_t(0);
   }
-  uint8_t* out_packed = packed + static_cast<int64_t>(row) * (k >> 1) + (k_base >> 1);
+  uint8_t* out_packed = packed + static_cast<int64_t>(c.row) * (k >> 1) + (c.k_base >> 1);
   float inv[kQuantLoadsPerLane];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -273,8 +297,7 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
   }
 #pragma unroll
   for (int j = 0; j < kQuantLoadsPerLane; ++j) {
-    const int k0 = k_base + j * 256;
-    if (row_live && k0 < k) {
+    if (kFull || (row_live && c.k_base + j * 256 < k)) {
       float x[8], y[8];
       unpack8<T>(raw[j], x);
 #pragma unroll
@@ -282,6 +305,23 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
       *reinterpret_cast<uint32_t*>(out_packed + j * 128) = e2m1x8(y);
     }
   }
+}
+
+// Rows >= m and scale columns >= k/16 inside the covered area receive scale byte 0 (the atom
+// layout's padding value for NVFP4).
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
+                           const float* __restrict__ global_scale, uint8_t* __restrict__ packed,
+                           uint8_t* __restrict__ scale_mma, int m, int k, int rows_cover,
+                           int k_cover, int k_atoms) {
+  QuantChunk c;
+  if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
+  const float gs = *global_scale;
+  if (c.row < m && (c.chunk + 1) * kQuantChunkElems <= k)
+    quantize_nvfp4_chunk<T, true>(c, src, ld_src, gs, packed, scale_mma, m, k, k_cover, k_atoms);
+  else
+    quantize_nvfp4_chunk<T, false>(c, src, ld_src, gs, packed, scale_mma, m, k, k_cover, k_atoms);
 }
 
 }  // namespace b12x_b200
