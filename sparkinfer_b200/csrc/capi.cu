@@ -480,13 +480,14 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   pl.max_segments = int(seg);
   pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
                                                   : SmallMTile<kNvfp4>::stage_bytes(pl.m_pad);
-  // Up to 64 padded rows a CTA takes at most half of an SM (shared and tensor memory), so that
-  // the next decode GEMM in the stream can start beside it; 128 rows need all 512 columns.
-  pl.issuers = (pl.m_pad <= 32) ? 2 : 1;
+  // Two issuing warps when four accumulators fit beside the scales (up to 64 padded rows).
+  // The ring takes all of the SM's shared memory: a CTA sized for two per SM (so that the
+  // next decode GEMM could run beside this one) was measured slower than a deep ring.
+  pl.issuers = (pl.m_pad <= 64) ? 2 : 1;
   pl.sf_col0 = 2 * pl.issuers * pl.m_pad;
   const int cols = pl.sf_col0 + 2 * SmallMTile<kMxfp8>::kSfColsPerIssuer;
   pl.tmem_cols = cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
-  const int smem_budget = (pl.tmem_cols <= 256) ? (227 * 1024) / 2 - 1024 : 227 * 1024;
+  const int smem_budget = 227 * 1024;
   int stages = (smem_budget - 2048) / pl.stage_bytes;
   if (stages > SmallMTile<kMxfp8>::kMaxStages) stages = SmallMTile<kMxfp8>::kMaxStages;
   // With two issuing warps taking alternate units, a stage must always come back to the same
@@ -513,7 +514,7 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
     const cudaError_t attr_err = cudaFuncSetAttribute(
         gemm_smallm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
-    // Largest shared-memory carve-out, so that two CTAs of ~112 KiB fit on one SM.
+    // Largest shared-memory carve-out: the ring takes nearly all of it.
     const cudaError_t carve_err = cudaFuncSetAttribute(
         gemm_smallm_kernel<KIND>, cudaFuncAttributePreferredSharedMemoryCarveout,
         cudaSharedmemCarveoutMaxShared);

@@ -24,13 +24,15 @@
 // Back-to-back launches overlap. A decode step is a chain of such GEMMs, each only a few
 // microseconds of streaming, and about as much again goes into fixed cost per launch: the gap
 // between dependent grids, the prologue, the ~2 us until the first weight bytes arrive, the
-// tail. So the kernel is built to run beside its predecessor: it takes at most half of an SM's
-// shared memory and (for up to 64 rows) half of its tensor memory, is launched with programmatic
-// stream serialization, and calls griddepcontrol.launch_dependents at once. The weight producer
-// starts streaming immediately (weights are not written by a predecessor that releases its
-// dependents early: only this kernel does that, and its output is never a weight operand); the
-// warps that read activations or write C, partials or counters wait for the predecessor to
-// finish (griddepcontrol.wait) first.
+// tail. The kernel is therefore launched with programmatic stream serialization and calls
+// griddepcontrol.launch_dependents at once, so the next grid's CTAs are placed as soon as this
+// grid's CTAs leave their SMs and run their prologue and first weight loads while this grid is
+// still finishing. The weight producer starts streaming immediately (weights are not written
+// by a predecessor that releases its dependents early: only this kernel does that, and its
+// output is never a weight operand); the warps that read activations or alpha, or write C,
+// partials or counters, wait for the predecessor to finish (griddepcontrol.wait) first.
+// Tensor memory is addressed relative to the allocation's base column and only as many columns
+// as needed are taken, so a CTA does not depend on being alone on its SM.
 //
 // Scratch ("workspace") layout: a 64 KiB block of per-tile int32 counters, then
 // [tiles][max_segments][m_pad][128] FP32 partials. Counters must be zero before the first
