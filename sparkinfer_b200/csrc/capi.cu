@@ -276,11 +276,6 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
   p.group_m = 16;
   p.num_stages = 0;  // filled per instantiation
-  p.debug_flags = 0;
-  if (const char* e = getenv("B12X_B200_DEBUG_FLAGS")) p.debug_flags = atoi(e);
-  if (const char* e = getenv("B12X_B200_STAGES")) p.num_stages = atoi(e);
-  p.prof = nullptr;
-  if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -623,8 +618,6 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
   p.issuers = pl.issuers;
   p.tmem_cols = pl.tmem_cols;
   p.sf_col0 = pl.sf_col0;
-  p.prof = nullptr;
-  if (const char* e = getenv("B12X_B200_PROF_PTR")) p.prof = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
   const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (kind == B12X_B200_KIND_MXFP8)

@@ -77,9 +77,6 @@ struct GemmParams {
   int group_m;           // tile-order grouping along M (L2 reuse)
   int num_stages;        // shared-memory ring depth actually used (<= GemmTile::kStages)
   int use_tma_store;     // 2-byte outputs with 16-byte aligned rows: stage in smem, TMA store
-  int debug_flags;       // bring-up switches: 1 = no MMA issue, 2 = no loads, 4 = no scale copies,
-                         // 8 = no global stores
-  long long* prof;       // optional cycle counters written by CTA 0 (bring-up only)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
@@ -214,8 +211,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    long long prof_wait = 0;
-    const long long prof_begin = clock64();
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -226,45 +221,31 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint8_t* sfa_src = p.sfa + static_cast<size_t>(tm) * p.k_atoms_total * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
       for (int kt = 0; kt < k_tiles; ++kt) {
-        const long long t0 = clock64();
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
           ok = false;
           break;
         }
-        prof_wait += clock64() - t0;
         if (elect_one()) {
           uint8_t* st = smem + stage * T::kStageBytes;
           uint64_t* bar = &full_bar[stage];
-          if (p.debug_flags & 2) {
-            mbar_arrive(bar);
-          } else {
-            const int katom0 = kt * T::kKAtoms;
-            const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
-            const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-            const bool skip_sf = (p.debug_flags & 16) != 0;
-            mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes +
-                                           (skip_sf ? 0u : sf_bytes * (1 + sfb_atoms)));
-            tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
-            tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0);
-            if (!skip_sf) {
-            bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
+          const int katom0 = kt * T::kKAtoms;
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
+          tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
+          tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0);
+          bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
+                    sf_bytes, bar);
+          for (int ra = 0; ra < sfb_atoms; ++ra)
+            bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
+                      sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
                       sf_bytes, bar);
-            for (int ra = 0; ra < sfb_atoms; ++ra)
-              bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
-                        sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
-                        sf_bytes, bar);
-            }
-          }
         }
         __syncwarp();
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       }
-    }
-    if (p.prof && blockIdx.x == 0 && lane == 0) {
-      p.prof[0] = clock64() - prof_begin;
-      p.prof[1] = prof_wait;
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
@@ -274,34 +255,27 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t phase = 0;
     int iter = 0;
     bool ok = true;
-    long long prof_wait_full = 0, prof_wait_acc = 0, prof_issue = 0;
-    const long long prof_begin = clock64();
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const uint32_t sfb_col_shift = static_cast<uint32_t>(((tn * BN) % 128) / 32);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
-      const long long ta = clock64();
       if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
         *abort_flag = 1;
         if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
         break;
       }
-      prof_wait_acc += clock64() - ta;
       tc_fence_after_sync();
       const uint32_t d_taddr = acc * BN;
       const uint32_t sfb_taddr = T::kSfbCol0 + sfb_col_shift;
       for (int kt = 0; kt < k_tiles; ++kt) {
-        const long long tf = clock64();
         if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
           ok = false;
           break;
         }
-        const long long ti = clock64();
-        prof_wait_full += ti - tf;
         tc_fence_after_sync();
         const uint32_t st = smem_u32 + stage * T::kStageBytes;
         const int mmas = min(T::kMmasPerStage,
@@ -309,7 +283,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
           // Scale atoms of this stage -> TMEM. Every atom slot of the stage is copied; slots the
           // producer did not fill (edge of N or K) only feed masked columns or skipped MMAs.
-          if (!(p.debug_flags & 4)) {
+          {
             const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
 #pragma unroll
             for (int ka = 0; ka < T::kKAtoms; ++ka) {
@@ -322,7 +296,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
-          if (!(p.debug_flags & 1)) {
+          {
             // 32 bytes of K per instruction: +2 in the (address >> 4) field.
             if (mmas == T::kMmasPerStage) {
 #pragma unroll
@@ -354,29 +328,19 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
-        prof_issue += clock64() - ti;
       }
-    }
-    if (p.prof && blockIdx.x == 0 && lane == 0) {
-      p.prof[2] = clock64() - prof_begin;
-      p.prof[3] = prof_wait_full;
-      p.prof[4] = prof_wait_acc;
-      p.prof[5] = prof_issue;
     }
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // TMEM lanes this warp may read
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     int iter = 0;
-    long long prof_wait = 0;
     bool store_pending = false;
-    const long long prof_begin = clock64();
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
-      const long long tw = clock64();
       // The epilogue warps meet at barriers in the TMA-store path, so they agree on the
       // outcome of the wait before going on.
       if (!epilogue_bar_and(mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag))) {
@@ -384,7 +348,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
         break;
       }
-      prof_wait += clock64() - tw;
       tc_fence_after_sync();
       const int row_in_tile = quarter * 32 + lane;
       const int row = tm * T::BM + row_in_tile;
@@ -442,7 +405,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           fence_proxy_async_smem();
           epilogue_bar_sync();
-          if (store_thread && !(p.debug_flags & 8)) {
+          if (store_thread) {
             for (int sub = 0; sub < (chunks + 1) / 2; ++sub) {
               const int col = tn * BN + pass * 128 + sub * 64;
               if (col < p.n) tma_store_2d(&map_c, c_stage + sub * (128 * 128), col, tm * T::BM);
@@ -461,17 +424,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
-        if (!(p.debug_flags & 8)) store_row_chunk(p, row, tn * BN + c * 32, vals);
+        store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
     }
     if (p.use_tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
-    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
-      p.prof[6] = clock64() - prof_begin;
-      p.prof[7] = prof_wait;
-    }
   }
 
   tc_fence_before_sync();

@@ -216,24 +216,18 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t phase = 0;
     int iter = 0;
     bool ok = true;
-    long long pf_local = 0, pf_peer = 0, pf_acc = 0, pf_issue = 0;
-    const long long pf_begin = clock64();
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++iter) {
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
-      const long long ta = clock64();
       if (!mbar_wait_bounded_cluster(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
         *abort_flag = 1;
         if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
         break;
       }
-      pf_acc += clock64() - ta;
       tc_fence_after_sync();
       const uint32_t d_taddr = acc * BN;
       for (int kt = 0; kt < k_tiles; ++kt) {
-        const long long t0 = clock64();
         const bool got_local = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
-        const long long t1 = clock64();
         if (!got_local ||
             !mbar_wait_bounded_cluster(&peer_full_bar[stage], phase, abort_flag)) {
           *abort_flag = 1;
@@ -241,9 +235,6 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           ok = false;
           break;
         }
-        const long long t2 = clock64();
-        pf_local += t1 - t0;
-        pf_peer += t2 - t1;
         tc_fence_after_sync();
         const uint32_t st = smem_u32 + stage * T::kStageBytes;
         const int mmas = min(T::kMmasPerStage,
@@ -251,7 +242,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
           const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
 #pragma unroll
-          for (int ka = 0; ka < ((p.debug_flags & 1) ? 0 : T::kKAtoms); ++ka) {
+          for (int ka = 0; ka < T::kKAtoms; ++ka) {
             tc_copy_sf_atom_pair(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
 #pragma unroll
             for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
@@ -260,7 +251,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
-          for (int j = 0; j < ((p.debug_flags & 1) ? 0 : mmas); ++j) {
+          for (int j = 0; j < mmas; ++j) {
             const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
             if (KIND == kMxfp8)
               tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
@@ -282,15 +273,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
         if (++stage == T::kStages) { stage = 0; phase ^= 1; }
-        pf_issue += clock64() - t2;
       }
-    }
-    if (p.prof && blockIdx.x == 0 && lane == 0) {
-      p.prof[2] = clock64() - pf_begin;
-      p.prof[3] = pf_local;
-      p.prof[4] = pf_acc;
-      p.prof[5] = pf_issue;
-      p.prof[6] = pf_peer;
     }
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------------

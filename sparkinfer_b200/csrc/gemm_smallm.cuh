@@ -65,7 +65,6 @@ struct SmallMParams {
   int issuers;             // MMA-issuing warps in use (2 when four accumulators fit, else 1)
   int tmem_cols;           // tensor memory to allocate: 128, 256 or 512 columns
   int sf_col0;             // first scale column (after the accumulators)
-  long long* prof;         // optional cycle counters of CTA 0 (bring-up only)
 };
 
 template <int KIND>
@@ -205,7 +204,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     int seg = 0;
     bool ok = true;
     int u = u_begin;
-    const long long mt0 = clock64();
     while (u < u_end && ok) {
       const int tile = u / p.k_tiles;
       const int tile_end = (tile + 1) * p.k_tiles;
@@ -263,7 +261,6 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       if (ok && first && lane == 0) mbar_arrive(&acc_full_bar[acc]);  // nothing issued here
       ++seg;
     }
-    if (p.prof && blockIdx.x == 0 && lane == 0) p.prof[1 + me * 8] = clock64() - mt0;
   } else {
     // ------------------------------ epilogue ------------------------------
     // alpha, C, the partial slots and the counters may be written or still read by the
