@@ -33,7 +33,7 @@ __version__ = "0.1.0"
 
 # group -> op names; one directory per op, checked by tests/test_registry.py.
 _OPS: dict[str, tuple[str, ...]] = {
-    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear"),
+    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear", "tensor_fp8_linear"),
     "quantization": ("nvfp4", "mxfp8"),
 }
 
@@ -62,6 +62,7 @@ def clear_all_caches() -> None:
     if dense is not None:
         dense._ALPHA_ONE_CACHE.clear()
         dense._FUSED_QUANT_SCRATCH.clear()
+        dense._UNIT_SCALE_CACHE.clear()
     launch = sys.modules.get(f"{__name__}._lib.launch")
     if launch is not None:
         launch._STATUS.clear()

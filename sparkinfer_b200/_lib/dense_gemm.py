@@ -201,6 +201,22 @@ def _select_default_mma_tiler_mn(m: int, n: int, sm_count: int) -> Tuple[int, in
     return (128, best)
 
 
+_UNIT_SCALE_CACHE: dict = {}
+
+
+def _unit_mxfp8_scales(device: torch.device, rows: int, k: int, groups: int) -> torch.Tensor:
+    """Cached MMA-layout scale view with every UE8M0 byte at 127 (2^0), for plain FP8."""
+    from .mxfp8_rows import pack_mxfp8_scales_for_dense_gemm
+
+    key = (device.type, device.index, int(rows), int(k), int(groups))
+    view = _UNIT_SCALE_CACHE.get(key)
+    if view is None:
+        ones = torch.full((groups, rows, k // 32), 127, dtype=torch.uint8, device=device)
+        view = pack_mxfp8_scales_for_dense_gemm(ones, m=rows, k=k, num_groups=groups)
+        _UNIT_SCALE_CACHE[key] = view
+    return view
+
+
 def dense_gemm(
     lhs: Tuple[torch.Tensor, torch.Tensor],
     rhs: Tuple[torch.Tensor, torch.Tensor],
@@ -276,8 +292,15 @@ def dense_gemm(
                               load_path=load_path, swap_ab=swap_ab,
                               sfb_k_replicated=sfb_k_replicated, sm_count=sm_count,
                               stream=stream)
+    if plain_fp8 and (ab_dtype != "float8_e4m3fn" or sf_dtype != "float8_e8m0fnu"
+                      or sf_vec_size != 32):
+        # Per-tensor FP8 rides on the MXFP8 kernel: the caller passes unit block scales and
+        # the one real scale as alpha (dense_gemm.py:7137-7139 in the reference).
+        raise ValueError("plain_fp8 requires float8_e4m3fn operands with float8_e8m0fnu/32 scales")
     if plain_fp8:
-        raise NotImplementedError("plain_fp8 (per-tensor FP8) is not part of this path")
+        # The caller's scale storage is not read in this mode: every block scale is 2^0.
+        sfa_torch = _unit_mxfp8_scales(a_torch.device, m, k, l)
+        sfb_torch = _unit_mxfp8_scales(a_torch.device, n, k, l)
     _kind_of(ab_dtype, sf_dtype, sf_vec_size)
     if mma_tiler_mn is None:
         # Tile width 0 in the op arguments means "the launcher chooses": the persistent tiled

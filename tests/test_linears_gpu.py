@@ -137,3 +137,88 @@ def test_block_fp8_quantize_input_and_prewarm():
     assert xq.scale_mma.shape == (32, 4, 1, 4, 2, 1)
     w_codes, w_scales, _, _ = _block_fp8_checkpoint(32, 128, 256)
     bfl.prewarm(bfl.pack_weight(w_codes, w_scales), [1, 4, 0, 4])
+
+
+def _tensor_fp8_case(seed, tokens, k, n, output_scale=0.0002):
+    """E4M3 source and weight (values clamped to +-4 as in the reference's test) and the FP32
+    product they stand for: the E4M3 codes decoded by the oracle, matmul in FP32, one scale."""
+    from gpu_util import DEV, to_dev
+
+    def codes(s, shape):
+        x = np.clip(seeded_bf16(s, shape).float().numpy(), -4.0, 4.0)
+        return O.e4m3_encode(x)
+
+    a, w = codes(seed, (tokens, k)), codes(seed + 1, (n, k))
+    ref = (O.e4m3_decode(a) @ O.e4m3_decode(w).T) * np.float32(output_scale)
+    scale = torch.tensor([output_scale], dtype=torch.float32, device=DEV)
+    return (to_dev(a).view(torch.float8_e4m3fn), to_dev(w).view(torch.float8_e4m3fn), scale, ref)
+
+
+@pytest.mark.parametrize("tokens,k,n,out_dtype", [
+    (7, 128, 64, torch.bfloat16), (3, 160, 40, torch.bfloat16), (130, 512, 384, torch.float16),
+    (16, 4096, 1024, torch.bfloat16),
+])
+def test_tensor_fp8_linear_matches_fp32_product(tokens, k, n, out_dtype):
+    """tests/gemm/test_tensor_fp8_linear.py:36-75: rtol 1e-2 / atol 2e-3 against
+    (source @ weight^T) * output_scale; K = 160 is padded to 256 with zero codes."""
+    from gpu_util import assert_gemm_close
+    from sparkinfer_b200.gemm import tensor_fp8_linear
+
+    source, weight, scale, ref = _tensor_fp8_case(tokens + k + n, tokens, k, n)
+    packed = tensor_fp8_linear.pack_weight(weight, scale)
+    assert packed.in_features == k and packed.padded_in_features == -(-k // 128) * 128
+    assert packed.values.shape == (n, packed.padded_in_features)
+    assert torch.count_nonzero(packed.values.view(torch.uint8)[:, k:]) == 0
+    out = tensor_fp8_linear.mm(source, packed, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    assert out.shape == (tokens, n) and out.dtype == out_dtype
+    got = out.float().cpu().numpy()
+    assert np.allclose(got, ref, rtol=1e-2, atol=2e-3)
+    assert_gemm_close(out, ref, out_dtype=out_dtype)
+
+
+def test_tensor_fp8_linear_ignores_scale_storage_bias_leading_dims_graph_and_errors():
+    """tests/gemm/test_tensor_fp8_linear.py:78-170: the block-scale storage of the packed
+    weight is not read (plain FP8), bias and leading dimensions, empty input, CUDA-graph
+    replay after prewarm, and the host-side argument errors."""
+    from dataclasses import replace
+
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import tensor_fp8_linear
+
+    source, weight, scale, ref = _tensor_fp8_case(77, 4, 128, 64)
+    packed = tensor_fp8_linear.pack_weight(weight, scale)
+    zeroed = replace(packed, scale_mma=torch.zeros_like(packed.scale_mma))
+    out = tensor_fp8_linear.mm(source, zeroed)
+    torch.cuda.synchronize()
+    assert np.allclose(out.float().cpu().numpy(), ref, rtol=1e-2, atol=2e-3)
+
+    bias = torch.linspace(-1, 1, 64, device=DEV).to(torch.bfloat16)
+    out3 = tensor_fp8_linear.mm(source.view(2, 2, 128), packed, bias=bias)
+    assert out3.shape == (2, 2, 64)
+    want = (torch.from_numpy(ref).to(DEV).to(torch.bfloat16) + bias).view(2, 2, 64)
+    assert torch.allclose(out3.float(), want.float(), rtol=1e-2, atol=1e-2)
+    empty = tensor_fp8_linear.mm(source[:0], packed)
+    assert empty.shape == (0, 64)
+
+    assert tensor_fp8_linear.prewarm(packed, [4, 4, 0]) == 1
+    eager = tensor_fp8_linear.mm(source, packed).clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = tensor_fp8_linear.mm(source, packed)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+
+    with pytest.raises(ValueError, match="float8_e4m3fn"):
+        tensor_fp8_linear.mm(source.view(torch.uint8).to(torch.bfloat16), packed)
+    with pytest.raises(ValueError, match="does not match"):
+        tensor_fp8_linear.mm(source[:, :64], packed)
+    with pytest.raises(TypeError):
+        tensor_fp8_linear.mm(source, weight)
+    with pytest.raises(ValueError, match="bf16/fp16"):
+        tensor_fp8_linear.mm(source, packed, out_dtype=torch.float32)
+    with pytest.raises(ValueError, match="one float32"):
+        tensor_fp8_linear.pack_weight(weight, torch.ones(2, device=DEV))
+    with pytest.raises(ValueError, match="multiple of 32"):
+        tensor_fp8_linear.pack_weight(weight[:, :48], scale)
