@@ -411,3 +411,31 @@ def test_decode_gemm_chain_back_to_back_matches_separate_launches(m, n, k):
             assert torch.equal(got, want)
     from sparkinfer_b200._lib.launch import check_kernel_status
     check_kernel_status(torch.device("cuda:0"))
+
+
+@pytest.mark.parametrize("kind,m,n,k", [
+    ("nvfp4", 65, 384, 512), ("nvfp4", 128, 640, 1024), ("mxfp8", 100, 256, 768),
+    ("mxfp8", 48, 1152, 512), ("nvfp4", 33, 2048, 2048),
+])
+def test_decode_kernel_on_request_up_to_128_rows(kind, m, n, k):
+    """M in 65..128 goes to the tiled kernel by default; the decode kernel still accepts it
+    through the C ABI (128 padded rows, one issuing warp, all 512 TMEM columns). Call the
+    launcher with ``small_m=True`` on the operands of the facade and compare with the oracle."""
+    from gpu_util import assert_gemm_close, mxfp8_operand, nvfp4_operand
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import KIND_MXFP8, KIND_NVFP4
+
+    if kind == "nvfp4":
+        (a, sfa), gsa, a_deq = nvfp4_operand(seeded_bf16(m + k, (m, k), 0.25))
+        (b, sfb), gsb, b_deq = nvfp4_operand(seeded_bf16(n + k, (n, k), 0.02))
+        alpha, code = _alpha(gsa, gsb), KIND_NVFP4
+    else:
+        (a, sfa), a_deq = mxfp8_operand(seeded_bf16(m + k, (m, k), 0.25))
+        (b, sfb), b_deq = mxfp8_operand(seeded_bf16(n + k, (n, k), 0.03))
+        alpha, code = None, KIND_MXFP8
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    # The 6-D scale views alias contiguous atom storage whose first byte is element 0.
+    launch.gemm_blockscaled(code, a, sfa, b, sfb, out, alpha, m, n, k, small_m=True)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(a.device)
+    assert_gemm_close(out, a_deq @ b_deq.T)
