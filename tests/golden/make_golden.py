@@ -14,6 +14,10 @@ Reference functions used (path:line in the b12x tree):
   _scale_u8_from_max_abs                                  b12x/gemm/_shared/wo_mxfp8.py:844-851
   ref_fp4_quant, dequantize_grouped_nvfp4,
   compute_global_scale, recover_grouped_e4m3_scales       tests/_reference/helpers.py:224-363
+  pack_fp8_block_scaled_weight_mxfp8 (re-quantization to UE8M0 block scales, expansion to
+  per-row scales, MMA layout)                             b12x/gemm/_shared/wo_mxfp8.py:873-1187
+    (these insist on CUDA tensors; the generator swaps the module's device check for a no-op
+     in its own process so that the same torch code runs on CPU tensors)
 """
 
 from __future__ import annotations
@@ -150,7 +154,36 @@ def main() -> None:
     gm["bf8_out"] = (a_d @ b_d.T).numpy()
     np.savez_compressed(HERE / "gemm_ref.npz", **gm)
 
-    for name in ("nvfp4_quant.npz", "mxfp8_quant.npz", "gemm_ref.npz"):
+    # ---------------- weight packers (checkpoint block-FP8 -> MXFP8 rows) ----------------
+    import b12x.gemm._shared.wo_mxfp8 as rw  # noqa: E402
+
+    rw._check_gpu_tensor = lambda name, tensor: None  # CPU run of device-agnostic torch code
+    pk = {}
+    for idx, (n_rows, k_cols, groups, seed, pow2) in enumerate([
+            (256, 384, 1, 4042, False), (128, 256, 2, 4043, False), (200, 128, 1, 4044, False),
+            (128, 256, 1, 4045, True)]):
+        gen = torch.Generator().manual_seed(seed)
+        w = (torch.randn((groups * n_rows, k_cols), generator=gen) * 100).clamp(-448, 448)
+        w8 = w.to(torch.float8_e4m3fn)
+        blocks = (groups, -(-n_rows // 128), k_cols // 128)
+        if pow2:
+            sc = torch.pow(2.0, torch.randint(-6, 3, blocks, generator=gen).float())
+        else:
+            sc = torch.rand(blocks, generator=gen) * 0.01 + 1e-4
+        sc = sc[0] if groups == 1 else sc
+        rows = rw.pack_fp8_block_scaled_weight_mxfp8(w8, sc, m=n_rows, k=k_cols, num_groups=groups)
+        pk[f"w{idx}"] = w8.view(torch.uint8).numpy()
+        pk[f"scale{idx}"] = sc.numpy()
+        pk[f"shape{idx}"] = np.array([n_rows, k_cols, groups], dtype=np.int64)
+        vals = rows.values if rows.values.ndim == 2 else rows.values.permute(2, 0, 1)
+        pk[f"values{idx}"] = vals.contiguous().view(torch.uint8).numpy()
+        pk[f"scale_rows{idx}"] = rows.scale_rows.contiguous().view(torch.uint8).numpy()
+        # Physical bytes of the MMA-layout scale tensor: [L][row_tile][k_tile][32][4][4].
+        pk[f"scale_mma{idx}"] = (rows.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous()
+                                 .view(torch.uint8).numpy().reshape(-1))
+    np.savez_compressed(HERE / "weight_pack.npz", **pk)
+
+    for name in ("nvfp4_quant.npz", "mxfp8_quant.npz", "gemm_ref.npz", "weight_pack.npz"):
         print(name, (HERE / name).stat().st_size, "bytes")
 
 

@@ -212,3 +212,27 @@ def test_custom_ops_have_fake_implementations():
         assert torch.ops.b12x.dense_gemm_launch(
             a, a, sf, sf, cc, alpha, 128, 128, 1, 1, "float4_e2m1fn", "float8_e4m3fn",
             "bfloat16", *tail) is None
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2, 3])
+def test_weight_packers_match_reference_fixture(monkeypatch, idx):
+    """pack_fp8_block_scaled_weight_mxfp8 (load-time torch code, device-agnostic apart from
+    its CUDA-tensor check, which is lifted here) against outputs of the reference's own
+    function on the same checkpoint-style inputs: re-quantized codes, per-row scale bytes and
+    the physical bytes of the MMA-layout scale tensor, one and two groups, ragged row count,
+    power-of-two scales passed through."""
+    from conftest import GOLDEN
+    from sparkinfer_b200._lib import mxfp8_rows as mr
+
+    monkeypatch.setattr(mr, "_check_gpu_tensor", lambda name, tensor: None)
+    g = np.load(GOLDEN / "weight_pack.npz")
+    m, k, groups = (int(v) for v in g[f"shape{idx}"])
+    weight = torch.from_numpy(g[f"w{idx}"]).view(torch.float8_e4m3fn)
+    scale = torch.from_numpy(g[f"scale{idx}"])
+    rows = mr.pack_fp8_block_scaled_weight_mxfp8(weight, scale, m=m, k=k, num_groups=groups)
+    values = rows.values if rows.values.ndim == 2 else rows.values.permute(2, 0, 1)
+    assert np.array_equal(values.contiguous().view(torch.uint8).numpy(), g[f"values{idx}"])
+    assert np.array_equal(rows.scale_rows.contiguous().view(torch.uint8).numpy(),
+                          g[f"scale_rows{idx}"])
+    physical = rows.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous().view(torch.uint8)
+    assert np.array_equal(physical.numpy().reshape(-1), g[f"scale_mma{idx}"])

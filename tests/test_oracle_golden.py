@@ -121,3 +121,25 @@ def test_swizzle_offsets_agree_with_formula():
     flat = O.swizzle_scales(scales)
     for r, c in [(0, 0), (31, 3), (32, 0), (127, 9), (128, 4), (299, 9)]:
         assert flat[O.scale_atom_offset(r, c, cols)] == scales[r, c]
+
+
+@pytest.mark.parametrize("idx", [0, 2, 3])
+def test_weight_requantization_matches_reference(idx):
+    """Checkpoint block-FP8 weight -> MXFP8 rows: the oracle's re-quantization onto UE8M0
+    block scales and the expansion to per-row scale bytes against the reference's
+    pack_fp8_block_scaled_weight_mxfp8 (single-group cases; case 3 carries power-of-two
+    scales, which the reference passes through without touching the codes)."""
+    g = np.load(GOLDEN / "weight_pack.npz")
+    m, k, groups = (int(v) for v in g[f"shape{idx}"])
+    assert groups == 1
+    codes, scale = g[f"w{idx}"], g[f"scale{idx}"]
+    exact_pow2 = bool(np.all(np.frexp(scale)[0] == 0.5))
+    if exact_pow2:
+        new_codes = codes
+        block_bytes = (np.round(np.log2(scale)) + 127).astype(np.uint8)
+    else:
+        new_codes, block_bytes = O.requantize_block_fp8_to_ue8m0(codes, scale)
+    rows = O.expand_block_scale_bytes(block_bytes, m, k)
+    assert np.array_equal(new_codes, g[f"values{idx}"])
+    assert np.array_equal(rows, g[f"scale_rows{idx}"].reshape(m, k // 32))
+    assert np.array_equal(O.swizzle_scales(rows, 127), g[f"scale_mma{idx}"])
