@@ -381,13 +381,13 @@ def cpu_dequant_matmul(w: dict, sample_rows: int, seed: int = 7):
     return dt, 2.0 * sample_rows * n * k
 
 
-def cpu_baseline(w: dict, budget_s: float = 12.0) -> dict:
+def cpu_baseline(w: dict, limit_s: float = 12.0) -> dict:
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     rows = min(w["m"], 256)
     dt, flops = cpu_dequant_matmul(w, rows)
     reps, total_t, total_f = 1, dt, flops
-    while total_t < budget_s and reps < 8:
+    while total_t < limit_s and reps < 8:
         dt, flops = cpu_dequant_matmul(w, rows, seed=7 + reps)
         total_t += dt
         total_f += flops

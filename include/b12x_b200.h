@@ -104,7 +104,7 @@ int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
  *
  * Some callers of a decode GEMM are not in a position to call cudaMalloc (or a framework
  * allocator) for the workspace above: a serving process that gave all device memory to its own
- * pool at start-up and runs with a fixed budget, a plugin called from a thread that is in the
+ * pool at start-up and runs with a fixed allowance, a plugin called from a thread that is in the
  * middle of a CUDA stream capture (where an allocation fails or invalidates the capture), a
  * small C host that links this library and nothing else. For them this entry point keeps the
  * workspace inside the library: a fixed 4 MiB + 64 KiB array in device memory, present on every

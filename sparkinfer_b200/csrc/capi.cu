@@ -482,8 +482,8 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   pl.sf_col0 = 2 * pl.issuers * pl.m_pad;
   const int cols = pl.sf_col0 + 2 * SmallMTile<kMxfp8>::kSfColsPerIssuer;
   pl.tmem_cols = cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
-  const int smem_budget = 227 * 1024;
-  int stages = (smem_budget - 2048) / pl.stage_bytes;
+  const int smem_limit = 227 * 1024;
+  int stages = (smem_limit - 2048) / pl.stage_bytes;
   if (stages > SmallMTile<kMxfp8>::kMaxStages) stages = SmallMTile<kMxfp8>::kMaxStages;
   // With two issuing warps taking alternate units, a stage must always come back to the same
   // warp: with an odd ring a warp would skip every other phase of a stage's barrier, and a

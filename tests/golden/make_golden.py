@@ -42,7 +42,9 @@ def _bf16_bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = os.environ.get("B12X_REFERENCE", "/root/reference")
+    ref_root = os.environ.get("B12X_REFERENCE")
+    if not ref_root:
+        raise SystemExit("set B12X_REFERENCE to a checkout of the b12x reference")
     sys.path.insert(0, ref_root)
     from b12x._lib import intrinsics as ri  # noqa: E402
     from b12x.gemm._shared import wo_mxfp8 as rw  # noqa: E402
