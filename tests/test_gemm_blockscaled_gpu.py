@@ -439,3 +439,88 @@ def test_decode_kernel_on_request_up_to_128_rows(kind, m, n, k):
     torch.cuda.synchronize()
     launch.check_kernel_status(a.device)
     assert_gemm_close(out, a_deq @ b_deq.T)
+
+
+def test_full_size_block_fp8_column_parallel_shape_on_sampled_rows():
+    """Config 3 at full size (4096 x 18432 x 7168, E4M3 with FP32 scales per 1x128 / 128x128
+    block = amax/448 of seeded data): sampled rows and columns against the oracle, linearity
+    in alpha over the whole output, and the two halves of N computed as separate column-parallel
+    shards must reproduce the unsharded output bit for bit."""
+    from gpu_util import DEV, to_dev
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 4096, 18432, 7168
+    rows = np.r_[0:8, m // 2:m // 2 + 8, m - 8:m]
+    col_blocks = [0, 71, 143]  # 128-column blocks of the weight that are checked
+    gen = torch.Generator().manual_seed(42 + 3000)
+    a = torch.randn((m, k), generator=gen).to(torch.bfloat16).float()
+    b = (torch.randn((n, k), generator=gen) * 0.02).to(torch.bfloat16).float()
+    sa = (a.view(m, k // 128, 128).abs().amax(dim=2) / 448.0).clamp_min(1e-12)
+    sb = (b.view(n // 128, 128, k // 128, 128).abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    a8 = (a.view(m, k // 128, 128) / sa[:, :, None]).reshape(m, k).to(torch.float8_e4m3fn)
+    b8 = (b.view(n // 128, 128, k // 128, 128) / sb[:, None, :, None]).reshape(n, k).to(
+        torch.float8_e4m3fn)
+    lhs = (a8.to(DEV).view(m, k, 1), sa.to(DEV).contiguous())
+    rhs = (b8.to(DEV).view(n, k, 1), sb.to(DEV).contiguous())
+    out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **BLOCK_FP8)
+    torch.cuda.synchronize()
+    a_codes = a8.view(torch.uint8).numpy()[rows]
+    for cb in col_blocks:
+        b_codes = b8.view(torch.uint8).numpy()[cb * 128:(cb + 1) * 128]
+        ref = O.gemm_block_fp8(a_codes, sa.numpy()[rows], b_codes, sb.numpy()[cb:cb + 1])
+        got = out[:, cb * 128:(cb + 1) * 128, 0][torch.from_numpy(rows).to(DEV)]
+        err = np.abs(got.float().cpu().numpy() - ref).max()
+        assert err <= 1e-2 * np.abs(ref).max()
+        assert err <= (2.0 ** -8 + 2.0 ** -16) * np.abs(ref).max()
+    alpha = torch.tensor([0.25], device=DEV)
+    out_q = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **BLOCK_FP8)
+    assert torch.equal(out_q.float() * 4.0, out.float())
+    half = n // 2
+    for lo in (0, half):
+        shard = blockscaled.mm(lhs, (rhs[0][lo:lo + half], rhs[1][lo // 128:(lo + half) // 128]),
+                               c_dtype="bfloat16", **BLOCK_FP8)
+        assert torch.equal(shard, out[:, lo:lo + half])
+    torch.cuda.synchronize()
+
+
+@pytest.fixture(scope="module")
+def decode_weight():
+    """Config-1 weight (14336 x 4096, randn * 0.02) quantized once by the oracle."""
+    from gpu_util import to_dev
+    from sparkinfer_b200._lib import layout
+
+    n, k = 14336, 4096
+    w = seeded_bf16(42 + 1001, (n, k), 0.02).float().numpy()
+    gsw = O.nvfp4_global_scale(w)
+    wp, ws = O.quantize_nvfp4_rows(w, gsw)
+    sf = layout.convert_sf_to_mma_layout(to_dev(O.swizzle_scales(ws, 0)), n, k, 1, 16)
+    return (to_dev(wp).reshape(n, k // 2, 1), sf), gsw, wp, ws
+
+
+@pytest.mark.parametrize("m", [1, 4, 16, 64])
+def test_full_size_decode_sweep_on_sampled_columns(m, decode_weight):
+    """Config 1 at full size (N = 14336, K = 4096, M in {1, 4, 16, 64}): activations
+    row-quantized on the GPU per call, weights quantized by the oracle, sampled output columns
+    against the oracle."""
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import blockscaled
+    from sparkinfer_b200.quantization import nvfp4
+
+    n, k = 14336, 4096
+    rhs, gsw, wp, ws = decode_weight
+    x = seeded_bf16(42 + 1000, (m, k)).to(DEV)
+    gsx = O.nvfp4_global_scale(x.float().cpu().numpy())
+    plan = nvfp4.plan(m, k)
+    outs = nvfp4.allocate_outputs(plan, device=DEV)
+    nvfp4.run(plan=plan, x=x, global_scale=torch.tensor([gsx], device=DEV), outputs=outs)
+    lhs = (outs.packed_a_view, outs.scale_mma_view(m, k))
+    out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsx, gsw), c_dtype="bfloat16", **NVFP4)
+    torch.cuda.synchronize()
+    cols = np.r_[0:64, n // 2:n // 2 + 64, n - 64:n]
+    pa, sa = O.quantize_nvfp4_rows(x.float().cpu().numpy(), gsx)
+    ref = O.dequantize_nvfp4(pa, sa, gsx) @ O.dequantize_nvfp4(wp[cols], ws[cols], gsw).T
+    got = out[:, :, 0][:, torch.from_numpy(cols).to(DEV)].float().cpu().numpy()
+    err = np.abs(got - ref).max()
+    assert err <= 1e-2 * np.abs(ref).max()
+    assert err <= (2.0 ** -8 + 2.0 ** -16) * np.abs(ref).max()
+    assert not torch.isnan(out.float()).any()
