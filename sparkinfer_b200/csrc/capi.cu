@@ -428,8 +428,19 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
+  // Output through TMA when rows of C are 16-byte aligned 2-byte values; otherwise the
+  // epilogue stores straight from registers.
+  CUtensorMap map_c;
+  memset(&map_c, 0, sizeof(map_c));
+  p.use_tma_store = 0;
+  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0 &&
+      !getenv("B12X_B200_DIRECT_STORE")) {
+    rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
+    if (rc != B12X_B200_OK) return rc;
+    p.use_tma_store = 1;
+  }
   gemm_block_fp8_kernel<<<grid, BlockFp8Tile::kThreads, BlockFp8Tile::kSmemBytes,
-                          reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+                          reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_c, p);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_block_fp8 launch");
   return B12X_B200_OK;

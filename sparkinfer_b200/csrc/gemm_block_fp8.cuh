@@ -13,7 +13,10 @@
 // 256 columns, i.e. half of one 128-column scale block). Promotion is a chain of TMEM load ->
 // wait -> FMA per warp, so it is the number of warps per scheduler (four) that hides the load
 // latency. The two 256-column TMEM buffers fill all 512 columns, so the MMA of k-block i+1
-// overlaps the promotion of k-block i.
+// overlaps the promotion of k-block i. At the end of a tile the promotion warps must get back
+// to the next tile quickly (the MMA warp can only run two k-blocks ahead of them), so 2-byte
+// outputs are converted into a 128-byte-swizzled staging area in shared memory and leave
+// through asynchronous TMA stores, one 64-column sub-tile per group of four warps.
 #pragma once
 
 #include "gemm_blockscaled.cuh"
@@ -26,9 +29,10 @@ struct BlockFp8Tile {
   static constexpr int kABytes = BM * 128;
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = 3;
+  static constexpr int kCStageBytes = BM * BN * 2;   // four sub-tiles of 128 rows x 64 columns
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kCStageBytes + kBarrierBytes + 1024;
   static constexpr int kEpilogueWarps = 16;
   static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
@@ -42,16 +46,24 @@ struct BlockFp8Params {
   int* status;
   int m, n, k, ldc, out_dtype;
   int tiles_m, tiles_n, group_m;
+  int use_tma_store;   // 2-byte outputs with 16-byte aligned rows
 };
+
+// Named barrier 1 + group over the 128 threads (four warps) that share an output sub-tile.
+__device__ __forceinline__ void group_bar_sync(int group) {
+  asm volatile("barrier.cta.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
 
 __global__ void __launch_bounds__(BlockFp8Tile::kThreads, 1)
 gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
-                      const __grid_constant__ CUtensorMap map_b, const BlockFp8Params p) {
+                      const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_c, const BlockFp8Params p) {
   using T = BlockFp8Tile;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + T::kStages * T::kStageBytes);
+  uint8_t* c_stage = smem + T::kStages * T::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(c_stage + T::kCStageBytes);
   uint64_t* empty_bar = full_bar + T::kStages;
   uint64_t* part_full_bar = empty_bar + T::kStages;
   uint64_t* part_empty_bar = part_full_bar + 2;
@@ -76,6 +88,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (p.use_tma_store) tma_prefetch_desc(&map_c);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
@@ -159,6 +172,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
     const int kb_total = k_blocks;
     uint32_t it = 0;
     bool ok = true;
+    bool store_pending = false;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -201,6 +215,38 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) mbar_arrive(&part_empty_bar[buf]);
       }
       if (!ok) break;
+      if (p.use_tma_store) {
+        // The four warps of a group own sub-tile `group`: rows 0..127, 64 columns = 128 bytes
+        // per row; 16-byte chunk j of row r sits at position j ^ (r % 8), the layout a
+        // 128-byte-swizzled TMA store expects. The sub-tile of the previous tile has long been
+        // read by its store; the wait is a formality.
+        const bool store_thread = (quarter == 2) && (lane == 0);  // first warp of the group
+        if (store_pending) {
+          if (store_thread) tma_store_wait_read<0>();
+          group_bar_sync(group);
+        }
+        const int r = quarter * 32 + lane;
+        uint8_t* sub = c_stage + group * (128 * 128) + r * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const float lo = acc[j * 8 + 2 * h] * alpha, hi = acc[j * 8 + 2 * h + 1] * alpha;
+            w[h] = (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+          }
+          *reinterpret_cast<uint4*>(sub + ((j ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();
+        group_bar_sync(group);
+        if (store_thread) {
+          const int m0 = tm * T::BM;
+          if (col0 < p.n && m0 < p.m) tma_store_2d(&map_c, c_stage + group * (128 * 128), col0, m0);
+          tma_store_commit();
+        }
+        store_pending = true;
+        continue;
+      }
       GemmParams gp;
       gp.c = p.c;
       gp.m = p.m;
@@ -215,6 +261,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         store_row_chunk(gp, row, col0 + c * 32, vals);
       }
     }
+    if (p.use_tma_store && quarter == 2 && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
