@@ -87,8 +87,15 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
  *   workspace  at least b12x_b200_gemm_smallm_workspace_bytes(...) bytes, 16-byte aligned.
  *              Its first 64 KiB hold per-tile counters that must be zero before the first
  *              launch that uses the buffer (zero the buffer once); each launch leaves them
- *              zero, so one buffer serves any sequence of shapes. Launches that share a
- *              workspace must not overlap on the device.
+ *              zero, so one buffer serves any sequence of shapes. Launches on different
+ *              streams that share a workspace must not overlap on the device.
+ *
+ * Ordering on one stream. The kernel is launched with programmatic stream serialization: a
+ * decode GEMM may start while the decode GEMM launched just before it on the same stream is
+ * still running. It reads x, sf_x and alpha and writes c and the workspace only after that
+ * predecessor has completed, but it starts streaming w and sf_w at once; w and sf_w must
+ * therefore not be outputs of the immediately preceding decode GEMM on the stream. Work of any
+ * other kind before it on the stream is ordered as usual.
  */
 int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
                                               int sm_count);
