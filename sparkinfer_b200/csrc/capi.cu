@@ -247,10 +247,11 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
   const int bn = block_n > 0 ? block_n : choose_block_n(m, n, sms);
 
-  // Large problems (at least one full wave of 256 x 256 pair tiles) go to the CTA-pair kernel
-  // unless a tile width was forced.
+  // Problems with enough 256 x 256 pair tiles go to the CTA-pair kernel unless a tile width was
+  // forced. "Enough" is two thirds of the pairs: measured on 148 SMs the pair kernel wins from
+  // 56 tiles up (512 x 7168, 1024 x 4096, 256 x 18432) and loses at 28-32 tiles.
   const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-  bool use_pair = (block_n == 0) && (sms >= 2) && (pair_tiles >= sms / 2);
+  bool use_pair = (block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms);
   if (const char* e = getenv("B12X_B200_PAIR")) use_pair = (block_n == 0) && (sms >= 2) && atoi(e) != 0;
 
   CUtensorMap map_a, map_b;
