@@ -84,3 +84,11 @@ def test_cuda_sources_target_sm100a_only_and_never_multicast():
     assert "compute_100a" in build_py and "sm_100a" in build_py
     for other in ("sm_90", "sm_120", "compute_120"):
         assert other not in build_py
+
+
+def test_graft_entry_build_runs_without_a_gpu():
+    """``build()`` is the does-it-build check that runs on a CPU-only machine: it compiles the
+    library (a no-op when it is current), loads it and imports the package."""
+    import __graft_entry__ as entry
+
+    entry.build()
