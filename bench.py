@@ -45,7 +45,7 @@ NCU_TRAFFIC_BYTES = {
     "cfg0_nvfp4_128x4096x4096": 9_763_584 + 0,
     "cfg1_nvfp4_decode_m16": 33_143_552 + 0,
     "cfg2_mxfp8_prefill": 269_895_424 + 98_209_536,
-    "cfg3_block_fp8_colpar": 295_418_368 + 125_971_200,
+    "cfg3_block_fp8_colpar": 295_902_464 + 128_936_960,
     "cfg4_nvfp4_rowpar": 205_942_016 + 43_922_176,
 }
 
