@@ -43,10 +43,10 @@ L2_FLUSH_BYTES = 256 << 20
 # bytes still held in the 126 MB L2 when the kernel ends are not in the write figure.
 NCU_TRAFFIC_BYTES = {
     "cfg0_nvfp4_128x4096x4096": 9_763_584 + 0,
-    "cfg1_nvfp4_decode_m16": 33_143_552 + 0,
-    "cfg2_mxfp8_prefill": 269_895_424 + 98_209_536,
+    "cfg1_nvfp4_decode_m16": 33_144_832 + 0,
+    "cfg2_mxfp8_prefill": 269_695_232 + 98_486_784,
     "cfg3_block_fp8_colpar": 295_902_464 + 128_936_960,
-    "cfg4_nvfp4_rowpar": 205_942_016 + 43_922_176,
+    "cfg4_nvfp4_rowpar": 205_454_592 + 44_247_040,
 }
 
 
