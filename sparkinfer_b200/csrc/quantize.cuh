@@ -211,6 +211,10 @@ __global__ void __launch_bounds__(256)
 quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ values,
                            uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma,
                            int m, int k, int rows_cover, int k_cover, int k_atoms) {
+  // A decode GEMM launched next on the stream with programmatic stream serialization may start
+  // now and stream its weights while these rows are quantized; it waits for this grid to
+  // finish before it reads them. Any other successor waits for completion as usual.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   QuantChunk c;
   if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
   if (c.row < m && (c.chunk + 1) * kQuantChunkElems <= k)
@@ -315,6 +319,8 @@ quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
                            const float* __restrict__ global_scale, uint8_t* __restrict__ packed,
                            uint8_t* __restrict__ scale_mma, int m, int k, int rows_cover,
                            int k_cover, int k_atoms) {
+  // See quantize_mxfp8_rows_kernel: lets a following decode GEMM begin its weight stream.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   QuantChunk c;
   if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
   const float gs = *global_scale;
