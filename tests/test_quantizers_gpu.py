@@ -213,3 +213,48 @@ def test_full_size_prefill_activation_rows(dev):
     assert np.array_equal(out.scale_rows.view(torch.uint8)[0][rows].cpu().numpy(), ref_rows)
     amax = xd.float().view(m, k // 32, 32).abs().amax(-1).cpu().numpy()
     assert np.array_equal(out.scale_rows.view(torch.uint8)[0].cpu().numpy(), O.ue8m0_from_amax(amax))
+
+
+@pytest.mark.parametrize("m,k,ld", [(5, 256, 320), (130, 1056, 2048), (16, 4096, 4104)])
+def test_row_quantizers_read_row_strided_sources_through_the_c_abi(dev, m, k, ld):
+    """The C entry points take a leading dimension for the source (rows of a wider activation
+    buffer, as the fused quantize-then-GEMM path passes them): same bytes as for a dense copy
+    of the rows, for MXFP8 (with and without the row-major scale output) and NVFP4 (K a
+    multiple of 16 but not of 64 in the second case)."""
+    import ctypes
+
+    from sparkinfer_b200 import _native
+
+    lib = _native.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    wide = seeded_bf16(7000 + m + k, (m, ld), 0.5).to(dev)
+    x = wide[:, :k]
+    dense = x.contiguous().float().cpu().numpy()
+
+    ref_values, ref_rows = O.quantize_mxfp8_rows(dense)
+    values = torch.empty((m, k), dtype=torch.uint8, device=dev)
+    rows = torch.empty((m, k // 32), dtype=torch.uint8, device=dev)
+    atoms = (-(-m // 128)) * (-(-k // 128)) * 512
+    mma = torch.full((atoms,), 127, dtype=torch.uint8, device=dev)
+    for with_rows in (True, False):
+        values.zero_()
+        rc = lib.b12x_b200_quantize_mxfp8_rows(
+            x.data_ptr(), _native.DT_BF16, ld, values.data_ptr(),
+            rows.data_ptr() if with_rows else None, mma.data_ptr(), m, k, stream)
+        _native.check(rc, "quantize_mxfp8_rows")
+        torch.cuda.synchronize()
+        assert np.array_equal(values.cpu().numpy(), ref_values)
+        assert np.array_equal(mma.cpu().numpy(), O.swizzle_scales(ref_rows, 127))
+    assert np.array_equal(rows.cpu().numpy(), ref_rows)
+
+    gs = O.nvfp4_global_scale(dense)
+    ref_packed, ref_scales = O.quantize_nvfp4_rows(dense, gs)
+    packed = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    sf = torch.zeros(((-(-m // 128)) * (-(-k // 64)) * 512,), dtype=torch.uint8, device=dev)
+    gs_dev = torch.tensor([gs], dtype=torch.float32, device=dev)
+    rc = lib.b12x_b200_quantize_nvfp4_rows(x.data_ptr(), _native.DT_BF16, ld, gs_dev.data_ptr(),
+                                           packed.data_ptr(), sf.data_ptr(), m, k, stream)
+    _native.check(rc, "quantize_nvfp4_rows")
+    torch.cuda.synchronize()
+    assert np.array_equal(packed.cpu().numpy(), ref_packed)
+    assert np.array_equal(sf.cpu().numpy(), O.swizzle_scales(ref_scales, 0))
