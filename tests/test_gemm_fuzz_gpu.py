@@ -1,0 +1,130 @@
+"""Seeded shape fuzz of the block-scaled GEMM against a plain PyTorch FP32 reference of the same
+op (operands dequantized on the GPU, FP32 matmul). Random codes and random scale bytes, random
+M / N / K including ragged edges, every kernel family (decode, tiled with each tile width, CTA
+pair), BF16 / FP16 / FP32 outputs. Complements the oracle-based parity tests, which use fewer
+and smaller shapes because the CPU oracle quantizes real data."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+E2M1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+
+def _atoms(scale_rows: torch.Tensor, pad: int) -> torch.Tensor:
+    """[rows, cols] scale bytes -> flat 512-byte atoms [row_tile][col_tile][32][4][4]."""
+    rows, cols = scale_rows.shape
+    rp, cp = -(-rows // 128) * 128, -(-cols // 4) * 4
+    padded = torch.full((rp, cp), pad, dtype=torch.uint8, device=scale_rows.device)
+    padded[:rows, :cols] = scale_rows
+    return padded.view(rp // 128, 4, 32, cp // 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(-1)
+
+
+def _operand(kind: str, rows: int, k: int, gen, dev):
+    """Random operand: (codes, scale atoms, dequantized FP32 [rows, k])."""
+    if kind == "mxfp8":
+        codes = torch.randint(0, 256, (rows, k), dtype=torch.uint8, device=dev, generator=gen)
+        codes = codes & 0xBF  # |value| < 2, no NaN pattern
+        scales = torch.randint(121, 129, (rows, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+        deq = codes.view(torch.float8_e4m3fn).float() * torch.exp2(
+            scales.float() - 127.0).repeat_interleave(32, dim=1)
+        return codes, _atoms(scales, 127), deq
+    packed = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev, generator=gen)
+    scales = torch.randint(0x18, 0x31, (rows, k // 16), dtype=torch.uint8, device=dev, generator=gen)
+    lut = torch.tensor(E2M1, dtype=torch.float32, device=dev)
+    vals = torch.stack((lut[(packed & 0xF).long()], lut[(packed >> 4).long()]), dim=-1).view(rows, k)
+    deq = vals * scales.view(torch.float8_e4m3fn).float().repeat_interleave(16, dim=1)
+    return packed, _atoms(scales, 0), deq
+
+
+def _cases():
+    rng = np.random.default_rng(20261125)
+    cases = []
+    for i in range(48):
+        kind = "mxfp8" if rng.random() < 0.5 else "nvfp4"
+        m = int(rng.choice([1, 3, 8, 17, 33, 64, 65, 127, 128, 129, 200, 256, 300, 511, 640]))
+        n = int(rng.choice([8, 24, 64, 72, 128, 136, 192, 200, 256, 264, 320, 504, 512, 776, 1024, 1288]))
+        k_unit = 32 if kind == "mxfp8" else 64
+        k = k_unit * int(rng.integers(1, 24))
+        route = str(rng.choice(["auto", "auto", "bn64", "bn128", "bn192", "bn256", "pair", "decode"]))
+        if route == "decode" and m > 128:
+            route = "auto"
+        dtype = [torch.bfloat16, torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 4))]
+        cases.append((i, kind, m, n, k, route, dtype))
+    return cases
+
+
+@pytest.mark.parametrize("index,kind,m,n,k,route,dtype", _cases())
+def test_gemm_matches_fp32_reference_on_random_shapes(monkeypatch, index, kind, m, n, k, route, dtype):
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import KIND_MXFP8, KIND_NVFP4
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(1000 + index)
+    a, sfa, a_deq = _operand(kind, m, k, gen, dev)
+    b, sfb, b_deq = _operand(kind, n, k, gen, dev)
+    alpha = torch.tensor([0.75], dtype=torch.float32, device=dev)
+    ldc = n + (8 if index % 3 == 0 else 0)  # sometimes a padded output pitch
+    out = torch.full((m, ldc), float("nan"), dtype=dtype, device=dev)
+    kwargs = {}
+    monkeypatch.delenv("B12X_B200_PAIR", raising=False)
+    if route.startswith("bn"):
+        kwargs["block_n"] = int(route[2:])
+    elif route == "pair":
+        monkeypatch.setenv("B12X_B200_PAIR", "1")
+        kwargs["small_m"] = False
+    elif route == "decode":
+        kwargs["small_m"] = True
+    launch.gemm_blockscaled(KIND_MXFP8 if kind == "mxfp8" else KIND_NVFP4, a, sfa, b, sfb, out,
+                            alpha, m, n, k, ldc=ldc, **kwargs)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(dev)
+    ref = 0.75 * (a_deq @ b_deq.T)
+    got = out[:, :n].float()
+    assert not torch.isnan(got).any()
+    if ldc > n:
+        assert torch.isnan(out[:, n:].float()).all(), "wrote past column N"
+    scale = float(ref.abs().max())
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -20}[dtype]
+    err = float((got - ref).abs().max())
+    assert err <= (eps + 2.0 ** -16) * scale + 1e-30, (err, scale)
+
+
+def _block_fp8_cases():
+    rng = np.random.default_rng(77)
+    cases = []
+    for i in range(16):
+        m = int(rng.choice([1, 5, 64, 128, 129, 255, 256, 300, 513]))
+        n = int(rng.choice([128, 256, 384, 640, 1152]))
+        k = 128 * int(rng.integers(1, 10))
+        dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
+        cases.append((i, m, n, k, dtype))
+    return cases
+
+
+@pytest.mark.parametrize("index,m,n,k,dtype", _block_fp8_cases())
+def test_block_fp8_gemm_matches_fp32_reference_on_random_shapes(index, m, n, k, dtype):
+    from sparkinfer_b200._lib import launch
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(5000 + index)
+    a = torch.randint(0, 256, (m, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    b = torch.randint(0, 256, (n, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    sa = torch.rand((m, k // 128), device=dev, generator=gen) + 0.25
+    sb = torch.rand((n // 128, k // 128), device=dev, generator=gen) + 0.25
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=dev)
+    launch.gemm_block_fp8(a, sa, b, sb, out, None, m, n, k)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(dev)
+    a_deq = a.view(torch.float8_e4m3fn).float() * sa.repeat_interleave(128, dim=1)
+    b_deq = b.view(torch.float8_e4m3fn).float() * sb.repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+    ref = a_deq @ b_deq.T
+    got = out.float()
+    assert not torch.isnan(got).any()
+    scale = float(ref.abs().max())
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -20}[dtype]
+    assert float((got - ref).abs().max()) <= (eps + 2.0 ** -16) * scale + 1e-30
