@@ -141,23 +141,26 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const uint32_t buf = it & 1;
-        if (!mbar_wait_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag) ||
-            !mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+        // The operands are normally there long before the TMEM buffer is handed back; wait for
+        // them first and have the descriptors ready, so that nothing but the issue itself
+        // follows the hand-over (which is on the critical path).
+        const uint32_t st = smem_u32 + stage * T::kStageBytes;
+        const uint64_t adesc = make_kmajor_sw128_desc(st);
+        const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag) ||
+            !mbar_wait_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t st = smem_u32 + stage * T::kStageBytes;
         if (elect_one()) {
-          const uint64_t adesc = make_kmajor_sw128_desc(st);
-          const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             tc_mma_f8(buf * T::BN, adesc + 2 * j, bdesc + 2 * j, idesc, j > 0 ? 1u : 0u);
-          tc_commit(&empty_bar[stage]);
           tc_commit(&part_full_bar[buf]);
+          tc_commit(&empty_bar[stage]);
         }
         __syncwarp();
         if (++stage == T::kStages) { stage = 0; phase ^= 1; }
@@ -205,14 +208,19 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int c = 0; c < kCols / 16; ++c) {
           tmem_load_wait();
-          if (c + 1 < kCols / 16) tmem_load_16cols(taddr + (c + 1) * 16, raw[(c + 1) & 1]);
+          if (c + 1 < kCols / 16) {
+            tmem_load_16cols(taddr + (c + 1) * 16, raw[(c + 1) & 1]);
+          } else {
+            // Everything of this buffer is in registers: give it back to the MMA warp before
+            // the last chunk is accumulated (the hand-over is on the critical path).
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&part_empty_bar[buf]);
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             acc[c * 16 + i] = fmaf(__uint_as_float(raw[c & 1][i]), scale, acc[c * 16 + i]);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&part_empty_bar[buf]);
       }
       if (!ok) break;
       if (p.use_tma_store) {
