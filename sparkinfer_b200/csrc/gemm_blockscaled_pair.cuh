@@ -314,7 +314,15 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int cc = 0; cc < 4; ++cc) {
             if (cc < 4) {
               tmem_load_wait();
-              if (cc + 1 < 4) tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
+              if (cc + 1 < 4) {
+                tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
+              } else if (pass == kPasses - 1) {
+                // The whole accumulator is in registers or staged: hand tensor memory back to
+                // the leader's MMA warp now, before the last chunk is converted and stored.
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+              }
               const uint32_t(&cur)[32] = raw[cc & 1];
               uint32_t packed[16];
               if (p.out_dtype == kOutBf16) {
@@ -338,11 +346,6 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                     packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
               }
             }
-          }
-          if (pass == kPasses - 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
           }
           fence_proxy_async_smem();
           epilogue_bar_sync();
