@@ -298,54 +298,40 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const uint32_t acc_empty_leader = map_to_cta(smem_addr_u32(&acc_empty_bar[acc]), 0);
       if (p.use_tma_store) {
-        constexpr int kPasses = (BN + 127) / 128;
+        // With one CTA per SM and 224 threads a thread may hold ~250 registers, enough for half
+        // of its accumulator row raw (128 columns) plus the other half already converted. So
+        // tensor memory is emptied with eight back-to-back loads in two groups and handed back
+        // to the MMA warp before anything is staged or stored: the next tile's MMAs wait for
+        // a few hundred cycles instead of the whole drain.
+        static_assert(BN == 256, "the register-resident drain is written for 256 columns");
         const bool store_thread = (threadIdx.x == 64);
-#pragma unroll 1
-        for (int pass = 0; pass < kPasses; ++pass) {
+        uint32_t raw[4][32];
+        uint32_t packed[64];
+        auto convert = [&]() {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float lo = __uint_as_float(raw[cc][2 * i]) * alpha;
+              const float hi = __uint_as_float(raw[cc][2 * i + 1]) * alpha;
+              packed[cc * 16 + i] =
+                  (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+            }
+          }
+        };
+        // Stages the 128 converted columns (two sub-tiles of 64 columns = 128-byte rows; 16-byte
+        // chunk j of row r at position j ^ (r % 8), the 128-byte-swizzled layout) and stores them.
+        auto stage_and_store = [&](int pass) {
           if (store_pending) {
             if (store_thread) tma_store_wait_read<0>();
             epilogue_bar_sync();
-            store_pending = false;
           }
-          // The TMEM load of chunk cc+1 is in flight while chunk cc is converted and staged.
-          uint32_t raw[2][32];
-          tmem_load_32cols(taddr + pass * 128, raw[0]);
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            if (cc < 4) {
-              tmem_load_wait();
-              if (cc + 1 < 4) {
-                tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
-              } else if (pass == kPasses - 1) {
-                // The whole accumulator is in registers or staged: hand tensor memory back to
-                // the leader's MMA warp now, before the last chunk is converted and stored.
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-              }
-              const uint32_t(&cur)[32] = raw[cc & 1];
-              uint32_t packed[16];
-              if (p.out_dtype == kOutBf16) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  packed[i] = pack_bf16x2(__uint_as_float(cur[2 * i]) * alpha,
-                                          __uint_as_float(cur[2 * i + 1]) * alpha);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  packed[i] = pack_f16x2(__uint_as_float(cur[2 * i]) * alpha,
-                                         __uint_as_float(cur[2 * i + 1]) * alpha);
-              }
-              // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
-              // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
-              uint8_t* sub = c_stage + (cc >> 1) * (128 * 128) + row_in_tile * 128;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int j = ((cc & 1) * 4 + i) ^ (row_in_tile & 7);
-                *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
-                    packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-              }
-            }
+          for (int q = 0; q < 16; ++q) {  // q = 16-byte chunk of the 256-byte half row
+            uint8_t* sub = c_stage + (q >> 3) * (128 * 128) + row_in_tile * 128;
+            const int j = (q & 7) ^ (row_in_tile & 7);
+            *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
+                packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
           }
           fence_proxy_async_smem();
           epilogue_bar_sync();
@@ -357,7 +343,20 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             tma_store_commit();
           }
           store_pending = true;
-        }
+        };
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + cc * 32, raw[cc]);
+        tmem_load_wait();
+        convert();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + 128 + cc * 32, raw[cc]);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        stage_and_store(0);
+        convert();
+        stage_and_store(1);
         continue;
       }
 #pragma unroll 1
