@@ -307,16 +307,13 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool store_thread = (threadIdx.x == 64);
         uint32_t raw[4][32];
         uint32_t packed[64];
-        auto convert = [&]() {
+        auto convert_chunk = [&](int cc) {
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float lo = __uint_as_float(raw[cc][2 * i]) * alpha;
-              const float hi = __uint_as_float(raw[cc][2 * i + 1]) * alpha;
-              packed[cc * 16 + i] =
-                  (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
-            }
+          for (int i = 0; i < 16; ++i) {
+            const float lo = __uint_as_float(raw[cc][2 * i]) * alpha;
+            const float hi = __uint_as_float(raw[cc][2 * i + 1]) * alpha;
+            packed[cc * 16 + i] =
+                (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           }
         };
         // Stages the 128 converted columns (two sub-tiles of 64 columns = 128-byte rows; 16-byte
@@ -347,15 +344,20 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + cc * 32, raw[cc]);
         tmem_load_wait();
-        convert();
+        // Each chunk of the first half is converted and its registers are refilled at once with
+        // the matching chunk of the second half, so those loads run under the conversion.
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + 128 + cc * 32, raw[cc]);
+        for (int cc = 0; cc < 4; ++cc) {
+          convert_chunk(cc);
+          tmem_load_32cols(taddr + 128 + cc * 32, raw[cc]);
+        }
         tmem_load_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         stage_and_store(0);
-        convert();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) convert_chunk(cc);
         stage_and_store(1);
         continue;
       }
