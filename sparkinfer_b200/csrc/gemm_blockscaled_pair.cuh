@@ -13,8 +13,9 @@
 //   relay (peer, warp 1) : wait own full[s]  -> arrive on the leader's peer_full[s]
 //   issuer (leader, w 1) : wait own full[s] and peer_full[s] -> scale copies + 4 MMAs for the
 //                          pair -> tcgen05.commit to empty[s] of both CTAs (two commits)
-//   epilogue (each CTA)  : wait own acc_full (committed by the leader to both CTAs) -> drain own
-//                          128 rows from tensor memory -> arrive on the leader's acc_empty
+//   epilogue (each CTA)  : wait own acc_full (committed by the leader to both CTAs) -> pull own
+//                          128 x 256 accumulator into registers -> arrive on the leader's
+//                          acc_empty -> convert, stage in swizzled shared memory, TMA store
 #pragma once
 
 #include "gemm_blockscaled.cuh"
