@@ -236,3 +236,30 @@ def test_weight_packers_match_reference_fixture(monkeypatch, idx):
                           g[f"scale_rows{idx}"])
     physical = rows.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous().view(torch.uint8)
     assert np.array_equal(physical.numpy().reshape(-1), g[f"scale_mma{idx}"])
+
+
+def test_tensor_fp8_linear_fake_op_and_host_validation():
+    """The per-tensor FP8 linear's custom op has a fake (meta) implementation, and its host
+    checks fire before anything touches a GPU (tests/gemm/test_tensor_fp8_linear.py and the
+    argument checks of b12x/gemm/tensor_fp8_linear/_kernel.py:120-150, 232-268)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from sparkinfer_b200.gemm import tensor_fp8_linear
+    from sparkinfer_b200.gemm.tensor_fp8_linear import _kernel  # noqa: F401  (registers the op)
+
+    with FakeTensorMode():
+        src = torch.empty((5, 160), dtype=torch.float8_e4m3fn)
+        w = torch.empty((40, 256), dtype=torch.float8_e4m3fn)
+        smma = torch.empty((32, 4, 1, 4, 2, 1), dtype=torch.float8_e8m0fnu)
+        scale = torch.empty(1)
+        out = torch.ops.b12x.tensor_fp8_linear_fused(src, w, smma, scale, 256, 40, 5,
+                                                     torch.float16, None)
+        assert out.shape == (5, 40) and out.dtype == torch.float16
+
+    w_cpu = torch.zeros((64, 128), dtype=torch.float8_e4m3fn)
+    with pytest.raises((ValueError, TypeError)):
+        tensor_fp8_linear.pack_weight(w_cpu, torch.ones(1))  # CPU tensors are refused
+    with pytest.raises(ValueError, match="CUDA"):
+        tensor_fp8_linear.mm(w_cpu, object())  # the device check comes first, as in the reference
+    assert isinstance(tensor_fp8_linear.is_supported(), bool)
+    assert "tensor_fp8_linear" in {m.name for m in __import__("sparkinfer_b200").list_ops()}
