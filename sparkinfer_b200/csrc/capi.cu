@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "gemm_blockscaled.cuh"
@@ -145,7 +146,7 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
   using T = GemmTile<KIND, BN>;
   // The large dynamic shared memory opt-in is per device: set it the first time each device
   // launches this instantiation.
-  static bool set_for[64] = {};
+  static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
@@ -168,7 +169,7 @@ template <int KIND, int BN>
 int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
                      const GemmParams& p, int pairs, cudaStream_t stream) {
   using T = PairTile<KIND, BN>;
-  static bool set_for[64] = {};
+  static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
@@ -419,7 +420,7 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   p.group_m = 16;
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
-  static bool set_for[64] = {};
+  static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
@@ -514,7 +515,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
 template <int KIND>
 int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
                   int grid, int smem_bytes, cudaStream_t stream) {
-  static bool set_for[64] = {};
+  static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
