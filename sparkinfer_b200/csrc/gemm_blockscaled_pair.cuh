@@ -43,7 +43,7 @@ struct PairTile {
   static constexpr int kAccStages = (2 * BN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
   static constexpr int kSfaCol0 = kAccStages * BN;
   static constexpr int kSfbCol0 = kSfaCol0 + kSfaCols;
-  static constexpr int kCStageBytes = 128 * 128 * 2;
+  static constexpr int kCStageBytes = 128 * 64 * 2;          // one 64-column output sub-tile
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kStagesRaw =
       (227 * 1024 - kBarrierBytes - 1024 - kCStageBytes) / kStageBytes;
@@ -317,30 +317,35 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                 (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           }
         };
-        // Stages the 128 converted columns (two sub-tiles of 64 columns = 128-byte rows; 16-byte
-        // chunk j of row r at position j ^ (r % 8), the 128-byte-swizzled layout) and stores them.
+        // Stages the 128 converted columns as two sub-tiles of 64 columns (128-byte rows; 16-byte
+        // chunk j of row r at position j ^ (r % 8), the 128-byte-swizzled layout) through one
+        // 16 KiB slot, one TMA store each. Tensor memory has been released by now, so the waits
+        // for the previous store to have read the slot are off the critical path, and the small
+        // slot leaves room for one more pipeline stage.
         auto stage_and_store = [&](int pass) {
-          if (store_pending) {
-            if (store_thread) tma_store_wait_read<0>();
-            epilogue_bar_sync();
-          }
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {  // q = 16-byte chunk of the 256-byte half row
-            uint8_t* sub = c_stage + (q >> 3) * (128 * 128) + row_in_tile * 128;
-            const int j = (q & 7) ^ (row_in_tile & 7);
-            *reinterpret_cast<uint4*>(sub + j * 16) = make_uint4(
-                packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-          }
-          fence_proxy_async_smem();
-          epilogue_bar_sync();
-          if (store_thread) {
-            for (int sub = 0; sub < 2; ++sub) {
-              const int col = tn * BN + pass * 128 + sub * 64;
-              if (col < p.n && m0 < p.m) tma_store_2d(&map_c, c_stage + sub * (128 * 128), col, m0);
+          for (int sub = 0; sub < 2; ++sub) {
+            if (store_pending) {
+              if (store_thread) tma_store_wait_read<0>();
+              epilogue_bar_sync();
             }
-            tma_store_commit();
+            uint8_t* row_ptr = c_stage + row_in_tile * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int j = q ^ (row_in_tile & 7);
+              const int w = (sub * 8 + q) * 4;
+              *reinterpret_cast<uint4*>(row_ptr + j * 16) =
+                  make_uint4(packed[w], packed[w + 1], packed[w + 2], packed[w + 3]);
+            }
+            fence_proxy_async_smem();
+            epilogue_bar_sync();
+            if (store_thread) {
+              const int col = tn * BN + pass * 128 + sub * 64;
+              if (col < p.n && m0 < p.m) tma_store_2d(&map_c, c_stage, col, m0);
+              tma_store_commit();
+            }
+            store_pending = true;
           }
-          store_pending = true;
         };
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + cc * 32, raw[cc]);
