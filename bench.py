@@ -44,9 +44,9 @@ L2_FLUSH_BYTES = 256 << 20
 NCU_TRAFFIC_BYTES = {
     "cfg0_nvfp4_128x4096x4096": 9_763_584 + 0,
     "cfg1_nvfp4_decode_m16": 33_144_832 + 0,
-    "cfg2_mxfp8_prefill": 268_367_872 + 97_345_024,
+    "cfg2_mxfp8_prefill": 268_549_632 + 98_470_400,
     "cfg3_block_fp8_colpar": 297_408_768 + 129_085_696,
-    "cfg4_nvfp4_rowpar": 205_184_512 + 43_986_432,
+    "cfg4_nvfp4_rowpar": 205_381_120 + 43_779_584,
 }
 
 
