@@ -7,9 +7,14 @@ One JSON line on stdout (rank 0). A step is one pass of the hot path over one ba
 seeded synthetic operands of the named configuration. Timing: CUDA events on the launching
 stream around every step, L2 flushed (a 256 MiB fill) between steps, max over ranks.
 
-Workloads (the reference's configurations; seeds 42 + 1000*cfg + {0: A, 1: B}):
+Operands are generated on the CPU (torch.Generator, seeds 42 + 1000*cfg + {0: A, 1: B}, FP32
+randn cast to BF16) so that the GPU arm, the CPU arm (`--impl reference`, `cpu_baseline`) and
+the oracle parity check in the line all see the same bits.
+
+Workloads (the reference's configurations):
   cfg0_nvfp4_128x4096x4096         NVFP4 x NVFP4, BF16 out (pre-quantized operands)
   cfg1_nvfp4_decode_m{1,4,16,64}   activation quantize_rows + NVFP4 GEMM, N=14336 K=4096
+  cfg1_nvfp4_decode_m{1,4,16}_fused  the same step as one kernel (quantizer fused in)
   cfg2_mxfp8_prefill               quantize_rows + MXFP8 GEMM, 8192 x 7168 x 7168
   cfg3_block_fp8_colpar            E4M3 + FP32 block scales, 4096 x 18432 x 7168, N / gpus
   cfg4_nvfp4_rowpar                quantize_rows + NVFP4 GEMM + BF16 all-reduce,
@@ -76,6 +81,9 @@ def workload_table() -> dict:
     for m in (1, 4, 16, 64):
         t[f"cfg1_nvfp4_decode_m{m}"] = dict(cfg=1, kind="nvfp4", m=m, n=14336, k=4096, quant=True,
                                             shard=None, bound="hbm")
+    for m in (1, 4, 16):
+        t[f"cfg1_nvfp4_decode_m{m}_fused"] = dict(cfg=1, kind="nvfp4", m=m, n=14336, k=4096,
+                                                  quant=True, fused=True, shard=None, bound="hbm")
     return t
 
 
@@ -160,13 +168,24 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-# Synthetic operands (seeded, generated on the device, quantized by this package's ops or,
-# for the block-FP8 recipe that has no quantizer op, by torch at set-up)
+# Synthetic operands (seeded, generated on the CPU, quantized by this package's ops or, for
+# the block-FP8 recipe that has no quantizer op, by torch at set-up)
 # --------------------------------------------------------------------------------------
-def seeded_randn(seed: int, shape, scale: float, device) -> torch.Tensor:
-    gen = torch.Generator(device=device).manual_seed(seed)
-    x = torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
+def seeded_randn_cpu(seed: int, shape, scale: float) -> torch.Tensor:
+    """BF16 [rows, k] from a CPU generator: the first r rows of a larger tensor with the same
+    seed and k are these r rows (the sampler fills in row order), which is what lets the CPU
+    arm work on a leading block of the GPU arm's operands."""
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=gen, dtype=torch.float32)
     return (x * scale).to(torch.bfloat16)
+
+
+def operand_scales(w: dict) -> tuple[float, float]:
+    return 1.0, (0.02 if w["kind"] != "block_fp8" else 1.0)
+
+
+PARITY_ROWS = 16
+PARITY_COLS = 64
 
 
 def block_fp8_quantize(x: torch.Tensor, block_rows: int):
@@ -196,8 +215,18 @@ class Step:
             k_shard = shard_range(k, world, rank)
             self.k_local = k_shard.size
         seed = 42 + 1000 * w["cfg"]
-        x = seeded_randn(seed, (m, k), 1.0, device)
-        wt = seeded_randn(seed + 1, (n, k), 0.02 if w["kind"] != "block_fp8" else 1.0, device)
+        sx, sw = operand_scales(w)
+        x_cpu = seeded_randn_cpu(seed, (m, k), sx)
+        wt_cpu = seeded_randn_cpu(seed + 1, (n, k), sw)
+        # Leading rows of A and the rows of B behind this rank's leading output columns, kept on
+        # the host (full K) for the oracle parity check of the output.
+        n0 = n_shard.begin if n_shard is not None else 0
+        self.parity_x = x_cpu[:min(PARITY_ROWS, m)].clone()
+        self.parity_w = wt_cpu[n0:n0 + min(PARITY_COLS, self.n_local)].clone()
+        self.amax_x = float(x_cpu.float().abs().max())
+        self.amax_w = float(wt_cpu.float().abs().max())
+        x, wt = x_cpu.to(device), wt_cpu.to(device)
+        del x_cpu, wt_cpu
         self.kernels_per_step = 1
         self.h2d_bytes = self.d2h_bytes = 0
         self.group = 1          # consecutive steps captured together (HBM-bound workloads)
@@ -221,7 +250,7 @@ class Step:
         wplan = nvfp4.plan(n, kl)
         wq = nvfp4.allocate_outputs(wplan, device=self.device)
         nvfp4.run(plan=wplan, x=wt, global_scale=gs_w, outputs=wq)
-        self.x, self.gs_x = x, gs_x
+        self.x, self.gs_x, self.gs_w = x, gs_x, gs_w
         self.xplan = nvfp4.plan(m, kl)
         self.xq = nvfp4.allocate_outputs(self.xplan, device=self.device)
         nvfp4.run(plan=self.xplan, x=x, global_scale=gs_x, outputs=self.xq)
@@ -239,11 +268,19 @@ class Step:
             scales = wq.scale_storage if r == 0 else wq.scale_storage.clone()
             rhs_list.append((codes.permute(1, 2, 0),
                              BF16Outputs(codes, scales).scale_mma_view(n, kl)))
-        self.gemms = [(lambda rhs=rhs: blockscaled.mm(lhs, rhs, self.out, **kw)) for rhs in rhs_list]
+        self.fused = bool(self.w.get("fused"))
+        if self.fused:
+            # One kernel per step: the decode GEMM quantizes the BF16 rows itself.
+            self.gemms = [(lambda rhs=rhs: blockscaled.mm_fused_quant_a_nvfp4(
+                self.x, self.gs_x, rhs[0], rhs[1], alpha=self.alpha, out=self.out))
+                for rhs in rhs_list]
+        else:
+            self.gemms = [(lambda rhs=rhs: blockscaled.mm(lhs, rhs, self.out, **kw))
+                          for rhs in rhs_list]
         self.gemm = lambda: [g() for g in self.gemms]
         self.quant = (lambda: nvfp4.run(plan=self.xplan, x=self.x, global_scale=self.gs_x,
-                                        outputs=self.xq)) if self.w["quant"] else None
-        self.kernels_per_step = 2 if self.w["quant"] else 1
+                                        outputs=self.xq)) if (self.w["quant"] and not self.fused) else None
+        self.kernels_per_step = 2 if self.quant is not None else 1
         self.host_in = x.cpu().pin_memory() if self.w["quant"] else None
         self.h2d_bytes = x.numel() * 2 if self.w["quant"] else (
             self.xq.packed_a_storage.numel() + self.xq.scale_storage.numel())
@@ -281,7 +318,7 @@ class Step:
         nl = wt.shape[0]
         a, sa = block_fp8_quantize(x, 1)
         b, sb = block_fp8_quantize(wt, 128)
-        self.a, self.sa = a, sa
+        self.a, self.sa, self.b, self.sb = a, sa, b, sb
         self.out = torch.empty((m, nl, 1), dtype=torch.bfloat16, device=self.device)
         kw = dict(ab_dtype="float8_e4m3fn", sf_dtype="float32", sf_vec_size=128,
                   c_dtype="bfloat16", block_fp8=True)
@@ -309,6 +346,36 @@ class Step:
 
     def flops(self) -> float:
         return 2.0 * self.w["m"] * self.w["n"] * self.w["k"]  # whole job, all ranks
+
+    def parity(self) -> dict:
+        """Leading PARITY_ROWS x PARITY_COLS block of the output of the last step against the
+        oracle (quantize the same BF16 rows on the CPU, dequantize to FP32, matmul). The bar is
+        the path's tolerance, max|err| <= 1e-2 * max|ref|; for row-parallel runs the output is
+        the all-reduced sum of the ranks' BF16 partials and still has to meet it."""
+        from oracle import blockscaled_oracle as O
+
+        rows, cols = self.parity_x.shape[0], self.parity_w.shape[0]
+        got = self.out[:rows, :cols, 0].float().cpu().numpy()
+        xa, wb = self.parity_x.float().numpy(), self.parity_w.float().numpy()
+        if self.w["kind"] == "nvfp4":
+            gsx, gsw = np.float32(self.gs_x.item()), np.float32(self.gs_w.item())
+            ref = (O.dequantize_nvfp4(*O.quantize_nvfp4_rows(xa, gsx), gsx)
+                   @ O.dequantize_nvfp4(*O.quantize_nvfp4_rows(wb, gsw), gsw).T)
+        elif self.w["kind"] == "mxfp8":
+            ref = (O.dequantize_mxfp8(*O.quantize_mxfp8_rows(xa))
+                   @ O.dequantize_mxfp8(*O.quantize_mxfp8_rows(wb)).T)
+        else:
+            # No quantizer op exists for this recipe: the codes and FP32 scales the GEMM consumed
+            # are read back (whole 128-row weight blocks) and multiplied by the oracle.
+            blk = -(-cols // 128)
+            ref = O.gemm_block_fp8(self.a[:rows].view(torch.uint8).cpu().numpy(),
+                                   self.sa[:rows].cpu().numpy(),
+                                   self.b[:blk * 128].view(torch.uint8).cpu().numpy(),
+                                   self.sb[:blk].cpu().numpy())[:, :cols]
+        scale = float(np.abs(ref).max())
+        err = float(np.abs(got - ref).max())
+        return {"max_err": err, "max_ref": scale, "tolerance": 1e-2 * scale,
+                "ok": bool(err <= 1e-2 * scale), "block": f"{rows}x{cols} leading block vs oracle"}
 
 
 # --------------------------------------------------------------------------------------
@@ -352,78 +419,215 @@ def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor, sync_ranks,
     return [b.elapsed_time(e) for b, e in zip(begins, ends)]
 
 
-def cpu_dequant_matmul(w: dict, sample_rows: int, seed: int = 7):
-    """The oracle port of the reference's CPU path (dequantize to FP32, matmul) on a bounded
-    sample: ``sample_rows`` rows of A against min(N, 2048) rows of B at full K. Returns
-    (seconds, flops)."""
-    from oracle import blockscaled_oracle as O
-
-    rng = np.random.RandomState(seed)
-    n = min(w["n"], 2048)
-    k = w["k"]
-    a = rng.standard_normal((sample_rows, k)).astype(np.float32)
-    b = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
-    if w["kind"] == "nvfp4":
-        gsa, gsb = O.nvfp4_global_scale(a), O.nvfp4_global_scale(b)
-        qa, qb = O.quantize_nvfp4_rows(a, gsa), O.quantize_nvfp4_rows(b, gsb)
-        t0 = time.perf_counter()
-        out = O.gemm_nvfp4(*qa, gsa, *qb, gsb)
-    elif w["kind"] == "mxfp8":
-        qa, qb = O.quantize_mxfp8_rows(a), O.quantize_mxfp8_rows(b)
-        t0 = time.perf_counter()
-        out = O.gemm_mxfp8(*qa, *qb)
-    else:
-        qa, qb = O.quantize_block_fp8(a, 1), O.quantize_block_fp8(b, 128)
-        t0 = time.perf_counter()
-        out = O.gemm_block_fp8(*qa, *qb)
-    dt = time.perf_counter() - t0
-    assert np.isfinite(out).all()
-    return dt, 2.0 * sample_rows * n * k
+# --------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU-runnable path (dequantize to FP32, torch.matmul) on a leading
+# block of the workload's own operands, dequantize and matmul timed separately
+# --------------------------------------------------------------------------------------
+E2M1_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
 
 
-def cpu_baseline(w: dict, limit_s: float = 12.0) -> dict:
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    rows = min(w["m"], 256)
-    dt, flops = cpu_dequant_matmul(w, rows)
-    reps, total_t, total_f = 1, dt, flops
-    while total_t < limit_s and reps < 8:
-        dt, flops = cpu_dequant_matmul(w, rows, seed=7 + reps)
-        total_t += dt
-        total_f += flops
-        reps += 1
-    return {"value": total_f / total_t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"{reps} x ({rows} rows of A) x ({min(w['n'], 2048)} rows of B) x K={w['k']}, "
-                      "oracle dequantize-to-FP32 + NumPy matmul (dequantize inside the timed region)"}
+class CpuReference:
+    """Threaded torch restatement of the reference's CPU dequantize-matmul
+    (tests/_reference/helpers.py:324-341, b12x/gemm/_shared/wo_mxfp8.py:1921-1943,
+    tests/gemm/test_gemm_stack.py:98-113) on the first `ra` rows of the workload's A and the
+    first `rb` rows of its B at full K. The quantized sample is built outside the timed region
+    by torch restatements of the oracle's quantizers; both directions are checked against the
+    NumPy oracle on a few rows when the object is built.
+
+    One `step()` times dequantize(A sample), dequantize(B sample) and the FP32 matmul
+    separately. The whole-configuration time is extrapolated by rows:
+        dequant_s = t_dequant_A * M / ra + t_dequant_B * N / rb
+        matmul_s  = t_matmul * (M * N) / (ra * rb)
+    and the reported rate is 2 * M * N * K / (dequant_s + matmul_s)."""
+
+    def __init__(self, w: dict, name: str):
+        from oracle import blockscaled_oracle as O
+
+        self.w, self.name = w, name
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        m, n, k = w["m"], w["n"], w["k"]
+        self.ra, self.rb = min(m, 2048), min(n, 4096)
+        seed = 42 + 1000 * w["cfg"]
+        sx, sw = operand_scales(w)
+        x = seeded_randn_cpu(seed, (self.ra, k), sx).float()
+        wt = seeded_randn_cpu(seed + 1, (self.rb, k), sw).float()
+        kind = w["kind"]
+        if kind == "nvfp4":
+            # The global scales come from the sample's own maxima (the GPU arm derives them from
+            # the whole tensors; timing does not depend on the value).
+            self.gs = [float(448.0 * 6.0 / t.abs().max()) for t in (x, wt)]
+            self.q = [self._quant_nvfp4(t, g) for t, g in zip((x, wt), self.gs)]
+            for (codes, scales), g, t in zip(self.q, self.gs, (x, wt)):
+                pa, sa = O.quantize_nvfp4_rows(t[:4].numpy(), np.float32(g))
+                assert np.array_equal(codes[:4].numpy(), pa) and np.array_equal(
+                    scales[:4].view(torch.uint8).numpy(), sa), "torch NVFP4 quantizer != oracle"
+                assert np.array_equal(self._deq_nvfp4(codes[:4], scales[:4], g).numpy(),
+                                      O.dequantize_nvfp4(pa, sa, np.float32(g)))
+        elif kind == "mxfp8":
+            self.q = [self._quant_mxfp8(t) for t in (x, wt)]
+            for (codes, scales), t in zip(self.q, (x, wt)):
+                va, sr = O.quantize_mxfp8_rows(t[:4].numpy())
+                assert np.array_equal(codes[:4].view(torch.uint8).numpy(), va) and np.array_equal(
+                    scales[:4].numpy(), sr), "torch MXFP8 quantizer != oracle"
+                assert np.array_equal(self._deq_mxfp8(codes[:4], scales[:4]).numpy(),
+                                      O.dequantize_mxfp8(va, sr))
+        else:
+            self.q = [block_fp8_quantize(x, 1), block_fp8_quantize(wt, 128)]
+            a8, sa = self.q[0]
+            b8, sb = self.q[1]
+            ref = O.gemm_block_fp8(a8[:4].view(torch.uint8).numpy(), sa[:4].numpy(),
+                                   b8[:128].view(torch.uint8).numpy(), sb[:1].numpy())
+            mine = self._deq_block_fp8(a8[:4], sa[:4], 1) @ self._deq_block_fp8(b8[:128], sb[:1], 128).T
+            assert np.abs(mine.numpy() - ref).max() <= 1e-5 * np.abs(ref).max(), \
+                "torch block-FP8 dequantize-matmul != oracle"
+
+    # ---- quantizers (set-up only) ----
+    @staticmethod
+    def _quant_nvfp4(x: torch.Tensor, gs: float):
+        r, k = x.shape
+        blocks = x.view(r, k // 16, 16)
+        gs_t = torch.tensor(gs, dtype=torch.float32)
+        s = gs_t * (blocks.abs().amax(-1) / 6.0)
+        s_q = s.to(torch.float8_e4m3fn)
+        t = s_q.float() * (torch.tensor(1.0) / gs_t)
+        inv = torch.where(t == 0, torch.zeros_like(t), 1.0 / t)
+        y = (blocks * inv[:, :, None]).clamp_(-6.0, 6.0)
+        mag = y.abs()
+        bounds = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+        ties_up = (0.75, 1.75, 3.5)  # round-to-nearest-even on the E2M1 grid
+        idx = torch.zeros(mag.shape, dtype=torch.uint8)
+        for b in bounds:
+            idx += (mag >= b).to(torch.uint8) if b in ties_up else (mag > b).to(torch.uint8)
+        codes = (idx | (((y < 0) & (idx > 0)).to(torch.uint8) << 3)).view(r, k // 2, 2)
+        return (codes[..., 0] | (codes[..., 1] << 4)).contiguous(), s_q.contiguous()
+
+    @staticmethod
+    def _quant_mxfp8(x: torch.Tensor):
+        r, k = x.shape
+        blocks = x.view(r, k // 32, 32)
+        amax = blocks.abs().amax(-1)
+        mant, exp = torch.frexp(amax / 448.0)           # v = mant * 2^exp, mant in [0.5, 1)
+        e = torch.where(mant > 0.5, exp, exp - 1).clamp_(-127, 127)
+        byte = torch.where(amax > 0, e + 127, torch.full_like(e, 127)).to(torch.uint8)
+        inv = torch.exp2(127.0 - byte.float())
+        q = (blocks * inv[:, :, None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn)
+        return q.view(r, k).contiguous(), byte.contiguous()
+
+    # ---- dequantizers (timed) ----
+    @staticmethod
+    def _deq_nvfp4(packed: torch.Tensor, scales: torch.Tensor, gs: float) -> torch.Tensor:
+        r, kb = packed.shape
+        lut = torch.tensor(E2M1_VALUES, dtype=torch.float32)
+        vals = torch.stack((lut[(packed & 0xF).long()], lut[(packed >> 4).long()]), dim=-1)
+        # value * scale / global_scale, in that order (tests/_reference/helpers.py:324-341)
+        sf = scales.float()
+        return (vals.view(r, kb * 2 // 16, 16) * sf[:, :, None]
+                / torch.tensor(gs, dtype=torch.float32)).view(r, kb * 2)
+
+    @staticmethod
+    def _deq_mxfp8(codes: torch.Tensor, scale_rows: torch.Tensor) -> torch.Tensor:
+        r, k = codes.shape
+        sf = torch.exp2(scale_rows.float() - 127.0)
+        return (codes.float().view(r, k // 32, 32) * sf[:, :, None]).view(r, k)
+
+    @staticmethod
+    def _deq_block_fp8(codes: torch.Tensor, scale: torch.Tensor, block_rows: int) -> torch.Tensor:
+        r, k = codes.shape
+        return (codes.float().view(r // block_rows, block_rows, k // 128, 128)
+                * scale[:, None, :, None]).view(r, k)
+
+    def _dequant(self, which: int) -> torch.Tensor:
+        kind = self.w["kind"]
+        if kind == "nvfp4":
+            return self._deq_nvfp4(*self.q[which], self.gs[which])
+        if kind == "mxfp8":
+            return self._deq_mxfp8(*self.q[which])
+        return self._deq_block_fp8(*self.q[which], 1 if which == 0 else 128)
+
+    def step(self) -> dict:
+        t0 = time.perf_counter()
+        a = self._dequant(0)
+        t1 = time.perf_counter()
+        b = self._dequant(1)
+        t2 = time.perf_counter()
+        out = a @ b.T
+        t3 = time.perf_counter()
+        assert bool(torch.isfinite(out).all())
+        m, n, k = self.w["m"], self.w["n"], self.w["k"]
+        dequant_s = (t1 - t0) * m / self.ra + (t2 - t1) * n / self.rb
+        matmul_s = (t3 - t2) * (m * n) / (self.ra * self.rb)
+        return {"dequant_s": dequant_s, "matmul_s": matmul_s, "sample_s": t3 - t0,
+                "matmul_sample_tflops": 2.0 * self.ra * self.rb * k / (t3 - t2) / 1e12,
+                "tflops": 2.0 * m * n * k / (dequant_s + matmul_s) / 1e12}
+
+    def describe(self, reps: int) -> str:
+        return (f"{reps} x [rows 0..{self.ra - 1} of A, rows 0..{self.rb - 1} of B, K={self.w['k']} of "
+                f"the {self.name} operands (same seeds as the GPU arm)]: torch dequantize-to-FP32 of "
+                f"each, then FP32 torch.matmul, on {self.cores} threads, timed separately; whole "
+                "configuration = t_deqA*M/ra + t_deqB*N/rb + t_mm*M*N/(ra*rb)")
+
+
+def cpu_baseline(w: dict, name: str, limit_s: float = 12.0, max_reps: int = 8) -> dict:
+    ref = CpuReference(w, name)
+    ref.step()  # warm-up (thread pool, page faults)
+    runs, spent = [], 0.0
+    while len(runs) < max_reps and (spent < limit_s or not runs):
+        r = ref.step()
+        runs.append(r)
+        spent += r["sample_s"]
+    return {"value": float(np.mean([r["tflops"] for r in runs])), "unit": "TFLOP/s",
+            "cores": ref.cores, "kind": "port",
+            "dequant_s": float(np.mean([r["dequant_s"] for r in runs])),
+            "matmul_s": float(np.mean([r["matmul_s"] for r in runs])),
+            "matmul_sample_tflops": float(np.mean([r["matmul_sample_tflops"] for r in runs])),
+            "sample": ref.describe(len(runs))}
+
+
+def config_dict(name: str, w: dict, world: int, steps: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    group = replicas_for(w, steps)
+    return {"workload": name, "m": w["m"], "n": w["n"], "k": w["k"],
+            "sharding": {"n": "column-parallel N/gpus, no communication",
+                         "k": "row-parallel K/gpus + NCCL BF16 all-reduce",
+                         None: "single GPU"}[w["shard"]],
+            "step": ("activation quantize_rows + " if w["quant"] else "") + "GEMM"
+                    + (" (one fused kernel)" if w.get("fused") else "")
+                    + (" + all-reduce" if w["shard"] == "k" and world > 1 else ""),
+            "l2": ("256 MiB fill between timed steps" if group == 1 else
+                   f"{group} rotating weight copies per graph replay (larger than "
+                   "L2 together) + 256 MiB fill between replays")}
+
+
+DTYPE_TEXT = {"nvfp4": "fp4_e2m1 x ue4m3 -> f32", "mxfp8": "fp8_e4m3 x ue8m0 -> f32",
+              "block_fp8": "fp8_e4m3 x f32 scales -> f32"}
 
 
 # --------------------------------------------------------------------------------------
 # Main
 # --------------------------------------------------------------------------------------
-def run_reference_arm(args, w: dict, name: str, rank: int) -> None:
+def run_reference_arm(args, w: dict, name: str, rank: int, world: int) -> None:
+    """`--impl reference`: the CPU path alone, on rank 0's host cores."""
     if rank != 0:
         return
-    vals = []
-    for _ in range(args.warmup):
-        cpu_dequant_matmul(w, min(w["m"], 256))
-    t_all = 0.0
-    for i in range(args.steps):
-        dt, flops = cpu_dequant_matmul(w, min(w["m"], 256), seed=100 + i)
-        vals.append(flops / dt / 1e12)
-        t_all += dt
-    value = float(np.mean(vals))
-    cores = os.cpu_count() or 1
-    sample = (f"each step: {min(w['m'], 256)} rows of A x {min(w['n'], 2048)} rows of B x "
-              f"K={w['k']} of the {name} operands, oracle port of the reference's CPU "
-              "dequantize-matmul")
+    ref = CpuReference(w, name)
+    for _ in range(max(args.warmup, 1)):
+        ref.step()
+    runs = [ref.step() for _ in range(max(args.steps, 1))]
+    value = float(np.mean([r["tflops"] for r in runs]))
+    dequant_s = float(np.mean([r["dequant_s"] for r in runs]))
+    matmul_s = float(np.mean([r["matmul_s"] for r in runs]))
     print(json.dumps({
         "impl": "reference", "metric": "block-scaled GEMM TFLOPS", "value": value,
         "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": t_all / max(args.steps, 1) * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": w["kind"], "data": "synthetic",
-        "config": {"workload": name, "m": w["m"], "n": w["n"], "k": w["k"]},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+        "ms_per_step": (dequant_s + matmul_s) * 1e3, "higher_is_better": True,
+        "scaling": "strong" if w["shard"] else "weak", "vs_baseline": None,
+        "dtype": DTYPE_TEXT[w["kind"]], "data": "synthetic",
+        "config": config_dict(name, w, world, args.steps),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": ref.cores, "kind": "port",
+                         "dequant_s": dequant_s, "matmul_s": matmul_s,
+                         "matmul_sample_tflops": float(np.mean([r["matmul_sample_tflops"] for r in runs])),
+                         "sample": ref.describe(len(runs))},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
@@ -483,6 +687,21 @@ def measure_e2e(step: Step, args, flush, sync_ranks, reduce_max) -> float:
     return reduce_max(float(np.mean(times)))
 
 
+def time_components(step: Step, flush, sync_ranks, reduce_max) -> dict:
+    """Device time of each part of a step, each timed alone (graph replays, L2 flushed)."""
+    out = {}
+    reps = max(1, 20 // step.group)
+    out["gemm_ms"] = reduce_max(float(np.mean(time_steps(step.gemm, reps, 3, flush, sync_ranks)))) / step.group
+    if step.quant is not None:
+        out["quant_ms"] = reduce_max(float(np.mean(time_steps(step.quant, 20, 3, flush, sync_ranks))))
+    if step.w["shard"] == "k" and step.world > 1:
+        import torch.distributed as dist
+
+        out["allreduce_ms"] = reduce_max(float(np.mean(
+            time_steps(lambda: dist.all_reduce(step.out), 20, 3, flush, sync_ranks, use_graph=False))))
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -503,7 +722,7 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
     if args.impl == "reference":
-        run_reference_arm(args, w, args.workload, rank)
+        run_reference_arm(args, w, args.workload, rank, world)
         return
 
     if not torch.cuda.is_available():
@@ -528,16 +747,26 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def parity_over_ranks(step: Step) -> dict:
+        step.run()
+        torch.cuda.synchronize()
+        par = step.parity()
+        par["max_err"] = reduce_max(par["max_err"])
+        par["ok"] = bool(par["max_err"] <= par["tolerance"])
+        return par
+
     peaks = measured_peaks()
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     step = Step(args.workload, w, rank, world, device, replicas=replicas_for(w, args.steps))
     step.run()
     sync_ranks()
+    parity = parity_over_ranks(step)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms_per_step, gemm_ms, _ = measure(step, args, flush, sync_ranks, reduce_max)
     clocks = sampler.stop() if sampler else None
     e2e_ms = measure_e2e(step, args, flush, sync_ranks, reduce_max)
+    h2d_d2h = (step.h2d_bytes, step.d2h_bytes)
 
     from sparkinfer_b200._lib.launch import check_kernel_status
 
@@ -564,53 +793,57 @@ def main() -> None:
                     "frac_of_nominal": achieved / NOMINAL["hbm_gbs"], "kernel_ms": gemm_ms,
                     "algorithmic_bytes": bytes_local}
 
+    # Every other configuration, timed the same way. On several GPUs only the configurations
+    # that shard are run (column-parallel and row-parallel), so that a scaling run records both.
     extra = {}
-    if world == 1 and not args.no_extra:
+    if not args.no_extra:
+        del step
+        torch.cuda.empty_cache()
         for name, other in table.items():
-            if name == args.workload:
+            if name == args.workload or (world > 1 and not other["shard"]):
                 continue
             try:
-                s = Step(name, other, 0, 1, device, replicas=replicas_for(other, 24))
-                s.run()
-                torch.cuda.synchronize()
-                t_all = float(np.mean(time_steps(s.run, max(1, 24 // s.group), 3, flush, sync_ranks))) / s.group
-                t_gemm = float(np.mean(time_steps(s.gemm, max(1, 24 // s.group), 3, flush, sync_ranks))) / s.group
+                s = Step(name, other, rank, world, device, replicas=replicas_for(other, 24))
+                par = parity_over_ranks(s)
+                reps = max(1, 24 // s.group)
+                t_all = reduce_max(float(np.mean(time_steps(s.run, reps, 3, flush, sync_ranks)))) / s.group
+                parts = time_components(s, flush, sync_ranks, reduce_max)
+                n_loc, k_loc = s.n_local, s.k_local
                 extra[name] = {
-                    "ms_per_step": t_all, "gemm_ms": t_gemm,
-                    "tflops": 2.0 * other["m"] * other["n"] * other["k"] / t_gemm / 1e9,
-                    "gbs": algorithmic_bytes(other, other["n"], other["k"]) / t_gemm / 1e6,
+                    "ms_per_step": t_all, **parts,
+                    "tflops": 2.0 * other["m"] * other["n"] * other["k"] / t_all / 1e9,
+                    "gemm_tflops_per_gpu": 2.0 * other["m"] * n_loc * k_loc / parts["gemm_ms"] / 1e9,
+                    "gbs": algorithmic_bytes(other, n_loc, k_loc) / parts["gemm_ms"] / 1e6,
+                    "parity_max_err": par["max_err"], "parity_tolerance": par["tolerance"],
+                    "parity_ok": par["ok"],
                 }
                 del s
                 torch.cuda.empty_cache()
             except Exception as exc:  # keep the headline line even if a side config fails
                 extra[name] = {"error": str(exc)[:160]}
+        check_kernel_status(device)
 
     if rank == 0:
-        baseline = cpu_baseline(w) if world == 1 else None
-        value = step.flops() / ms_per_step / 1e9
+        baseline = cpu_baseline(w, args.workload) if world == 1 else None
+        flops = 2.0 * w["m"] * w["n"] * w["k"]
+        value = flops / ms_per_step / 1e9
+        group = replicas_for(w, args.steps)
+        kernels_per_step = 2 if (w["quant"] and not w.get("fused")) else 1
         line = {
             "metric": "block-scaled GEMM TFLOPS", "value": value, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": max(1, args.steps // step.group) * step.group,
+            "n_gpus": world, "steps": max(1, args.steps // group) * group,
             "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if w["shard"] else "weak", "vs_baseline": None,
-            "dtype": {"nvfp4": "fp4_e2m1 x ue4m3 -> f32", "mxfp8": "fp8_e4m3 x ue8m0 -> f32",
-                      "block_fp8": "fp8_e4m3 x f32 scales -> f32"}[w["kind"]],
+            "dtype": DTYPE_TEXT[w["kind"]],
             "data": "synthetic",
-            "config": {"workload": args.workload, "m": w["m"], "n": w["n"], "k": w["k"],
-                       "sharding": {"n": "column-parallel N/gpus, no communication",
-                                    "k": "row-parallel K/gpus + NCCL BF16 all-reduce",
-                                    None: "single GPU"}[w["shard"]],
-                       "step": ("activation quantize_rows + " if w["quant"] else "") + "GEMM"
-                               + (" + all-reduce" if w["shard"] == "k" and world > 1 else ""),
-                       "l2": ("256 MiB fill between timed steps" if step.group == 1 else
-                              f"{step.group} rotating weight copies per graph replay (larger than "
-                              "L2 together) + 256 MiB fill between replays")},
+            "config": config_dict(args.workload, w, world, args.steps),
             "roofline": roofline,
-            "e2e": {"value": step.flops() / e2e_ms / 1e9, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes,
+            "parity": parity,
+            "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d_d2h[0], "d2h_bytes_per_step": h2d_d2h[1],
                     "ms_per_step": e2e_ms},
-            "gpu_launches": (max(1, args.steps // step.group) * step.group * step.kernels_per_step),
+            "gpu_launches": max(1, args.steps // group) * group * kernels_per_step,
             "clocks": clocks,
             "pct_of_nominal_peak": 100.0 * value / world / nominal_tensor,
         }

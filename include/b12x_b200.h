@@ -48,6 +48,12 @@ enum {
   B12X_B200_FP32 = 2
 };
 
+/*
+ * Value of `block_n` that sends b12x_b200_gemm_blockscaled to the CTA-pair kernel (two SMs per
+ * 256 x 256 tile) whatever the problem size; 0 lets the library choose between the kernels.
+ */
+#define B12X_B200_BLOCK_N_PAIR (-256)
+
 /* Library identification: "b12x_b200 <version> sm_100a". */
 const char* b12x_b200_version(void);
 
@@ -65,7 +71,8 @@ const char* b12x_b200_last_error(void);
  *   sfb    scale atoms of B: ceil(N/128) x the same
  *   c      [M, ldc] output of c_dtype
  *   alpha  device FP32 scalar read by the kernel at run time, or NULL for 1
- *   block_n 0 = choose, else one of 64, 128, 192, 256
+ *   block_n 0 = choose, else one of 64, 128, 192, 256 (single-CTA tile width) or
+ *          B12X_B200_BLOCK_N_PAIR
  *   sm_count 0 = all SMs of the current device
  *   status device int32 the kernel raises to a non-zero KernelStatus when a bounded wait
  *          ran out; may be NULL
@@ -90,12 +97,15 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
  *              zero, so one buffer serves any sequence of shapes. Launches on different
  *              streams that share a workspace must not overlap on the device.
  *
- * Ordering on one stream. The kernel is launched with programmatic stream serialization: a
- * decode GEMM may start while the decode GEMM launched just before it on the same stream is
- * still running. It reads x, sf_x and alpha and writes c and the workspace only after that
- * predecessor has completed, but it starts streaming w and sf_w at once; w and sf_w must
- * therefore not be outputs of the immediately preceding decode GEMM on the stream. Work of any
- * other kind before it on the stream is ordered as usual.
+ * Ordering on one stream. The kernel is launched with programmatic stream serialization: it
+ * may start while the kernel launched just before it on the same stream is still running, if
+ * that kernel releases its dependents early. In this library the decode GEMMs do, and the row
+ * quantizers do for matrices of at most 128 rows. The decode GEMM reads x, sf_x and alpha and
+ * writes c and the workspace only after its predecessor has completed. A weight of more than
+ * 128 rows is streamed at once (no kernel of this library that releases early can have written
+ * it); a weight of 128 rows or fewer is streamed after the predecessor has completed, like the
+ * other operands. A foreign kernel that releases its dependents early (griddepcontrol /
+ * cudaTriggerProgrammaticLaunchCompletion) must not be the writer of w or sf_w.
  */
 int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
                                               int sm_count);
@@ -104,6 +114,41 @@ int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
                                       int64_t m, int64_t n, int64_t k, int64_t ldc,
                                       void* workspace, int64_t workspace_bytes, int sm_count,
                                       int* status, b12x_b200_stream_t stream);
+
+/*
+ * Decode-shape GEMM with the activation quantizer fused in (1 <= M <= 16): the BF16 rows are
+ * quantized inside the GEMM kernel by dedicated warps, with the arithmetic of
+ * b12x_b200_quantize_mxfp8_rows / b12x_b200_quantize_nvfp4_rows, so the result equals, bit for
+ * bit, quantizing the rows and calling b12x_b200_gemm_blockscaled_smallm. Replaces
+ * dense_gemm_fused_quant_a (b12x/_lib/dense_gemm.py:6897-7051; producer-warp quantizer
+ * :3443-3726), which the reference has for MXFP8 and M <= 8; the NVFP4 recipe is an addition.
+ *
+ *   x_bf16          [M, ld_x] BF16 rows, 16-byte aligned, ld_x % 8 == 0
+ *   x_global_scale  NVFP4: device FP32 scalar (448 * 6 / amax), read at run time; MXFP8: NULL
+ *   workspace       as for b12x_b200_gemm_blockscaled_smallm (same size query)
+ * Other arguments and stream ordering as for b12x_b200_gemm_blockscaled_smallm.
+ */
+int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x,
+                                      const float* x_global_scale, const void* w,
+                                      const void* sf_w, void* c, int c_dtype, const float* alpha,
+                                      int64_t m, int64_t n, int64_t k, int64_t ldc,
+                                      void* workspace, int64_t workspace_bytes, int sm_count,
+                                      int* status, b12x_b200_stream_t stream);
+
+/*
+ * b12x_b200_gemm_blockscaled_smallm that also records, per CTA, eight 64-bit values in
+ * `stamps` (global-timer nanoseconds at entry, after set-up, after the dependency wait, at the
+ * first full pipeline stage, at the last finished accumulator and at the end of the epilogue,
+ * then the SM id and a spare). For the timeline summaries of the decode GEMM; it has no
+ * counterpart in the reference. stamps_len (in 64-bit words) must be at least 8 x the grid
+ * size, for which 8 x the SM count always suffices.
+ */
+int b12x_b200_gemm_smallm_timeline(int kind, const void* x, const void* sf_x, const void* w,
+                                   const void* sf_w, void* c, int c_dtype, const float* alpha,
+                                   int64_t m, int64_t n, int64_t k, int64_t ldc, void* workspace,
+                                   int64_t workspace_bytes, int sm_count,
+                                   unsigned long long* stamps, int64_t stamps_len, int* status,
+                                   b12x_b200_stream_t stream);
 
 /*
  * b12x_b200_gemm_blockscaled_smallm for callers that cannot allocate device memory. It has no
@@ -184,6 +229,15 @@ int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src
 int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int64_t ld_src,
                                   const float* global_scale, void* packed, void* scale_mma,
                                   int64_t m, int64_t k, b12x_b200_stream_t stream);
+
+/*
+ * Self-test of the bounded waits every kernel of this library uses: launches one warp that
+ * waits, for at most max_polls polls (1..65536), on a barrier nothing will ever complete, and
+ * then reports exactly as a GEMM kernel does when a wait runs out: *status is raised to 2 and
+ * the kernel returns normally. Lets a host verify its handling of the status word without any
+ * fault. It has no counterpart in the reference.
+ */
+int b12x_b200_selftest_wait_timeout(int* status, int max_polls, b12x_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -56,17 +56,13 @@ def find_op(qualname: str) -> OpMeta:
 
 
 def clear_all_caches() -> None:
-    """Drop host-side caches (alpha scalars, small-M quantization scratch, status buffers).
-    Kernels are compiled ahead of time, so there is no compile cache to clear."""
+    """Drop host-side caches (alpha scalars, unit-scale tensors). Kernels are compiled ahead of
+    time, so there is no compile cache to clear. The per-device status words and the decode
+    workspaces are deliberately kept: a captured CUDA graph may hold their addresses."""
     dense = sys.modules.get(f"{__name__}._lib.dense_gemm")
     if dense is not None:
         dense._ALPHA_ONE_CACHE.clear()
-        dense._FUSED_QUANT_SCRATCH.clear()
         dense._UNIT_SCALE_CACHE.clear()
-    launch = sys.modules.get(f"{__name__}._lib.launch")
-    if launch is not None:
-        launch._STATUS.clear()
-        launch._WORKSPACE.clear()
 
 
 def install_as_b12x() -> None:

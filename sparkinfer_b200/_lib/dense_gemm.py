@@ -6,8 +6,9 @@ custom ops ``b12x::dense_gemm_launch`` / ``b12x::dense_gemm_launch_functional``
 meaning and host-side errors; the device work is the sm_100a tcgen05 kernel behind the C
 ABI. Tuning keywords of the reference's SM120 kernel (``load_path``, ``swap_ab``,
 ``cluster_shape_mn``, ``sfb_k_replicated``, the policy booleans of the custom ops) are
-accepted and ignored; ``mma_tiler_mn[1]`` selects the tile width when it is one the kernel
-has (64/128/192/256).
+accepted and ignored; ``mma_tiler_mn`` selects a kernel when it names a tile one of them has:
+``(128, 64/128/192/256)`` the single-CTA kernel with that tile width, ``(256, 256)`` the
+CTA-pair kernel.
 
 Operand contract (same as the reference): ``lhs = (A[M, Kp, L], SFA)``, ``rhs = (B[N, Kp, L],
 SFB)``, K-major, ``Kp = K/2`` bytes for ``float4_e2m1fn`` (two codes per byte, low nibble
@@ -40,7 +41,6 @@ _MXFP6_AB_DTYPES = ("float6_e3m2fn", "float6_e2m3fn")
 _C_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
 _KERNEL_BLOCK_N = (64, 128, 192, 256)
 _ALPHA_ONE_CACHE: dict[tuple[str, int | None], torch.Tensor] = {}
-_FUSED_QUANT_SCRATCH: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def get_num_sm(device: torch.device) -> int:
@@ -101,7 +101,8 @@ def _check_operand(name: str, t: torch.Tensor, rows: int, row_bytes: int, l: int
 
 def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int, ab_dtype: str,
                             sf_dtype: str, sf_vec_size: int, mma_tile_n: int, sm_count: int,
-                            alpha_is_one: bool, stream_int: Optional[int]) -> None:
+                            alpha_is_one: bool, stream_int: Optional[int],
+                            mma_tile_m: int = 128) -> None:
     kind = _kind_of(ab_dtype, sf_dtype, sf_vec_size)
     m = int(a.shape[0])
     row_bytes = k // 2 if kind == _native.KIND_NVFP4 else k
@@ -120,6 +121,8 @@ def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int,
     if m == 0 or n == 0:
         return
     block_n = mma_tile_n if mma_tile_n in _KERNEL_BLOCK_N else 0
+    if mma_tile_m == 256 and mma_tile_n == 256:
+        block_n = _native.BLOCK_N_PAIR
     k_tiles = -(-(-(-k // sf_vec_size)) // 4)
     sfa_group = (-(-m // 128)) * k_tiles * 512
     sfb_group = (-(-n // 128)) * k_tiles * 512
@@ -150,7 +153,7 @@ def _dense_gemm_launch_op(
         a_tensor_gpu, b_tensor_gpu, sfa_tensor_gpu, sfb_tensor_gpu, c_tensor_gpu,
         alpha_tensor_gpu, n=n, k=k, l=l, ab_dtype=ab_dtype, sf_dtype=sf_dtype,
         sf_vec_size=sf_vec_size, mma_tile_n=mma_tile_n, sm_count=sm_count,
-        alpha_is_one=alpha_is_one, stream_int=stream_int)
+        alpha_is_one=alpha_is_one, stream_int=stream_int, mma_tile_m=mma_tile_m)
 
 
 @_dense_gemm_launch_op.register_fake
@@ -175,7 +178,7 @@ def _dense_gemm_launch_functional_op(
         a_tensor_gpu, b_tensor_gpu, sfa_tensor_gpu, sfb_tensor_gpu, out, alpha_tensor_gpu,
         n=n, k=k, l=l, ab_dtype=ab_dtype, sf_dtype=sf_dtype, sf_vec_size=sf_vec_size,
         mma_tile_n=mma_tile_n, sm_count=sm_count, alpha_is_one=alpha_is_one,
-        stream_int=stream_int)
+        stream_int=stream_int, mma_tile_m=mma_tile_m)
     return out
 
 
@@ -338,6 +341,14 @@ def dense_gemm(
     return out
 
 
+def _fused_quant_rhs(name: str, b: torch.Tensor, sfb: torch.Tensor, row_bytes: int):
+    if b.ndim != 3 or int(b.shape[1]) != row_bytes or int(b.shape[2]) != 1:
+        raise ValueError(f"B must have shape [N,{row_bytes},1], got {tuple(b.shape)}")
+    if b.element_size() != 1 or b.stride(1) != 1 or b.stride(0) != row_bytes:
+        raise ValueError(f"{name}: B must be K-major one-byte codes")
+    return b.select(2, 0), (sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb)
+
+
 def dense_gemm_fused_quant_a(
     source: torch.Tensor,
     b: torch.Tensor,
@@ -352,12 +363,11 @@ def dense_gemm_fused_quant_a(
     _atomic_output_precleared: bool = False,
     stream: object = None,
 ) -> torch.Tensor:
-    """Small-M BF16 activations -> MXFP8 GEMM (b12x/_lib/dense_gemm.py:6897-7051).
+    """Small-M BF16 activations -> MXFP8 GEMM in one kernel (b12x/_lib/dense_gemm.py:6897-7051).
 
-    The activation rows are quantized to E4M3 + UE8M0/32 by the row quantizer into a
-    per-device scratch that is created on the first call for a given K (so a warm-up call
-    must precede CUDA-graph capture, as for every op here), then the MXFP8 GEMM runs on the
-    same stream. Results equal ``quantize_rows`` followed by ``mm``.
+    The decode kernel's quantizer warps turn the BF16 rows into E4M3 codes and UE8M0/32 scales
+    inside shared memory while the weight streams in; nothing is written to global memory but
+    the output. Results equal ``quantize_rows`` followed by ``mm`` bit for bit.
     """
     if source.dtype != torch.bfloat16:
         raise ValueError("fused MXFP8 activation quantization requires BF16 A")
@@ -369,8 +379,7 @@ def dense_gemm_fused_quant_a(
     if m < 1 or m > 8 or k % 128 != 0:
         raise ValueError(
             f"fused MXFP8 activation quantization requires 1<=M<=8 and K%128=0, got M={m}, K={k}")
-    if b.ndim != 3 or int(b.shape[1]) != k or int(b.shape[2]) != 1:
-        raise ValueError(f"B must have shape [N,{k},1], got {tuple(b.shape)}")
+    w, sfw = _fused_quant_rhs("mm_fused_quant_a", b, sfb, k)
     n = int(b.shape[0])
     if out is None:
         if _atomic_output_precleared:
@@ -379,23 +388,51 @@ def dense_gemm_fused_quant_a(
     if out.shape != (m, n, 1) or out.dtype != torch.bfloat16:
         raise ValueError(
             f"out must be BF16 with shape {(m, n, 1)}, got {out.dtype} {tuple(out.shape)}")
-    dev_index = source.device.index if source.device.index is not None else torch.cuda.current_device()
-    key = (dev_index, 8, k)
-    scratch = _FUSED_QUANT_SCRATCH.get(key)
-    if scratch is None:
-        values = torch.empty((8, k), dtype=torch.uint8, device=source.device)
-        scale_mma = torch.full(((k // 128) * 512,), 127, dtype=torch.uint8, device=source.device)
-        scratch = (values, scale_mma)
-        _FUSED_QUANT_SCRATCH[key] = scratch
-    values, scale_mma = scratch
-    stream_int = cuda_stream_to_int(stream)
-    launch.quantize_mxfp8_rows(source, values, None, scale_mma, stream_int=stream_int)
-    launch.gemm_blockscaled(
-        _native.KIND_MXFP8, values, scale_mma, b.select(2, 0),
-        sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb, out.select(2, 0), None,
-        m, n, k, ldc=n, block_n=(mma_tiler_mn[1] if mma_tiler_mn and mma_tiler_mn[1] in _KERNEL_BLOCK_N else 0),
-        stream_int=stream_int)
+    launch.gemm_smallm_fused_quant(_native.KIND_MXFP8, source, None, w, sfw, out.select(2, 0),
+                                   None, m, n, k, ldc=n, stream_int=cuda_stream_to_int(stream))
     return out
 
 
-__all__ = ["dense_gemm", "dense_gemm_fused_quant_a", "get_num_sm"]
+def dense_gemm_fused_quant_a_nvfp4(
+    source: torch.Tensor,
+    global_scale: torch.Tensor,
+    b: torch.Tensor,
+    sfb: torch.Tensor,
+    *,
+    alpha: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    c_dtype: str = "bfloat16",
+    stream: object = None,
+) -> torch.Tensor:
+    """NVFP4 counterpart of :func:`dense_gemm_fused_quant_a` (the reference fuses MXFP8 only):
+    BF16 ``source [M, K]`` with ``M <= 16`` is quantized inside the decode kernel with the
+    caller's ``global_scale`` (device FP32 scalar, read at run time) exactly as
+    ``quantization.nvfp4.run`` would, then multiplied with the NVFP4 weight ``b [N, K/2, 1]`` /
+    ``sfb``. ``alpha`` is normally ``1 / (global_scale_x * global_scale_w)``."""
+    if source.dtype != torch.bfloat16 or source.ndim != 2 or not source.is_contiguous():
+        raise ValueError("fused NVFP4 activation quantization requires contiguous BF16 [M,K]")
+    m, k = map(int, source.shape)
+    if m < 1 or m > launch.FUSED_QUANT_MAX_M or k % 64 != 0:
+        raise ValueError(
+            f"fused NVFP4 activation quantization requires 1<=M<={launch.FUSED_QUANT_MAX_M} and "
+            f"K%64=0, got M={m}, K={k}")
+    if global_scale.dtype != torch.float32 or global_scale.numel() != 1 or not global_scale.is_cuda:
+        raise ValueError("global_scale must be a CUDA float32 tensor with one element")
+    if alpha is not None and (alpha.dtype != torch.float32 or alpha.numel() != 1):
+        raise ValueError("alpha must be a float32 tensor with one element")
+    if c_dtype not in _C_DTYPES:
+        raise KeyError(f"unsupported c_dtype string: {c_dtype!r}")
+    w, sfw = _fused_quant_rhs("mm_fused_quant_a_nvfp4", b, sfb, k // 2)
+    n = int(b.shape[0])
+    if out is None:
+        out = torch.empty((m, n, 1), dtype=_C_DTYPES[c_dtype], device=source.device)
+    if out.shape != (m, n, 1) or out.dtype != _C_DTYPES[c_dtype]:
+        raise ValueError(f"out must be {c_dtype} with shape {(m, n, 1)}, got {out.dtype} "
+                         f"{tuple(out.shape)}")
+    launch.gemm_smallm_fused_quant(_native.KIND_NVFP4, source, global_scale, w, sfw,
+                                   out.select(2, 0), alpha, m, n, k, ldc=n,
+                                   stream_int=cuda_stream_to_int(stream))
+    return out
+
+
+__all__ = ["dense_gemm", "dense_gemm_fused_quant_a", "dense_gemm_fused_quant_a_nvfp4", "get_num_sm"]

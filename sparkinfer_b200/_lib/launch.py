@@ -16,16 +16,23 @@ from .. import _native
 
 _STATUS_LOCK = Lock()
 _STATUS: dict[int, torch.Tensor] = {}
-_WORKSPACE: dict[int, torch.Tensor] = {}
+# (device index, stream handle) -> every decode workspace ever handed out for that stream, the
+# newest last. Superseded buffers are kept: a captured CUDA graph or a kernel still in flight
+# may hold their address.
+_WORKSPACES: dict[tuple[int, int], list[torch.Tensor]] = {}
+# device index -> zeroed workspaces not yet bound to a stream. A stream first seen during CUDA
+# graph capture (torch captures on a side stream) takes one of these instead of allocating,
+# which inside a capture would add a fill node to every replay.
+_SPARE_WORKSPACES: dict[int, list[torch.Tensor]] = {}
+_SPARES_PER_DEVICE = 2
 SMALL_M_MAX = 128        # largest M the decode kernel accepts
-SMALL_M_AUTO = 64        # largest M routed to it automatically
+SMALL_M_AUTO = 64        # largest M always routed to it
+FUSED_QUANT_MAX_M = 16   # largest M of the decode kernel with the activation quantizer fused in
+_WORKSPACE_MIN_BYTES = 8 << 20
+_COUNTER_BYTES = 64 << 10  # counter block at the start of a decode workspace
 
 _DTYPE_CODE = {torch.bfloat16: _native.DT_BF16, torch.float16: _native.DT_FP16,
                torch.float32: _native.DT_FP32}
-
-import os as _os
-
-_SMALL_M_DISABLED = _os.getenv("B12X_B200_DISABLE_SMALL_M", "0") == "1"
 
 KERNEL_STATUS_TEXT = {
     1: "TMA producer timed out waiting for a free pipeline stage",
@@ -51,6 +58,26 @@ def _stream_ptr(stream_int: int | None, device: torch.device) -> ctypes.c_void_p
     return ctypes.c_void_p(int(stream_int))
 
 
+def _zeros_ready_for_any_stream(nbytes: int, index: int, dtype=torch.uint8) -> torch.Tensor:
+    """Zero-filled device buffer whose fill has completed before it is handed to a kernel on
+    some other stream. Under stream capture the fill is captured in order instead (the kernels
+    that use the buffer are captured on the same stream) and nothing is synchronised."""
+    device = torch.device("cuda", index)
+    buf = torch.zeros(nbytes, dtype=dtype, device=device)
+    if not torch.cuda.is_current_stream_capturing():
+        torch.cuda.current_stream(device).synchronize()
+    return buf
+
+
+def _top_up_spares(index: int, size: int) -> None:
+    """Keep a few zeroed workspaces of at least ``size`` bytes ready for streams that first
+    show up inside a capture. Called with the lock held, outside any capture."""
+    spares = _SPARE_WORKSPACES.setdefault(index, [])
+    spares[:] = [b for b in spares if b.numel() >= size]
+    while len(spares) < _SPARES_PER_DEVICE:
+        spares.append(_zeros_ready_for_any_stream(size, index))
+
+
 def status_buffer(device: torch.device) -> torch.Tensor:
     """Per-device int32[4] the kernels raise when a bounded wait runs out. Allocated once, on
     first use (call an op once before CUDA-graph capture, as with any warm-up)."""
@@ -58,18 +85,30 @@ def status_buffer(device: torch.device) -> torch.Tensor:
     with _STATUS_LOCK:
         buf = _STATUS.get(index)
         if buf is None:
-            buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("call the op once on this device before capturing it into a "
+                                   "CUDA graph (the kernel status word is created on first use)")
+            buf = _zeros_ready_for_any_stream(4, index, torch.int32)
             _STATUS[index] = buf
         return buf
 
 
 def check_kernel_status(device: torch.device | None = None) -> None:
-    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait. A kernel
+    that gave up may have left per-tile counters of a decode workspace non-zero, so those are
+    cleared together with the status word before the exception leaves."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    index = device.index if device.index is not None else torch.cuda.current_device()
     buf = status_buffer(device)
+    torch.cuda.synchronize(device)
     code = int(buf[0].item())
     if code != 0:
         buf.zero_()
+        with _STATUS_LOCK:
+            stale = [w for (dev, _), ws in _WORKSPACES.items() if dev == index for w in ws]
+        for w in stale:
+            w[:_COUNTER_BYTES].zero_()
+        torch.cuda.synchronize(device)
         raise RuntimeError(f"b12x kernel status {code}: {KERNEL_STATUS_TEXT.get(code, 'unknown')}")
 
 
@@ -81,23 +120,49 @@ def _require_cuda(name: str, t: torch.Tensor) -> None:
 
 
 def smallm_workspace(kind: int, m: int, n: int, k: int, device: torch.device,
-                     sm_count: int = 0) -> torch.Tensor:
-    """Per-device scratch of the decode-shape kernel (FP32 partial tiles + per-tile counters).
-    Created zeroed and grown on demand, so the first call for a larger shape allocates (warm up
-    before CUDA-graph capture). Every launch leaves the counters zero, and launches on one
-    device share the buffer, so they must not overlap on the GPU (same stream, or ordered)."""
+                     sm_count: int = 0, stream_int: int | None = None) -> torch.Tensor:
+    """Scratch of the decode-shape kernel (per-tile counters + FP32 partial tiles) for launches
+    on one stream of one device. Launches on the same stream run in order and share a buffer;
+    every stream has its own, so decode GEMMs on different streams never meet in one. A buffer
+    is created zeroed the first time a stream needs one, or a larger one (so warm up before
+    CUDA-graph capture), and is never released while the process lives."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     with torch.cuda.device(index):
         need = int(_native.load().b12x_b200_gemm_smallm_workspace_bytes(kind, m, n, k, sm_count))
     if need < 0:
         raise _native.NativeLibraryError(f"no decode-shape plan for M={m}, N={n}, K={k}")
+    if stream_int is None:
+        stream_int = torch.cuda.current_stream(torch.device("cuda", index)).cuda_stream
+    key = (index, int(stream_int))
+    capturing = torch.cuda.is_current_stream_capturing()
     with _STATUS_LOCK:
-        buf = _WORKSPACE.get(index)
-        if buf is None or buf.numel() < need:
-            buf = torch.zeros(max(need, 1 << 20), dtype=torch.uint8,
-                              device=torch.device("cuda", index))
-            _WORKSPACE[index] = buf
-        return buf
+        bufs = _WORKSPACES.setdefault(key, [])
+        if not bufs or bufs[-1].numel() < need:
+            size = _WORKSPACE_MIN_BYTES
+            while size < need:
+                size *= 2
+            spares = _SPARE_WORKSPACES.get(index, [])
+            fit = next((b for b in spares if b.numel() >= size), None) if capturing else None
+            if fit is not None:
+                spares[:] = [b for b in spares if b is not fit]
+                bufs.append(fit)
+            else:
+                bufs.append(_zeros_ready_for_any_stream(size, index))
+        if not capturing:
+            _top_up_spares(index, bufs[-1].numel())
+        return bufs[-1]
+
+
+def route_to_decode_kernel(m: int, n: int, device: torch.device, sm_count: int = 0) -> bool:
+    """Whether an unforced GEMM of ``m`` rows goes to the weight-streaming decode kernel: always
+    up to 64 rows, and up to 128 rows while the tiled kernel's 128 x 64 tiles would leave more
+    than half of the SMs without work (the decode kernel splits K over the idle ones)."""
+    if m <= SMALL_M_AUTO:
+        return True
+    if m > SMALL_M_MAX:
+        return False
+    sms = sm_count if sm_count > 0 else torch.cuda.get_device_properties(device).multi_processor_count
+    return -(-n // 64) * 2 < sms
 
 
 def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
@@ -108,17 +173,18 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)`` for one group. ``a``/``b`` are row
     pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom.
 
-    Decode shapes (M <= 128, unless ``small_m=False`` or a tile width is forced) go to the
-    weight-streaming stream-K kernel, everything else to the persistent tiled kernel."""
+    Decode shapes (see :func:`route_to_decode_kernel`; never when a tile width is forced, always
+    with ``small_m=True``) go to the weight-streaming stream-K kernel, everything else to the
+    persistent tiled kernels; ``block_n=_native.BLOCK_N_PAIR`` forces the CTA-pair kernel."""
     for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
         _require_cuda(name, t)
     if c.dtype not in _DTYPE_CODE:
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = a.device
     if small_m is None:
-        small_m = m <= SMALL_M_AUTO and block_n == 0 and not _SMALL_M_DISABLED
+        small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and route_to_decode_kernel(m, n, dev, sm_count)
     if small_m and 0 < m <= SMALL_M_MAX and n > 0:
-        work = smallm_workspace(kind, m, n, k, dev, sm_count)
+        work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
         with torch.cuda.device(dev):
             rc = _native.load().b12x_b200_gemm_blockscaled_smallm(
                 kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
@@ -134,6 +200,57 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
             m, n, k, ldc if ldc is not None else n, block_n, sm_count,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
     _native.check(rc, "b12x_b200_gemm_blockscaled")
+
+
+def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tensor | None,
+                            w: torch.Tensor, sfw: torch.Tensor, c: torch.Tensor,
+                            alpha: torch.Tensor | None, m: int, n: int, k: int, *,
+                            ldc: int | None = None, sm_count: int = 0,
+                            stream_int: int | None = None) -> None:
+    """Decode GEMM that quantizes its BF16 activation rows ``x [M, K]`` (M <= 16) inside the
+    kernel; bit for bit ``quantize rows`` followed by :func:`gemm_blockscaled`."""
+    for name, t in (("x", x), ("w", w), ("sfw", sfw), ("c", c)):
+        _require_cuda(name, t)
+    if x.dtype != torch.bfloat16 or x.stride(-1) != 1:
+        raise ValueError("fused activation quantization needs BF16 rows with unit column stride")
+    if c.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported output dtype {c.dtype}")
+    dev = x.device
+    work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_gemm_smallm_fused_quant(
+            kind, x.data_ptr(), x.stride(0) if m > 1 else k,
+            global_scale.data_ptr() if global_scale is not None else None, w.data_ptr(),
+            sfw.data_ptr(), c.data_ptr(), _DTYPE_CODE[c.dtype],
+            alpha.data_ptr() if alpha is not None else None, m, n, k,
+            ldc if ldc is not None else n, work.data_ptr(), work.numel(), sm_count,
+            status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_smallm_fused_quant")
+
+
+def gemm_smallm_timeline(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
+                         sfb: torch.Tensor, c: torch.Tensor, alpha: torch.Tensor | None,
+                         m: int, n: int, k: int, stamps: torch.Tensor, *,
+                         stream_int: int | None = None) -> None:
+    """Decode GEMM that also writes its per-CTA time stamps into ``stamps`` (int64, 8 per SM)."""
+    dev = a.device
+    work = smallm_workspace(kind, m, n, k, dev, 0, stream_int)
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_gemm_smallm_timeline(
+            kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+            _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None, m, n, k, n,
+            work.data_ptr(), work.numel(), 0, stamps.data_ptr(), stamps.numel(),
+            status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_smallm_timeline")
+
+
+def selftest_wait_timeout(device: torch.device, max_polls: int = 4096) -> None:
+    """Launch the library's wait self-test: one warp gives up a bounded wait and raises the
+    device's status word like a GEMM kernel would (see :func:`check_kernel_status`)."""
+    with torch.cuda.device(device):
+        rc = _native.load().b12x_b200_selftest_wait_timeout(
+            status_buffer(device).data_ptr(), max_polls, _stream_ptr(None, device))
+    _native.check(rc, "b12x_b200_selftest_wait_timeout")
 
 
 def gemm_block_fp8(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: torch.Tensor,
@@ -181,5 +298,7 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
 
 __all__ = [
     "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled",
-    "gemm_block_fp8", "quantize_mxfp8_rows", "quantize_nvfp4_rows", "KERNEL_STATUS_TEXT",
+    "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
+    "route_to_decode_kernel", "smallm_workspace", "quantize_mxfp8_rows", "quantize_nvfp4_rows",
+    "KERNEL_STATUS_TEXT",
 ]

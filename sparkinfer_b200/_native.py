@@ -20,6 +20,7 @@ KIND_NVFP4 = 1
 DT_BF16 = 0
 DT_FP16 = 1
 DT_FP32 = 2
+BLOCK_N_PAIR = -256  # B12X_B200_BLOCK_N_PAIR: force the CTA-pair kernel
 
 _c_void_p = ctypes.c_void_p
 _c_int = ctypes.c_int
@@ -40,6 +41,18 @@ SIGNATURES = {
         [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
          _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_int, _c_void_p, _c_void_p],
     ),
+    "b12x_b200_gemm_smallm_fused_quant": (
+        _c_int,
+        [_c_int, _c_void_p, _c_i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_int, _c_void_p, _c_void_p],
+    ),
+    "b12x_b200_gemm_smallm_timeline": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_int, _c_void_p, _c_i64,
+         _c_void_p, _c_void_p],
+    ),
+    "b12x_b200_selftest_wait_timeout": (_c_int, [_c_void_p, _c_int, _c_void_p]),
     "b12x_b200_gemm_smallm_noalloc_capacity_bytes": (_c_i64, []),
     "b12x_b200_gemm_blockscaled_smallm_noalloc": (
         _c_int,

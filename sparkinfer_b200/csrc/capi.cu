@@ -120,6 +120,25 @@ int device_info(DeviceInfo* out) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Experiment switches, read from the environment once per process (never on the launch path).
+// They exist for measurements of kernel variants; none is part of the interface.
+struct Switches {
+  bool decode_overlap = true;   // programmatic stream serialization for decode GEMMs / quantizers
+  bool decode_full_grid = false;  // one decode CTA per SM even when that splits every tile
+  bool pair_tail_split = true;  // split-K the last partial round of the CTA-pair kernel
+};
+
+const Switches& switches() {
+  static const Switches sw = [] {
+    Switches v;
+    if (const char* e = getenv("B12X_B200_DECODE_OVERLAP")) v.decode_overlap = atoi(e) != 0;
+    if (const char* e = getenv("B12X_B200_DECODE_FULL_GRID")) v.decode_full_grid = atoi(e) != 0;
+    if (const char* e = getenv("B12X_B200_PAIR_TAIL_SPLIT")) v.pair_tail_split = atoi(e) != 0;
+    return v;
+  }();
+  return sw;
+}
+
 // Tile width: fewest (waves x per-tile cost). The per-tile cost model is the bytes one k-step
 // pulls through shared memory, (128 + BN) rows of 128 bytes, which tracks both the MMA time
 // (proportional to BN) and the operand traffic.
@@ -198,6 +217,27 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
   return B12X_B200_OK;
 }
 
+// Rows up to which a quantized matrix is taken for an activation (its quantization releases the
+// next kernel early) and a decode GEMM's weight for something a predecessor may just have
+// written (its stream waits for the predecessor). One constant, so the two rules meet.
+constexpr int kEarlyReleaseRows = 128;
+
+// Launch configuration of a row quantizer: 256 threads, programmatic stream serialization.
+struct QuantLaunch {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  QuantLaunch(unsigned blocks, cudaStream_t stream) {
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = switches().decode_overlap ? 1 : 0;
+  }
+};
+
 template <int KIND>
 int dispatch_block_n(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b,
                      const CUtensorMap& map_c, const GemmParams& p, int grid,
@@ -231,6 +271,10 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
   if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (block_n != 0 && block_n != B12X_B200_BLOCK_N_PAIR && block_n != 64 && block_n != 128 &&
+      block_n != 192 && block_n != 256)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT,
+                "block_n must be 0, 64, 128, 192, 256 or B12X_B200_BLOCK_N_PAIR");
   if (m == 0 || n == 0) return B12X_B200_OK;
   if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
@@ -246,14 +290,16 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   if (rc != B12X_B200_OK) return rc;
   if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  if (block_n == B12X_B200_BLOCK_N_PAIR && sms < 2)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "the CTA-pair kernel needs two SMs");
   const int bn = block_n > 0 ? block_n : choose_block_n(m, n, sms);
 
   // Problems with enough 256 x 256 pair tiles go to the CTA-pair kernel unless a tile width was
   // forced. "Enough" is two thirds of the pairs: measured on 148 SMs the pair kernel wins from
   // 56 tiles up (512 x 7168, 1024 x 4096, 256 x 18432) and loses at 28-32 tiles.
   const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-  bool use_pair = (block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms);
-  if (const char* e = getenv("B12X_B200_PAIR")) use_pair = (block_n == 0) && (sms >= 2) && atoi(e) != 0;
+  const bool use_pair = (block_n == B12X_B200_BLOCK_N_PAIR) ||
+                        ((block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms));
 
   CUtensorMap map_a, map_b;
   rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(row_bytes), 128);
@@ -286,8 +332,7 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
   CUtensorMap map_c;
   memset(&map_c, 0, sizeof(map_c));
   p.use_tma_store = 0;
-  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0 &&
-      !getenv("B12X_B200_DIRECT_STORE")) {
+  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0) {
     rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
     if (rc != B12X_B200_OK) return rc;
     p.use_tma_store = 1;
@@ -324,18 +369,21 @@ extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int
   if (quant_warps(rows_cover, k_cover) > INT32_MAX)
     return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
   const int64_t blocks = (quant_warps(rows_cover, k_cover) + 7) / 8;  // 8 warps per CTA
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  QuantLaunch launch(unsigned(blocks), reinterpret_cast<cudaStream_t>(stream));
+  const int early = m <= kEarlyReleaseRows ? 1 : 0;
+  cudaError_t err;
   if (src_dtype == B12X_B200_BF16)
-    quantize_mxfp8_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(src), ld_src, static_cast<uint8_t*>(values),
-        static_cast<uint8_t*>(scale_rows), static_cast<uint8_t*>(scale_mma), int(m), int(k),
-        rows_cover, k_cover, k_atoms);
+    err = cudaLaunchKernelEx(&launch.cfg, quantize_mxfp8_rows_kernel<__nv_bfloat16>,
+                             static_cast<const __nv_bfloat16*>(src), ld_src,
+                             static_cast<uint8_t*>(values), static_cast<uint8_t*>(scale_rows),
+                             static_cast<uint8_t*>(scale_mma), int(m), int(k), rows_cover, k_cover,
+                             k_atoms, early);
   else
-    quantize_mxfp8_rows_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(
-        static_cast<const __half*>(src), ld_src, static_cast<uint8_t*>(values),
-        static_cast<uint8_t*>(scale_rows), static_cast<uint8_t*>(scale_mma), int(m), int(k),
-        rows_cover, k_cover, k_atoms);
-  const cudaError_t err = cudaGetLastError();
+    err = cudaLaunchKernelEx(&launch.cfg, quantize_mxfp8_rows_kernel<__half>,
+                             static_cast<const __half*>(src), ld_src,
+                             static_cast<uint8_t*>(values), static_cast<uint8_t*>(scale_rows),
+                             static_cast<uint8_t*>(scale_mma), int(m), int(k), rows_cover, k_cover,
+                             k_atoms, early);
   if (err != cudaSuccess) return fail_cuda(err, "quantize_mxfp8_rows launch");
   return B12X_B200_OK;
 }
@@ -360,17 +408,19 @@ extern "C" int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int
   if (quant_warps(rows_cover, k_cover) > INT32_MAX)
     return fail(B12X_B200_ERR_UNSUPPORTED, "tensor too large");
   const int64_t blocks = (quant_warps(rows_cover, k_cover) + 7) / 8;  // 8 warps per CTA
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  QuantLaunch launch(unsigned(blocks), reinterpret_cast<cudaStream_t>(stream));
+  const int early = m <= kEarlyReleaseRows ? 1 : 0;
+  cudaError_t err;
   if (src_dtype == B12X_B200_BF16)
-    quantize_nvfp4_rows_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(src), ld_src, global_scale,
-        static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scale_mma), int(m), int(k),
-        rows_cover, k_cover, k_atoms);
+    err = cudaLaunchKernelEx(&launch.cfg, quantize_nvfp4_rows_kernel<__nv_bfloat16>,
+                             static_cast<const __nv_bfloat16*>(src), ld_src, global_scale,
+                             static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scale_mma),
+                             int(m), int(k), rows_cover, k_cover, k_atoms, early);
   else
-    quantize_nvfp4_rows_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(
-        static_cast<const __half*>(src), ld_src, global_scale, static_cast<uint8_t*>(packed),
-        static_cast<uint8_t*>(scale_mma), int(m), int(k), rows_cover, k_cover, k_atoms);
-  const cudaError_t err = cudaGetLastError();
+    err = cudaLaunchKernelEx(&launch.cfg, quantize_nvfp4_rows_kernel<__half>,
+                             static_cast<const __half*>(src), ld_src, global_scale,
+                             static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scale_mma),
+                             int(m), int(k), rows_cover, k_cover, k_atoms, early);
   if (err != cudaSuccess) return fail_cuda(err, "quantize_nvfp4_rows launch");
   return B12X_B200_OK;
 }
@@ -435,8 +485,7 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   CUtensorMap map_c;
   memset(&map_c, 0, sizeof(map_c));
   p.use_tma_store = 0;
-  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0 &&
-      !getenv("B12X_B200_DIRECT_STORE")) {
+  if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0) {
     rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
     if (rc != B12X_B200_OK) return rc;
     p.use_tma_store = 1;
@@ -463,6 +512,9 @@ struct SmallMPlan {
 // Geometry of the decode-shape kernel for (kind, m, n, k) on `sms` SMs.
 int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* out) {
   if (m < 1 || m > 128) return fail(B12X_B200_ERR_UNSUPPORTED, "decode kernel needs 1 <= M <= 128");
+  if (n < 1 || k < 1 || n > INT32_MAX || k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (sms < 1) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "no SMs");
   const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
   const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
   SmallMPlan pl;
@@ -475,12 +527,12 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   // Grid: with no more tiles than SMs, a whole number of CTAs per tile (capped by the k-tiles a
   // tile has) keeps every CTA range inside one tile, so a tile that gets a single CTA needs no
   // partial sums at all; with more tiles than SMs one CTA per SM streams an equal share.
-  if (pl.tiles <= sms) {
+  if (pl.tiles <= sms && !switches().decode_full_grid) {
     int per_tile = sms / pl.tiles;
     if (per_tile > pl.k_tiles) per_tile = pl.k_tiles;
     pl.grid = pl.tiles * per_tile;
   } else {
-    pl.grid = sms;
+    pl.grid = int(units < sms ? units : sms);
   }
   const int64_t units_per_cta = units / pl.grid;  // >= 1
   int64_t seg = (pl.k_tiles + units_per_cta - 1) / units_per_cta + 1;
@@ -512,7 +564,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   return B12X_B200_OK;
 }
 
-template <int KIND>
+template <int KIND, bool FUSED>
 int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
                   int grid, int smem_bytes, cudaStream_t stream) {
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
@@ -520,11 +572,11 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        gemm_smallm_kernel<KIND, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     // Largest shared-memory carve-out: the ring takes nearly all of it.
     const cudaError_t carve_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        gemm_smallm_kernel<KIND, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout,
         cudaSharedmemCarveoutMaxShared);
     if (carve_err != cudaSuccess) return fail_cuda(carve_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
@@ -535,21 +587,146 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(grid), 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.blockDim = dim3(FUSED ? 512 : 256, 1, 1);
   cfg.dynamicSmemBytes = size_t(smem_bytes);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  static const bool overlap = []() {
-    const char* e = getenv("B12X_B200_DECODE_OVERLAP");
-    return !(e && atoi(e) == 0);
-  }();
-  cfg.numAttrs = overlap ? 1 : 0;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND>, map_w, map_x, p);
+  cfg.numAttrs = switches().decode_overlap ? 1 : 0;
+  const cudaError_t err =
+      cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND, FUSED>, map_w, map_x, p);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;
+}
+
+// One decode-shape GEMM request, as every entry point of the family describes it. `x` / `sf_x`
+// are codes and scale atoms; with `x_src` set instead the activation rows are BF16 and are
+// quantized inside the kernel (`x_gs` = their NVFP4 global scale).
+struct SmallMCall {
+  int kind;
+  const void* x;
+  const void* sf_x;
+  const void* x_src;
+  int64_t ld_x;
+  const float* x_gs;
+  const void* w;
+  const void* sf_w;
+  void* c;
+  int c_dtype;
+  const float* alpha;
+  int64_t m, n, k, ldc;
+  int sm_count;
+  int* status;
+  unsigned long long* timeline;
+  cudaStream_t stream;
+};
+
+// Argument checks shared by the decode-shape entry points. On success *empty is set when there
+// is nothing to compute, otherwise *plan and *sms describe the launch. Nothing is enqueued.
+int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empty) {
+  *empty = false;
+  const bool fused = a.x_src != nullptr;
+  if (a.kind != B12X_B200_KIND_MXFP8 && a.kind != B12X_B200_KIND_NVFP4)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
+  if (a.c_dtype < B12X_B200_BF16 || a.c_dtype > B12X_B200_FP32)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
+  if (a.m < 0 || a.n < 0 || a.k <= 0 || a.n > INT32_MAX || a.k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
+  if (a.m == 0 || a.n == 0) {
+    *empty = true;
+    return B12X_B200_OK;
+  }
+  if (!a.w || !a.sf_w || !a.c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (a.ldc < a.n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  if (a.k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
+  const int64_t row_bytes = (a.kind == B12X_B200_KIND_MXFP8) ? a.k : a.k / 2;
+  if (row_bytes % 16 != 0 || !aligned16(a.w) || !aligned16(a.sf_w))
+    return fail(B12X_B200_ERR_ALIGNMENT, "operands and scales must be 16-byte aligned");
+  if (fused) {
+    if (a.m > 16)
+      return fail(B12X_B200_ERR_UNSUPPORTED, "fused activation quantization needs M <= 16");
+    if (a.kind == B12X_B200_KIND_NVFP4 && !a.x_gs)
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "NVFP4 activations need a global scale");
+    if (a.ld_x < a.k || a.ld_x % 8 != 0 || !aligned16(a.x_src))
+      return fail(B12X_B200_ERR_ALIGNMENT, "activation rows must be 16-byte aligned");
+  } else {
+    if (!a.x || !a.sf_x) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+    if (!aligned16(a.x) || !aligned16(a.sf_x))
+      return fail(B12X_B200_ERR_ALIGNMENT, "operands and scales must be 16-byte aligned");
+  }
+  DeviceInfo info;
+  int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  *sms_out = (a.sm_count > 0 && a.sm_count < info.sm_count) ? a.sm_count : info.sm_count;
+  return plan_smallm(a.kind, a.m, a.n, a.k, *sms_out, plan);
+}
+
+int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
+               int64_t workspace_bytes) {
+  const bool fused = a.x_src != nullptr;
+  if (!workspace) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (!aligned16(workspace))
+    return fail(B12X_B200_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
+  if (workspace_bytes < int64_t(pl.total_bytes))
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "workspace smaller than b12x_b200_gemm_smallm_workspace_bytes");
+  const int64_t row_bytes = (a.kind == B12X_B200_KIND_MXFP8) ? a.k : a.k / 2;
+  CUtensorMap map_w, map_x;
+  int rc = make_operand_map(&map_w, a.w, uint64_t(a.n), uint64_t(row_bytes), 128);
+  if (rc != B12X_B200_OK) return rc;
+  if (fused) {
+    map_x = map_w;  // unused by the fused kernel
+  } else {
+    rc = make_operand_map(&map_x, a.x, uint64_t(a.m), uint64_t(row_bytes), uint32_t(pl.m_pad));
+    if (rc != B12X_B200_OK) return rc;
+  }
+
+  SmallMParams p;
+  memset(&p, 0, sizeof(p));
+  p.sf_w = static_cast<const uint8_t*>(a.sf_w);
+  p.sf_x = static_cast<const uint8_t*>(a.sf_x);
+  p.c = a.c;
+  p.alpha = a.alpha;
+  p.status = a.status;
+  p.counters = static_cast<int*>(workspace);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSmallMCounterBytes);
+  p.m = int(a.m);
+  p.n = int(a.n);
+  p.k = int(a.k);
+  p.ldc = int(a.ldc);
+  p.out_dtype = a.c_dtype;
+  p.m_pad = pl.m_pad;
+  p.tiles = pl.tiles;
+  p.k_tiles = pl.k_tiles;
+  p.k_atoms_total = pl.k_atoms;
+  p.max_segments = pl.max_segments;
+  p.num_stages = pl.stages;
+  p.stage_bytes = pl.stage_bytes;
+  p.issuers = pl.issuers;
+  p.tmem_cols = pl.tmem_cols;
+  p.sf_col0 = pl.sf_col0;
+  p.x_src = static_cast<const __nv_bfloat16*>(a.x_src);
+  p.ld_x = a.ld_x;
+  p.x_gs = a.x_gs;
+  p.wait_for_weights = a.n <= kEarlyReleaseRows ? 1 : 0;
+  p.timeline = a.timeline;
+  const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
+  if (a.kind == B12X_B200_KIND_MXFP8)
+    return fused ? launch_smallm<kMxfp8, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
+                 : launch_smallm<kMxfp8, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
+  return fused ? launch_smallm<kNvfp4, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
+               : launch_smallm<kNvfp4, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
+}
+
+int smallm_entry(const SmallMCall& a, void* workspace, int64_t workspace_bytes) {
+  SmallMPlan pl;
+  int sms = 0;
+  bool empty = false;
+  const int rc = check_smallm(a, &pl, &sms, &empty);
+  if (rc != B12X_B200_OK || empty) return rc;
+  return run_smallm(a, pl, workspace, workspace_bytes);
 }
 
 }  // namespace
@@ -558,12 +735,10 @@ extern "C" int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, in
                                                          int sm_count) {
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
   if (n <= 0 || k <= 0) return -1;
+  // Same SM count as the launch will use: the caller's limit, capped by the device.
   DeviceInfo info;
-  int sms = sm_count;
-  if (sms <= 0) {
-    if (device_info(&info) != B12X_B200_OK) return -1;
-    sms = info.sm_count;
-  }
+  if (device_info(&info) != B12X_B200_OK) return -1;
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
   SmallMPlan pl;
   if (plan_smallm(kind, m, n, k, sms, &pl) != B12X_B200_OK) return -1;
   return int64_t(pl.total_bytes);
@@ -576,66 +751,44 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
                                                  void* workspace, int64_t workspace_bytes,
                                                  int sm_count, int* status,
                                                  b12x_b200_stream_t stream) {
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
-  if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
-  if (n < 0 || k <= 0 || n > INT32_MAX || k > INT32_MAX)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
-  if (m == 0 || n == 0) return B12X_B200_OK;
-  if (!x || !w || !sf_x || !sf_w || !c || !workspace)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
-  if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
-  if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
-  const int64_t row_bytes = (kind == B12X_B200_KIND_MXFP8) ? k : k / 2;
-  if (row_bytes % 16 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(sf_x) ||
-      !aligned16(sf_w) || !aligned16(workspace))
-    return fail(B12X_B200_ERR_ALIGNMENT, "operands, scales and workspace must be 16-byte aligned");
-  DeviceInfo info;
-  int rc = device_info(&info);
-  if (rc != B12X_B200_OK) return rc;
-  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
-  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  SmallMCall a = {kind, x,     sf_x, nullptr, 0,   nullptr,  w,      sf_w,    c, c_dtype,
+                  alpha, m,    n,    k,       ldc, sm_count, status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x,
+                                                 const float* x_global_scale, const void* w,
+                                                 const void* sf_w, void* c, int c_dtype,
+                                                 const float* alpha, int64_t m, int64_t n,
+                                                 int64_t k, int64_t ldc, void* workspace,
+                                                 int64_t workspace_bytes, int sm_count,
+                                                 int* status, b12x_b200_stream_t stream) {
+  if (!x_bf16) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  SmallMCall a = {kind,  nullptr, nullptr, x_bf16, ld_x, x_global_scale, w,      sf_w,    c, c_dtype,
+                  alpha, m,       n,       k,      ldc,  sm_count,       status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int b12x_b200_gemm_smallm_timeline(int kind, const void* x, const void* sf_x,
+                                              const void* w, const void* sf_w, void* c,
+                                              int c_dtype, const float* alpha, int64_t m,
+                                              int64_t n, int64_t k, int64_t ldc, void* workspace,
+                                              int64_t workspace_bytes, int sm_count,
+                                              unsigned long long* stamps, int64_t stamps_len,
+                                              int* status, b12x_b200_stream_t stream) {
+  SmallMCall a = {kind, x,     sf_x, nullptr, 0,   nullptr,  w,      sf_w,   c, c_dtype,
+                  alpha, m,    n,    k,       ldc, sm_count, status, stamps,
+                  reinterpret_cast<cudaStream_t>(stream)};
   SmallMPlan pl;
-  rc = plan_smallm(kind, m, n, k, sms, &pl);
-  if (rc != B12X_B200_OK) return rc;
-  if (workspace_bytes < int64_t(pl.total_bytes))
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "workspace smaller than b12x_b200_gemm_smallm_workspace_bytes");
-
-  CUtensorMap map_w, map_x;
-  rc = make_operand_map(&map_w, w, uint64_t(n), uint64_t(row_bytes), 128);
-  if (rc != B12X_B200_OK) return rc;
-  rc = make_operand_map(&map_x, x, uint64_t(m), uint64_t(row_bytes), uint32_t(pl.m_pad));
-  if (rc != B12X_B200_OK) return rc;
-
-  SmallMParams p;
-  p.sf_w = static_cast<const uint8_t*>(sf_w);
-  p.sf_x = static_cast<const uint8_t*>(sf_x);
-  p.c = c;
-  p.alpha = alpha;
-  p.status = status;
-  p.counters = static_cast<int*>(workspace);
-  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSmallMCounterBytes);
-  p.m = int(m);
-  p.n = int(n);
-  p.k = int(k);
-  p.ldc = int(ldc);
-  p.out_dtype = c_dtype;
-  p.m_pad = pl.m_pad;
-  p.tiles = pl.tiles;
-  p.k_tiles = pl.k_tiles;
-  p.k_atoms_total = pl.k_atoms;
-  p.max_segments = pl.max_segments;
-  p.num_stages = pl.stages;
-  p.stage_bytes = pl.stage_bytes;
-  p.issuers = pl.issuers;
-  p.tmem_cols = pl.tmem_cols;
-  p.sf_col0 = pl.sf_col0;
-  const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (kind == B12X_B200_KIND_MXFP8)
-    return launch_smallm<kMxfp8>(map_w, map_x, p, pl.grid, smem_bytes, s);
-  return launch_smallm<kNvfp4>(map_w, map_x, p, pl.grid, smem_bytes, s);
+  int sms = 0;
+  bool empty = false;
+  const int rc = check_smallm(a, &pl, &sms, &empty);
+  if (rc != B12X_B200_OK || empty) return rc;
+  if (!stamps || stamps_len < int64_t(pl.grid) * kTimelineSlots)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "stamp buffer needs 8 entries per SM");
+  return run_smallm(a, pl, workspace, workspace_bytes);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -666,21 +819,16 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm_noalloc(int kind, const void* x
                                                          int64_t m, int64_t n, int64_t k,
                                                          int64_t ldc, int sm_count, int* status,
                                                          b12x_b200_stream_t stream) {
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
-  if (m == 0 || n == 0) return B12X_B200_OK;
-  if (n < 0 || k <= 0) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "device index out of range");
-  DeviceInfo info;
-  int rc = device_info(&info);
-  if (rc != B12X_B200_OK) return rc;
-  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  // Every argument check (the device's compute capability among them) comes before the symbol
+  // look-up and before anything is put on the stream, so a refused call leaves no trace.
+  SmallMCall a = {kind, x,     sf_x, nullptr, 0,   nullptr,  w,      sf_w,    c, c_dtype,
+                  alpha, m,    n,    k,       ldc, sm_count, status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
   SmallMPlan pl;
-  rc = plan_smallm(kind, m, n, k, sms, &pl);
-  if (rc != B12X_B200_OK) return rc;
+  int sms = 0;
+  bool empty = false;
+  int rc = check_smallm(a, &pl, &sms, &empty);
+  if (rc != B12X_B200_OK || empty) return rc;
   if (pl.total_bytes > kNoAllocScratchBytes) {
     snprintf(g_last_error, sizeof(g_last_error),
              "M=%lld N=%lld K=%lld needs %zu bytes of scratch; the built-in scratch of the "
@@ -689,6 +837,10 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm_noalloc(int kind, const void* x
              pl.total_bytes, kNoAllocScratchBytes);
     return B12X_B200_ERR_UNSUPPORTED;
   }
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "device index out of range");
   void* scratch = nullptr;
   {
     // First call on this device: resolve the device address of the static array (the device
@@ -704,10 +856,47 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm_noalloc(int kind, const void* x
   }
   // The array keeps whatever the previous call left. Only the per-tile counters have to start
   // at zero; partial slots are fully written before they are read.
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  err = cudaMemsetAsync(scratch, 0, size_t(pl.tiles) * sizeof(int), s);
+  err = cudaMemsetAsync(scratch, 0, size_t(pl.tiles) * sizeof(int), a.stream);
   if (err != cudaSuccess) return fail_cuda(err, "cudaMemsetAsync(counters)");
-  return b12x_b200_gemm_blockscaled_smallm(kind, x, sf_x, w, sf_w, c, c_dtype, alpha, m, n, k, ldc,
-                                           scratch, int64_t(kNoAllocScratchBytes), sm_count,
-                                           status, stream);
+  return run_smallm(a, pl, scratch, int64_t(kNoAllocScratchBytes));
+}
+
+// ----------------------------------------------------------------------------------------
+// Self-test of the bounded waits
+// ----------------------------------------------------------------------------------------
+namespace b12x_b200 {
+namespace {
+
+// One warp waits on an mbarrier that nothing will ever complete (no copy is in flight, nobody
+// arrives), with a small poll limit, and reports the time-out exactly as the GEMM kernels do:
+// status word raised, normal return.
+__global__ void selftest_wait_timeout_kernel(int* status, uint32_t max_polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  bool completed = false;
+  for (uint32_t polls = 0; polls < max_polls && !completed; ++polls) completed = mbar_try_wait(&bar, 0);
+  if (!completed && status && threadIdx.x == 0) atomicMax(status, kStatusMmaTimeout);
+}
+
+}  // namespace
+}  // namespace b12x_b200
+
+extern "C" int b12x_b200_selftest_wait_timeout(int* status, int max_polls,
+                                               b12x_b200_stream_t stream) {
+  if (!status) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (max_polls < 1 || max_polls > 65536)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "max_polls must be in [1, 65536]");
+  DeviceInfo info;
+  const int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  selftest_wait_timeout_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      status, uint32_t(max_polls));
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "selftest launch");
+  return B12X_B200_OK;
 }

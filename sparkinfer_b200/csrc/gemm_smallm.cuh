@@ -27,22 +27,35 @@
 // tail. The kernel is therefore launched with programmatic stream serialization and calls
 // griddepcontrol.launch_dependents at once, so the next grid's CTAs are placed as soon as this
 // grid's CTAs leave their SMs and run their prologue and first weight loads while this grid is
-// still finishing. The weight producer starts streaming immediately (weights are not written
-// by a predecessor that releases its dependents early: only this kernel does that, and its
-// output is never a weight operand); the warps that read activations or alpha, or write C,
-// partials or counters, wait for the predecessor to finish (griddepcontrol.wait) first.
+// still finishing. The weight producer starts streaming immediately when the weight has more
+// than 128 rows: the only kernels that release their dependents early are this one (output of
+// at most 128 rows) and the row quantizers (only for matrices of at most 128 rows), so such a
+// weight cannot be a predecessor's output still being written. The warps that read activations
+// or alpha, or write C, partials or counters, wait for the predecessor to finish
+// (griddepcontrol.wait) first, and so does the weight producer for a weight of 128 rows or fewer.
 // Tensor memory is addressed relative to the allocation's base column and only as many columns
 // as needed are taken, so a CTA does not depend on being alone on its SM.
 //
 // Scratch ("workspace") layout: a 64 KiB block of per-tile int32 counters, then
 // [tiles][max_segments][m_pad][128] FP32 partials. Counters must be zero before the first
 // launch; every launch leaves them zero again, whatever the shape.
+//
+// Fused activation quantization (template parameter FUSED, M <= 16). The caller passes the
+// BF16 activation rows instead of codes and scales. Eight extra warps take the place of the
+// activation TMA producer: for every unit they read the 128 bytes of K of each live row (256
+// NVFP4 or 128 MXFP8 elements), quantize them with exactly the arithmetic of the row
+// quantizers in quantize.cuh, and write codes (128-byte-swizzled, as TMA would) and scale
+// bytes (atom layout) straight into the stage, then arrive on the stage's full barrier. Global
+// loads run three units ahead of the arithmetic. Every CTA quantizes the K range it multiplies,
+// so the rows are re-quantized once per weight tile a CTA owns: cheap next to the 16 KiB of
+// weights of a unit for a handful of rows, and the reason for the M <= 16 limit.
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "gemm_blockscaled.cuh"
+#include "quantize.cuh"
 
 namespace b12x_b200 {
 
@@ -65,7 +78,53 @@ struct SmallMParams {
   int issuers;             // MMA-issuing warps in use (2 when four accumulators fit, else 1)
   int tmem_cols;           // tensor memory to allocate: 128, 256 or 512 columns
   int sf_col0;             // first scale column (after the accumulators)
+  // Fused activation quantization only: BF16 rows [M, ld_x] and, for NVFP4, their global scale.
+  const __nv_bfloat16* x_src;
+  long long ld_x;
+  const float* x_gs;
+  // Non-zero: the weight stream too waits for the previous grid (weights of few rows may be a
+  // predecessor's fresh output, see the header comment).
+  int wait_for_weights;
+  // Optional per-CTA time stamps (8 x uint64 per CTA, see kTimeline*); null in normal use.
+  unsigned long long* timeline;
 };
+
+// Slots of SmallMParams::timeline per CTA (global timer, nanoseconds).
+enum : int {
+  kTimelineEntry = 0,       // first instruction of the CTA
+  kTimelineSetup = 1,       // barriers initialised, tensor memory allocated
+  kTimelineDepsDone = 2,    // griddepcontrol.wait returned in the epilogue warps
+  kTimelineFirstStage = 3,  // issuer 0 saw its first full stage
+  kTimelineLastAcc = 4,     // epilogue saw the last accumulator of the CTA complete
+  kTimelineExit = 5,        // epilogue done
+  kTimelineSm = 6,          // SM id
+  kTimelineSlots = 8,
+};
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ unsigned int sm_id() {
+  unsigned int r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+
+// Named barrier 3: the weight producer arrives without blocking once the stage barriers exist,
+// every other warp waits for it (and for each other) before touching them.
+__device__ __forceinline__ void setup_bar_arrive(uint32_t threads) {
+  asm volatile("barrier.cta.arrive 3, %0;" ::"r"(threads) : "memory");
+}
+__device__ __forceinline__ void setup_bar_sync(uint32_t threads) {
+  asm volatile("barrier.cta.sync 3, %0;" ::"r"(threads) : "memory");
+}
+// Named barrier 2 over the eight quantizer warps of the fused variant.
+__device__ __forceinline__ void quant_bar_sync() {
+  asm volatile("barrier.cta.sync 2, 256;" ::: "memory");
+}
 
 template <int KIND>
 struct SmallMTile {
@@ -90,8 +149,94 @@ __device__ __forceinline__ int owner_of_unit(int u, int units, int ctas) {
   return static_cast<int>(((static_cast<long long>(u) + 1) * ctas - 1) / units);
 }
 
+// ----------------------------------------------------------------------------------------
+// Fused activation quantization: what one quantizer warp does for one unit
+// ----------------------------------------------------------------------------------------
+// A "slot" is one warp-wide 16-byte-per-lane load, i.e. 256 consecutive BF16 elements: one row
+// of an NVFP4 unit, or two rows of an MXFP8 unit (lanes 0..15 / 16..31). Warp q of the eight
+// takes slot q and, for NVFP4 with more than eight rows, slot q + 8.
 template <int KIND>
-__global__ void __launch_bounds__(256, 1)
+struct FusedQuant {
+  static constexpr int kWarps = 8;
+  static constexpr int kSlotsPerWarp = (KIND == kNvfp4) ? 2 : 1;
+  static constexpr int kDepth = 3;  // units whose loads are in flight ahead of the arithmetic
+
+  __device__ static __forceinline__ int row_of(int slot, int lane) {
+    return (KIND == kNvfp4) ? slot : 2 * slot + (lane >> 4);
+  }
+  __device__ static __forceinline__ int elem_of(int lane) {
+    return (KIND == kNvfp4) ? lane * 8 : (lane & 15) * 8;
+  }
+
+  __device__ static __forceinline__ void load(const SmallMParams& p, int kt, int wq, int lane,
+                                              uint4 (&buf)[kSlotsPerWarp]) {
+    using T = SmallMTile<KIND>;
+#pragma unroll
+    for (int s = 0; s < kSlotsPerWarp; ++s) {
+      const int row = row_of(wq + s * kWarps, lane);
+      const int k0 = kt * T::kElemsPerStage + elem_of(lane);
+      buf[s] = (row < p.m && k0 < p.k)
+                   ? ld_nc_16(p.x_src + static_cast<long long>(row) * p.ld_x + k0)
+                   : make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  // Quantize the loaded rows into the stage: codes where TMA would have put them (row r at
+  // r * 128, 16-byte chunk j at position j ^ (r % 8)), scale bytes into the activation atoms.
+  __device__ static __forceinline__ void store(const SmallMParams& p, uint8_t* st, int wq, int lane,
+                                               const uint4 (&buf)[kSlotsPerWarp], float gs,
+                                               float gs_rcp) {
+    using T = SmallMTile<KIND>;
+    uint8_t* x_tile = st + T::kXOffset;
+    uint8_t* sf_x = st + T::kWBytes + T::kSfBytes;
+#pragma unroll
+    for (int s = 0; s < kSlotsPerWarp; ++s) {
+      const int row = row_of(wq + s * kWarps, lane);
+      // Whole warps skip slots without a live row (the shuffles below stay warp-uniform).
+      if (wq + s * kWarps >= ((KIND == kNvfp4) ? p.m : (p.m + 1) / 2)) continue;
+      float x[8];
+      unpack8<__nv_bfloat16>(buf[s], x);
+      float amax = amax8<__nv_bfloat16>(buf[s]);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      if (KIND == kNvfp4) {
+        const float sc = __fmul_rn(gs, __fdiv_rn(amax, 6.0f));
+        const uint32_t s_byte =
+            static_cast<uint32_t>(__nv_cvt_float_to_fp8(sc, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
+        const float t = __fmul_rn(e4m3_to_float(s_byte), gs_rcp);
+        const float inv = (t == 0.0f) ? 0.0f : __frcp_rn(t);
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv);
+        const uint32_t codes = e2m1x8(y);
+        if (row < p.m) {
+          const int b = lane * 4;  // byte of the row's 128
+          *reinterpret_cast<uint32_t*>(x_tile + row * 128 + ((((b >> 4) ^ (row & 7))) << 4) + (b & 15)) =
+              codes;
+          const int kb = lane >> 1;  // 16-element block inside the unit
+          if ((lane & 1) == 0) sf_x[(kb >> 2) * 512 + row * 16 + (kb & 3)] = static_cast<uint8_t>(s_byte);
+        }
+      } else {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t byte = ue8m0_from_amax(amax);
+        const float inv = ue8m0_reciprocal(byte);
+        uint2 out;
+        out.x = e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv),
+                       __fmul_rn(x[3], inv));
+        out.y = e4m3x4(__fmul_rn(x[4], inv), __fmul_rn(x[5], inv), __fmul_rn(x[6], inv),
+                       __fmul_rn(x[7], inv));
+        if (row < p.m) {
+          const int b = (lane & 15) * 8;
+          *reinterpret_cast<uint2*>(x_tile + row * 128 + ((((b >> 4) ^ (row & 7))) << 4) + (b & 15)) = out;
+          const int kb = (lane & 15) >> 2;  // 32-element block inside the unit
+          if ((lane & 3) == 0) sf_x[row * 16 + kb] = static_cast<uint8_t>(byte);
+        }
+      }
+    }
+  }
+};
+
+template <int KIND, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? 512 : 256, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
   using T = SmallMTile<KIND>;
@@ -108,38 +253,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  unsigned long long* stamps =
+      p.timeline ? p.timeline + static_cast<size_t>(blockIdx.x) * kTimelineSlots : nullptr;
+  if (stamps && threadIdx.x == 0) {
+    stamps[kTimelineEntry] = global_timer_ns();
+    stamps[kTimelineSm] = sm_id();
+  }
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.num_stages; ++s) {
-      mbar_init(&full_bar[s], 2);  // weight producer + activation producer
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&acc_full_bar[a], 2);  // one arrival per issuer warp
-      mbar_init(&acc_empty_bar[a], 4);
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&map_w);
-    tma_prefetch_desc(&map_x);
-  }
   // Let the next grid in the stream start its own prologue and weight stream now.
   grid_launch_dependents();
-  if (warp == 1) tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  // Column offset of this CTA's allocation (another CTA may hold the rest of the SM's tensor
-  // memory); the lane field must be zero.
-  const uint32_t tmem_base = *tmem_slot;
-  if ((tmem_base >> 16) != 0) {
-    if (threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
-    return;
-  }
 
   // Unit arithmetic is 32-bit in the loops (the host rejects tiles * k_tiles >= 2^31); the
   // range ends use 64-bit products once.
@@ -148,14 +270,32 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
   const int u_end = static_cast<int>(static_cast<long long>(units) * (blockIdx.x + 1) / gridDim.x);
   const uint32_t smem_u32 = smem_addr_u32(smem);
   const uint32_t x_bytes = static_cast<uint32_t>(p.m_pad) * 128u;
+  // Arrivals that complete a stage: the weight producer plus either the activation producer or
+  // the eight quantizer warps.
+  constexpr uint32_t kFullArrivals = FUSED ? 1 + FusedQuant<KIND>::kWarps : 2;
 
-  if (warp == 0 || warp == 6) {
-    // ------------------------------ TMA producers ------------------------------
-    // Two warps share the four copies of a unit so that a stage is armed in about half the
-    // time: warp 0 brings the weight tile and its scales, warp 6 the activation rows and
-    // theirs. Both arrive on the stage's full barrier with their own byte counts.
-    const bool weights = (warp == 0);
-    if (!weights) grid_dependency_wait();  // activations may come from the previous grid
+  uint32_t tmem_base = 0;
+  if (warp == 0) {
+    // ------------------------------ weight producer ------------------------------
+    // This warp owns the stage barriers: it creates them and starts the weight stream without
+    // waiting for tensor memory or for the other warps, which only need the barriers to exist
+    // by the time they pass the set-up barrier below.
+    if (lane == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < p.num_stages; ++s) {
+        mbar_init(&full_bar[s], kFullArrivals);
+        mbar_init(&empty_bar[s], 1);
+      }
+      fence_mbar_init();
+      fence_proxy_async_smem();
+      tma_prefetch_desc(&map_w);
+    }
+    __syncwarp();
+    setup_bar_arrive(blockDim.x);
+    // A weight of more than 128 rows is never the output of a predecessor that releases its
+    // dependents early (decode GEMMs write at most 128 rows, the row quantizers release early
+    // only for matrices of at most 128 rows), so its stream starts at once.
+    if (p.wait_for_weights) grid_dependency_wait();
     int stage = 0;
     uint32_t phase = 0;
     int tile = u_begin / p.k_tiles;
@@ -172,206 +312,270 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         const int katom0 = kt * T::kKAtoms;
         const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
         const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-        if (weights) {
-          mbar_arrive_expect_tx(bar, T::kWBytes + sf_bytes);
-          tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
-          bulk_load(st + T::kWBytes,
-                    p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512,
-                    sf_bytes, bar);
-        } else {
-          mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
-          tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
-          bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
-                    sf_bytes, bar);
-        }
+        mbar_arrive_expect_tx(bar, T::kWBytes + sf_bytes);
+        tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
+        bulk_load(st + T::kWBytes,
+                  p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512,
+                  sf_bytes, bar);
       }
       __syncwarp();
       if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       if (++kt == p.k_tiles) { kt = 0; ++tile; }
     }
-  } else if (warp == 1 || warp == 7) {
-    // ------------------------------ MMA issuers ------------------------------
-    // Unit number q of the CTA's range (q = u - u_begin) belongs to issuer q % issuers. Both
-    // warps walk every unit to keep the ring position; each arrives once per segment on the
-    // accumulator barrier, through a commit if it issued anything there, plainly otherwise.
-    const int me = (warp == 1) ? 0 : 1;
-    const uint32_t idesc_base = make_idesc_block_scaled(
-        128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
-    const uint32_t sfw_col = tmem_base + p.sf_col0 + me * T::kSfColsPerIssuer;
-    const uint32_t sfx_col = sfw_col + 16;
-    int stage = 0;
-    uint32_t phase = 0;
-    int seg = 0;
-    bool ok = true;
-    int u = u_begin;
-    while (u < u_end && ok) {
-      const int tile = u / p.k_tiles;
-      const int tile_end = (tile + 1) * p.k_tiles;
-      const int seg_end = tile_end < u_end ? tile_end : u_end;
-      int kt = u - tile * p.k_tiles;
-      const int acc = seg & 1;
-      if (!mbar_wait_bounded(&acc_empty_bar[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
-        *abort_flag = 1;
-        if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t d_taddr = tmem_base + static_cast<uint32_t>((acc * p.issuers + me) * p.m_pad);
-      bool first = true;
-      for (; u < seg_end; ++u, ++kt) {
-        const bool mine = (p.issuers == 2) ? (((u - u_begin) & 1) == me) : (me == 0);
-        if (mine) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
-            *abort_flag = 1;
-            if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t st = smem_u32 + stage * p.stage_bytes;
-          const int mmas =
-              min(4, (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
-          if (elect_one()) {
-            const uint64_t sf_desc = make_sf_chunk_desc(st + T::kWBytes);
-#pragma unroll
-            for (int ka = 0; ka < T::kKAtoms; ++ka) {
-              tc_copy_sf_atom(sfw_col + ka * 4, sf_desc + ((ka * 512) >> 4));
-              tc_copy_sf_atom(sfx_col + ka * 4, sf_desc + ((T::kSfBytes + ka * 512) >> 4));
-            }
-            const uint64_t wdesc = make_kmajor_sw128_desc(st);
-            const uint64_t xdesc = make_kmajor_sw128_desc(st + T::kXOffset);
-            for (int j = 0; j < mmas; ++j) {
-              const uint32_t accumulate = (first && j == 0) ? 0u : 1u;
-              if (KIND == kMxfp8)
-                tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
-                            idesc_with_sf_ids(idesc_base, j, j), accumulate, sfw_col, sfx_col);
-              else
-                tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
-                            sfw_col + j * 4, sfx_col + j * 4);
-            }
-            tc_commit(&empty_bar[stage]);
-            // Last unit of this issuer in the segment: the next one of its parity is past the end.
-            if (u + p.issuers >= seg_end) tc_commit(&acc_full_bar[acc]);
-          }
-          __syncwarp();
-          first = false;
-        }
-        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
-      }
-      if (ok && first && lane == 0) mbar_arrive(&acc_full_bar[acc]);  // nothing issued here
-      ++seg;
-    }
   } else {
-    // ------------------------------ epilogue ------------------------------
-    // alpha, C, the partial slots and the counters may be written or still read by the
-    // previous grid.
-    grid_dependency_wait();
-    const int quarter = warp & 3;
-    const int n_local = quarter * 32 + lane;          // weight row inside the tile
-    const float alpha = p.alpha ? *p.alpha : 1.0f;
-    const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
-    int seg = 0;
-    int u = u_begin;
-    while (u < u_end) {
-      const int tile = u / p.k_tiles;
-      const int tile_begin = tile * p.k_tiles;
-      const int tile_end = tile_begin + p.k_tiles;
-      const int seg_end = tile_end < u_end ? tile_end : u_end;
-      const bool whole = (u == tile_begin) && (seg_end == tile_end);
-      const int acc = seg & 1;
-      // The four epilogue warps meet at barriers further down, so they leave together or not
-      // at all: the outcome of the wait is AND-reduced across them first.
-      if (!epilogue_bar_and(mbar_wait_bounded(&acc_full_bar[acc], (seg >> 1) & 1, abort_flag))) {
-        *abort_flag = 1;
-        if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
-        break;
-      }
-      tc_fence_after_sync();
-      // Which issuers hold a partial of this segment: both, unless it is a single unit.
-      const int first_issuer = (p.issuers == 2) ? ((u - u_begin) & 1) : 0;
-      const bool both = (p.issuers == 2) && (seg_end - u >= 2);
-      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      const uint32_t taddr0 =
-          lane_base + static_cast<uint32_t>((acc * p.issuers + (both ? 0 : first_issuer)) * p.m_pad);
-      const uint32_t taddr1 = lane_base + static_cast<uint32_t>((acc * p.issuers + 1) * p.m_pad);
-      const int n_global = tile * 128 + n_local;
-      const bool n_ok = n_global < p.n;
-      int first_cta = 0, segments = 1, slot = 0;
-      if (!whole) {
-        first_cta = owner_of_unit(tile_begin, units, gridDim.x);
-        segments = owner_of_unit(tile_end - 1, units, gridDim.x) - first_cta + 1;
-        slot = static_cast<int>(blockIdx.x) - first_cta;
-      }
-      float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
-      for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
-        uint32_t raw[16];
-        tmem_load_16cols(taddr0 + c0, raw);
-        if (both) {
-          uint32_t other[16];
-          tmem_load_16cols(taddr1 + c0, other);
-          tmem_load_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            raw[i] = __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(other[i])));
-        } else {
-          tmem_load_wait();
+    if (warp == 1) {
+      if (lane == 0) {
+        for (int a = 0; a < 2; ++a) {
+          mbar_init(&acc_full_bar[a], 2);  // one arrival per issuer warp
+          mbar_init(&acc_empty_bar[a], 4);
         }
-        if (whole) {
+        fence_mbar_init();
+      }
+      __syncwarp();
+      tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
+    }
+    if (!FUSED && warp == 6 && lane == 0) tma_prefetch_desc(&map_x);
+    tc_fence_before_sync();
+    setup_bar_sync(blockDim.x);
+    tc_fence_after_sync();
+    if (stamps && threadIdx.x == 32) stamps[kTimelineSetup] = global_timer_ns();
+    // Column offset of this CTA's allocation (another CTA may hold the rest of the SM's tensor
+    // memory); the lane field must be zero. Otherwise nothing is issued and everyone leaves
+    // through the common tear-down (the producer sees the abort flag).
+    tmem_base = *tmem_slot;
+    const bool tmem_ok = (tmem_base >> 16) == 0;
+    if (!tmem_ok && threadIdx.x == 32) {
+      *abort_flag = 1;
+      if (p.status) atomicMax(p.status, kStatusTmemLayout);
+    }
+
+    if (!tmem_ok) {
+      // nothing
+    } else if (!FUSED && warp == 6) {
+      // ------------------------------ activation producer ------------------------------
+      grid_dependency_wait();  // activations may come from the previous grid
+      int stage = 0;
+      uint32_t phase = 0;
+      int kt = u_begin % p.k_tiles;
+      for (int u = u_begin; u < u_end; ++u) {
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          break;
+        }
+        if (elect_one()) {
+          uint8_t* st = smem + stage * p.stage_bytes;
+          uint64_t* bar = &full_bar[stage];
+          const int katom0 = kt * T::kKAtoms;
+          const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
+          const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
+          mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
+          tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
+          bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
+                    sf_bytes, bar);
+        }
+        __syncwarp();
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
+        if (++kt == p.k_tiles) kt = 0;
+      }
+    } else if (FUSED && warp >= 8) {
+      // ------------------------------ activation quantizers ------------------------------
+      using Q = FusedQuant<KIND>;
+      const int wq = warp - 8;
+      // Rows and scale columns nobody writes must hold finite codes and neutral scales: clear
+      // the activation part of every stage once (zero codes; scale byte 0 = +0 in E4M3, 127 =
+      // 2^0 in UE8M0).
+      {
+        const uint32_t sf_fill = (KIND == kNvfp4) ? 0u : 0x7F7F7F7Fu;
+        const int t = threadIdx.x - 256;
+        for (int s = 0; s < p.num_stages; ++s) {
+          uint8_t* st = smem + s * p.stage_bytes;
+          for (int i = t * 16; i < T::kSfBytes; i += 256 * 16)
+            *reinterpret_cast<uint4*>(st + T::kWBytes + T::kSfBytes + i) =
+                make_uint4(sf_fill, sf_fill, sf_fill, sf_fill);
+          for (int i = t * 16; i < static_cast<int>(x_bytes); i += 256 * 16)
+            *reinterpret_cast<uint4*>(st + T::kXOffset + i) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      quant_bar_sync();
+      grid_dependency_wait();  // the rows may come from the previous grid
+      float gs = 1.0f, gs_rcp = 1.0f;
+      if (KIND == kNvfp4) {
+        gs = *p.x_gs;
+        gs_rcp = (gs == 0.0f) ? 0.0f : __frcp_rn(gs);
+      }
+      const int n_units = u_end - u_begin;
+      const int kt0 = u_begin % p.k_tiles;
+      auto kt_of = [&](int q) { return (kt0 + q) % p.k_tiles; };
+      uint4 raw[Q::kDepth][Q::kSlotsPerWarp];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int mrow = c0 + i;
-            if (n_ok && mrow < p.m) {
-              const float v = __uint_as_float(raw[i]) * alpha;
-              const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
-              if (p.out_dtype == kOutBf16)
-                static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
-              else if (p.out_dtype == kOutFp16)
-                static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
-              else
-                static_cast<float*>(p.c)[idx] = v;
+      for (int d = 0; d < Q::kDepth - 1; ++d)
+        if (d < n_units) Q::load(p, kt_of(d), wq, lane, raw[d]);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int q0 = 0; q0 < n_units && ok; q0 += Q::kDepth) {
+#pragma unroll
+        for (int d = 0; d < Q::kDepth; ++d) {
+          const int q = q0 + d;
+          if (q < n_units && ok) {
+            if (q + Q::kDepth - 1 < n_units)
+              Q::load(p, kt_of(q + Q::kDepth - 1), wq, lane, raw[(d + Q::kDepth - 1) % Q::kDepth]);
+            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+              *abort_flag = 1;
+              if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+              ok = false;
+            } else {
+              Q::store(p, smem + stage * p.stage_bytes, wq, lane, raw[d], gs, gs_rcp);
+              // The tensor core reads the stage through the async proxy.
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&full_bar[stage]);
+              if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
             }
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            my_slot[static_cast<size_t>(c0 + i) * 128 + n_local] = __uint_as_float(raw[i]);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
-
-      if (!whole) {
-        // Publish the partial, count the arrival, and let the last arriver finish the tile.
-        __threadfence();
-        epilogue_bar_sync();
-        if (warp == 2 && lane == 0) {
-          const int prev = atomicAdd(&p.counters[tile], 1);
-          *last_flag = (prev == segments - 1) ? 1 : 0;
-          if (prev == segments - 1) p.counters[tile] = 0;
+    } else if (warp == 1 || warp == 7) {
+      // ------------------------------ MMA issuers ------------------------------
+      // Unit number q of the CTA's range (q = u - u_begin) belongs to issuer q % issuers. Both
+      // warps walk every unit to keep the ring position; each arrives once per segment on the
+      // accumulator barrier, through a commit if it issued anything there, plainly otherwise.
+      const int me = (warp == 1) ? 0 : 1;
+      const uint32_t idesc_base = make_idesc_block_scaled(
+          128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+      const uint32_t sfw_col = tmem_base + p.sf_col0 + me * T::kSfColsPerIssuer;
+      const uint32_t sfx_col = sfw_col + 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      int seg = 0;
+      bool ok = true;
+      bool stamped = false;
+      int u = u_begin;
+      while (u < u_end && ok) {
+        const int tile = u / p.k_tiles;
+        const int tile_end = (tile + 1) * p.k_tiles;
+        const int seg_end = tile_end < u_end ? tile_end : u_end;
+        int kt = u - tile * p.k_tiles;
+        const int acc = seg & 1;
+        if (!mbar_wait_bounded(&acc_empty_bar[acc], ((seg >> 1) & 1) ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+          break;
         }
-        epilogue_bar_sync();
-        if (*last_flag) {
-          __threadfence();
-          const float* tile_slots = p.partials + static_cast<size_t>(tile) * p.max_segments * slot_floats;
-          // Eight rows at a time so that 8 x segments loads are in flight per thread.
-          for (int m0 = 0; m0 < p.m; m0 += 8) {
-            float sum[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
-            for (int s = 0; s < segments; ++s) {
-              const float* src = tile_slots + s * slot_floats + static_cast<size_t>(m0) * 128 + n_local;
-              float v[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = (m0 + i < p.m) ? __ldcg(src + i * 128) : 0.0f;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) sum[i] += v[i];
+        tc_fence_after_sync();
+        const uint32_t d_taddr = tmem_base + static_cast<uint32_t>((acc * p.issuers + me) * p.m_pad);
+        bool first = true;
+        for (; u < seg_end; ++u, ++kt) {
+          const bool mine = (p.issuers == 2) ? (((u - u_begin) & 1) == me) : (me == 0);
+          if (mine) {
+            if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+              *abort_flag = 1;
+              if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
+              ok = false;
+              break;
             }
+            tc_fence_after_sync();
+            if (stamps && !stamped && me == 0 && lane == 0) {
+              stamps[kTimelineFirstStage] = global_timer_ns();
+              stamped = true;
+            }
+            const uint32_t st = smem_u32 + stage * p.stage_bytes;
+            const int mmas =
+                min(4, (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
+            if (elect_one()) {
+              const uint64_t sf_desc = make_sf_chunk_desc(st + T::kWBytes);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int mrow = m0 + i;
+              for (int ka = 0; ka < T::kKAtoms; ++ka) {
+                tc_copy_sf_atom(sfw_col + ka * 4, sf_desc + ((ka * 512) >> 4));
+                tc_copy_sf_atom(sfx_col + ka * 4, sf_desc + ((T::kSfBytes + ka * 512) >> 4));
+              }
+              const uint64_t wdesc = make_kmajor_sw128_desc(st);
+              const uint64_t xdesc = make_kmajor_sw128_desc(st + T::kXOffset);
+              for (int j = 0; j < mmas; ++j) {
+                const uint32_t accumulate = (first && j == 0) ? 0u : 1u;
+                if (KIND == kMxfp8)
+                  tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, j, j), accumulate, sfw_col, sfx_col);
+                else
+                  tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
+                              sfw_col + j * 4, sfx_col + j * 4);
+              }
+              tc_commit(&empty_bar[stage]);
+              // Last unit of this issuer in the segment: the next one of its parity is past the end.
+              if (u + p.issuers >= seg_end) tc_commit(&acc_full_bar[acc]);
+            }
+            __syncwarp();
+            first = false;
+          }
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
+        }
+        if (ok && first && lane == 0) mbar_arrive(&acc_full_bar[acc]);  // nothing issued here
+        ++seg;
+      }
+    } else if (warp >= 2 && warp <= 5) {
+      // ------------------------------ epilogue ------------------------------
+      // alpha, C, the partial slots and the counters may be written or still read by the
+      // previous grid.
+      grid_dependency_wait();
+      if (stamps && threadIdx.x == 64) stamps[kTimelineDepsDone] = global_timer_ns();
+      const int quarter = warp & 3;
+      const int n_local = quarter * 32 + lane;          // weight row inside the tile
+      const float alpha = p.alpha ? *p.alpha : 1.0f;
+      const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
+      int seg = 0;
+      int u = u_begin;
+      while (u < u_end) {
+        const int tile = u / p.k_tiles;
+        const int tile_begin = tile * p.k_tiles;
+        const int tile_end = tile_begin + p.k_tiles;
+        const int seg_end = tile_end < u_end ? tile_end : u_end;
+        const bool whole = (u == tile_begin) && (seg_end == tile_end);
+        const int acc = seg & 1;
+        // The four epilogue warps meet at barriers further down, so they leave together or not
+        // at all: the outcome of the wait is AND-reduced across them first.
+        if (!epilogue_bar_and(mbar_wait_bounded(&acc_full_bar[acc], (seg >> 1) & 1, abort_flag))) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        if (stamps && threadIdx.x == 64 && seg_end == u_end) stamps[kTimelineLastAcc] = global_timer_ns();
+        // Which issuers hold a partial of this segment: both, unless it is a single unit.
+        const int first_issuer = (p.issuers == 2) ? ((u - u_begin) & 1) : 0;
+        const bool both = (p.issuers == 2) && (seg_end - u >= 2);
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t taddr0 =
+            lane_base + static_cast<uint32_t>((acc * p.issuers + (both ? 0 : first_issuer)) * p.m_pad);
+        const uint32_t taddr1 = lane_base + static_cast<uint32_t>((acc * p.issuers + 1) * p.m_pad);
+        const int n_global = tile * 128 + n_local;
+        const bool n_ok = n_global < p.n;
+        int first_cta = 0, segments = 1, slot = 0;
+        if (!whole) {
+          first_cta = owner_of_unit(tile_begin, units, gridDim.x);
+          segments = owner_of_unit(tile_end - 1, units, gridDim.x) - first_cta + 1;
+          slot = static_cast<int>(blockIdx.x) - first_cta;
+        }
+        float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
+        for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+          uint32_t raw[16];
+          tmem_load_16cols(taddr0 + c0, raw);
+          if (both) {
+            uint32_t other[16];
+            tmem_load_16cols(taddr1 + c0, other);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              raw[i] = __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(other[i])));
+          } else {
+            tmem_load_wait();
+          }
+          if (whole) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int mrow = c0 + i;
               if (n_ok && mrow < p.m) {
-                const float v = sum[i] * alpha;
+                const float v = __uint_as_float(raw[i]) * alpha;
                 const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
                 if (p.out_dtype == kOutBf16)
                   static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
@@ -381,12 +585,64 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                   static_cast<float*>(p.c)[idx] = v;
               }
             }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              my_slot[static_cast<size_t>(c0 + i) * 128 + n_local] = __uint_as_float(raw[i]);
           }
         }
-        epilogue_bar_sync();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+
+        if (!whole) {
+          // Publish the partial, count the arrival, and let the last arriver finish the tile.
+          __threadfence();
+          epilogue_bar_sync();
+          if (warp == 2 && lane == 0) {
+            const int prev = atomicAdd(&p.counters[tile], 1);
+            *last_flag = (prev == segments - 1) ? 1 : 0;
+            if (prev == segments - 1) p.counters[tile] = 0;
+          }
+          epilogue_bar_sync();
+          if (*last_flag) {
+            __threadfence();
+            const float* tile_slots = p.partials + static_cast<size_t>(tile) * p.max_segments * slot_floats;
+            // Eight rows at a time so that 8 x segments loads are in flight per thread.
+            for (int m0 = 0; m0 < p.m; m0 += 8) {
+              float sum[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+              for (int s = 0; s < segments; ++s) {
+                const float* src = tile_slots + s * slot_floats + static_cast<size_t>(m0) * 128 + n_local;
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (m0 + i < p.m) ? __ldcg(src + i * 128) : 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] += v[i];
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int mrow = m0 + i;
+                if (n_ok && mrow < p.m) {
+                  const float v = sum[i] * alpha;
+                  const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+                  if (p.out_dtype == kOutBf16)
+                    static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
+                  else if (p.out_dtype == kOutFp16)
+                    static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
+                  else
+                    static_cast<float*>(p.c)[idx] = v;
+                }
+              }
+            }
+          }
+          epilogue_bar_sync();
+        }
+        u = seg_end;
+        ++seg;
       }
-      u = seg_end;
-      ++seg;
+      if (stamps && threadIdx.x == 64) stamps[kTimelineExit] = global_timer_ns();
     }
   }
 
@@ -396,7 +652,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    tmem_dealloc(*tmem_slot, static_cast<uint32_t>(p.tmem_cols));
   }
 }
 

@@ -204,17 +204,30 @@ __device__ __forceinline__ void quantize_mxfp8_chunk(const QuantChunk& c, const 
   }
 }
 
+// Both quantizers are launched with programmatic stream serialization, so in a decode step
+// (GEMM, quantize, GEMM, ...) nothing waits for a whole grid to drain and a new one to start:
+//   - griddepcontrol.wait: this grid may have been started while its predecessor on the stream
+//     was still running; nothing is read or written before the predecessor has completed.
+//   - griddepcontrol.launch_dependents, only when the quantized matrix has at most 128 rows
+//     (early_release): the next kernel on the stream, if it too was launched with programmatic
+//     serialization, may start now. In this library that is the decode GEMM, which streams its
+//     weight operand at once and waits for this grid before it reads activations. A matrix of
+//     more than 128 rows may be somebody's weight operand, so its quantization never releases
+//     early (and the decode GEMM waits before streaming a weight of 128 rows or fewer).
+__device__ __forceinline__ void quant_grid_prologue(int early_release) {
+  if (early_release) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // The launch covers rows_cover x k_cover elements: rows >= m and scale columns >= k/32 inside
 // the cover only receive the neutral scale byte 127 in the atom layout.
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_mxfp8_rows_kernel(const T* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ values,
                            uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma,
-                           int m, int k, int rows_cover, int k_cover, int k_atoms) {
-  // A decode GEMM launched next on the stream with programmatic stream serialization may start
-  // now and stream its weights while these rows are quantized; it waits for this grid to
-  // finish before it reads them. Any other successor waits for completion as usual.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                           int m, int k, int rows_cover, int k_cover, int k_atoms,
+                           int early_release) {
+  quant_grid_prologue(early_release);
   QuantChunk c;
   if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
   if (c.row < m && (c.chunk + 1) * kQuantChunkElems <= k)
@@ -318,9 +331,8 @@ __global__ void __launch_bounds__(256)
 quantize_nvfp4_rows_kernel(const T* __restrict__ src, int64_t ld_src,
                            const float* __restrict__ global_scale, uint8_t* __restrict__ packed,
                            uint8_t* __restrict__ scale_mma, int m, int k, int rows_cover,
-                           int k_cover, int k_atoms) {
-  // See quantize_mxfp8_rows_kernel: lets a following decode GEMM begin its weight stream.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                           int k_cover, int k_atoms, int early_release) {
+  quant_grid_prologue(early_release);
   QuantChunk c;
   if (!quant_chunk_of_warp(rows_cover, k_cover, c)) return;  // whole warps leave
   const float gs = *global_scale;

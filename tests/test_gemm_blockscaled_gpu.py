@@ -192,13 +192,16 @@ def test_mm_fused_quant_a_equals_quantize_then_mm():
         blockscaled.mm_fused_quant_a(seeded_bf16(1, (9, k)).to(DEV), rhs[0], rhs[1])
 
 
-@pytest.mark.parametrize("recipe", ["mxfp8_prefill", "nvfp4_row_parallel_shard"])
+@pytest.mark.parametrize("recipe", ["mxfp8_prefill", "nvfp4_row_parallel_shard",
+                                    "nvfp4_row_parallel_unsharded"])
 def test_full_size_configurations_on_sampled_rows(recipe):
-    """Full-size operands (the MXFP8 prefill GEMM 8192 x 7168 x 7168 and one 1/8 K-shard of the
-    row-parallel NVFP4 GEMM, 4096 x 7168 x 2304): quantized on the GPU by the row quantizers,
-    multiplied by the GEMM, and compared with the oracle on a sample of rows; then linearity
-    in alpha over the whole output."""
-    from gpu_util import DEV
+    """Full-size operands (the MXFP8 prefill GEMM 8192 x 7168 x 7168; the row-parallel NVFP4
+    GEMM 4096 x 7168 x 18432 on one GPU; one 1/8 K-shard of it, K = 2304): quantized on the GPU
+    by the row quantizers and multiplied by the GEMM into a NaN-prefilled output. Checked three
+    ways: a sample of rows and columns against the CPU oracle, EVERY output element against an
+    FP32 matmul of the operands dequantized with torch ops on the GPU, and linearity in alpha."""
+    from gpu_util import (DEV, assert_whole_output_close, torch_dequant_mxfp8,
+                          torch_dequant_nvfp4)
     from sparkinfer_b200._lib import layout
     from sparkinfer_b200._lib.mxfp8_rows import empty_mxfp8_rows_for_dense_gemm, quantize_mxfp8_rows
     from sparkinfer_b200.gemm import blockscaled
@@ -206,6 +209,8 @@ def test_full_size_configurations_on_sampled_rows(recipe):
 
     if recipe == "mxfp8_prefill":
         m, n, k = 8192, 7168, 7168
+    elif recipe == "nvfp4_row_parallel_unsharded":
+        m, n, k = 4096, 7168, 18432
     else:
         m, n, k = 4096, 7168, 2304
     x = seeded_bf16(42 + 2000, (m, k)).to(DEV)
@@ -223,28 +228,37 @@ def test_full_size_configurations_on_sampled_rows(recipe):
         kw = MXFP8
         a_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(x[rows].float().cpu().numpy()))
         b_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(w[cols].float().cpu().numpy()))
+        a_all = torch_dequant_mxfp8(xq.values, xq.scale_mma, m, k)
+        b_all = torch_dequant_mxfp8(wq.values, wq.scale_mma, n, k)
     else:
         gsx = O.nvfp4_global_scale(x.float().cpu().numpy())
         gsw = O.nvfp4_global_scale(w.float().cpu().numpy())
-        ops = []
+        ops, deqs = [], []
         for t, gs, r in ((x, gsx, m), (w, gsw, n)):
             plan = nvfp4.plan(r, k)
             outs = nvfp4.allocate_outputs(plan, device=DEV)
             nvfp4.run(plan=plan, x=t, global_scale=torch.tensor([gs], device=DEV), outputs=outs)
             ops.append((outs.packed_a_view, outs.scale_mma_view(r, k)))
+            deqs.append(torch_dequant_nvfp4(outs.packed_a_storage, outs.scale_flat, r, k))
         lhs, rhs = ops
+        a_all, b_all = deqs
         alpha = _alpha(gsx, gsw)
         kw = NVFP4
         pa, sa = O.quantize_nvfp4_rows(x[rows].float().cpu().numpy(), gsx)
         pb, sb = O.quantize_nvfp4_rows(w[cols].float().cpu().numpy(), gsw)
         a_deq, b_deq = O.dequantize_nvfp4(pa, sa, gsx), O.dequantize_nvfp4(pb, sb, gsw)
-    out = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **kw)
+    del x, w
+    out = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm(lhs, rhs, out, alpha=alpha, c_dtype="bfloat16", **kw)
     torch.cuda.synchronize()
     got = out[:, :, 0][torch.from_numpy(rows).to(DEV)][:, torch.from_numpy(cols).to(DEV)]
     ref = a_deq @ b_deq.T
     err = np.abs(got.float().cpu().numpy() - ref).max()
     assert err <= 1e-2 * np.abs(ref).max()
     assert err <= (2.0 ** -8 + 2.0 ** -16) * np.abs(ref).max()
+    assert_whole_output_close(out[:, :, 0], a_all, b_all, float(alpha.item()))
+    del a_all, b_all
+    torch.cuda.empty_cache()
     alpha2 = alpha * 4.0
     out2 = blockscaled.mm(lhs, rhs, alpha=alpha2, c_dtype="bfloat16", **kw)
     torch.cuda.synchronize()
@@ -346,22 +360,22 @@ def test_mm_block_fp8_rejects_bad_scales():
     ("nvfp4", 256, 256, 128), ("nvfp4", 300, 504, 640), ("nvfp4", 1024, 2048, 1024),
     ("mxfp8", 256, 512, 256), ("mxfp8", 130, 264, 384), ("mxfp8", 768, 1280, 2048),
 ])
-def test_cta_pair_kernel_matches_oracle(monkeypatch, kind, m, n, k):
+def test_cta_pair_kernel_matches_oracle(kind, m, n, k):
     """The cta_group::2 kernel (two CTAs per 256 x 256 tile) is chosen automatically only for
-    problems with at least two thirds of a wave of pair tiles; force it here on small and ragged shapes,
-    including ones whose second CTA lies entirely below the matrix."""
+    problems with at least two thirds of a wave of pair tiles; ask for its tile here on small and
+    ragged shapes, including ones whose second CTA lies entirely below the matrix."""
     from gpu_util import assert_gemm_close, mxfp8_operand, nvfp4_operand
     from sparkinfer_b200.gemm import blockscaled
 
-    monkeypatch.setenv("B12X_B200_PAIR", "1")
     if kind == "nvfp4":
         lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(m + 3 * k, (m, k), 0.25))
         rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(n + 5 * k, (n, k), 0.02))
-        out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype="bfloat16", **NVFP4)
+        out = blockscaled.mm(lhs, rhs, alpha=_alpha(gsa, gsb), c_dtype="bfloat16",
+                             mma_tiler_mn=(256, 256), **NVFP4)
     else:
         lhs, a_deq = mxfp8_operand(seeded_bf16(m + 3 * k, (m, k), 0.25))
         rhs, b_deq = mxfp8_operand(seeded_bf16(n + 5 * k, (n, k), 0.03))
-        out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **MXFP8)
+        out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", mma_tiler_mn=(256, 256), **MXFP8)
     torch.cuda.synchronize()
     assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
 
@@ -462,8 +476,16 @@ def test_full_size_block_fp8_column_parallel_shape_on_sampled_rows():
         torch.float8_e4m3fn)
     lhs = (a8.to(DEV).view(m, k, 1), sa.to(DEV).contiguous())
     rhs = (b8.to(DEV).view(n, k, 1), sb.to(DEV).contiguous())
-    out = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **BLOCK_FP8)
+    out = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm(lhs, rhs, out, c_dtype="bfloat16", **BLOCK_FP8)
     torch.cuda.synchronize()
+    # Every output element against an FP32 matmul of the operands dequantized on the GPU.
+    from gpu_util import assert_whole_output_close
+    a_all = lhs[0][:, :, 0].float() * lhs[1].repeat_interleave(128, dim=1)
+    b_all = rhs[0][:, :, 0].float() * rhs[1].repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+    assert_whole_output_close(out[:, :, 0], a_all, b_all)
+    del a_all, b_all
+    torch.cuda.empty_cache()
     a_codes = a8.view(torch.uint8).numpy()[rows]
     for cb in col_blocks:
         b_codes = b8.view(torch.uint8).numpy()[cb * 128:(cb + 1) * 128]
@@ -524,3 +546,214 @@ def test_full_size_decode_sweep_on_sampled_columns(m, decode_weight):
     assert err <= 1e-2 * np.abs(ref).max()
     assert err <= (2.0 ** -8 + 2.0 ** -16) * np.abs(ref).max()
     assert not torch.isnan(out.float()).any()
+
+
+@pytest.mark.parametrize("tile", [None, (128, 64), (128, 128), (256, 256)])
+def test_config0_nvfp4_128x4096x4096_whole_output_against_oracle(tile):
+    """Configuration 0 at its stated size: A = randn, B = randn * 0.02 (seeds 42 and 43),
+    both quantized to NVFP4 by the oracle with gs = 448 * 6 / amax, alpha = 1 / (gsA * gsB),
+    BF16 out; every output element against the oracle's dequantize-to-FP32 matmul. Runs through
+    the automatic route (the decode kernel splitting K over the idle SMs) and through each
+    tiled kernel."""
+    from gpu_util import DEV, assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 128, 4096, 4096
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(42, (m, k)))
+    rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(43, (n, k), 0.02))
+    out = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm(lhs, rhs, out, alpha=_alpha(gsa, gsb), c_dtype="bfloat16", mma_tiler_mn=tile,
+                   **NVFP4)
+    torch.cuda.synchronize()
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
+
+
+# --------------------------------------------------------------------------------------
+# Activation quantizer fused into the decode GEMM
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (5, 512, 512), (8, 4096, 4096), (8, 640, 7168),
+                                   (3, 24064, 1024), (7, 200, 384)])
+def test_mm_fused_quant_a_mxfp8_equals_quantize_then_mm_bit_for_bit(m, n, k):
+    """The in-kernel quantizer must reproduce quantize_rows + mm exactly (same codes, same scale
+    bytes, same accumulation order), and both must match the oracle. Shapes cover one CTA per
+    tile, tiles split along K over several CTAs, several tiles per CTA (the rows are
+    re-quantized per tile) and a ragged N."""
+    from gpu_util import DEV, assert_gemm_close, mxfp8_operand
+    from sparkinfer_b200._lib.mxfp8_rows import empty_mxfp8_rows_for_dense_gemm, quantize_mxfp8_rows
+    from sparkinfer_b200.gemm import blockscaled
+
+    x = seeded_bf16(15 + m, (m, k), 0.25)
+    x[0, :32] = 0  # an all-zero block: scale byte 127
+    rhs, b_deq = mxfp8_operand(seeded_bf16(16 + n, (n, k), 0.03))
+    _, a_deq = mxfp8_operand(x)
+    xd = x.to(DEV)
+    fused = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm_fused_quant_a(xd, rhs[0], rhs[1], out=fused)
+    xq = empty_mxfp8_rows_for_dense_gemm(m, k, device=DEV)
+    quantize_mxfp8_rows(xd, xq.values, xq.scale_rows, xq.scale_mma)
+    unfused = blockscaled.mm((xq.values.view(m, k, 1), xq.scale_mma), rhs, c_dtype="bfloat16", **MXFP8)
+    torch.cuda.synchronize()
+    assert_gemm_close(fused[:, :, 0], a_deq @ b_deq.T)
+    assert torch.equal(fused.view(torch.int16), unfused.view(torch.int16))
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (4, 512, 512), (16, 14336, 4096), (13, 1024, 2048),
+                                   (9, 24064, 1024), (16, 200, 320), (2, 4096, 7168)])
+def test_mm_fused_quant_a_nvfp4_equals_quantize_then_mm_bit_for_bit(m, n, k):
+    """NVFP4 variant of the fused activation quantizer (M <= 16), against quantization.nvfp4 +
+    mm (bit for bit) and the oracle. K = 320 ends in a half-filled unit; zero rows and a zero
+    block exercise the zero-scale path."""
+    from gpu_util import DEV, assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+    from sparkinfer_b200.quantization import nvfp4
+
+    x = seeded_bf16(25 + m, (m, k))
+    x[m - 1, 16:48] = 0
+    rhs, gsw, b_deq = nvfp4_operand(seeded_bf16(26 + n, (n, k), 0.02))
+    _, gsx, a_deq = nvfp4_operand(x)
+    xd = x.to(DEV)
+    gs = torch.tensor([gsx], dtype=torch.float32, device=DEV)
+    alpha = _alpha(gsx, gsw)
+    fused = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm_fused_quant_a_nvfp4(xd, gs, rhs[0], rhs[1], alpha=alpha, out=fused)
+    plan = nvfp4.plan(m, k)
+    outs = nvfp4.allocate_outputs(plan, device=DEV)
+    nvfp4.run(plan=plan, x=xd, global_scale=gs, outputs=outs)
+    unfused = blockscaled.mm((outs.packed_a_view, outs.scale_mma_view(m, k)), rhs, alpha=alpha,
+                             c_dtype="bfloat16", **NVFP4)
+    torch.cuda.synchronize()
+    assert_gemm_close(fused[:, :, 0], a_deq @ b_deq.T)
+    assert torch.equal(fused.view(torch.int16), unfused.view(torch.int16))
+    # A live global scale: CUDA-graph replays read it (and alpha) at run time.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        blockscaled.mm_fused_quant_a_nvfp4(xd, gs, rhs[0], rhs[1], alpha=alpha, out=fused)
+    gs.mul_(0.5)
+    alpha.mul_(2.0)
+    graph.replay()
+    nvfp4.run(plan=plan, x=xd, global_scale=gs, outputs=outs)
+    unfused2 = blockscaled.mm((outs.packed_a_view, outs.scale_mma_view(m, k)), rhs, alpha=alpha,
+                              c_dtype="bfloat16", **NVFP4)
+    torch.cuda.synchronize()
+    assert torch.equal(fused.view(torch.int16), unfused2.view(torch.int16))
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
+
+
+def test_mm_fused_quant_a_nvfp4_rejects_what_the_kernel_cannot_do():
+    from gpu_util import DEV
+    from sparkinfer_b200.gemm import blockscaled
+
+    b = torch.zeros((128, 128, 1), dtype=torch.uint8, device=DEV)
+    sfb = torch.zeros((512 * 4,), dtype=torch.uint8, device=DEV)
+    gs = torch.ones(1, device=DEV)
+    with pytest.raises(ValueError, match="1<=M<=16"):
+        blockscaled.mm_fused_quant_a_nvfp4(torch.zeros((17, 256), dtype=torch.bfloat16, device=DEV),
+                                           gs, b, sfb)
+    with pytest.raises(ValueError, match="contiguous BF16"):
+        blockscaled.mm_fused_quant_a_nvfp4(torch.zeros((4, 256), dtype=torch.float16, device=DEV),
+                                           gs, b, sfb)
+    with pytest.raises(ValueError, match="global_scale"):
+        blockscaled.mm_fused_quant_a_nvfp4(torch.zeros((4, 256), dtype=torch.bfloat16, device=DEV),
+                                           torch.ones(2, device=DEV), b, sfb)
+
+
+# --------------------------------------------------------------------------------------
+# Stream ordering of the kernels that start before their predecessor has finished
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [128, 256])
+def test_decode_gemm_right_after_the_quantization_of_its_own_weight(n):
+    """The row quantizers release the next kernel early only for matrices of at most 128 rows,
+    and the decode GEMM waits for its predecessor before streaming a weight of at most 128
+    rows, so a weight quantized by the kernel launched immediately before the GEMM is never
+    read half-written. Both sides of the 128-row rule, repeated to give a race a chance."""
+    from gpu_util import DEV, assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200.gemm import blockscaled
+    from sparkinfer_b200.quantization import nvfp4
+
+    m, k = 4, 8192
+    w = seeded_bf16(70 + n, (n, k), 0.02)
+    lhs, gsx, a_deq = nvfp4_operand(seeded_bf16(71, (m, k)))
+    _, gsw, b_deq = nvfp4_operand(w)
+    wd = w.to(DEV)
+    gs = torch.tensor([gsw], dtype=torch.float32, device=DEV)
+    plan = nvfp4.plan(n, k)
+    outs = nvfp4.allocate_outputs(plan, device=DEV)
+    alpha = _alpha(gsx, gsw)
+    ref = a_deq @ b_deq.T
+    for _ in range(5):
+        outs.packed_a_storage.zero_()
+        outs.scale_storage.zero_()
+        nvfp4.run(plan=plan, x=wd, global_scale=gs, outputs=outs)
+        out = blockscaled.mm(lhs, (outs.packed_a_view, outs.scale_mma_view(n, k)), alpha=alpha,
+                             c_dtype="bfloat16", **NVFP4)
+        torch.cuda.synchronize()
+        assert_gemm_close(out[:, :, 0], ref)
+
+
+def test_decode_gemms_on_two_streams_use_separate_workspaces():
+    """Every stream gets its own partial-sum workspace, so decode GEMMs whose tiles are split
+    over several CTAs may run on two streams at once."""
+    from gpu_util import DEV, nvfp4_operand
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 8, 1024, 8192   # 8 tiles, 18 CTAs each: every tile goes through the workspace
+    lhs, gsa, _ = nvfp4_operand(seeded_bf16(81, (m, k)))
+    weights = [nvfp4_operand(seeded_bf16(82 + i, (n, k), 0.02)) for i in range(2)]
+    alphas = [_alpha(gsa, w[1]) for w in weights]
+    want = []
+    for (rhs, _, _), alpha in zip(weights, alphas):
+        want.append(blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **NVFP4))
+        torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=DEV) for _ in range(2)]
+    outs = [torch.empty_like(w) for w in want]
+    for _ in range(3):
+        for o in outs:
+            o.zero_()
+        torch.cuda.synchronize()
+        for rep in range(20):
+            for s, (rhs, _, _), alpha, o in zip(streams, weights, alphas, outs):
+                blockscaled.mm(lhs, rhs, o, alpha=alpha, c_dtype="bfloat16", stream=s, **NVFP4)
+        torch.cuda.synchronize()
+        for o, w_ in zip(outs, want):
+            assert torch.equal(o, w_)
+    keys = {key for key in launch._WORKSPACES if key[0] == 0}
+    assert len({k_[1] for k_ in keys}) >= 3  # the default stream and the two side streams
+    launch.check_kernel_status(DEV)
+
+
+def test_a_timed_out_wait_is_reported_and_the_next_gemm_is_correct():
+    """Every device wait in the library is bounded and reports through a status word. The
+    library's self-test kernel waits (4096 polls) on a barrier nothing completes, with no copy
+    in flight, and raises the word exactly as a GEMM kernel would; the host must turn that into
+    an exception, clear the word and the decode counters, and keep working."""
+    from gpu_util import DEV, assert_gemm_close, nvfp4_operand
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 8, 1024, 4096
+    lhs, gsa, a_deq = nvfp4_operand(seeded_bf16(91, (m, k)))
+    rhs, gsb, b_deq = nvfp4_operand(seeded_bf16(92, (n, k), 0.02))
+    alpha = _alpha(gsa, gsb)
+    blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **NVFP4)  # creates the workspace
+    launch.check_kernel_status(DEV)
+    launch.selftest_wait_timeout(DEV, 4096)
+    torch.cuda.synchronize()
+    assert int(launch.status_buffer(DEV)[0].item()) == 2
+    # Pretend the kernel that gave up had left a tile counter behind.
+    work = launch.smallm_workspace(1, m, n, k, DEV)
+    work[:4].fill_(1)
+    with pytest.raises(RuntimeError, match="MMA issuer timed out"):
+        launch.check_kernel_status(DEV)
+    assert int(launch.status_buffer(DEV)[0].item()) == 0
+    assert int(work[:65536].count_nonzero()) == 0
+    launch.check_kernel_status(DEV)  # cleared: does not raise again
+    out = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **NVFP4)
+    torch.cuda.synchronize()
+    assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
+    launch.check_kernel_status(DEV)

@@ -59,9 +59,9 @@ def _cases():
 
 
 @pytest.mark.parametrize("index,kind,m,n,k,route,dtype", _cases())
-def test_gemm_matches_fp32_reference_on_random_shapes(monkeypatch, index, kind, m, n, k, route, dtype):
+def test_gemm_matches_fp32_reference_on_random_shapes(index, kind, m, n, k, route, dtype):
     from sparkinfer_b200._lib import launch
-    from sparkinfer_b200._native import KIND_MXFP8, KIND_NVFP4
+    from sparkinfer_b200._native import BLOCK_N_PAIR, KIND_MXFP8, KIND_NVFP4
 
     dev = torch.device("cuda:0")
     gen = torch.Generator(device=dev).manual_seed(1000 + index)
@@ -71,12 +71,10 @@ def test_gemm_matches_fp32_reference_on_random_shapes(monkeypatch, index, kind, 
     ldc = n + (8 if index % 3 == 0 else 0)  # sometimes a padded output pitch
     out = torch.full((m, ldc), float("nan"), dtype=dtype, device=dev)
     kwargs = {}
-    monkeypatch.delenv("B12X_B200_PAIR", raising=False)
     if route.startswith("bn"):
         kwargs["block_n"] = int(route[2:])
     elif route == "pair":
-        monkeypatch.setenv("B12X_B200_PAIR", "1")
-        kwargs["small_m"] = False
+        kwargs["block_n"] = BLOCK_N_PAIR
     elif route == "decode":
         kwargs["small_m"] = True
     launch.gemm_blockscaled(KIND_MXFP8 if kind == "mxfp8" else KIND_NVFP4, a, sfa, b, sfb, out,

@@ -5,9 +5,10 @@ decode GEMM (all memory already handed to their own pool, or the calling thread 
 stream capture), so ``b12x_b200_gemm_blockscaled_smallm_noalloc`` carries its partial-sum
 scratch inside the library. This test checks that it produces the same bytes as the
 caller-workspace entry point, twice in a row on different inputs (the built-in scratch keeps
-the previous call's contents), and that a shape beyond the built-in capacity is refused with
-a readable message. The file name sorts last so a run that stops at the first failure has
-already run every other test.
+the previous call's contents), that its results match the CPU oracle when a call that splits
+many tiles is followed by one that splits few, and that a shape beyond the built-in capacity
+is refused with a readable message and leaves nothing on the stream. The file name sorts last
+so a run that stops at the first failure has already run every other test.
 """
 
 from __future__ import annotations
@@ -66,6 +67,42 @@ def test_noalloc_entry_point_matches_workspace_entry_point_twice():
         assert float(got.float().abs().max()) > 0
         # Same kernel, same deterministic reduction order: equal bytes (tolerance zero).
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {call} differs"
+
+
+def test_noalloc_entry_point_matches_the_oracle_after_a_larger_problem():
+    """A call with 32 split tiles, then one with 4: the second must not be disturbed by what the
+    first left in the shared scratch (counters or partial sums). Both against the oracle's
+    dequantize-to-FP32 matmul of the same random codes and scale bytes."""
+    from gpu_util import assert_gemm_close
+    from oracle import blockscaled_oracle as O
+    from sparkinfer_b200 import _native
+
+    lib = _native.load()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    kind = _native.KIND_NVFP4
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    rng = np.random.default_rng(99)
+    for m, n, k in ((16, 4096, 2048), (3, 512, 4096)):
+        assert (lib.b12x_b200_gemm_smallm_workspace_bytes(kind, m, n, k, 0)
+                <= lib.b12x_b200_gemm_smallm_noalloc_capacity_bytes())
+        ops = []
+        for rows in (m, n):
+            packed = rng.integers(0, 256, (rows, k // 2), dtype=np.uint8)
+            scales = rng.integers(0x30, 0x40, (rows, k // 16), dtype=np.uint8)
+            ops.append((torch.from_numpy(packed).to(dev),
+                        torch.from_numpy(O.swizzle_scales(scales, 0)).to(dev),
+                        O.dequantize_nvfp4(packed, scales, np.float32(1.0))))
+        (x, sfx, x_deq), (w, sfw, w_deq) = ops
+        got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev)
+        rc = lib.b12x_b200_gemm_blockscaled_smallm_noalloc(
+            kind, x.data_ptr(), sfx.data_ptr(), w.data_ptr(), sfw.data_ptr(), got.data_ptr(),
+            _native.DT_BF16, None, m, n, k, n, 0, status.data_ptr(), stream)
+        _native.check(rc, "smallm_noalloc")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        assert_gemm_close(got, x_deq @ w_deq.T)
 
 
 def test_noalloc_entry_point_refuses_shapes_beyond_its_scratch():
