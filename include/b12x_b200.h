@@ -83,6 +83,29 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
                                int sm_count, int* status, b12x_b200_stream_t stream);
 
 /*
+ * b12x_b200_gemm_blockscaled with caller-owned scratch. The CTA-pair kernel (chosen for large
+ * problems, or with B12X_B200_BLOCK_N_PAIR) runs whole rounds of 256 x 256 tiles over the SM
+ * pairs; when the tiles left for the last round would occupy at most half of the pairs, it cuts
+ * them along K over all pairs instead and adds the FP32 partial tiles up through this scratch
+ * (in a fixed order: results do not depend on timing). Without scratch, or where no split
+ * applies, the call is exactly b12x_b200_gemm_blockscaled. Plays the role of the reference's
+ * split-K / stream-K policy (b12x/_lib/dense_gemm.py:387-454, 6671-6894) for large M.
+ *
+ *   workspace  NULL, or at least b12x_b200_gemm_blockscaled_workspace_bytes(...) bytes (0 means
+ *              the shape needs none), 16-byte aligned. Same buffer and same rules as the decode
+ *              GEMM's workspace: its first 64 KiB must be zero before the first launch that
+ *              uses it, every launch leaves them zero, and launches that share it must not
+ *              overlap on the device.
+ */
+int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
+                                                   int block_n, int sm_count);
+int b12x_b200_gemm_blockscaled_ws(int kind, const void* a, const void* sfa, const void* b,
+                                  const void* sfb, void* c, int c_dtype, const float* alpha,
+                                  int64_t m, int64_t n, int64_t k, int64_t ldc, int block_n,
+                                  int sm_count, void* workspace, int64_t workspace_bytes,
+                                  int* status, b12x_b200_stream_t stream);
+
+/*
  * Decode-shape (1 <= M <= 128) variant of b12x_b200_gemm_blockscaled: the weight matrix is
  * streamed once, split evenly over all SMs along N and K (stream-K), and partial sums meet in
  * a caller-owned FP32 workspace. Stands in for the reference's small-M split-K policy and its

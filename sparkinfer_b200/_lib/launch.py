@@ -119,18 +119,13 @@ def _require_cuda(name: str, t: torch.Tensor) -> None:
         raise ValueError(f"{name} must be on CUDA")
 
 
-def smallm_workspace(kind: int, m: int, n: int, k: int, device: torch.device,
-                     sm_count: int = 0, stream_int: int | None = None) -> torch.Tensor:
-    """Scratch of the decode-shape kernel (per-tile counters + FP32 partial tiles) for launches
-    on one stream of one device. Launches on the same stream run in order and share a buffer;
-    every stream has its own, so decode GEMMs on different streams never meet in one. A buffer
-    is created zeroed the first time a stream needs one, or a larger one (so warm up before
-    CUDA-graph capture), and is never released while the process lives."""
+def stream_workspace(need: int, device: torch.device, stream_int: int | None = None) -> torch.Tensor:
+    """Scratch (counters + FP32 partial tiles) for the kernels that split work along K, for
+    launches on one stream of one device. Launches on the same stream run in order and share a
+    buffer; every stream has its own, so such kernels on different streams never meet in one. A
+    buffer is created zeroed the first time a stream needs one, or a larger one (so warm up
+    before CUDA-graph capture), and is never released while the process lives."""
     index = device.index if device.index is not None else torch.cuda.current_device()
-    with torch.cuda.device(index):
-        need = int(_native.load().b12x_b200_gemm_smallm_workspace_bytes(kind, m, n, k, sm_count))
-    if need < 0:
-        raise _native.NativeLibraryError(f"no decode-shape plan for M={m}, N={n}, K={k}")
     if stream_int is None:
         stream_int = torch.cuda.current_stream(torch.device("cuda", index)).cuda_stream
     key = (index, int(stream_int))
@@ -153,16 +148,23 @@ def smallm_workspace(kind: int, m: int, n: int, k: int, device: torch.device,
         return bufs[-1]
 
 
+def smallm_workspace(kind: int, m: int, n: int, k: int, device: torch.device,
+                     sm_count: int = 0, stream_int: int | None = None) -> torch.Tensor:
+    """:func:`stream_workspace` sized for the decode-shape kernel on (M, N, K)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(index):
+        need = int(_native.load().b12x_b200_gemm_smallm_workspace_bytes(kind, m, n, k, sm_count))
+    if need < 0:
+        raise _native.NativeLibraryError(f"no decode-shape plan for M={m}, N={n}, K={k}")
+    return stream_workspace(need, device, stream_int)
+
+
 def route_to_decode_kernel(m: int, n: int, device: torch.device, sm_count: int = 0) -> bool:
-    """Whether an unforced GEMM of ``m`` rows goes to the weight-streaming decode kernel: always
-    up to 64 rows, and up to 128 rows while the tiled kernel's 128 x 64 tiles would leave more
-    than half of the SMs without work (the decode kernel splits K over the idle ones)."""
-    if m <= SMALL_M_AUTO:
-        return True
-    if m > SMALL_M_MAX:
-        return False
-    sms = sm_count if sm_count > 0 else torch.cuda.get_device_properties(device).multi_processor_count
-    return -(-n // 64) * 2 < sms
+    """Whether an unforced GEMM of ``m`` rows goes to the weight-streaming decode kernel: up to
+    64 rows. With 65..128 rows the decode kernel (one issuing warp, 128 padded rows per stage)
+    was measured far behind the tiled kernel even on a grid the tiled kernel fills less than
+    half (128 x 4096 x 4096: 25 us against 9 us), so it is only used there on request."""
+    return 0 < m <= SMALL_M_AUTO
 
 
 def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
@@ -193,13 +195,19 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
                 status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
         _native.check(rc, "b12x_b200_gemm_blockscaled_smallm")
         return
+    lib = _native.load()
     with torch.cuda.device(dev):
-        rc = _native.load().b12x_b200_gemm_blockscaled(
+        # Scratch for the CTA-pair kernel's split last round (0 when the shape has none).
+        need = int(lib.b12x_b200_gemm_blockscaled_workspace_bytes(kind, m, n, k, block_n, sm_count))
+    work = stream_workspace(need, dev, stream_int) if need > 0 else None
+    with torch.cuda.device(dev):
+        rc = lib.b12x_b200_gemm_blockscaled_ws(
             kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
             _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
             m, n, k, ldc if ldc is not None else n, block_n, sm_count,
+            work.data_ptr() if work is not None else None, work.numel() if work is not None else 0,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-    _native.check(rc, "b12x_b200_gemm_blockscaled")
+    _native.check(rc, "b12x_b200_gemm_blockscaled_ws")
 
 
 def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tensor | None,
@@ -299,6 +307,7 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
 __all__ = [
     "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled",
     "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
-    "route_to_decode_kernel", "smallm_workspace", "quantize_mxfp8_rows", "quantize_nvfp4_rows",
+    "route_to_decode_kernel", "smallm_workspace", "stream_workspace", "quantize_mxfp8_rows",
+    "quantize_nvfp4_rows",
     "KERNEL_STATUS_TEXT",
 ]

@@ -35,6 +35,13 @@ SIGNATURES = {
         [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
          _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_void_p],
     ),
+    "b12x_b200_gemm_blockscaled_workspace_bytes": (
+        _c_i64, [_c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
+    "b12x_b200_gemm_blockscaled_ws": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_i64, _c_void_p, _c_void_p],
+    ),
     "b12x_b200_gemm_smallm_workspace_bytes": (_c_i64, [_c_int, _c_i64, _c_i64, _c_i64, _c_int]),
     "b12x_b200_gemm_blockscaled_smallm": (
         _c_int,

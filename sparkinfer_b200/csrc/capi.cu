@@ -72,6 +72,27 @@ int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return B12X_B200_OK;
 }
 
+// Row-major BF16 matrix [rows, cols] with row pitch `ld` elements -> unswizzled boxes of
+// box_cols x box_rows elements (the raw activation rows of the fused-quantizer decode GEMM).
+int make_raw_rows_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
+         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(raw rows) failed (%d)", int(r));
+    return B12X_B200_ERR_CUDA;
+  }
+  return B12X_B200_OK;
+}
+
 // Row-major 2-byte matrix [rows, cols] with row pitch `ld` elements -> boxes of 64 columns
 // (128 bytes) x 128 rows, 128-byte swizzle; used for TMA stores of BF16/FP16 outputs.
 int make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
@@ -124,7 +145,6 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // They exist for measurements of kernel variants; none is part of the interface.
 struct Switches {
   bool decode_overlap = true;   // programmatic stream serialization for decode GEMMs / quantizers
-  bool decode_full_grid = false;  // one decode CTA per SM even when that splits every tile
   bool pair_tail_split = true;  // split-K the last partial round of the CTA-pair kernel
 };
 
@@ -132,7 +152,6 @@ const Switches& switches() {
   static const Switches sw = [] {
     Switches v;
     if (const char* e = getenv("B12X_B200_DECODE_OVERLAP")) v.decode_overlap = atoi(e) != 0;
-    if (const char* e = getenv("B12X_B200_DECODE_FULL_GRID")) v.decode_full_grid = atoi(e) != 0;
     if (const char* e = getenv("B12X_B200_PAIR_TAIL_SPLIT")) v.pair_tail_split = atoi(e) != 0;
     return v;
   }();
@@ -186,7 +205,7 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
 // CTA-pair kernel: clusters of two CTAs, one 256 x BN tile per pair.
 template <int KIND, int BN>
 int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
-                     const GemmParams& p, int pairs, cudaStream_t stream) {
+                     const GemmParams& p, const PairTail& tail, int pairs, cudaStream_t stream) {
   using T = PairTile<KIND, BN>;
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
@@ -212,7 +231,7 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t err =
-      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN>, map_a, map_b, map_c, p);
+      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN>, map_a, map_b, map_c, p, tail);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled_pair launch");
   return B12X_B200_OK;
 }
@@ -251,6 +270,43 @@ int dispatch_block_n(int bn, const CUtensorMap& map_a, const CUtensorMap& map_b,
   }
 }
 
+// Workspace layout shared by the kernels that need scratch (one buffer per stream serves them
+// all, launches on a stream being ordered): 60 KiB of per-tile counters of the decode kernel,
+// 4 KiB of counters of the CTA-pair kernel's split tail, then FP32 partial tiles from 64 KiB on.
+constexpr size_t kSmallMCounterBytes = 60 * 1024;
+constexpr size_t kPairCounterOffset = kSmallMCounterBytes;
+constexpr size_t kPairCounterBytes = 4 * 1024;
+constexpr size_t kWorkspaceHeaderBytes = kPairCounterOffset + kPairCounterBytes;
+
+// Whether (and how) the CTA-pair kernel splits its last, partial round along K: `segments` per
+// leftover tile (0 = no split) and the scratch it needs.
+struct PairTailPlan {
+  int pairs = 0, left = 0, segments = 0;
+  size_t bytes = 0;
+};
+
+PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int sms) {
+  PairTailPlan t;
+  const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  t.pairs = int(tiles < sms / 2 ? tiles : sms / 2);
+  if (t.pairs < 1 || !switches().pair_tail_split) return t;
+  const int64_t rounds = tiles / t.pairs;
+  t.left = int(tiles - rounds * t.pairs);
+  const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
+  const int64_t k_tiles = (k + elems_per_stage - 1) / elems_per_stage;
+  // Split only when the leftover tiles would keep at most half of the pairs busy, and never
+  // below two k-tiles per segment.
+  if (t.left == 0 || t.left * 2 > t.pairs || size_t(t.left) * 2 * sizeof(int) > kPairCounterBytes)
+    return t;
+  int64_t seg = t.pairs / t.left;
+  if (seg > k_tiles / 2) seg = k_tiles / 2;
+  if (seg < 2) return t;
+  t.segments = int(seg);
+  t.bytes = kWorkspaceHeaderBytes +
+            size_t(t.left) * t.segments * 2 * kPairPartialFloats * sizeof(float);
+  return t;
+}
+
 }  // namespace
 }  // namespace b12x_b200
 
@@ -260,11 +316,12 @@ extern "C" const char* b12x_b200_version(void) { return "b12x_b200 0.1.0 sm_100a
 
 extern "C" const char* b12x_b200_last_error(void) { return g_last_error; }
 
-extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const void* b,
-                                          const void* sfb, void* c, int c_dtype,
-                                          const float* alpha, int64_t m, int64_t n, int64_t k,
-                                          int64_t ldc, int block_n, int sm_count, int* status,
-                                          b12x_b200_stream_t stream) {
+namespace {
+
+int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* b, const void* sfb,
+                          void* c, int c_dtype, const float* alpha, int64_t m, int64_t n, int64_t k,
+                          int64_t ldc, int block_n, int sm_count, void* workspace,
+                          int64_t workspace_bytes, int* status, b12x_b200_stream_t stream) {
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
@@ -342,13 +399,62 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
     p.tiles_n = int((n + 255) / 256);
     p.group_m = 8;
     const int pairs = int(pair_tiles < sms / 2 ? pair_tiles : sms / 2);
+    // The last partial round is split along K when the caller brought scratch for it.
+    PairTail tail;
+    tail.counters = nullptr;
+    tail.partials = nullptr;
+    tail.segments = 0;
+    const PairTailPlan tp = plan_pair_tail(kind, m, n, k, sms);
+    if (workspace && tp.segments >= 2 && workspace_bytes >= int64_t(tp.bytes) &&
+        aligned16(workspace)) {
+      tail.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kPairCounterOffset);
+      tail.partials =
+          reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kWorkspaceHeaderBytes);
+      tail.segments = tp.segments;
+    }
     if (kind == B12X_B200_KIND_MXFP8)
-      return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, pairs, s);
-    return launch_gemm_pair<kNvfp4, 256>(map_a, map_b, map_c, p, pairs, s);
+      return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
+    return launch_gemm_pair<kNvfp4, 256>(map_a, map_b, map_c, p, tail, pairs, s);
   }
   if (kind == B12X_B200_KIND_MXFP8)
     return dispatch_block_n<kMxfp8>(bn, map_a, map_b, map_c, p, grid, s);
   return dispatch_block_n<kNvfp4>(bn, map_a, map_b, map_c, p, grid, s);
+}
+
+}  // namespace
+
+extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const void* b,
+                                          const void* sfb, void* c, int c_dtype,
+                                          const float* alpha, int64_t m, int64_t n, int64_t k,
+                                          int64_t ldc, int block_n, int sm_count, int* status,
+                                          b12x_b200_stream_t stream) {
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
+                               sm_count, nullptr, 0, status, stream);
+}
+
+extern "C" int b12x_b200_gemm_blockscaled_ws(int kind, const void* a, const void* sfa,
+                                             const void* b, const void* sfb, void* c, int c_dtype,
+                                             const float* alpha, int64_t m, int64_t n, int64_t k,
+                                             int64_t ldc, int block_n, int sm_count,
+                                             void* workspace, int64_t workspace_bytes, int* status,
+                                             b12x_b200_stream_t stream) {
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
+                               sm_count, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n,
+                                                              int64_t k, int block_n, int sm_count) {
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  DeviceInfo info;
+  if (device_info(&info) != B12X_B200_OK) return -1;
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const bool use_pair = (block_n == B12X_B200_BLOCK_N_PAIR) ||
+                        ((block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms));
+  if (!use_pair || sms < 2) return 0;
+  const PairTailPlan tp = plan_pair_tail(kind, m, n, k, sms);
+  return tp.segments >= 2 ? int64_t(tp.bytes) : 0;
 }
 
 extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src,
@@ -499,18 +605,16 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
 
 namespace {
 
-// The workspace starts with a fixed-size block of per-tile counters, so the counters of every
-// shape live at the same offsets and stay zero between launches of different shapes.
-constexpr size_t kSmallMCounterBytes = 64 * 1024;
-
 struct SmallMPlan {
   int m_pad, tiles, k_tiles, k_atoms, grid, max_segments, stages, stage_bytes;
-  int issuers, sf_col0, tmem_cols;
+  int issuers, sf_col0, tmem_cols, raw_rows;
   size_t partial_bytes, total_bytes;
 };
 
-// Geometry of the decode-shape kernel for (kind, m, n, k) on `sms` SMs.
-int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* out) {
+// Geometry of the decode-shape kernel for (kind, m, n, k) on `sms` SMs; `fused` adds the raw
+// BF16 activation rows (8 or 16 of them) to every stage. The workspace need does not depend on
+// `fused`.
+int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, SmallMPlan* out) {
   if (m < 1 || m > 128) return fail(B12X_B200_ERR_UNSUPPORTED, "decode kernel needs 1 <= M <= 128");
   if (n < 1 || k < 1 || n > INT32_MAX || k > INT32_MAX)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
@@ -527,7 +631,9 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   // Grid: with no more tiles than SMs, a whole number of CTAs per tile (capped by the k-tiles a
   // tile has) keeps every CTA range inside one tile, so a tile that gets a single CTA needs no
   // partial sums at all; with more tiles than SMs one CTA per SM streams an equal share.
-  if (pl.tiles <= sms && !switches().decode_full_grid) {
+  // (One CTA per SM regardless, which splits every tile of a 112-tile problem over two or three
+  // CTAs, was measured slower: 12.6 us against 10.9 us for 16 x 14336 x 4096.)
+  if (pl.tiles <= sms) {
     int per_tile = sms / pl.tiles;
     if (per_tile > pl.k_tiles) per_tile = pl.k_tiles;
     pl.grid = pl.tiles * per_tile;
@@ -540,6 +646,14 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   pl.max_segments = int(seg);
   pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
                                                   : SmallMTile<kNvfp4>::stage_bytes(pl.m_pad);
+  pl.raw_rows = 0;
+  if (fused) {
+    pl.raw_rows = m <= 8 ? 8 : 16;
+    const int x_offset = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::kXOffset
+                                                        : SmallMTile<kNvfp4>::kXOffset;
+    const int raw_bytes = pl.raw_rows * elems_per_stage * 2;
+    pl.stage_bytes = ((x_offset + pl.m_pad * 128 + raw_bytes + 1023) / 1024) * 1024;
+  }
   // Two issuing warps when four accumulators fit beside the scales (up to 64 padded rows).
   // The ring takes all of the SM's shared memory: a CTA sized for two per SM (so that the
   // next decode GEMM could run beside this one) was measured slower than a deep ring.
@@ -559,7 +673,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, SmallMPlan* 
   pl.partial_bytes = size_t(pl.tiles) * pl.max_segments * pl.m_pad * 128 * sizeof(float);
   if (size_t(pl.tiles) * sizeof(int) > kSmallMCounterBytes)
     return fail(B12X_B200_ERR_UNSUPPORTED, "N too large for the decode kernel's counter block");
-  pl.total_bytes = kSmallMCounterBytes + pl.partial_bytes;
+  pl.total_bytes = kWorkspaceHeaderBytes + pl.partial_bytes;
   *out = pl;
   return B12X_B200_OK;
 }
@@ -661,7 +775,7 @@ int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empt
   if (rc != B12X_B200_OK) return rc;
   if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
   *sms_out = (a.sm_count > 0 && a.sm_count < info.sm_count) ? a.sm_count : info.sm_count;
-  return plan_smallm(a.kind, a.m, a.n, a.k, *sms_out, plan);
+  return plan_smallm(a.kind, a.m, a.n, a.k, *sms_out, fused, plan);
 }
 
 int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
@@ -677,7 +791,10 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   int rc = make_operand_map(&map_w, a.w, uint64_t(a.n), uint64_t(row_bytes), 128);
   if (rc != B12X_B200_OK) return rc;
   if (fused) {
-    map_x = map_w;  // unused by the fused kernel
+    const uint32_t elems = (a.kind == B12X_B200_KIND_MXFP8) ? 128u : 256u;
+    rc = make_raw_rows_map(&map_x, a.x_src, uint64_t(a.m), uint64_t(a.k), uint64_t(a.ld_x), elems,
+                           uint32_t(pl.raw_rows));
+    if (rc != B12X_B200_OK) return rc;
   } else {
     rc = make_operand_map(&map_x, a.x, uint64_t(a.m), uint64_t(row_bytes), uint32_t(pl.m_pad));
     if (rc != B12X_B200_OK) return rc;
@@ -691,7 +808,7 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.alpha = a.alpha;
   p.status = a.status;
   p.counters = static_cast<int*>(workspace);
-  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSmallMCounterBytes);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kWorkspaceHeaderBytes);
   p.m = int(a.m);
   p.n = int(a.n);
   p.k = int(a.k);
@@ -707,9 +824,8 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.issuers = pl.issuers;
   p.tmem_cols = pl.tmem_cols;
   p.sf_col0 = pl.sf_col0;
-  p.x_src = static_cast<const __nv_bfloat16*>(a.x_src);
-  p.ld_x = a.ld_x;
   p.x_gs = a.x_gs;
+  p.raw_rows = pl.raw_rows;
   p.wait_for_weights = a.n <= kEarlyReleaseRows ? 1 : 0;
   p.timeline = a.timeline;
   const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
@@ -740,7 +856,7 @@ extern "C" int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, in
   if (device_info(&info) != B12X_B200_OK) return -1;
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
   SmallMPlan pl;
-  if (plan_smallm(kind, m, n, k, sms, &pl) != B12X_B200_OK) return -1;
+  if (plan_smallm(kind, m, n, k, sms, false, &pl) != B12X_B200_OK) return -1;
   return int64_t(pl.total_bytes);
 }
 
@@ -799,7 +915,7 @@ namespace {
 // Scratch of the allocation-free entry point: the 64 KiB counter block plus 4 MiB of FP32
 // partial tiles. It is part of the library image, so every GPU that loads the library keeps
 // these bytes for the life of the process.
-constexpr size_t kNoAllocScratchBytes = kSmallMCounterBytes + (size_t(4) << 20);
+constexpr size_t kNoAllocScratchBytes = kWorkspaceHeaderBytes + (size_t(4) << 20);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 // Device address of g_noalloc_scratch per device. In host code the array's name is only a

@@ -16,7 +16,21 @@
 //   epilogue (each CTA)  : wait own acc_full (committed by the leader to both CTAs) -> pull own
 //                          128 x 256 accumulator into registers -> arrive on the leader's
 //                          acc_empty -> convert, stage in swizzled shared memory, TMA store
+//
+// Last, partial round. With T tiles on P pairs the first T / P rounds keep every pair busy; the
+// T % P tiles left would occupy a few pairs for a whole tile time while the rest idle (448 tiles
+// on 74 pairs: 4 tiles, a seventh round at 5 % occupancy). When at most half of the pairs would
+// be busy, each leftover tile is instead cut along K into S = P / (T % P) segments, one per pair.
+// A pair multiplies its segment as usual, writes its FP32 partial tile to scratch, and counts
+// itself in on the tile's counter; once all 2S CTAs of the tile have arrived (a bounded wait on
+// the counter: all pairs of the grid are resident, one CTA per SM), every CTA adds up the S
+// partials of its own share of the tile (one sixteenth-or-so of the columns, its own 128 rows)
+// in segment order, scales, converts and stores it. The reduction is thus spread over all the
+// CTAs that computed the tile and its result does not depend on timing.
 #pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "gemm_blockscaled.cuh"
 
@@ -51,11 +65,61 @@ struct PairTile {
   static constexpr int kSmemBytes = kStages * kStageBytes + kCStageBytes + kBarrierBytes + 1024;
 };
 
+// One piece of work of a pair: a tile and a range of its k-tiles. segments == 1: the whole tile,
+// stored by the usual epilogue; otherwise segment `seg` of leftover tile `tail_index`.
+struct PairWork {
+  int tile, kt_begin, kt_end, seg, segments, tail_index;
+};
+
+// it-th piece of work of `pair` (P pairs, T tiles, tail_segments = S or <= 1 for no split).
+__device__ __forceinline__ bool pair_work(int it, int pair, int num_pairs, int num_tiles,
+                                          int k_tiles, int tail_segments, PairWork& w) {
+  const int rounds = num_tiles / num_pairs;
+  w.kt_begin = 0;
+  w.kt_end = k_tiles;
+  w.seg = 0;
+  w.segments = 1;
+  w.tail_index = 0;
+  if (it < rounds) {
+    w.tile = pair + it * num_pairs;
+    return true;
+  }
+  if (it > rounds) return false;
+  const int first = rounds * num_pairs;
+  const int left = num_tiles - first;
+  if (tail_segments <= 1) {
+    w.tile = first + pair;
+    return pair < left;
+  }
+  if (pair >= left * tail_segments) return false;
+  w.tail_index = pair / tail_segments;
+  w.tile = first + w.tail_index;
+  w.seg = pair - w.tail_index * tail_segments;
+  w.segments = tail_segments;
+  w.kt_begin = static_cast<int>(static_cast<long long>(k_tiles) * w.seg / tail_segments);
+  w.kt_end = static_cast<int>(static_cast<long long>(k_tiles) * (w.seg + 1) / tail_segments);
+  return true;
+}
+
+// Scratch of the split tail (caller-owned, inside the per-stream workspace): two int32 counters
+// per leftover tile (arrived, done; zero between launches) and, per leftover tile and segment,
+// two FP32 partial tiles of 128 x 256 (one per CTA of the pair) stored as [64 column quads][128
+// rows][4], so that the 32 lanes of a warp write and read consecutive 16-byte pieces.
+struct PairTail {
+  int* counters;
+  float* partials;
+  int segments;  // S, or <= 1 when the tail is not split
+};
+
+constexpr int kPairPartialFloats = 128 * 256;
+constexpr uint32_t kPairReducePolls = 1u << 20;
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(224, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                              const __grid_constant__ CUtensorMap map_b,
-                             const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+                             const __grid_constant__ CUtensorMap map_c, const GemmParams p,
+                             const PairTail tail) {
   using T = PairTile<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -117,18 +181,13 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+    PairWork w;
+    for (int it = 0; ok && pair_work(it, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++it) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int m0 = tm * 256 + static_cast<int>(rank) * 128;
       const int n0 = tn * BN;
-      const int sfa_atom = tm * 2 + static_cast<int>(rank);
-      const bool sfa_ok = sfa_atom < m_row_atoms;
-      const int sfb_atom0 = n0 / 128;
-      const int sfb_atoms = min(T::kSfbRowAtoms, n_row_atoms - sfb_atom0);
-      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
-      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
-      for (int kt = 0; kt < k_tiles; ++kt) {
+      for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
         if (!mbar_wait_bounded_cluster(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
@@ -154,9 +213,10 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+    PairWork w;
+    for (int it = 0; ok && pair_work(it, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++it) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int n0 = tn * BN;
       const int sfa_atom = tm * 2 + static_cast<int>(rank);
       const bool sfa_ok = sfa_atom < m_row_atoms;
@@ -164,7 +224,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int sfb_atoms = min(T::kSfbRowAtoms, n_row_atoms - sfb_atom0);
       const uint8_t* sfa_src = p.sfa + static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
       const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
-      for (int kt = 0; kt < k_tiles; ++kt) {
+      for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
         if (!mbar_wait_bounded_cluster(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
@@ -195,8 +255,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
+    PairWork w;
+    for (int it = 0; ok && pair_work(it, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++it) {
+      for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
         if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
@@ -215,9 +276,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         256, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
     int stage = 0;
     uint32_t phase = 0;
-    int iter = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++iter) {
+    PairWork w;
+    for (int iter = 0; ok && pair_work(iter, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++iter) {
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       if (!mbar_wait_bounded_cluster(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
@@ -227,7 +288,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_after_sync();
       const uint32_t d_taddr = acc * BN;
-      for (int kt = 0; kt < k_tiles; ++kt) {
+      for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
         const bool got_local = mbar_wait_bounded(&full_bar[stage], phase, abort_flag);
         if (!got_local ||
             !mbar_wait_bounded_cluster(&peer_full_bar[stage], phase, abort_flag)) {
@@ -253,7 +314,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
           for (int j = 0; j < mmas; ++j) {
-            const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
+            const uint32_t accumulate = (kt > w.kt_begin || j > 0) ? 1u : 0u;
             if (KIND == kMxfp8)
               tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                                idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
@@ -266,7 +327,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t empty_addr = smem_addr_u32(&empty_bar[stage]);
           tc_commit_pair(empty_addr);
           tc_commit_pair(map_to_cta(empty_addr, 1));
-          if (kt == k_tiles - 1) {
+          if (kt == w.kt_end - 1) {
             const uint32_t full_addr = smem_addr_u32(&acc_full_bar[acc]);
             tc_commit_pair(full_addr);
             tc_commit_pair(map_to_cta(full_addr, 1));
@@ -280,11 +341,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quarter = warp & 3;
     const float alpha = p.alpha ? *p.alpha : 1.0f;
-    int iter = 0;
     bool store_pending = false;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++iter) {
+    PairWork w;
+    for (int iter = 0; pair_work(iter, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++iter) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       if (!epilogue_bar_and(mbar_wait_bounded_cluster(&acc_full_bar[acc], acc_phase, abort_flag))) {
@@ -298,6 +359,103 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row = m0 + row_in_tile;
       const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const uint32_t acc_empty_leader = map_to_cta(smem_addr_u32(&acc_empty_bar[acc]), 0);
+      if (w.segments > 1) {
+        // ---- segment of a leftover tile: FP32 partial to scratch, then the shared reduction ----
+        const int s_count = w.segments;
+        float* slots = tail.partials +
+                       static_cast<size_t>(w.tail_index) * s_count * 2 * kPairPartialFloats;
+        float4* mine = reinterpret_cast<float4*>(
+            slots + (static_cast<size_t>(w.seg) * 2 + rank) * kPairPartialFloats);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t raw[32];
+          tmem_load_32cols(taddr + c * 32, raw);
+          tmem_load_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            mine[(c * 8 + q) * 128 + row_in_tile] =
+                make_float4(__uint_as_float(raw[4 * q]), __uint_as_float(raw[4 * q + 1]),
+                            __uint_as_float(raw[4 * q + 2]), __uint_as_float(raw[4 * q + 3]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        // Publish, count this CTA in, and wait (bounded) for the 2 * S CTAs of the tile.
+        __threadfence();
+        epilogue_bar_sync();
+        int* arrived = tail.counters + 2 * w.tail_index;
+        int* done = arrived + 1;
+        bool all_in = true;
+        if (threadIdx.x == 64) {
+          atomicAdd(arrived, 1);
+          uint32_t polls = 0;
+          while (*reinterpret_cast<volatile int*>(arrived) < 2 * s_count) {
+            if (++polls >= kPairReducePolls || *abort_flag != 0) {
+              all_in = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+          __threadfence();
+        }
+        if (!epilogue_bar_and(all_in)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusReduceTimeout);
+          break;
+        }
+        // This CTA's share: column quads [q_begin, q_end) of its own 128 rows, summed over the
+        // segments in order.
+        const int per = (BN / 4 + s_count - 1) / s_count;
+        const int q_begin = w.seg * per;
+        const int q_end = min(BN / 4, q_begin + per);
+        const float4* base = reinterpret_cast<const float4*>(slots + static_cast<size_t>(rank) * kPairPartialFloats);
+#pragma unroll 1
+        for (int q = q_begin; q < q_end; ++q) {
+          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          int sg = 0;
+#pragma unroll 1
+          for (; sg + 6 <= s_count; sg += 6) {
+            float4 v[6];
+#pragma unroll
+            for (int i = 0; i < 6; ++i)
+              v[i] = __ldcg(base + static_cast<size_t>(sg + i) * (2 * kPairPartialFloats / 4) + q * 128 + row_in_tile);
+#pragma unroll
+            for (int i = 0; i < 6; ++i) {
+              sum.x += v[i].x; sum.y += v[i].y; sum.z += v[i].z; sum.w += v[i].w;
+            }
+          }
+          for (; sg < s_count; ++sg) {
+            const float4 v = __ldcg(base + static_cast<size_t>(sg) * (2 * kPairPartialFloats / 4) + q * 128 + row_in_tile);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+          const int col = tn * BN + q * 4;
+          if (row < p.m && col < p.n) {
+            const float o[4] = {sum.x * alpha, sum.y * alpha, sum.z * alpha, sum.w * alpha};
+            const size_t idx = static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (col + i < p.n) {
+                if (p.out_dtype == kOutBf16)
+                  static_cast<__nv_bfloat16*>(p.c)[idx + i] = __float2bfloat16_rn(o[i]);
+                else if (p.out_dtype == kOutFp16)
+                  static_cast<__half*>(p.c)[idx + i] = __float2half_rn(o[i]);
+                else
+                  static_cast<float*>(p.c)[idx + i] = o[i];
+              }
+            }
+          }
+        }
+        // The last CTA to finish reading clears the tile's counters for the next launch.
+        epilogue_bar_sync();
+        if (threadIdx.x == 64) {
+          const int prev = atomicAdd(done, 1);
+          if (prev == 2 * s_count - 1) {
+            *arrived = 0;
+            *done = 0;
+          }
+        }
+        continue;
+      }
       if (p.use_tma_store) {
         // With one CTA per SM and 224 threads a thread may hold ~250 registers, enough for half
         // of its accumulator row raw (128 columns) plus the other half already converted. So

@@ -41,14 +41,18 @@
 // launch; every launch leaves them zero again, whatever the shape.
 //
 // Fused activation quantization (template parameter FUSED, M <= 16). The caller passes the
-// BF16 activation rows instead of codes and scales. Eight extra warps take the place of the
-// activation TMA producer: for every unit they read the 128 bytes of K of each live row (256
-// NVFP4 or 128 MXFP8 elements), quantize them with exactly the arithmetic of the row
-// quantizers in quantize.cuh, and write codes (128-byte-swizzled, as TMA would) and scale
-// bytes (atom layout) straight into the stage, then arrive on the stage's full barrier. Global
-// loads run three units ahead of the arithmetic. Every CTA quantizes the K range it multiplies,
-// so the rows are re-quantized once per weight tile a CTA owns: cheap next to the 16 KiB of
-// weights of a unit for a handful of rows, and the reason for the M <= 16 limit.
+// BF16 activation rows instead of codes and scales. The activation producer brings the raw
+// rows of a unit (8 or 16 rows x 256 NVFP4 / 128 MXFP8 elements) into an extra area of the
+// stage with one TMA copy, in the same queue as the weights. Eight extra warps wait for the
+// stage's full barrier, quantize the raw rows with exactly the arithmetic of the row
+// quantizers in quantize.cuh, write codes (128-byte-swizzled, as TMA would) and scale bytes
+// (atom layout) into the stage, and arrive on the stage's "ready" barrier, which is what the
+// MMA issuers wait for. (Quantizer warps that loaded the rows themselves with ordinary global
+// loads were measured at twice the kernel time: such a load queues behind the ~180 KiB of
+// weight requests the SM has outstanding and takes microseconds.) Every CTA quantizes the K
+// range it multiplies, so the rows are re-quantized once per weight tile a CTA owns: cheap
+// next to the 16 KiB of weights of a unit for a handful of rows, and the reason for the
+// M <= 16 limit.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -78,10 +82,10 @@ struct SmallMParams {
   int issuers;             // MMA-issuing warps in use (2 when four accumulators fit, else 1)
   int tmem_cols;           // tensor memory to allocate: 128, 256 or 512 columns
   int sf_col0;             // first scale column (after the accumulators)
-  // Fused activation quantization only: BF16 rows [M, ld_x] and, for NVFP4, their global scale.
-  const __nv_bfloat16* x_src;
-  long long ld_x;
+  // Fused activation quantization only: the NVFP4 global scale of the rows, and how many raw
+  // BF16 rows (8 or 16) a stage holds behind the code tile.
   const float* x_gs;
+  int raw_rows;
   // Non-zero: the weight stream too waits for the previous grid (weights of few rows may be a
   // predecessor's fresh output, see the header comment).
   int wait_for_weights;
@@ -152,14 +156,14 @@ __device__ __forceinline__ int owner_of_unit(int u, int units, int ctas) {
 // ----------------------------------------------------------------------------------------
 // Fused activation quantization: what one quantizer warp does for one unit
 // ----------------------------------------------------------------------------------------
-// A "slot" is one warp-wide 16-byte-per-lane load, i.e. 256 consecutive BF16 elements: one row
-// of an NVFP4 unit, or two rows of an MXFP8 unit (lanes 0..15 / 16..31). Warp q of the eight
-// takes slot q and, for NVFP4 with more than eight rows, slot q + 8.
+// A "slot" is one warp-wide 16-byte-per-lane read of the raw rows in shared memory, i.e. 256
+// consecutive BF16 elements: one row of an NVFP4 unit, or two rows of an MXFP8 unit (lanes
+// 0..15 / 16..31). Warp q of the eight takes slot q and, for NVFP4 with more than eight rows,
+// slot q + 8.
 template <int KIND>
 struct FusedQuant {
   static constexpr int kWarps = 8;
   static constexpr int kSlotsPerWarp = (KIND == kNvfp4) ? 2 : 1;
-  static constexpr int kDepth = 3;  // units whose loads are in flight ahead of the arithmetic
 
   __device__ static __forceinline__ int row_of(int slot, int lane) {
     return (KIND == kNvfp4) ? slot : 2 * slot + (lane >> 4);
@@ -168,15 +172,20 @@ struct FusedQuant {
     return (KIND == kNvfp4) ? lane * 8 : (lane & 15) * 8;
   }
 
-  __device__ static __forceinline__ void load(const SmallMParams& p, int kt, int wq, int lane,
-                                              uint4 (&buf)[kSlotsPerWarp]) {
-    using T = SmallMTile<KIND>;
+  // Raw BF16 rows of a unit sit row-major behind the code tile: row r at r * kRawRowBytes.
+  static constexpr int kRawRowBytes = SmallMTile<KIND>::kElemsPerStage * 2;
+  __device__ static constexpr int raw_offset(int m_pad) {
+    return SmallMTile<KIND>::kXOffset + m_pad * 128;
+  }
+
+  __device__ static __forceinline__ void load(const SmallMParams& p, const uint8_t* st, int wq,
+                                              int lane, uint4 (&buf)[kSlotsPerWarp]) {
+    const uint8_t* raw = st + raw_offset(p.m_pad);
 #pragma unroll
     for (int s = 0; s < kSlotsPerWarp; ++s) {
       const int row = row_of(wq + s * kWarps, lane);
-      const int k0 = kt * T::kElemsPerStage + elem_of(lane);
-      buf[s] = (row < p.m && k0 < p.k)
-                   ? ld_nc_16(p.x_src + static_cast<long long>(row) * p.ld_x + k0)
+      buf[s] = (row < p.raw_rows)
+                   ? *reinterpret_cast<const uint4*>(raw + row * kRawRowBytes + elem_of(lane) * 2)
                    : make_uint4(0, 0, 0, 0);
     }
   }
@@ -245,7 +254,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.num_stages * p.stage_bytes);
   uint64_t* empty_bar = full_bar + T::kMaxStages;
-  uint64_t* acc_full_bar = empty_bar + T::kMaxStages;
+  uint64_t* ready_bar = empty_bar + T::kMaxStages;  // fused variant: codes and scales written
+  uint64_t* acc_full_bar = ready_bar + T::kMaxStages;
   uint64_t* acc_empty_bar = acc_full_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -270,9 +280,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
   const int u_end = static_cast<int>(static_cast<long long>(units) * (blockIdx.x + 1) / gridDim.x);
   const uint32_t smem_u32 = smem_addr_u32(smem);
   const uint32_t x_bytes = static_cast<uint32_t>(p.m_pad) * 128u;
-  // Arrivals that complete a stage: the weight producer plus either the activation producer or
-  // the eight quantizer warps.
-  constexpr uint32_t kFullArrivals = FUSED ? 1 + FusedQuant<KIND>::kWarps : 2;
+  // Bytes of raw BF16 rows one stage of the fused variant receives.
+  const uint32_t raw_bytes =
+      FUSED ? static_cast<uint32_t>(p.raw_rows) * FusedQuant<KIND>::kRawRowBytes : 0u;
 
   uint32_t tmem_base = 0;
   if (warp == 0) {
@@ -283,8 +293,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     if (lane == 0) {
       *abort_flag = 0;
       for (int s = 0; s < p.num_stages; ++s) {
-        mbar_init(&full_bar[s], kFullArrivals);
+        mbar_init(&full_bar[s], 2);  // weight producer + activation producer
         mbar_init(&empty_bar[s], 1);
+        if (FUSED) mbar_init(&ready_bar[s], FusedQuant<KIND>::kWarps);
       }
       fence_mbar_init();
       fence_proxy_async_smem();
@@ -334,7 +345,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       __syncwarp();
       tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
     }
-    if (!FUSED && warp == 6 && lane == 0) tma_prefetch_desc(&map_x);
+    if (warp == 6 && lane == 0) tma_prefetch_desc(&map_x);
     tc_fence_before_sync();
     setup_bar_sync(blockDim.x);
     tc_fence_after_sync();
@@ -351,8 +362,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 
     if (!tmem_ok) {
       // nothing
-    } else if (!FUSED && warp == 6) {
+    } else if (warp == 6) {
       // ------------------------------ activation producer ------------------------------
+      // Codes and scale atoms, or (fused variant) the raw BF16 rows the quantizer warps turn
+      // into codes and scales.
       grid_dependency_wait();  // activations may come from the previous grid
       int stage = 0;
       uint32_t phase = 0;
@@ -369,10 +382,16 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           const int katom0 = kt * T::kKAtoms;
           const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
           const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-          mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
-          tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
-          bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
-                    sf_bytes, bar);
+          if (FUSED) {
+            mbar_arrive_expect_tx(bar, raw_bytes);
+            tma_load_2d(st + FusedQuant<KIND>::raw_offset(p.m_pad), &map_x, bar,
+                        kt * T::kElemsPerStage, 0);
+          } else {
+            mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
+            tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
+            bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
+                      sf_bytes, bar);
+          }
         }
         __syncwarp();
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
@@ -398,43 +417,31 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         }
       }
       quant_bar_sync();
-      grid_dependency_wait();  // the rows may come from the previous grid
       float gs = 1.0f, gs_rcp = 1.0f;
       if (KIND == kNvfp4) {
+        grid_dependency_wait();  // the scale may come from the previous grid
         gs = *p.x_gs;
         gs_rcp = (gs == 0.0f) ? 0.0f : __frcp_rn(gs);
       }
-      const int n_units = u_end - u_begin;
-      const int kt0 = u_begin % p.k_tiles;
-      auto kt_of = [&](int q) { return (kt0 + q) % p.k_tiles; };
-      uint4 raw[Q::kDepth][Q::kSlotsPerWarp];
-#pragma unroll
-      for (int d = 0; d < Q::kDepth - 1; ++d)
-        if (d < n_units) Q::load(p, kt_of(d), wq, lane, raw[d]);
       int stage = 0;
       uint32_t phase = 0;
-      bool ok = true;
-      for (int q0 = 0; q0 < n_units && ok; q0 += Q::kDepth) {
-#pragma unroll
-        for (int d = 0; d < Q::kDepth; ++d) {
-          const int q = q0 + d;
-          if (q < n_units && ok) {
-            if (q + Q::kDepth - 1 < n_units)
-              Q::load(p, kt_of(q + Q::kDepth - 1), wq, lane, raw[(d + Q::kDepth - 1) % Q::kDepth]);
-            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
-              *abort_flag = 1;
-              if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
-              ok = false;
-            } else {
-              Q::store(p, smem + stage * p.stage_bytes, wq, lane, raw[d], gs, gs_rcp);
-              // The tensor core reads the stage through the async proxy.
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&full_bar[stage]);
-              if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
-            }
-          }
+      for (int u = u_begin; u < u_end; ++u) {
+        // Weights and raw rows of the unit have landed (which also means the tensor core is
+        // done with whatever the stage held before).
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+          *abort_flag = 1;
+          if (p.status && lane == 0) atomicMax(p.status, kStatusProducerTimeout);
+          break;
         }
+        uint8_t* st = smem + stage * p.stage_bytes;
+        uint4 raw[Q::kSlotsPerWarp];
+        Q::load(p, st, wq, lane, raw);
+        Q::store(p, st, wq, lane, raw, gs, gs_rcp);
+        // The tensor core reads the stage through the async proxy.
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready_bar[stage]);
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
       }
     } else if (warp == 1 || warp == 7) {
       // ------------------------------ MMA issuers ------------------------------
@@ -469,7 +476,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         for (; u < seg_end; ++u, ++kt) {
           const bool mine = (p.issuers == 2) ? (((u - u_begin) & 1) == me) : (me == 0);
           if (mine) {
-            if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            // Fused variant: the stage is usable once the quantizer warps have written codes
+            // and scales ("ready"); the full barrier has then long completed, and waiting on it
+            // as well keeps the issuer a direct observer of the TMA writes.
+            if ((FUSED && !mbar_wait_bounded(&ready_bar[stage], phase, abort_flag)) ||
+                !mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
               *abort_flag = 1;
               if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
               ok = false;

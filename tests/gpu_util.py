@@ -73,9 +73,10 @@ def torch_dequant_nvfp4(packed: torch.Tensor, atoms: torch.Tensor, rows: int, k:
     return (vals.view(rows, k // 16, 16) * scales[:, :, None]).view(rows, k)
 
 
-def torch_dequant_mxfp8(values: torch.Tensor, atoms: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+def torch_dequant_mxfp8(values: torch.Tensor, scale_rows: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """E4M3 codes x 2^(byte - 127) from the row-major UE8M0 bytes [rows, k / 32]."""
     v = values.reshape(rows, k).view(torch.float8_e4m3fn).float()
-    scales = torch.exp2(unswizzle_atoms(atoms, rows, k // 32).float() - 127.0)
+    scales = torch.exp2(scale_rows.reshape(rows, k // 32).view(torch.uint8).float() - 127.0)
     return (v.view(rows, k // 32, 32) * scales[:, :, None]).view(rows, k)
 
 

@@ -228,8 +228,8 @@ def test_full_size_configurations_on_sampled_rows(recipe):
         kw = MXFP8
         a_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(x[rows].float().cpu().numpy()))
         b_deq = O.dequantize_mxfp8(*O.quantize_mxfp8_rows(w[cols].float().cpu().numpy()))
-        a_all = torch_dequant_mxfp8(xq.values, xq.scale_mma, m, k)
-        b_all = torch_dequant_mxfp8(wq.values, wq.scale_mma, n, k)
+        a_all = torch_dequant_mxfp8(xq.values, xq.scale_rows, m, k)
+        b_all = torch_dequant_mxfp8(wq.values, wq.scale_rows, n, k)
     else:
         gsx = O.nvfp4_global_scale(x.float().cpu().numpy())
         gsw = O.nvfp4_global_scale(w.float().cpu().numpy())
@@ -553,8 +553,7 @@ def test_config0_nvfp4_128x4096x4096_whole_output_against_oracle(tile):
     """Configuration 0 at its stated size: A = randn, B = randn * 0.02 (seeds 42 and 43),
     both quantized to NVFP4 by the oracle with gs = 448 * 6 / amax, alpha = 1 / (gsA * gsB),
     BF16 out; every output element against the oracle's dequantize-to-FP32 matmul. Runs through
-    the automatic route (the decode kernel splitting K over the idle SMs) and through each
-    tiled kernel."""
+    the automatic route and through each tiled kernel."""
     from gpu_util import DEV, assert_gemm_close, nvfp4_operand
     from sparkinfer_b200.gemm import blockscaled
 

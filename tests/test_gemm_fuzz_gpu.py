@@ -126,3 +126,55 @@ def test_block_fp8_gemm_matches_fp32_reference_on_random_shapes(index, m, n, k, 
     scale = float(ref.abs().max())
     eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -20}[dtype]
     assert float((got - ref).abs().max()) <= (eps + 2.0 ** -16) * scale + 1e-30
+
+
+@pytest.mark.parametrize("kind,m,n,k,dtype", [
+    ("nvfp4", 2048, 2560, 2048, torch.bfloat16),   # 80 pair tiles on 74 pairs: 6 left, 4 segments
+    ("mxfp8", 1536, 3328, 1024, torch.bfloat16),   # 78 tiles: 4 left
+    ("nvfp4", 2000, 2500, 1536, torch.float32),    # ragged edges inside the leftover tiles
+    ("mxfp8", 4100, 1290, 1664, torch.float16),    # 17 x 6 = 102 tiles: 28 left, 2 segments
+    ("nvfp4", 256, 19200, 1024, torch.bfloat16),   # one tile row: 75 tiles, 1 left, 2 k-tiles each
+])
+def test_cta_pair_split_tail_matches_fp32_reference(kind, m, n, k, dtype):
+    """The CTA-pair kernel cuts the tiles of its last partial round along K over all SM pairs
+    and adds the FP32 partials up through the per-stream workspace. Every output element against
+    the FP32 reference, twice in a row with identical bytes (the reduction order is fixed and
+    the counters return to zero), and against the unsplit kernel (no workspace passed)."""
+    import ctypes
+
+    from sparkinfer_b200 import _native
+    from sparkinfer_b200._lib import launch
+
+    dev = torch.device("cuda:0")
+    code = _native.KIND_MXFP8 if kind == "mxfp8" else _native.KIND_NVFP4
+    need = _native.load().b12x_b200_gemm_blockscaled_workspace_bytes(code, m, n, k, 0, 0)
+    assert need > 0, "shape chosen to have a split tail"
+    gen = torch.Generator(device=dev).manual_seed(4242 + m + n)
+    a, sfa, a_deq = _operand(kind, m, k, gen, dev)
+    b, sfb, b_deq = _operand(kind, n, k, gen, dev)
+    alpha = torch.tensor([0.5], dtype=torch.float32, device=dev)
+    ref = 0.5 * (a_deq @ b_deq.T)
+    scale = float(ref.abs().max())
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -20}[dtype]
+    outs = []
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), dtype=dtype, device=dev)
+        launch.gemm_blockscaled(code, a, sfa, b, sfb, out, alpha, m, n, k)
+        torch.cuda.synchronize()
+        launch.check_kernel_status(dev)
+        assert not torch.isnan(out.float()).any()
+        assert float((out.float() - ref).abs().max()) <= (eps + 2.0 ** -16) * scale
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    work = launch.stream_workspace(need, dev)
+    assert int(work[:65536].count_nonzero()) == 0, "counters must return to zero"
+    unsplit = torch.full((m, n), float("nan"), dtype=dtype, device=dev)
+    rc = _native.load().b12x_b200_gemm_blockscaled(
+        code, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), unsplit.data_ptr(),
+        {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[dtype], alpha.data_ptr(), m, n, k, n,
+        0, 0, launch.status_buffer(dev).data_ptr(),
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "b12x_b200_gemm_blockscaled")
+    torch.cuda.synchronize()
+    assert float((unsplit.float() - ref).abs().max()) <= (eps + 2.0 ** -16) * scale
+    assert float((unsplit.float() - outs[0].float()).abs().max()) <= 2 * eps * scale + 1e-30
