@@ -366,16 +366,21 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                        static_cast<size_t>(w.tail_index) * s_count * 2 * kPairPartialFloats;
         float4* mine = reinterpret_cast<float4*>(
             slots + (static_cast<size_t>(w.seg) * 2 + rank) * kPairPartialFloats);
+        // Four tensor-memory loads in flight at a time (128 columns), as in the main epilogue.
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t raw[32];
-          tmem_load_32cols(taddr + c * 32, raw);
+        for (int half = 0; half < BN / 128; ++half) {
+          uint32_t raw[4][32];
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) tmem_load_32cols(taddr + half * 128 + cc * 32, raw[cc]);
           tmem_load_wait();
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            mine[(c * 8 + q) * 128 + row_in_tile] =
-                make_float4(__uint_as_float(raw[4 * q]), __uint_as_float(raw[4 * q + 1]),
-                            __uint_as_float(raw[4 * q + 2]), __uint_as_float(raw[4 * q + 3]));
+          for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              mine[((half * 4 + cc) * 8 + q) * 128 + row_in_tile] = make_float4(
+                  __uint_as_float(raw[cc][4 * q]), __uint_as_float(raw[cc][4 * q + 1]),
+                  __uint_as_float(raw[cc][4 * q + 2]), __uint_as_float(raw[cc][4 * q + 3]));
+          }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -409,38 +414,56 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const int q_begin = w.seg * per;
         const int q_end = min(BN / 4, q_begin + per);
         const float4* base = reinterpret_cast<const float4*>(slots + static_cast<size_t>(rank) * kPairPartialFloats);
+        constexpr size_t kSegStride = 2 * kPairPartialFloats / 4;  // float4 between segments
+        // Eight column quads at a time, four segments per trip: up to thirty-two independent
+        // 16-byte loads are in flight per thread (the loop is bound by load latency, not by
+        // bytes). The adds run in segment order whatever the batching.
 #pragma unroll 1
-        for (int q = q_begin; q < q_end; ++q) {
-          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          int sg = 0;
+        for (int q0 = q_begin; q0 < q_end; q0 += 8) {
+          float4 sum[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 1
-          for (; sg + 6 <= s_count; sg += 6) {
-            float4 v[6];
+          for (int sg = 0; sg < s_count; sg += 4) {
+            float4 v[4][8];
 #pragma unroll
-            for (int i = 0; i < 6; ++i)
-              v[i] = __ldcg(base + static_cast<size_t>(sg + i) * (2 * kPairPartialFloats / 4) + q * 128 + row_in_tile);
+            for (int j = 0; j < 4; ++j) {
 #pragma unroll
-            for (int i = 0; i < 6; ++i) {
-              sum.x += v[i].x; sum.y += v[i].y; sum.z += v[i].z; sum.w += v[i].w;
+              for (int i = 0; i < 8; ++i) {
+                v[j][i] = (sg + j < s_count && q0 + i < q_end)
+                              ? __ldcg(base + static_cast<size_t>(sg + j) * kSegStride +
+                                       (q0 + i) * 128 + row_in_tile)
+                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              }
+            }
+            // Adding +0.0f for an absent segment leaves the sum unchanged bit for bit (the sum
+            // is never -0.0f: it starts at +0.0f).
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                sum[i].x += v[j][i].x; sum[i].y += v[j][i].y;
+                sum[i].z += v[j][i].z; sum[i].w += v[j][i].w;
+              }
             }
           }
-          for (; sg < s_count; ++sg) {
-            const float4 v = __ldcg(base + static_cast<size_t>(sg) * (2 * kPairPartialFloats / 4) + q * 128 + row_in_tile);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-          }
-          const int col = tn * BN + q * 4;
-          if (row < p.m && col < p.n) {
-            const float o[4] = {sum.x * alpha, sum.y * alpha, sum.z * alpha, sum.w * alpha};
-            const size_t idx = static_cast<size_t>(row) * p.ldc + col;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (col + i < p.n) {
-                if (p.out_dtype == kOutBf16)
-                  static_cast<__nv_bfloat16*>(p.c)[idx + i] = __float2bfloat16_rn(o[i]);
-                else if (p.out_dtype == kOutFp16)
-                  static_cast<__half*>(p.c)[idx + i] = __float2half_rn(o[i]);
-                else
-                  static_cast<float*>(p.c)[idx + i] = o[i];
+          for (int i = 0; i < 8; ++i) {
+            const int q = q0 + i;
+            const int col = tn * BN + q * 4;
+            if (q < q_end && row < p.m && col < p.n) {
+              const float o[4] = {sum[i].x * alpha, sum[i].y * alpha, sum[i].z * alpha, sum[i].w * alpha};
+              const size_t idx = static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col + j < p.n) {
+                  if (p.out_dtype == kOutBf16)
+                    static_cast<__nv_bfloat16*>(p.c)[idx + j] = __float2bfloat16_rn(o[j]);
+                  else if (p.out_dtype == kOutFp16)
+                    static_cast<__half*>(p.c)[idx + j] = __float2half_rn(o[j]);
+                  else
+                    static_cast<float*>(p.c)[idx + j] = o[j];
+                }
               }
             }
           }
