@@ -296,9 +296,13 @@ PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int sms) 
   t.left = int(tiles - rounds * t.pairs);
   const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
   const int64_t k_tiles = (k + elems_per_stage - 1) / elems_per_stage;
-  // Split only when the leftover tiles would keep at most half of the pairs busy, and never
-  // below two k-tiles per segment.
-  if (t.left == 0 || t.left * 2 > t.pairs || size_t(t.left) * 2 * sizeof(int) > kPairCounterBytes)
+  // Split only when the leftover tiles would keep at most a tenth of the pairs busy, and never
+  // below two k-tiles per segment. The split round is not free: it ends when the slowest pair
+  // of each tile has delivered (the pairs drift apart by several microseconds over a dozen
+  // rounds) and then pays for the partial tiles' round trip through L2, together about half a
+  // tile time on 4096 x 7168 x 18432 (4 tiles left on 74 pairs: 213 -> 200 us) and a whole one
+  // on 8192 x 7168 x 7168 (8 left: 294 -> 296 us).
+  if (t.left == 0 || t.left * 10 > t.pairs || size_t(t.left) * 2 * sizeof(int) > kPairCounterBytes)
     return t;
   int64_t seg = t.pairs / t.left;
   if (seg > k_tiles / 2) seg = k_tiles / 2;

@@ -8,9 +8,8 @@
 // multiplied unscaled (tcgen05 kind::f8f6f4, four K=32 instructions) into a TMEM buffer and
 // promoted into FP32 register accumulators with one FMA per element.
 //
-// One CTA (640 threads) owns a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer
-// (warps 2 and 3 idle: the four make up a warpgroup that hands its registers over), warps
-// 4..19 = promotion/epilogue (four warps per 32-lane TMEM quarter, each taking 64 of the
+// One CTA (576 threads) owns a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer,
+// warps 2..17 = promotion/epilogue (four warps per 32-lane TMEM quarter, each taking 64 of the
 // 256 columns, i.e. half of one 128-column scale block). Promotion is a chain of TMEM load ->
 // wait -> FMA per warp, so it is the number of warps per scheduler (four) that hides the load
 // latency. The two 256-column TMEM buffers fill all 512 columns, so the MMA of k-block i+1
@@ -36,14 +35,7 @@ struct BlockFp8Tile {
   static constexpr int kSmemBytes = kStages * kStageBytes + kCStageBytes + kBarrierBytes + 1024;
   static constexpr int kEpilogueWarps = 16;
   static constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
-  // Warps 0..3 form the control warpgroup (0 = TMA producer, 1 = MMA issuer, 2 and 3 idle) so
-  // that register counts can be moved between whole warpgroups: the control group gives most
-  // of its registers back and the four promotion warpgroups take more than the 96 an even
-  // split of the register file over 640 threads allows.
-  static constexpr int kControlWarps = 4;
-  static constexpr int kThreads = 32 * (kControlWarps + kEpilogueWarps);
-  static constexpr int kControlRegs = 56;
-  static constexpr int kPromotionRegs = 112;  // 128 * 56 + 512 * 112 = 64512 <= 65536
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 };
 
 struct BlockFp8Params {
@@ -59,8 +51,8 @@ struct BlockFp8Params {
                        // the promotion warps do
 };
 
-// Bounded wait that polls with the non-suspending test_wait: a suspended try_wait was measured
-// to resume hundreds of cycles after the barrier completed, which matters on the hand-over of a
+// Bounded wait that polls with the non-suspending test_wait instead of try_wait (which may
+// park the warp): for measuring what the wake-up of a parked warp costs on the hand-over of a
 // tensor-memory buffer between the MMA issuer and the promotion warps.
 __device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {
@@ -79,15 +71,6 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity
     if ((polls & 8191u) == 8191u && *abort_flag != 0) return false;
   }
   return false;
-}
-
-template <int REGS>
-__device__ __forceinline__ void warpgroup_regs_release() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
-}
-template <int REGS>
-__device__ __forceinline__ void warpgroup_regs_take() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
 }
 
 // Named barrier 1 + group over the 128 threads (four warps) that share an output sub-tile.
@@ -147,10 +130,6 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
   const int k_blocks = p.k / 128;
   const uint32_t smem_u32 = smem_addr_u32(smem);
 
-  // The register hand-over and each group's code sit in the same branch, so that the compiler
-  // can allocate the promotion code against the larger budget.
-  if (warp < T::kControlWarps) {
-  warpgroup_regs_release<T::kControlRegs>();
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     int stage = 0;
@@ -215,12 +194,10 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++stage == T::kStages) { stage = 0; phase ^= 1; }
       }
     }
-  }
   } else {
-    warpgroup_regs_take<T::kPromotionRegs>();
     // ------------------------- promotion + epilogue -------------------------
     const int quarter = warp & 3;
-    const int group = (warp - T::kControlWarps) >> 2;  // which 64 of the tile's 256 columns
+    const int group = (warp - 2) >> 2;  // which 64 of the tile's 256 columns
     constexpr int kCols = T::kColsPerWarp;
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     const int kb_total = k_blocks;
@@ -280,7 +257,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         // per row; 16-byte chunk j of row r sits at position j ^ (r % 8), the layout a
         // 128-byte-swizzled TMA store expects. The sub-tile of the previous tile has long been
         // read by its store; the wait is a formality.
-        const bool store_thread = (quarter == 0) && (lane == 0);  // first warp of the group
+        const bool store_thread = (quarter == 2) && (lane == 0);  // first warp of the group
         if (store_pending) {
           if (store_thread) tma_store_wait_read<0>();
           group_bar_sync(group);
@@ -321,7 +298,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         store_row_chunk(gp, row, col0 + c * 32, vals);
       }
     }
-    if (p.use_tma_store && quarter == 0 && lane == 0) tma_store_wait_all<0>();
+    if (p.use_tma_store && quarter == 2 && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();

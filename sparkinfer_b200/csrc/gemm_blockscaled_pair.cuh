@@ -19,8 +19,8 @@
 //
 // Last, partial round. With T tiles on P pairs the first T / P rounds keep every pair busy; the
 // T % P tiles left would occupy a few pairs for a whole tile time while the rest idle (448 tiles
-// on 74 pairs: 4 tiles, a seventh round at 5 % occupancy). When at most half of the pairs would
-// be busy, each leftover tile is instead cut along K into S = P / (T % P) segments, one per pair.
+// on 74 pairs: 4 tiles, a seventh round at 5 % occupancy). When at most a tenth of the pairs
+// would be busy, each leftover tile is instead cut along K into S = P / (T % P) segments, one per pair.
 // A pair multiplies its segment as usual, writes its FP32 partial tile to scratch, and counts
 // itself in on the tile's counter; once all 2S CTAs of the tile have arrived (a bounded wait on
 // the counter: all pairs of the grid are resident, one CTA per SM), every CTA adds up the S
@@ -454,6 +454,14 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             if (q < q_end && row < p.m && col < p.n) {
               const float o[4] = {sum[i].x * alpha, sum[i].y * alpha, sum[i].z * alpha, sum[i].w * alpha};
               const size_t idx = static_cast<size_t>(row) * p.ldc + col;
+              if (p.out_dtype != kOutFp32 && col + 4 <= p.n &&
+                  ((reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(p.c) + idx) & 7) == 0)) {
+                const bool bf = p.out_dtype == kOutBf16;
+                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.c) + idx) =
+                    make_uint2(bf ? pack_bf16x2(o[0], o[1]) : pack_f16x2(o[0], o[1]),
+                               bf ? pack_bf16x2(o[2], o[3]) : pack_f16x2(o[2], o[3]));
+                continue;
+              }
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 if (col + j < p.n) {
