@@ -146,7 +146,6 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 struct Switches {
   bool decode_overlap = true;   // programmatic stream serialization for decode GEMMs / quantizers
   bool pair_tail_split = true;  // split-K the last partial round of the CTA-pair kernel
-  int block_fp8_spin = 0;       // bit 0 / 1: non-suspending barrier polls in issuer / promotion
 };
 
 const Switches& switches() {
@@ -154,7 +153,6 @@ const Switches& switches() {
     Switches v;
     if (const char* e = getenv("B12X_B200_DECODE_OVERLAP")) v.decode_overlap = atoi(e) != 0;
     if (const char* e = getenv("B12X_B200_PAIR_TAIL_SPLIT")) v.pair_tail_split = atoi(e) != 0;
-    if (const char* e = getenv("B12X_B200_BLOCK_FP8_SPIN")) v.block_fp8_spin = atoi(e);
     return v;
   }();
   return sw;
@@ -580,7 +578,6 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   p.tiles_m = int((m + BlockFp8Tile::BM - 1) / BlockFp8Tile::BM);
   p.tiles_n = int((n + BlockFp8Tile::BN - 1) / BlockFp8Tile::BN);
   p.group_m = 16;
-  p.spin_waits = switches().block_fp8_spin;
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless

@@ -47,31 +47,7 @@ struct BlockFp8Params {
   int m, n, k, ldc, out_dtype;
   int tiles_m, tiles_n, group_m;
   int use_tma_store;   // 2-byte outputs with 16-byte aligned rows
-  int spin_waits;      // bit 0: the MMA issuer polls its barriers without suspending; bit 1:
-                       // the promotion warps do
 };
-
-// Bounded wait that polls with the non-suspending test_wait instead of try_wait (which may
-// park the warp): for measuring what the wake-up of a parked warp costs on the hand-over of a
-// tensor-memory buffer between the MMA issuer and the promotion warps.
-__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
-  for (uint32_t polls = 0; polls < (kMaxBarrierPolls << 3); ++polls) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred P;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, P;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_addr_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((polls & 8191u) == 8191u && *abort_flag != 0) return false;
-  }
-  return false;
-}
 
 // Named barrier 1 + group over the 128 threads (four warps) that share an output sub-tile.
 __device__ __forceinline__ void group_bar_sync(int group) {
@@ -171,12 +147,8 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t st = smem_u32 + stage * T::kStageBytes;
         const uint64_t adesc = make_kmajor_sw128_desc(st);
         const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
-        const bool got = (p.spin_waits & 1)
-                             ? (mbar_spin_bounded(&full_bar[stage], phase, abort_flag) &&
-                                mbar_spin_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag))
-                             : (mbar_wait_bounded(&full_bar[stage], phase, abort_flag) &&
-                                mbar_wait_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag));
-        if (!got) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag) ||
+            !mbar_wait_bounded(&part_empty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusMmaTimeout);
           ok = false;
@@ -221,8 +193,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         // Scales of this k-block are fetched before the wait so their latency hides behind it.
         const float scale = __fmul_rn(row_ok ? __ldg(sfa_row + kb) : 0.0f,
                                       col_ok ? __ldg(sfb_row + kb) : 0.0f);
-        if (!((p.spin_waits & 2) ? mbar_spin_bounded(&part_full_bar[buf], (it >> 1) & 1, abort_flag)
-                                 : mbar_wait_bounded(&part_full_bar[buf], (it >> 1) & 1, abort_flag))) {
+        if (!mbar_wait_bounded(&part_full_bar[buf], (it >> 1) & 1, abort_flag)) {
           *abort_flag = 1;
           if (p.status && lane == 0) atomicMax(p.status, kStatusEpilogueTimeout);
           ok = false;
