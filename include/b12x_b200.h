@@ -54,6 +54,37 @@ enum {
  */
 #define B12X_B200_BLOCK_N_PAIR (-256)
 
+/*
+ * Optional epilogue of the *_ex entry points (a NULL pointer, or all-zero contents, means none).
+ * Stands in for the reference's bias add after its linears
+ * (b12x/gemm/mxfp8_linear/_kernel.py:264-265) and for its quantized-C GEMM output
+ * (dense_gemm(..., _quantized_c=...), b12x/_lib/dense_gemm.py:7497-7588, kernel :2854-3090).
+ *
+ *   bias   [N] values of the output dtype. Added the way a separate bias add on the stored
+ *          output would: out = cvt(float(cvt(alpha * acc)) + float(bias[n])) for BF16 / FP16
+ *          outputs, a plain FP32 add for FP32 outputs.
+ *   quant_values  decode-shape entry points only, BF16 / FP16 output, N % 32 == 0: besides C,
+ *          the rounded output rows are re-quantized to MXFP8 along N exactly as
+ *          b12x_b200_quantize_mxfp8_rows would quantize C: E4M3 codes into
+ *          quant_values[M, quant_ld] at columns quant_col0 .. quant_col0 + N - 1.
+ *   quant_scale_rows  UE8M0 bytes, row-major [M, quant_cols / 32], or NULL.
+ *   quant_scale_mma   the same bytes in scale atoms of an [M, quant_cols] operand (row tile 0..,
+ *          ceil(quant_cols / 128) atoms per row tile), or NULL. Bytes of rows >= M are not
+ *          written (pre-fill with 127).
+ *   quant_ld, quant_col0, quant_cols  pitch of quant_values in bytes, first column and total
+ *          width of the quantized matrix this GEMM writes into (several GEMMs may fill one
+ *          matrix side by side, as the reference's grouped WO-A projection does).
+ */
+typedef struct b12x_b200_epilogue {
+  const void* bias;
+  void* quant_values;
+  void* quant_scale_rows;
+  void* quant_scale_mma;
+  int64_t quant_ld;
+  int64_t quant_col0;
+  int64_t quant_cols;
+} b12x_b200_epilogue_t;
+
 /* Library identification: "b12x_b200 <version> sm_100a". */
 const char* b12x_b200_version(void);
 
@@ -83,7 +114,8 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
                                int sm_count, int* status, b12x_b200_stream_t stream);
 
 /*
- * b12x_b200_gemm_blockscaled with caller-owned scratch. The CTA-pair kernel (chosen for large
+ * b12x_b200_gemm_blockscaled with caller-owned scratch and an optional epilogue (bias only;
+ * see b12x_b200_epilogue_t). The CTA-pair kernel (chosen for large
  * problems, or with B12X_B200_BLOCK_N_PAIR) runs whole rounds of 256 x 256 tiles over the SM
  * pairs; when the tiles left for the last round would occupy at most a tenth of the pairs, it cuts
  * them along K over all pairs instead and adds the FP32 partial tiles up through this scratch
@@ -99,11 +131,12 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
  */
 int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
                                                    int block_n, int sm_count);
-int b12x_b200_gemm_blockscaled_ws(int kind, const void* a, const void* sfa, const void* b,
+int b12x_b200_gemm_blockscaled_ex(int kind, const void* a, const void* sfa, const void* b,
                                   const void* sfb, void* c, int c_dtype, const float* alpha,
                                   int64_t m, int64_t n, int64_t k, int64_t ldc, int block_n,
                                   int sm_count, void* workspace, int64_t workspace_bytes,
-                                  int* status, b12x_b200_stream_t stream);
+                                  const b12x_b200_epilogue_t* epilogue, int* status,
+                                  b12x_b200_stream_t stream);
 
 /*
  * Decode-shape (1 <= M <= 128) variant of b12x_b200_gemm_blockscaled: the weight matrix is
@@ -137,6 +170,13 @@ int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
                                       int64_t m, int64_t n, int64_t k, int64_t ldc,
                                       void* workspace, int64_t workspace_bytes, int sm_count,
                                       int* status, b12x_b200_stream_t stream);
+/* The same with an epilogue (bias and / or MXFP8 re-quantization of the output rows). */
+int b12x_b200_gemm_blockscaled_smallm_ex(int kind, const void* x, const void* sf_x,
+                                         const void* w, const void* sf_w, void* c, int c_dtype,
+                                         const float* alpha, int64_t m, int64_t n, int64_t k,
+                                         int64_t ldc, void* workspace, int64_t workspace_bytes,
+                                         const b12x_b200_epilogue_t* epilogue, int sm_count,
+                                         int* status, b12x_b200_stream_t stream);
 
 /*
  * Decode-shape GEMM with the activation quantizer fused in (1 <= M <= 16): the BF16 rows are
@@ -149,13 +189,15 @@ int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const void* sf_x,
  *   x_bf16          [M, ld_x] BF16 rows, 16-byte aligned, ld_x % 8 == 0
  *   x_global_scale  NVFP4: device FP32 scalar (448 * 6 / amax), read at run time; MXFP8: NULL
  *   workspace       as for b12x_b200_gemm_blockscaled_smallm (same size query)
+ *   epilogue        optional, as for b12x_b200_gemm_blockscaled_smallm_ex
  * Other arguments and stream ordering as for b12x_b200_gemm_blockscaled_smallm.
  */
 int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x,
                                       const float* x_global_scale, const void* w,
                                       const void* sf_w, void* c, int c_dtype, const float* alpha,
                                       int64_t m, int64_t n, int64_t k, int64_t ldc,
-                                      void* workspace, int64_t workspace_bytes, int sm_count,
+                                      void* workspace, int64_t workspace_bytes,
+                                      const b12x_b200_epilogue_t* epilogue, int sm_count,
                                       int* status, b12x_b200_stream_t stream);
 
 /*
@@ -221,6 +263,12 @@ int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const void* b, con
                              void* c, int c_dtype, const float* alpha, int64_t m, int64_t n,
                              int64_t k, int64_t ldc, int sm_count, int* status,
                              b12x_b200_stream_t stream);
+/* The same with an epilogue (bias only; see b12x_b200_epilogue_t). */
+int b12x_b200_gemm_block_fp8_ex(const void* a, const float* sfa, const void* b, const float* sfb,
+                                void* c, int c_dtype, const float* alpha, int64_t m, int64_t n,
+                                int64_t k, int64_t ldc, int sm_count,
+                                const b12x_b200_epilogue_t* epilogue, int* status,
+                                b12x_b200_stream_t stream);
 
 /*
  * MXFP8 row quantizer. Replaces quantize_mxfp8_rows_cute

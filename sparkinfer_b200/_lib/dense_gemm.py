@@ -102,7 +102,9 @@ def _check_operand(name: str, t: torch.Tensor, rows: int, row_bytes: int, l: int
 def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int, ab_dtype: str,
                             sf_dtype: str, sf_vec_size: int, mma_tile_n: int, sm_count: int,
                             alpha_is_one: bool, stream_int: Optional[int],
-                            mma_tile_m: int = 128) -> None:
+                            mma_tile_m: int = 128,
+                            quantized_c: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
+                            ) -> None:
     kind = _kind_of(ab_dtype, sf_dtype, sf_vec_size)
     m = int(a.shape[0])
     row_bytes = k // 2 if kind == _native.KIND_NVFP4 else k
@@ -132,10 +134,14 @@ def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int,
     sfb_base = torch.as_strided(sfb_flat, (l * sfb_group,), (1,))
     ldc = c.stride(0) if m > 1 else n
     for g in range(l):
+        # Quantized C: group g fills columns [g * N, (g + 1) * N) of the [M, N * L] MXFP8 matrix.
+        qc = None if quantized_c is None else launch.QuantizedC(
+            quantized_c[0], quantized_c[1], quantized_c[2], col0=g * n, total_cols=n * l)
         launch.gemm_blockscaled(
             kind, a.select(2, g), sfa_base[g * sfa_group:], b.select(2, g),
             sfb_base[g * sfb_group:], c.select(2, g), None if alpha_is_one else alpha,
-            m, n, k, ldc=ldc, block_n=block_n, sm_count=sm_count, stream_int=stream_int)
+            m, n, k, ldc=ldc, block_n=block_n, sm_count=sm_count, stream_int=stream_int,
+            quantized_c=qc)
 
 
 @torch.library.custom_op("b12x::dense_gemm_launch", mutates_args=("c_tensor_gpu",))
@@ -273,8 +279,8 @@ def dense_gemm(
         raise ValueError(
             "a_preexpanded/b_preexpanded/a_fmt/b_fmt/x_bf16/w_gscale are only "
             f"supported with an MX-FP6 ab_dtype, got ab_dtype={ab_dtype!r}")
-    if rhs_values_tiled is not None or _quantized_c is not None:
-        raise NotImplementedError("tile-major RHS and quantized-C outputs are not part of this path")
+    if rhs_values_tiled is not None:
+        raise NotImplementedError("a tile-major RHS belongs to the WO projection path")
     if c_dtype not in _C_DTYPES:
         raise KeyError(f"unsupported c_dtype string: {c_dtype!r}")
 
@@ -316,6 +322,29 @@ def dense_gemm(
     if alpha is None:
         alpha = _cached_alpha_one(a_torch.device)
     stream_int = cuda_stream_to_int(stream)
+    if _quantized_c is not None:
+        # The GEMM also emits the MXFP8 re-quantization of its BF16 output rows (the decode
+        # kernel's epilogue does it): restricted, as in the reference, to the small-M layout its
+        # WO-A projection uses (b12x/_lib/dense_gemm.py:7497-7588).
+        q_values, q_scale_rows, q_scale_mma = _quantized_c
+        width = n * l
+        if (swap_ab or c_dtype != "bfloat16" or m < 1 or m > 16 or n % 32 != 0 or width % 128 != 0
+                or block_fp8 or plain_fp8
+                or tuple(q_values.shape) != (m, width) or not q_values.is_contiguous()
+                or q_values.dtype != torch.float8_e4m3fn
+                or tuple(q_scale_rows.shape) != (m, width // 32) or not q_scale_rows.is_contiguous()
+                or q_scale_rows.dtype != torch.float8_e8m0fnu
+                or tuple(q_scale_mma.shape) != (32, 4, 1, 4, width // 128, 1)
+                or q_scale_mma.dtype != torch.float8_e8m0fnu):
+            raise ValueError("quantized C is restricted to the BF16 WO-A decode layout")
+        if out is None:
+            out = _empty_dense_gemm_output(m, n, l, dtype=torch.bfloat16, device=a_torch.device)
+        _dense_gemm_launch_flat(
+            a_torch, b_torch, sfa_torch, sfb_torch, out, alpha, n=n, k=k, l=l, ab_dtype=ab_dtype,
+            sf_dtype=sf_dtype, sf_vec_size=sf_vec_size, mma_tile_n=0, sm_count=int(sm_count),
+            alpha_is_one=alpha_is_one, stream_int=stream_int,
+            quantized_c=(q_values, q_scale_rows, q_scale_mma))
+        return out
     op_tail = (
         alpha_dtype, sf_vec_size, mma_k, sf_vec_size * 8 if ab_dtype == "float4_e2m1fn" else 128,
         int(mma_tiler_mn[0]), int(mma_tiler_mn[1]), int(cluster_shape_mn[0]),

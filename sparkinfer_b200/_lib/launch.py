@@ -167,11 +167,51 @@ def route_to_decode_kernel(m: int, n: int, device: torch.device, sm_count: int =
     return 0 < m <= SMALL_M_AUTO
 
 
+class QuantizedC:
+    """Where a decode GEMM also writes the MXFP8 re-quantization of its rounded output rows:
+    ``values [M, total_cols]`` E4M3 (row pitch ``values.stride(0)``), ``scale_rows
+    [M, total_cols / 32]`` and/or flat ``scale_mma`` atoms; this GEMM fills columns
+    ``col0 .. col0 + N - 1`` of the ``total_cols``-wide matrix."""
+
+    def __init__(self, values: torch.Tensor, scale_rows: torch.Tensor | None,
+                 scale_mma: torch.Tensor | None, col0: int = 0, total_cols: int | None = None):
+        self.values, self.scale_rows, self.scale_mma = values, scale_rows, scale_mma
+        self.col0 = int(col0)
+        self.total_cols = int(values.shape[-1] if total_cols is None else total_cols)
+
+
+def _epilogue(c: torch.Tensor, n: int, bias: torch.Tensor | None,
+              quantized_c: QuantizedC | None):
+    """ctypes ``Epilogue`` (or None) after the checks only the host can make."""
+    if bias is None and quantized_c is None:
+        return None
+    ep = _native.Epilogue()
+    if bias is not None:
+        _require_cuda("bias", bias)
+        if bias.dtype != c.dtype or bias.ndim != 1 or bias.shape[0] != n or bias.stride(0) != 1:
+            raise ValueError(f"a fused bias must be a contiguous [{n}] tensor of the output dtype "
+                             f"{c.dtype}, got {bias.dtype} {tuple(bias.shape)}")
+        ep.bias = bias.data_ptr()
+    if quantized_c is not None:
+        q = quantized_c
+        _require_cuda("quantized-C values", q.values)
+        if q.values.element_size() != 1 or q.values.stride(-1) != 1:
+            raise ValueError("quantized-C values must be one-byte elements with unit column stride")
+        ep.quant_values = q.values.data_ptr()
+        ep.quant_scale_rows = q.scale_rows.data_ptr() if q.scale_rows is not None else None
+        ep.quant_scale_mma = q.scale_mma.data_ptr() if q.scale_mma is not None else None
+        ep.quant_ld = q.values.stride(0) if q.values.ndim > 1 and q.values.shape[0] > 1 else q.total_cols
+        ep.quant_col0 = q.col0
+        ep.quant_cols = q.total_cols
+    return ep
+
+
 def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
                      sfb: torch.Tensor, c: torch.Tensor, alpha: torch.Tensor | None,
                      m: int, n: int, k: int, *, ldc: int | None = None, block_n: int = 0,
                      sm_count: int = 0, stream_int: int | None = None,
-                     small_m: bool | None = None) -> None:
+                     small_m: bool | None = None, bias: torch.Tensor | None = None,
+                     quantized_c: QuantizedC | None = None) -> None:
     """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)`` for one group. ``a``/``b`` are row
     pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom.
 
@@ -183,17 +223,20 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     if c.dtype not in _DTYPE_CODE:
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = a.device
+    ep = _epilogue(c, n, bias, quantized_c)
     if small_m is None:
-        small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and route_to_decode_kernel(m, n, dev, sm_count)
+        small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and (
+            quantized_c is not None or route_to_decode_kernel(m, n, dev, sm_count))
     if small_m and 0 < m <= SMALL_M_MAX and n > 0:
         work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
         with torch.cuda.device(dev):
-            rc = _native.load().b12x_b200_gemm_blockscaled_smallm(
+            rc = _native.load().b12x_b200_gemm_blockscaled_smallm_ex(
                 kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
                 _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
-                m, n, k, ldc if ldc is not None else n, work.data_ptr(), work.numel(), sm_count,
+                m, n, k, ldc if ldc is not None else n, work.data_ptr(), work.numel(),
+                ctypes.byref(ep) if ep is not None else None, sm_count,
                 status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-        _native.check(rc, "b12x_b200_gemm_blockscaled_smallm")
+        _native.check(rc, "b12x_b200_gemm_blockscaled_smallm_ex")
         return
     lib = _native.load()
     with torch.cuda.device(dev):
@@ -201,20 +244,22 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
         need = int(lib.b12x_b200_gemm_blockscaled_workspace_bytes(kind, m, n, k, block_n, sm_count))
     work = stream_workspace(need, dev, stream_int) if need > 0 else None
     with torch.cuda.device(dev):
-        rc = lib.b12x_b200_gemm_blockscaled_ws(
+        rc = lib.b12x_b200_gemm_blockscaled_ex(
             kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
             _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
             m, n, k, ldc if ldc is not None else n, block_n, sm_count,
             work.data_ptr() if work is not None else None, work.numel() if work is not None else 0,
+            ctypes.byref(ep) if ep is not None else None,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-    _native.check(rc, "b12x_b200_gemm_blockscaled_ws")
+    _native.check(rc, "b12x_b200_gemm_blockscaled_ex")
 
 
 def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tensor | None,
                             w: torch.Tensor, sfw: torch.Tensor, c: torch.Tensor,
                             alpha: torch.Tensor | None, m: int, n: int, k: int, *,
                             ldc: int | None = None, sm_count: int = 0,
-                            stream_int: int | None = None) -> None:
+                            stream_int: int | None = None, bias: torch.Tensor | None = None,
+                            quantized_c: QuantizedC | None = None) -> None:
     """Decode GEMM that quantizes its BF16 activation rows ``x [M, K]`` (M <= 16) inside the
     kernel; bit for bit ``quantize rows`` followed by :func:`gemm_blockscaled`."""
     for name, t in (("x", x), ("w", w), ("sfw", sfw), ("c", c)):
@@ -224,6 +269,7 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
     if c.dtype not in _DTYPE_CODE:
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = x.device
+    ep = _epilogue(c, n, bias, quantized_c)
     work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
     with torch.cuda.device(dev):
         rc = _native.load().b12x_b200_gemm_smallm_fused_quant(
@@ -231,7 +277,8 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
             global_scale.data_ptr() if global_scale is not None else None, w.data_ptr(),
             sfw.data_ptr(), c.data_ptr(), _DTYPE_CODE[c.dtype],
             alpha.data_ptr() if alpha is not None else None, m, n, k,
-            ldc if ldc is not None else n, work.data_ptr(), work.numel(), sm_count,
+            ldc if ldc is not None else n, work.data_ptr(), work.numel(),
+            ctypes.byref(ep) if ep is not None else None, sm_count,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
     _native.check(rc, "b12x_b200_gemm_smallm_fused_quant")
 
@@ -264,18 +311,19 @@ def selftest_wait_timeout(device: torch.device, max_polls: int = 4096) -> None:
 def gemm_block_fp8(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: torch.Tensor,
                    c: torch.Tensor, alpha: torch.Tensor | None, m: int, n: int, k: int, *,
                    ldc: int | None = None, sm_count: int = 0,
-                   stream_int: int | None = None) -> None:
+                   stream_int: int | None = None, bias: torch.Tensor | None = None) -> None:
     """E4M3 operands with FP32 scales ``sfa [M, K/128]`` / ``sfb [N/128, K/128]``."""
     for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
         _require_cuda(name, t)
     dev = a.device
+    ep = _epilogue(c, n, bias, None)
     with torch.cuda.device(dev):
-        rc = _native.load().b12x_b200_gemm_block_fp8(
+        rc = _native.load().b12x_b200_gemm_block_fp8_ex(
             a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
             _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None, m, n, k,
-            ldc if ldc is not None else n, sm_count, status_buffer(dev).data_ptr(),
-            _stream_ptr(stream_int, dev))
-    _native.check(rc, "b12x_b200_gemm_block_fp8")
+            ldc if ldc is not None else n, sm_count, ctypes.byref(ep) if ep is not None else None,
+            status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_block_fp8_ex")
 
 
 def quantize_mxfp8_rows(src: torch.Tensor, values: torch.Tensor, scale_rows: torch.Tensor | None,
@@ -305,7 +353,7 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
 
 
 __all__ = [
-    "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled",
+    "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
     "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
     "route_to_decode_kernel", "smallm_workspace", "stream_workspace", "quantize_mxfp8_rows",
     "quantize_nvfp4_rows",

@@ -26,6 +26,17 @@ _c_void_p = ctypes.c_void_p
 _c_int = ctypes.c_int
 _c_i64 = ctypes.c_int64
 
+
+class Epilogue(ctypes.Structure):
+    """``b12x_b200_epilogue_t``: optional bias and MXFP8 re-quantization of the output."""
+
+    _fields_ = [("bias", _c_void_p), ("quant_values", _c_void_p), ("quant_scale_rows", _c_void_p),
+                ("quant_scale_mma", _c_void_p), ("quant_ld", _c_i64), ("quant_col0", _c_i64),
+                ("quant_cols", _c_i64)]
+
+
+_c_epilogue_p = ctypes.POINTER(Epilogue)
+
 # name -> (restype, argtypes); one entry per function declared in include/b12x_b200.h.
 SIGNATURES = {
     "b12x_b200_version": (ctypes.c_char_p, []),
@@ -37,10 +48,22 @@ SIGNATURES = {
     ),
     "b12x_b200_gemm_blockscaled_workspace_bytes": (
         _c_i64, [_c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
-    "b12x_b200_gemm_blockscaled_ws": (
+    "b12x_b200_gemm_blockscaled_ex": (
         _c_int,
         [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
-         _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_i64, _c_void_p, _c_void_p],
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_i64, _c_epilogue_p,
+         _c_void_p, _c_void_p],
+    ),
+    "b12x_b200_gemm_blockscaled_smallm_ex": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_epilogue_p, _c_int, _c_void_p,
+         _c_void_p],
+    ),
+    "b12x_b200_gemm_block_fp8_ex": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_epilogue_p, _c_void_p, _c_void_p],
     ),
     "b12x_b200_gemm_smallm_workspace_bytes": (_c_i64, [_c_int, _c_i64, _c_i64, _c_i64, _c_int]),
     "b12x_b200_gemm_blockscaled_smallm": (
@@ -51,7 +74,8 @@ SIGNATURES = {
     "b12x_b200_gemm_smallm_fused_quant": (
         _c_int,
         [_c_int, _c_void_p, _c_i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
-         _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_int, _c_void_p, _c_void_p],
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_epilogue_p, _c_int, _c_void_p,
+         _c_void_p],
     ),
     "b12x_b200_gemm_smallm_timeline": (
         _c_int,

@@ -52,6 +52,33 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Checks of the optional epilogue description that do not depend on the kernel. `allow_quant`:
+// whether the kernel that will run can re-quantize its output (only the decode kernel can).
+int check_epilogue(const b12x_b200_epilogue_t* e, int c_dtype, int64_t n, bool allow_quant) {
+  if (!e) return B12X_B200_OK;
+  if (e->bias) {
+    const uintptr_t align = (c_dtype == B12X_B200_FP32) ? 3 : 1;
+    if (reinterpret_cast<uintptr_t>(e->bias) & align)
+      return fail(B12X_B200_ERR_ALIGNMENT, "bias must be aligned to its element size");
+  }
+  if (e->quant_values) {
+    if (!allow_quant)
+      return fail(B12X_B200_ERR_UNSUPPORTED,
+                  "output re-quantization is available in the decode kernel only (M <= 128)");
+    if (c_dtype == B12X_B200_FP32)
+      return fail(B12X_B200_ERR_UNSUPPORTED, "output re-quantization needs a BF16 or FP16 output");
+    if (n % 32 != 0 || e->quant_cols % 32 != 0 || e->quant_col0 % 32 != 0 || e->quant_col0 < 0 ||
+        e->quant_col0 + n > e->quant_cols || e->quant_ld < e->quant_cols ||
+        e->quant_cols > INT32_MAX)
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT,
+                  "re-quantized output: N, quant_col0 and quant_cols must be multiples of 32, "
+                  "quant_col0 + N <= quant_cols <= quant_ld");
+  } else if (e->quant_scale_rows || e->quant_scale_mma) {
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "quant scales given without quant_values");
+  }
+  return B12X_B200_OK;
+}
+
 // K-major byte matrix [rows, row_bytes] -> boxes of 128 bytes x box_rows, 128-byte swizzle.
 int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                      uint32_t box_rows) {
@@ -325,7 +352,8 @@ namespace {
 int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* b, const void* sfb,
                           void* c, int c_dtype, const float* alpha, int64_t m, int64_t n, int64_t k,
                           int64_t ldc, int block_n, int sm_count, void* workspace,
-                          int64_t workspace_bytes, int* status, b12x_b200_stream_t stream) {
+                          int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue,
+                          int* status, b12x_b200_stream_t stream) {
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
@@ -339,6 +367,10 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   if (m == 0 || n == 0) return B12X_B200_OK;
   if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  {
+    const int erc = check_epilogue(epilogue, c_dtype, n, false);
+    if (erc != B12X_B200_OK) return erc;
+  }
   const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
   if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
   const int64_t row_bytes = (kind == B12X_B200_KIND_MXFP8) ? k : k / 2;
@@ -384,6 +416,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   p.tiles_n = int((n + bn - 1) / bn);
   p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
   p.group_m = 16;
+  p.bias = epilogue ? epilogue->bias : nullptr;
   p.num_stages = 0;  // filled per instantiation
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
@@ -433,17 +466,18 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
                                           int64_t ldc, int block_n, int sm_count, int* status,
                                           b12x_b200_stream_t stream) {
   return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
-                               sm_count, nullptr, 0, status, stream);
+                               sm_count, nullptr, 0, nullptr, status, stream);
 }
 
-extern "C" int b12x_b200_gemm_blockscaled_ws(int kind, const void* a, const void* sfa,
+extern "C" int b12x_b200_gemm_blockscaled_ex(int kind, const void* a, const void* sfa,
                                              const void* b, const void* sfb, void* c, int c_dtype,
                                              const float* alpha, int64_t m, int64_t n, int64_t k,
                                              int64_t ldc, int block_n, int sm_count,
-                                             void* workspace, int64_t workspace_bytes, int* status,
+                                             void* workspace, int64_t workspace_bytes,
+                                             const b12x_b200_epilogue_t* epilogue, int* status,
                                              b12x_b200_stream_t stream) {
   return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
-                               sm_count, workspace, workspace_bytes, status, stream);
+                               sm_count, workspace, workspace_bytes, epilogue, status, stream);
 }
 
 extern "C" int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n,
@@ -535,11 +569,12 @@ extern "C" int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int
   return B12X_B200_OK;
 }
 
-extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const void* b,
-                                        const float* sfb, void* c, int c_dtype,
-                                        const float* alpha, int64_t m, int64_t n, int64_t k,
-                                        int64_t ldc, int sm_count, int* status,
-                                        b12x_b200_stream_t stream) {
+namespace {
+
+int gemm_block_fp8_impl(const void* a, const float* sfa, const void* b, const float* sfb, void* c,
+                        int c_dtype, const float* alpha, int64_t m, int64_t n, int64_t k,
+                        int64_t ldc, int sm_count, const b12x_b200_epilogue_t* epilogue,
+                        int* status, b12x_b200_stream_t stream) {
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
   if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
@@ -552,6 +587,10 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   if (!aligned16(a) || !aligned16(b) || (reinterpret_cast<uintptr_t>(sfa) & 3) ||
       (reinterpret_cast<uintptr_t>(sfb) & 3))
     return fail(B12X_B200_ERR_ALIGNMENT, "operands must be 16-byte and scales 4-byte aligned");
+  {
+    const int erc = check_epilogue(epilogue, c_dtype, n, false);
+    if (erc != B12X_B200_OK) return erc;
+  }
   DeviceInfo info;
   int rc = device_info(&info);
   if (rc != B12X_B200_OK) return rc;
@@ -578,6 +617,7 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   p.tiles_m = int((m + BlockFp8Tile::BM - 1) / BlockFp8Tile::BM);
   p.tiles_n = int((n + BlockFp8Tile::BN - 1) / BlockFp8Tile::BN);
   p.group_m = 16;
+  p.bias = epilogue ? epilogue->bias : nullptr;
   const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
   const int grid = int(tiles < sms ? tiles : sms);
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
@@ -605,6 +645,27 @@ extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const v
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_block_fp8 launch");
   return B12X_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int b12x_b200_gemm_block_fp8(const void* a, const float* sfa, const void* b,
+                                        const float* sfb, void* c, int c_dtype,
+                                        const float* alpha, int64_t m, int64_t n, int64_t k,
+                                        int64_t ldc, int sm_count, int* status,
+                                        b12x_b200_stream_t stream) {
+  return gemm_block_fp8_impl(a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, sm_count, nullptr,
+                             status, stream);
+}
+
+extern "C" int b12x_b200_gemm_block_fp8_ex(const void* a, const float* sfa, const void* b,
+                                           const float* sfb, void* c, int c_dtype,
+                                           const float* alpha, int64_t m, int64_t n, int64_t k,
+                                           int64_t ldc, int sm_count,
+                                           const b12x_b200_epilogue_t* epilogue, int* status,
+                                           b12x_b200_stream_t stream) {
+  return gemm_block_fp8_impl(a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, sm_count, epilogue,
+                             status, stream);
 }
 
 namespace {
@@ -739,6 +800,7 @@ struct SmallMCall {
   int* status;
   unsigned long long* timeline;
   cudaStream_t stream;
+  const b12x_b200_epilogue_t* epilogue = nullptr;
 };
 
 // Argument checks shared by the decode-shape entry points. On success *empty is set when there
@@ -758,6 +820,10 @@ int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empt
   }
   if (!a.w || !a.sf_w || !a.c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   if (a.ldc < a.n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
+  {
+    const int erc = check_epilogue(a.epilogue, a.c_dtype, a.n, true);
+    if (erc != B12X_B200_OK) return erc;
+  }
   if (a.k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
   const int64_t row_bytes = (a.kind == B12X_B200_KIND_MXFP8) ? a.k : a.k / 2;
   if (row_bytes % 16 != 0 || !aligned16(a.w) || !aligned16(a.sf_w))
@@ -830,6 +896,15 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.sf_col0 = pl.sf_col0;
   p.x_gs = a.x_gs;
   p.raw_rows = pl.raw_rows;
+  if (a.epilogue) {
+    p.bias = a.epilogue->bias;
+    p.quant_values = static_cast<uint8_t*>(a.epilogue->quant_values);
+    p.quant_scale_rows = static_cast<uint8_t*>(a.epilogue->quant_scale_rows);
+    p.quant_scale_mma = static_cast<uint8_t*>(a.epilogue->quant_scale_mma);
+    p.quant_ld = a.epilogue->quant_ld;
+    p.quant_col0 = int(a.epilogue->quant_col0);
+    p.quant_cols = int(a.epilogue->quant_cols);
+  }
   p.wait_for_weights = a.n <= kEarlyReleaseRows ? 1 : 0;
   p.timeline = a.timeline;
   const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
@@ -877,17 +952,35 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm(int kind, const void* x, const 
   return smallm_entry(a, workspace, workspace_bytes);
 }
 
+extern "C" int b12x_b200_gemm_blockscaled_smallm_ex(int kind, const void* x, const void* sf_x,
+                                                    const void* w, const void* sf_w, void* c,
+                                                    int c_dtype, const float* alpha, int64_t m,
+                                                    int64_t n, int64_t k, int64_t ldc,
+                                                    void* workspace, int64_t workspace_bytes,
+                                                    const b12x_b200_epilogue_t* epilogue,
+                                                    int sm_count, int* status,
+                                                    b12x_b200_stream_t stream) {
+  SmallMCall a = {kind, x,     sf_x, nullptr, 0,   nullptr,  w,      sf_w,    c, c_dtype,
+                  alpha, m,    n,    k,       ldc, sm_count, status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  a.epilogue = epilogue;
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
 extern "C" int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x,
                                                  const float* x_global_scale, const void* w,
                                                  const void* sf_w, void* c, int c_dtype,
                                                  const float* alpha, int64_t m, int64_t n,
                                                  int64_t k, int64_t ldc, void* workspace,
-                                                 int64_t workspace_bytes, int sm_count,
-                                                 int* status, b12x_b200_stream_t stream) {
+                                                 int64_t workspace_bytes,
+                                                 const b12x_b200_epilogue_t* epilogue,
+                                                 int sm_count, int* status,
+                                                 b12x_b200_stream_t stream) {
   if (!x_bf16) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   SmallMCall a = {kind,  nullptr, nullptr, x_bf16, ld_x, x_global_scale, w,      sf_w,    c, c_dtype,
                   alpha, m,       n,       k,      ldc,  sm_count,       status, nullptr,
                   reinterpret_cast<cudaStream_t>(stream)};
+  a.epilogue = epilogue;
   return smallm_entry(a, workspace, workspace_bytes);
 }
 

@@ -47,6 +47,7 @@ struct BlockFp8Params {
   int m, n, k, ldc, out_dtype;
   int tiles_m, tiles_n, group_m;
   int use_tma_store;   // 2-byte outputs with 16-byte aligned rows
+  const void* bias;    // [N] values of the output dtype added to every row, or null
 };
 
 // Named barrier 1 + group over the 128 threads (four warps) that share an output sub-tile.
@@ -235,12 +236,25 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         const int r = quarter * 32 + lane;
         uint8_t* sub = c_stage + group * (128 * 128) + r * 128;
+        if (p.bias != nullptr) {
+          // acc becomes float(cvt(alpha * acc)) + bias; the packing below rounds the sum.
+#pragma unroll
+          for (int c = 0; c < kCols / 32; ++c) {
+            float vals[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) vals[i] = acc[c * 32 + i] * alpha;
+            add_bias_32(vals, p.bias, p.out_dtype, col0 + c * 32, p.n);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = vals[i];
+          }
+        }
+        const float out_scale = (p.bias != nullptr) ? 1.0f : alpha;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint32_t w[4];
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            const float lo = acc[j * 8 + 2 * h] * alpha, hi = acc[j * 8 + 2 * h + 1] * alpha;
+            const float lo = acc[j * 8 + 2 * h] * out_scale, hi = acc[j * 8 + 2 * h + 1] * out_scale;
             w[h] = (p.out_dtype == kOutBf16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
           }
           *reinterpret_cast<uint4*>(sub + ((j ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -266,6 +280,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = acc[c * 32 + i] * alpha;
+        add_bias_32(vals, p.bias, p.out_dtype, col0 + c * 32, p.n);
         store_row_chunk(gp, row, col0 + c * 32, vals);
       }
     }

@@ -18,6 +18,9 @@
 // for 128 rows of A and BN rows of B plus that slice's scale atoms.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "sm100_ptx.cuh"
 
 namespace b12x_b200 {
@@ -77,6 +80,7 @@ struct GemmParams {
   int group_m;           // tile-order grouping along M (L2 reuse)
   int num_stages;        // shared-memory ring depth actually used (<= GemmTile::kStages)
   int use_tma_store;     // 2-byte outputs with 16-byte aligned rows: stage in smem, TMA store
+  const void* bias;      // [N] values of the output dtype added to every row, or null
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
@@ -100,6 +104,68 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+
+// Bias epilogue on 32 consecutive output columns of one row (`vals` already carry alpha). The
+// result is what adding a bias tensor to the stored output gives: for 2-byte outputs the
+// product is first rounded to the output type, then the sum is formed in FP32 and rounded again
+// by the store (out = cvt(float(cvt(alpha * acc)) + float(bias[n]))); for FP32 outputs it is a
+// plain FP32 add. Every thread of a warp asks for the same 32 bias values, so the loads
+// broadcast; columns at or beyond N read as zero.
+__device__ __forceinline__ void add_bias_32(float (&vals)[32], const void* bias, int out_dtype,
+                                            int col0, int n) {
+  if (bias == nullptr) return;
+  if (out_dtype == kOutFp32) {
+    const float* b = static_cast<const float*>(bias);
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < n) vals[i] = __fadd_rn(vals[i], __ldg(b + col0 + i));
+    return;
+  }
+  const uint16_t* b = static_cast<const uint16_t*>(bias);
+  uint32_t packed[16];
+  if (col0 + 32 <= n && ((reinterpret_cast<uintptr_t>(b + col0) & 15) == 0)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(b + col0) + i);
+      packed[4 * i] = v.x; packed[4 * i + 1] = v.y; packed[4 * i + 2] = v.z; packed[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t lo = (col0 + 2 * i < n) ? __ldg(b + col0 + 2 * i) : 0u;
+      const uint32_t hi = (col0 + 2 * i + 1 < n) ? __ldg(b + col0 + 2 * i + 1) : 0u;
+      packed[i] = lo | (hi << 16);
+    }
+  }
+  if (out_dtype == kOutBf16) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t y = pack_bf16x2(vals[2 * i], vals[2 * i + 1]);
+      vals[2 * i] = __fadd_rn(__uint_as_float(y << 16), __uint_as_float(packed[i] << 16));
+      vals[2 * i + 1] = __fadd_rn(__uint_as_float(y & 0xFFFF0000u), __uint_as_float(packed[i] & 0xFFFF0000u));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t y = pack_f16x2(vals[2 * i], vals[2 * i + 1]);
+      const float2 yf = __half22float2(*reinterpret_cast<const __half2*>(&y));
+      const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&packed[i]));
+      vals[2 * i] = __fadd_rn(yf.x, bf.x);
+      vals[2 * i + 1] = __fadd_rn(yf.y, bf.y);
+    }
+  }
+}
+
+// Same for a single output value (column `col`).
+__device__ __forceinline__ float add_bias_1(float v, const void* bias, int out_dtype, int col, int n) {
+  if (bias == nullptr || col >= n) return v;
+  if (out_dtype == kOutFp32) return __fadd_rn(v, __ldg(static_cast<const float*>(bias) + col));
+  const uint32_t b = __ldg(static_cast<const uint16_t*>(bias) + col);
+  if (out_dtype == kOutBf16)
+    return __fadd_rn(__bfloat162float(__float2bfloat16_rn(v)), __uint_as_float(b << 16));
+  const __half_raw hr = {static_cast<unsigned short>(b)};
+  return __fadd_rn(__half2float(__float2half_rn(v)), __half2float(__half(hr)));
 }
 
 // Writes 32 consecutive output columns of one row. `vals` already carry alpha.
@@ -375,17 +441,17 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
               tmem_load_wait();
               if (cc + 1 < chunks) tmem_load_32cols(taddr + pass * 128 + (cc + 1) * 32, raw[(cc + 1) & 1]);
               const uint32_t(&cur)[32] = raw[cc & 1];
+              float vals[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(cur[i]) * alpha;
+              add_bias_32(vals, p.bias, p.out_dtype, tn * BN + pass * 128 + cc * 32, p.n);
               uint32_t packed[16];
               if (p.out_dtype == kOutBf16) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  packed[i] = pack_bf16x2(__uint_as_float(cur[2 * i]) * alpha,
-                                          __uint_as_float(cur[2 * i + 1]) * alpha);
+                for (int i = 0; i < 16; ++i) packed[i] = pack_bf16x2(vals[2 * i], vals[2 * i + 1]);
               } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  packed[i] = pack_f16x2(__uint_as_float(cur[2 * i]) * alpha,
-                                         __uint_as_float(cur[2 * i + 1]) * alpha);
+                for (int i = 0; i < 16; ++i) packed[i] = pack_f16x2(vals[2 * i], vals[2 * i + 1]);
               }
               // Sub-tile of 64 columns = 128-byte rows; 16-byte chunk j of row r lives at
               // position j ^ (r % 8), the layout a 128-byte-swizzled TMA store expects.
@@ -424,6 +490,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
+        add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
         store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();

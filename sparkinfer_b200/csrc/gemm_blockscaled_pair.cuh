@@ -452,7 +452,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             const int q = q0 + i;
             const int col = tn * BN + q * 4;
             if (q < q_end && row < p.m && col < p.n) {
-              const float o[4] = {sum[i].x * alpha, sum[i].y * alpha, sum[i].z * alpha, sum[i].w * alpha};
+              float o[4] = {sum[i].x * alpha, sum[i].y * alpha, sum[i].z * alpha, sum[i].w * alpha};
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[j] = add_bias_1(o[j], p.bias, p.out_dtype, col + j, p.n);
+              }
               const size_t idx = static_cast<size_t>(row) * p.ldc + col;
               if (p.out_dtype != kOutFp32 && col + 4 <= p.n &&
                   ((reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(p.c) + idx) & 7) == 0)) {
@@ -497,7 +501,20 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool store_thread = (threadIdx.x == 64);
         uint32_t raw[4][32];
         uint32_t packed[64];
-        auto convert_chunk = [&](int cc) {
+        // `half` = which 128 columns of the tile raw[] currently holds.
+        auto convert_chunk = [&](int cc, int half) {
+          if (p.bias != nullptr) {
+            float vals[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[cc][i]) * alpha;
+            add_bias_32(vals, p.bias, p.out_dtype, tn * BN + half * 128 + cc * 32, p.n);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              packed[cc * 16 + i] = (p.out_dtype == kOutBf16)
+                                        ? pack_bf16x2(vals[2 * i], vals[2 * i + 1])
+                                        : pack_f16x2(vals[2 * i], vals[2 * i + 1]);
+            return;
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float lo = __uint_as_float(raw[cc][2 * i]) * alpha;
@@ -543,7 +560,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         // the matching chunk of the second half, so those loads run under the conversion.
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          convert_chunk(cc);
+          convert_chunk(cc, 0);
           tmem_load_32cols(taddr + 128 + cc * 32, raw[cc]);
         }
         tmem_load_wait();
@@ -552,7 +569,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         stage_and_store(0);
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) convert_chunk(cc);
+        for (int cc = 0; cc < 4; ++cc) convert_chunk(cc, 1);
         stage_and_store(1);
         continue;
       }
@@ -564,6 +581,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
+        add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
         store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();

@@ -86,6 +86,16 @@ struct SmallMParams {
   // BF16 rows (8 or 16) a stage holds behind the code tile.
   const float* x_gs;
   int raw_rows;
+  // Epilogue extras. bias: [N] values of the output dtype added to every row (null = none).
+  // quant_*: MXFP8 re-quantization of the rounded output rows along N (null = off): E4M3 codes
+  // [M, quant_ld], UE8M0 bytes row-major [M, quant_cols / 32] and/or in scale atoms, this GEMM's
+  // columns starting at column quant_col0 of a quant_cols-wide matrix.
+  const void* bias;
+  uint8_t* quant_values;
+  uint8_t* quant_scale_rows;
+  uint8_t* quant_scale_mma;
+  long long quant_ld;
+  int quant_col0, quant_cols;
   // Non-zero: the weight stream too waits for the previous grid (weights of few rows may be a
   // predecessor's fresh output, see the header comment).
   int wait_for_weights;
@@ -534,6 +544,47 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       const int n_local = quarter * 32 + lane;          // weight row inside the tile
       const float alpha = p.alpha ? *p.alpha : 1.0f;
       const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
+      const bool quantize_c = p.quant_values != nullptr;
+      // Final value of output element (mrow, n_global): scale, round to the output type, add the
+      // bias, store; then, if asked, the MXFP8 codes of the rounded row. A warp holds 32
+      // consecutive columns of the row, which is exactly one scale block, so the block maximum
+      // is one warp-wide integer max of the magnitudes' bit patterns. Called by whole warps.
+      auto emit = [&](int mrow, int n_global, bool n_ok, float acc_value) {
+        float v = acc_value * alpha;
+        if (p.bias != nullptr) v = add_bias_1(v, p.bias, p.out_dtype, n_global, p.n);
+        const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+        float stored = v;
+        if (p.out_dtype == kOutBf16) {
+          const __nv_bfloat16 h = __float2bfloat16_rn(v);
+          if (n_ok) static_cast<__nv_bfloat16*>(p.c)[idx] = h;
+          stored = __bfloat162float(h);
+        } else if (p.out_dtype == kOutFp16) {
+          const __half h = __float2half_rn(v);
+          if (n_ok) static_cast<__half*>(p.c)[idx] = h;
+          stored = __half2float(h);
+        } else if (n_ok) {
+          static_cast<float*>(p.c)[idx] = v;
+        }
+        if (quantize_c) {
+          const uint32_t mag = n_ok ? (__float_as_uint(stored) & 0x7FFFFFFFu) : 0u;
+          const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, mag));
+          const uint32_t byte = ue8m0_from_amax(amax);
+          const float inv = ue8m0_reciprocal(byte);
+          if (n_ok) {
+            const int qcol = p.quant_col0 + n_global;
+            p.quant_values[static_cast<size_t>(mrow) * p.quant_ld + qcol] =
+                static_cast<uint8_t>(e4m3x4(__fmul_rn(stored, inv), 0.0f, 0.0f, 0.0f) & 0xFFu);
+            if (lane == 0) {
+              if (p.quant_scale_rows)
+                p.quant_scale_rows[static_cast<size_t>(mrow) * (p.quant_cols >> 5) + (qcol >> 5)] =
+                    static_cast<uint8_t>(byte);
+              if (p.quant_scale_mma)
+                p.quant_scale_mma[sf_atom_offset(mrow, qcol >> 5, (p.quant_cols + 127) >> 7)] =
+                    static_cast<uint8_t>(byte);
+            }
+          }
+        }
+      };
       int seg = 0;
       int u = u_begin;
       while (u < u_end) {
@@ -585,16 +636,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int mrow = c0 + i;
-              if (n_ok && mrow < p.m) {
-                const float v = __uint_as_float(raw[i]) * alpha;
-                const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
-                if (p.out_dtype == kOutBf16)
-                  static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
-                else if (p.out_dtype == kOutFp16)
-                  static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
-                else
-                  static_cast<float*>(p.c)[idx] = v;
-              }
+              if (mrow < p.m) emit(mrow, n_global, n_ok, __uint_as_float(raw[i]));
             }
           } else {
 #pragma unroll
@@ -635,16 +677,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int mrow = m0 + i;
-                if (n_ok && mrow < p.m) {
-                  const float v = sum[i] * alpha;
-                  const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
-                  if (p.out_dtype == kOutBf16)
-                    static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
-                  else if (p.out_dtype == kOutFp16)
-                    static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
-                  else
-                    static_cast<float*>(p.c)[idx] = v;
-                }
+                if (mrow < p.m) emit(mrow, n_global, n_ok, sum[i]);
               }
             }
           }

@@ -1,4 +1,7 @@
-"""Host side of the ModelOpt MXFP8 linear (b12x/gemm/mxfp8_linear/_kernel.py:21-266)."""
+"""Host side of the ModelOpt MXFP8 linear (b12x/gemm/mxfp8_linear/_kernel.py:21-266): weight
+packing, the ``b12x::mxfp8_linear_fused`` custom op and ``mxfp8_linear``. The forward step
+(pad K, quantize rows, GEMM, bias) is the shared core of :mod:`sparkinfer_b200._lib.linear_core`.
+"""
 
 from __future__ import annotations
 
@@ -6,15 +9,27 @@ from dataclasses import dataclass
 
 import torch
 
-from ..._lib.dense_gemm import dense_gemm
 from ..._lib.launch import cuda_stream_to_int
+from ..._lib.linear_core import (
+    K_STEP,
+    SourceRows,
+    bias_fuses,
+    output_dtype_name,
+    pad_columns,
+    quantize_then_gemm,
+    require_cuda_tensor,
+    round_up,
+)
 from ..._lib.mxfp8_rows import (
     MXFP8Rows,
-    MXFP8_SCALE_VEC_SIZE,
-    _check_gpu_tensor,
+    SCALE_BLOCK,
+    UNIT_SCALE,
+    empty_mxfp8_rows_bases,
+    mxfp8_rows_from_bases,
     pack_mxfp8_scales_for_dense_gemm,
 )
-from .._shared.block_fp8 import quantize_block_fp8_linear_input_mxfp8
+
+_OWNER = "b12x MXFP8 linear"
 
 
 @dataclass(frozen=True)
@@ -27,27 +42,6 @@ class MXFP8LinearWeight:
     out_features: int
 
 
-def _align_up(value: int, alignment: int) -> int:
-    return -(-int(value) // int(alignment)) * int(alignment)
-
-
-def _c_dtype_name(dtype: torch.dtype) -> str:
-    if dtype == torch.bfloat16:
-        return "bfloat16"
-    if dtype == torch.float16:
-        return "float16"
-    raise ValueError(f"b12x MXFP8 linear output dtype must be bf16/fp16, got {dtype}")
-
-
-def _zero_pad_columns(t: torch.Tensor, width: int) -> torch.Tensor:
-    rows, cols = map(int, t.shape)
-    if cols == width:
-        return t.contiguous()
-    padded = t.new_zeros((rows, width))
-    padded[:, :cols] = t
-    return padded
-
-
 def is_mxfp8_linear_supported() -> tuple[bool, str | None]:
     return True, None
 
@@ -58,47 +52,51 @@ def pack_mxfp8_linear_weight(weight: torch.Tensor, weight_scale: torch.Tensor) -
     Checkpoints only guarantee ``K % 32 == 0``; the GEMM consumes K in 128-element steps, so
     K is padded with zero codes and UE8M0 1.0 (byte 127) scales.
     """
-    _check_gpu_tensor("weight", weight)
-    _check_gpu_tensor("weight_scale", weight_scale)
+    require_cuda_tensor("weight", weight)
+    require_cuda_tensor("weight_scale", weight_scale)
     if weight.ndim != 2:
         raise ValueError(f"weight must have shape [N,K], got {tuple(weight.shape)}")
     if weight.dtype != torch.float8_e4m3fn:
         raise ValueError(f"weight must be float8_e4m3fn, got {weight.dtype}")
     if weight_scale.ndim != 2:
         raise ValueError(f"weight_scale must have shape [N,K/32], got {tuple(weight_scale.shape)}")
-    out_features, in_features = map(int, weight.shape)
+    if weight_scale.dtype not in (torch.uint8, torch.float8_e8m0fnu):
+        raise ValueError(f"weight_scale must be uint8/e8m0, got {weight_scale.dtype}")
+    out_features, in_features = (int(v) for v in weight.shape)
     if out_features <= 0:
         raise ValueError("out_features must be positive")
-    if in_features <= 0 or in_features % MXFP8_SCALE_VEC_SIZE != 0:
+    if in_features <= 0 or in_features % SCALE_BLOCK:
         raise ValueError(
-            f"ModelOpt MXFP8 weight K must be a positive multiple of {MXFP8_SCALE_VEC_SIZE}, "
-            f"got {in_features}")
-    scale_k = in_features // MXFP8_SCALE_VEC_SIZE
-    if int(weight_scale.shape[0]) < out_features or int(weight_scale.shape[1]) < scale_k:
-        raise ValueError(
-            f"weight_scale must have at least shape {(out_features, scale_k)}, "
-            f"got {tuple(weight_scale.shape)}")
-    if weight_scale.dtype == torch.float8_e8m0fnu:
-        scale_u8 = weight_scale.view(torch.uint8)
-    elif weight_scale.dtype == torch.uint8:
-        scale_u8 = weight_scale
-    else:
-        raise ValueError(f"weight_scale must be uint8/e8m0, got {weight_scale.dtype}")
+            f"ModelOpt MXFP8 weight K must be a positive multiple of {SCALE_BLOCK}, got {in_features}")
+    blocks = in_features // SCALE_BLOCK
+    if weight_scale.shape[0] < out_features or weight_scale.shape[1] < blocks:
+        raise ValueError(f"weight_scale must have at least shape {(out_features, blocks)}, "
+                         f"got {tuple(weight_scale.shape)}")
 
-    padded_in = _align_up(in_features, 128)
-    padded_scale_k = padded_in // MXFP8_SCALE_VEC_SIZE
-    values = _zero_pad_columns(weight[:out_features, :in_features].view(torch.uint8), padded_in)
-    values = values.view(torch.float8_e4m3fn)
-    scale_rows = torch.full((out_features, padded_scale_k), 127, dtype=torch.uint8,
-                            device=weight.device)
-    scale_rows[:, :scale_k] = scale_u8[:out_features, :scale_k]
-    scale_rows = scale_rows.view(torch.float8_e8m0fnu)
-    scale_mma = pack_mxfp8_scales_for_dense_gemm(scale_rows, m=out_features, k=padded_in,
-                                                 num_groups=1)
+    padded_in = round_up(in_features, K_STEP)
+    codes = pad_columns(weight.view(torch.uint8), padded_in).view(torch.float8_e4m3fn)
+    scale_bytes = weight_scale.view(torch.uint8)[:out_features, :blocks]
+    scale_rows = torch.nn.functional.pad(scale_bytes, (0, padded_in // SCALE_BLOCK - blocks),
+                                         value=UNIT_SCALE).contiguous().view(torch.float8_e8m0fnu)
     return MXFP8LinearWeight(
-        weight=MXFP8Rows(values=values, scale_rows=scale_rows.reshape(1, out_features, padded_scale_k),
-                         scale_mma=scale_mma),
+        weight=MXFP8Rows(values=codes, scale_rows=scale_rows.unsqueeze(0),
+                         scale_mma=pack_mxfp8_scales_for_dense_gemm(
+                             scale_rows, m=out_features, k=padded_in, num_groups=1)),
         in_features=in_features, padded_in_features=padded_in, out_features=out_features)
+
+
+def _forward(source_2d: torch.Tensor, weight_values: torch.Tensor, weight_scale_mma: torch.Tensor,
+             *, padded_in: int, out_features: int, bias: torch.Tensor | None,
+             stream_int: int | None) -> torch.Tensor:
+    tokens = int(source_2d.shape[0])
+    output_dtype_name(source_2d.dtype, _OWNER)
+    x_q = mxfp8_rows_from_bases(
+        *empty_mxfp8_rows_bases(tokens, padded_in, num_groups=1, device=source_2d.device),
+        tokens, padded_in, num_groups=1)
+    out = torch.empty((tokens, out_features, 1), dtype=source_2d.dtype, device=source_2d.device)
+    return quantize_then_gemm(pad_columns(source_2d, padded_in), weight_values, weight_scale_mma,
+                              padded_k=padded_in, out_features=out_features, x_q=x_q, out=out,
+                              bias=bias, stream=stream_int)
 
 
 @torch.library.custom_op("b12x::mxfp8_linear_fused", mutates_args=())
@@ -106,53 +104,62 @@ def _mxfp8_linear_fused_op(source_2d: torch.Tensor, weight_values: torch.Tensor,
                            weight_scale_rows: torch.Tensor, weight_scale_mma: torch.Tensor,
                            in_features: int, padded_in_features: int, out_features: int,
                            expected_m: int, stream_int: int | None) -> torch.Tensor:
-    del weight_scale_rows
-    tokens = int(source_2d.shape[0])
-    x_q = quantize_block_fp8_linear_input_mxfp8(_zero_pad_columns(source_2d, int(padded_in_features)))
-    return dense_gemm(
-        (x_q.values.reshape(tokens, padded_in_features, 1), x_q.scale_mma),
-        (weight_values.reshape(out_features, padded_in_features, 1), weight_scale_mma),
-        ab_dtype="float8_e4m3fn", sf_dtype="float8_e8m0fnu",
-        c_dtype=_c_dtype_name(source_2d.dtype), sf_vec_size=MXFP8_SCALE_VEC_SIZE,
-        expected_m=expected_m, stream=stream_int)[:, :, 0]
+    del weight_scale_rows, in_features, expected_m
+    return _forward(source_2d, weight_values, weight_scale_mma, padded_in=int(padded_in_features),
+                    out_features=int(out_features), bias=None, stream_int=stream_int)
 
 
 @_mxfp8_linear_fused_op.register_fake
 def _mxfp8_linear_fused_fake(source_2d, weight_values, weight_scale_rows, weight_scale_mma,
                              in_features, padded_in_features, out_features, expected_m,
                              stream_int) -> torch.Tensor:
-    return torch.empty((source_2d.shape[0], out_features), dtype=source_2d.dtype,
-                       device=source_2d.device)
+    return source_2d.new_empty((source_2d.shape[0], out_features))
+
+
+@torch.library.custom_op("b12x::mxfp8_linear_bias_fused", mutates_args=())
+def _mxfp8_linear_bias_fused_op(source_2d: torch.Tensor, weight_values: torch.Tensor,
+                                weight_scale_mma: torch.Tensor, bias: torch.Tensor,
+                                padded_in_features: int, out_features: int,
+                                stream_int: int | None) -> torch.Tensor:
+    """The linear with its bias added in the GEMM epilogue (the reference has no such op: its
+    bias is a separate add after ``b12x::mxfp8_linear_fused``)."""
+    return _forward(source_2d, weight_values, weight_scale_mma, padded_in=int(padded_in_features),
+                    out_features=int(out_features), bias=bias, stream_int=stream_int)
+
+
+@_mxfp8_linear_bias_fused_op.register_fake
+def _mxfp8_linear_bias_fused_fake(source_2d, weight_values, weight_scale_mma, bias,
+                                  padded_in_features, out_features, stream_int) -> torch.Tensor:
+    return source_2d.new_empty((source_2d.shape[0], out_features))
 
 
 def mxfp8_linear(source: torch.Tensor, packed_weight: MXFP8LinearWeight, *,
                  bias: torch.Tensor | None = None, expected_m: int | None = None,
                  stream: object = None) -> torch.Tensor:
     """``source[..., K] @ W^T (+ bias)`` through the MXFP8 GEMM."""
-    _check_gpu_tensor("source", source)
+    require_cuda_tensor("source", source)
     if not isinstance(packed_weight, MXFP8LinearWeight):
         raise TypeError("packed_weight must be an MXFP8LinearWeight")
-    if source.ndim < 2:
-        raise ValueError(f"source must have at least 2 dims, got {tuple(source.shape)}")
-    source_2d = source.reshape(-1, source.shape[-1]).contiguous()
-    tokens, in_features = map(int, source_2d.shape)
-    if in_features != int(packed_weight.in_features):
-        raise ValueError(
-            f"input K={in_features} does not match packed weight K={packed_weight.in_features}")
-    if source_2d.dtype not in (torch.bfloat16, torch.float16):
-        raise ValueError(f"source dtype must be bf16/fp16, got {source_2d.dtype}")
-    out_features = int(packed_weight.out_features)
-    if tokens == 0:
-        output = source_2d.new_empty((0, out_features))
-    else:
-        output = torch.ops.b12x.mxfp8_linear_fused(
-            source_2d, packed_weight.weight.values, packed_weight.weight.scale_rows,
-            packed_weight.weight.scale_mma, packed_weight.in_features,
-            packed_weight.padded_in_features, packed_weight.out_features,
-            int(expected_m) if expected_m is not None else tokens, cuda_stream_to_int(stream))
+    rows = SourceRows.of(source, packed_in_features=packed_weight.in_features,
+                         dtypes=(torch.bfloat16, torch.float16),
+                         dtype_error="source dtype must be bf16/fp16, got {dtype}")
+    n = int(packed_weight.out_features)
+    weight = packed_weight.weight
+    if rows.tokens == 0:
+        output = rows.rows.new_empty((0, n))
+        return rows.restore(output + bias if bias is not None else output, n)
+    if bias_fuses(bias, rows.rows.dtype, n):
+        output = torch.ops.b12x.mxfp8_linear_bias_fused(
+            rows.rows, weight.values, weight.scale_mma, bias, packed_weight.padded_in_features, n,
+            cuda_stream_to_int(stream))
+        return rows.restore(output, n)
+    output = torch.ops.b12x.mxfp8_linear_fused(
+        rows.rows, weight.values, weight.scale_rows, weight.scale_mma, packed_weight.in_features,
+        packed_weight.padded_in_features, n,
+        int(expected_m) if expected_m is not None else rows.tokens, cuda_stream_to_int(stream))
     if bias is not None:
         output = output + bias
-    return output.view(*source.shape[:-1], out_features)
+    return rows.restore(output, n)
 
 
 __all__ = ["MXFP8LinearWeight", "is_mxfp8_linear_supported", "mxfp8_linear",

@@ -756,3 +756,116 @@ def test_a_timed_out_wait_is_reported_and_the_next_gemm_is_correct():
     torch.cuda.synchronize()
     assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T)
     launch.check_kernel_status(DEV)
+
+
+# --------------------------------------------------------------------------------------
+# Epilogues: bias and MXFP8 re-quantization of the output
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("route,m,n,k,dtype", [
+    ("decode", 8, 512, 512, torch.bfloat16), ("decode", 33, 2048, 1024, torch.float16),
+    ("decode", 5, 200, 384, torch.float32), ("bn64", 130, 264, 384, torch.bfloat16),
+    ("bn128", 256, 512, 256, torch.float32), ("bn256", 300, 504, 640, torch.float16),
+    ("pair", 768, 1280, 1024, torch.bfloat16), ("pair", 300, 504, 640, torch.float32),
+    ("auto", 2048, 2560, 2048, torch.bfloat16),    # CTA-pair kernel with a split last round
+])
+def test_fused_bias_equals_a_bias_add_on_the_stored_output(route, m, n, k, dtype):
+    """The bias epilogue of every GEMM kernel must give, bit for bit, what adding the bias
+    tensor to the kernel's own stored output gives (for BF16 / FP16 outputs that means two
+    roundings: the product is rounded to the output type, the sum again)."""
+    from gpu_util import DEV, mxfp8_operand
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import BLOCK_N_PAIR, KIND_MXFP8
+
+    (a, sfa), _ = mxfp8_operand(seeded_bf16(m + 2 * k, (m, k), 0.25))
+    (b, sfb), _ = mxfp8_operand(seeded_bf16(n + 3 * k, (n, k), 0.03))
+    bias = (seeded_bf16(n, (n,), 2.0).float() if dtype == torch.float32 else seeded_bf16(n, (n,), 2.0)
+            ).to(dtype).to(DEV)
+    kwargs = {"decode": dict(small_m=True), "pair": dict(block_n=BLOCK_N_PAIR), "auto": {}}.get(
+        route, dict(block_n=int(route[2:])) if route.startswith("bn") else {})
+    alpha = torch.tensor([0.5], dtype=torch.float32, device=DEV)
+    plain = torch.empty((m, n), dtype=dtype, device=DEV)
+    fused = torch.full((m, n), float("nan"), dtype=dtype, device=DEV)
+    launch.gemm_blockscaled(KIND_MXFP8, a, sfa, b, sfb, plain, alpha, m, n, k, **kwargs)
+    launch.gemm_blockscaled(KIND_MXFP8, a, sfa, b, sfb, fused, alpha, m, n, k, bias=bias, **kwargs)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(DEV)
+    assert torch.equal(fused, plain + bias)
+
+
+def test_fused_bias_in_the_block_fp8_gemm_and_its_argument_checks():
+    from gpu_util import DEV
+    from sparkinfer_b200._lib import launch
+
+    for (m, n, k, dtype) in ((129, 256, 256, torch.bfloat16), (300, 384, 1024, torch.float32),
+                             (8, 128, 512, torch.float16)):
+        lhs, rhs, _ = _block_fp8_operands(m + n, m, n, k)
+        bias = seeded_bf16(n, (n,), 2.0).float().to(dtype).to(DEV)
+        plain = torch.empty((m, n), dtype=dtype, device=DEV)
+        fused = torch.full((m, n), float("nan"), dtype=dtype, device=DEV)
+        launch.gemm_block_fp8(lhs[0][:, :, 0], lhs[1], rhs[0][:, :, 0], rhs[1], plain, None, m, n, k)
+        launch.gemm_block_fp8(lhs[0][:, :, 0], lhs[1], rhs[0][:, :, 0], rhs[1], fused, None, m, n, k,
+                              bias=bias)
+        torch.cuda.synchronize()
+        assert torch.equal(fused, plain + bias)
+    with pytest.raises(ValueError, match="fused bias"):
+        launch.gemm_block_fp8(lhs[0][:, :, 0], lhs[1], rhs[0][:, :, 0], rhs[1], fused, None, m, n, k,
+                              bias=bias.float())
+
+
+@pytest.mark.parametrize("kind,m,n,k,groups", [
+    ("mxfp8", 5, 512, 512, 1), ("mxfp8", 16, 1024, 2048, 1), ("nvfp4", 1, 256, 512, 1),
+    ("nvfp4", 8, 14336, 1024, 1), ("mxfp8", 4, 64, 256, 2), ("mxfp8", 7, 96, 384, 4),
+])
+def test_quantized_c_equals_row_quantization_of_the_bf16_output(kind, m, n, k, groups):
+    """``mm(..., _quantized_c=...)`` (the reference's small-M quantized-C GEMM,
+    b12x/_lib/dense_gemm.py:7497-7588): besides the BF16 output the kernel writes its MXFP8
+    re-quantization along N. Codes, row-major scale bytes and scale atoms must equal, bit for
+    bit, ``quantization.mxfp8.quantize_rows`` applied to the BF16 output (groups side by side)."""
+    from gpu_util import DEV, mxfp8_operand, nvfp4_operand, to_dev
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200._lib.mxfp8_rows import empty_mxfp8_rows_for_dense_gemm, quantize_mxfp8_rows
+    from sparkinfer_b200.gemm import blockscaled
+
+    if groups == 1:
+        if kind == "mxfp8":
+            lhs, _ = mxfp8_operand(seeded_bf16(m + k, (m, k), 0.25))
+            rhs, _ = mxfp8_operand(seeded_bf16(n + k, (n, k), 0.05))
+            kw, alpha = MXFP8, None
+        else:
+            lhs, gsa, _ = nvfp4_operand(seeded_bf16(m + k, (m, k), 0.25))
+            rhs, gsb, _ = nvfp4_operand(seeded_bf16(n + k, (n, k), 0.05))
+            kw, alpha = NVFP4, _alpha(gsa, gsb)
+    else:
+        av, asw, bv, bsw = [], [], [], []
+        for g in range(groups):
+            a_q = O.quantize_mxfp8_rows(seeded_bf16(50 + g, (m, k), 0.25 * (g + 1)).float().numpy())
+            b_q = O.quantize_mxfp8_rows(seeded_bf16(60 + g, (n, k), 0.05).float().numpy())
+            av.append(a_q[0]); bv.append(b_q[0])
+            asw.append(O.swizzle_scales(a_q[1], 127)); bsw.append(O.swizzle_scales(b_q[1], 127))
+        lhs = (to_dev(np.stack(av)).view(torch.float8_e4m3fn).as_strided((m, k, groups), (k, 1, m * k)),
+               layout.convert_sf_to_mma_layout(to_dev(np.concatenate(asw)), m, k, groups, 32))
+        rhs = (to_dev(np.stack(bv)).view(torch.float8_e4m3fn).as_strided((n, k, groups), (k, 1, n * k)),
+               layout.convert_sf_to_mma_layout(to_dev(np.concatenate(bsw)), n, k, groups, 32))
+        kw, alpha = MXFP8, None
+    width = n * groups
+    q = empty_mxfp8_rows_for_dense_gemm(m, width, device=DEV)
+    q.values.view(torch.uint8).fill_(0xEE)
+    out = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16",
+                         _quantized_c=(q.values, q.scale_rows[0], q.scale_mma), **kw)
+    plain = blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="bfloat16", **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain), "the BF16 output must not change"
+    flat = out.permute(0, 2, 1).reshape(m, width).contiguous()      # [M, L * N], groups side by side
+    want = empty_mxfp8_rows_for_dense_gemm(m, width, device=DEV)
+    quantize_mxfp8_rows(flat, want.values, want.scale_rows, want.scale_mma)
+    torch.cuda.synchronize()
+    assert torch.equal(q.values.view(torch.uint8), want.values.view(torch.uint8))
+    assert torch.equal(q.scale_rows.view(torch.uint8), want.scale_rows.view(torch.uint8))
+    got_atoms = q.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous().view(torch.uint8)
+    want_atoms = want.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous().view(torch.uint8)
+    assert torch.equal(got_atoms, want_atoms)   # rows >= M keep the pre-filled 127 in both
+    with pytest.raises(ValueError, match="quantized C is restricted"):
+        blockscaled.mm(lhs, rhs, alpha=alpha, c_dtype="float16",
+                       _quantized_c=(q.values, q.scale_rows[0], q.scale_mma), **kw)
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
