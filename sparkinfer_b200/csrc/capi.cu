@@ -205,9 +205,9 @@ int choose_block_n(int64_t m, int64_t n, int sms) {
   return best;
 }
 
-template <int KIND, int BN>
-int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
-                const GemmParams& p, int grid, cudaStream_t stream) {
+template <int KIND, int BN, bool BIAS>
+int launch_gemm_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                     const GemmParams& p, int grid, cudaStream_t stream) {
   using T = GemmTile<KIND, BN>;
   // The large dynamic shared memory opt-in is per device: set it the first time each device
   // launches this instantiation.
@@ -216,30 +216,38 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err =
-        cudaFuncSetAttribute(gemm_blockscaled_kernel<KIND, BN>,
+        cudaFuncSetAttribute(gemm_blockscaled_kernel<KIND, BN, BIAS>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
   GemmParams q = p;
   q.num_stages = (p.num_stages >= 2 && p.num_stages <= T::kStages) ? p.num_stages : T::kStages;
-  gemm_blockscaled_kernel<KIND, BN><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, map_c, q);
+  gemm_blockscaled_kernel<KIND, BN, BIAS><<<grid, 192, T::kSmemBytes, stream>>>(map_a, map_b, map_c, q);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled launch");
   return B12X_B200_OK;
 }
 
-// CTA-pair kernel: clusters of two CTAs, one 256 x BN tile per pair.
 template <int KIND, int BN>
-int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
-                     const GemmParams& p, const PairTail& tail, int pairs, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                const GemmParams& p, int grid, cudaStream_t stream) {
+  return p.bias ? launch_gemm_impl<KIND, BN, true>(map_a, map_b, map_c, p, grid, stream)
+                : launch_gemm_impl<KIND, BN, false>(map_a, map_b, map_c, p, grid, stream);
+}
+
+// CTA-pair kernel: clusters of two CTAs, one 256 x BN tile per pair.
+template <int KIND, int BN, bool BIAS>
+int launch_gemm_pair_impl(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                          const CUtensorMap& map_c, const GemmParams& p, const PairTail& tail,
+                          int pairs, cudaStream_t stream) {
   using T = PairTile<KIND, BN>;
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err =
-        cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, BN>,
+        cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, BN, BIAS>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
@@ -258,9 +266,16 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t err =
-      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN>, map_a, map_b, map_c, p, tail);
+      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN, BIAS>, map_a, map_b, map_c, p, tail);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled_pair launch");
   return B12X_B200_OK;
+}
+
+template <int KIND, int BN>
+int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                     const GemmParams& p, const PairTail& tail, int pairs, cudaStream_t stream) {
+  return p.bias ? launch_gemm_pair_impl<KIND, BN, true>(map_a, map_b, map_c, p, tail, pairs, stream)
+                : launch_gemm_pair_impl<KIND, BN, false>(map_a, map_b, map_c, p, tail, pairs, stream);
 }
 
 // Rows up to which a quantized matrix is taken for an activation (its quantization releases the
@@ -624,9 +639,13 @@ int gemm_block_fp8_impl(const void* a, const float* sfa, const void* b, const fl
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
-    const cudaError_t attr_err =
-        cudaFuncSetAttribute(gemm_block_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             BlockFp8Tile::kSmemBytes);
+    cudaError_t attr_err =
+        cudaFuncSetAttribute(gemm_block_fp8_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, BlockFp8Tile::kSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_block_fp8_kernel<true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      BlockFp8Tile::kSmemBytes);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
   }
@@ -640,8 +659,12 @@ int gemm_block_fp8_impl(const void* a, const float* sfa, const void* b, const fl
     if (rc != B12X_B200_OK) return rc;
     p.use_tma_store = 1;
   }
-  gemm_block_fp8_kernel<<<grid, BlockFp8Tile::kThreads, BlockFp8Tile::kSmemBytes,
-                          reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_c, p);
+  if (p.bias)
+    gemm_block_fp8_kernel<true><<<grid, BlockFp8Tile::kThreads, BlockFp8Tile::kSmemBytes,
+                                  reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_c, p);
+  else
+    gemm_block_fp8_kernel<false><<<grid, BlockFp8Tile::kThreads, BlockFp8Tile::kSmemBytes,
+                                   reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_c, p);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "gemm_block_fp8 launch");
   return B12X_B200_OK;
@@ -743,19 +766,19 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   return B12X_B200_OK;
 }
 
-template <int KIND, bool FUSED>
-int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
-                  int grid, int smem_bytes, cudaStream_t stream) {
+template <int KIND, bool FUSED, bool EPI>
+int launch_smallm_impl(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
+                       int grid, int smem_bytes, cudaStream_t stream) {
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        gemm_smallm_kernel<KIND, FUSED, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     // Largest shared-memory carve-out: the ring takes nearly all of it.
     const cudaError_t carve_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        gemm_smallm_kernel<KIND, FUSED, EPI>, cudaFuncAttributePreferredSharedMemoryCarveout,
         cudaSharedmemCarveoutMaxShared);
     if (carve_err != cudaSuccess) return fail_cuda(carve_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
@@ -775,9 +798,17 @@ int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const Smal
   cfg.attrs = attr;
   cfg.numAttrs = switches().decode_overlap ? 1 : 0;
   const cudaError_t err =
-      cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND, FUSED>, map_w, map_x, p);
+      cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND, FUSED, EPI>, map_w, map_x, p);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;
+}
+
+template <int KIND, bool FUSED>
+int launch_smallm(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
+                  int grid, int smem_bytes, cudaStream_t stream) {
+  return (p.bias || p.quant_values)
+             ? launch_smallm_impl<KIND, FUSED, true>(map_w, map_x, p, grid, smem_bytes, stream)
+             : launch_smallm_impl<KIND, FUSED, false>(map_w, map_x, p, grid, smem_bytes, stream);
 }
 
 // One decode-shape GEMM request, as every entry point of the family describes it. `x` / `sf_x`

@@ -210,7 +210,8 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
   }
 }
 
-template <int KIND, int BN>
+// BIAS: the instantiation with the bias epilogue (the plain one carries none of its code).
+template <int KIND, int BN, bool BIAS>
 __global__ void __launch_bounds__(192, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
@@ -444,7 +445,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
               float vals[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(cur[i]) * alpha;
-              add_bias_32(vals, p.bias, p.out_dtype, tn * BN + pass * 128 + cc * 32, p.n);
+              if constexpr (BIAS)
+                add_bias_32(vals, p.bias, p.out_dtype, tn * BN + pass * 128 + cc * 32, p.n);
               uint32_t packed[16];
               if (p.out_dtype == kOutBf16) {
 #pragma unroll
@@ -490,7 +492,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
-        add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
+        if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
         store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();

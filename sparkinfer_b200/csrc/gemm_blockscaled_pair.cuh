@@ -114,7 +114,8 @@ struct PairTail {
 constexpr int kPairPartialFloats = 128 * 256;
 constexpr uint32_t kPairReducePolls = 1u << 20;
 
-template <int KIND, int BN>
+// BIAS: the instantiation with the bias epilogue (the plain one carries none of its code).
+template <int KIND, int BN, bool BIAS>
 __global__ void __launch_bounds__(224, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                              const __grid_constant__ CUtensorMap map_b,
@@ -453,7 +454,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             const int col = tn * BN + q * 4;
             if (q < q_end && row < p.m && col < p.n) {
               float o[4] = {sum[i].x * alpha, sum[i].y * alpha, sum[i].z * alpha, sum[i].w * alpha};
-              if (p.bias != nullptr) {
+              if constexpr (BIAS) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o[j] = add_bias_1(o[j], p.bias, p.out_dtype, col + j, p.n);
               }
@@ -503,7 +504,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         uint32_t packed[64];
         // `half` = which 128 columns of the tile raw[] currently holds.
         auto convert_chunk = [&](int cc, int half) {
-          if (p.bias != nullptr) {
+          if constexpr (BIAS) {
             float vals[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[cc][i]) * alpha;
@@ -515,6 +516,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                         : pack_f16x2(vals[2 * i], vals[2 * i + 1]);
             return;
           }
+          (void)half;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float lo = __uint_as_float(raw[cc][2 * i]) * alpha;
@@ -581,7 +583,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         float vals[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
-        add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
+        if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
         store_row_chunk(p, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();

@@ -254,7 +254,9 @@ struct FusedQuant {
   }
 };
 
-template <int KIND, bool FUSED>
+// EPI: the instantiation whose epilogue can add a bias and re-quantize the output rows; the
+// plain one carries none of that code.
+template <int KIND, bool FUSED, bool EPI>
 __global__ void __launch_bounds__(FUSED ? 512 : 256, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
@@ -544,15 +546,27 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       const int n_local = quarter * 32 + lane;          // weight row inside the tile
       const float alpha = p.alpha ? *p.alpha : 1.0f;
       const size_t slot_floats = static_cast<size_t>(p.m_pad) * 128;
-      const bool quantize_c = p.quant_values != nullptr;
-      // Final value of output element (mrow, n_global): scale, round to the output type, add the
-      // bias, store; then, if asked, the MXFP8 codes of the rounded row. A warp holds 32
-      // consecutive columns of the row, which is exactly one scale block, so the block maximum
-      // is one warp-wide integer max of the magnitudes' bit patterns. Called by whole warps.
+      const bool quantize_c = EPI && p.quant_values != nullptr;
+      // Final value of output element (mrow, n_global): scale, round to the output type, store.
+      // With EPI also: add the bias and, if asked, emit the MXFP8 codes of the rounded row. A
+      // warp holds 32 consecutive columns of the row, which is exactly one scale block, so the
+      // block maximum is one warp-wide integer max of the magnitudes' bit patterns. Called by
+      // whole warps.
       auto emit = [&](int mrow, int n_global, bool n_ok, float acc_value) {
         float v = acc_value * alpha;
-        if (p.bias != nullptr) v = add_bias_1(v, p.bias, p.out_dtype, n_global, p.n);
         const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+        if constexpr (!EPI) {
+          if (n_ok) {
+            if (p.out_dtype == kOutBf16)
+              static_cast<__nv_bfloat16*>(p.c)[idx] = __float2bfloat16_rn(v);
+            else if (p.out_dtype == kOutFp16)
+              static_cast<__half*>(p.c)[idx] = __float2half_rn(v);
+            else
+              static_cast<float*>(p.c)[idx] = v;
+          }
+          return;
+        }
+        if (p.bias != nullptr) v = add_bias_1(v, p.bias, p.out_dtype, n_global, p.n);
         float stored = v;
         if (p.out_dtype == kOutBf16) {
           const __nv_bfloat16 h = __float2bfloat16_rn(v);
