@@ -139,6 +139,41 @@ int b12x_b200_gemm_blockscaled_ex(int kind, const void* a, const void* sfa, cons
                                   b12x_b200_stream_t stream);
 
 /*
+ * Grouped (batched) block-scaled GEMM: `groups` independent problems of one shape in ONE launch,
+ * C[g] = cvt(alpha * (A[g] . SFA[g]) (B[g] . SFB[g])^T). This is the reference's L > 1 form of
+ * dense_gemm (operands [M, Kp, L] over physical [L, M, Kp], output [M, N, L] over physical
+ * [L, M, N]; b12x/_lib/dense_gemm.py:7068-7098, 6469-6491), which its grouped projections use
+ * (:5803-5944). The tiles (decode kernel: the weight tiles and k-tiles) of all groups form one
+ * work list for the persistent scheduler, so small groups fill the machine together.
+ *
+ *   a, b      stacked K-major codes, group after group: [groups, M, Kbytes], [groups, N, Kbytes]
+ *   sfa, sfb  each group's dense scale atoms, group after group
+ *   c         [groups, M, ldc]; alpha, bias: shared by all groups
+ *   epilogue  bias in both entry points; output re-quantization in the decode-shape one, where
+ *             group g fills columns quant_col0 + g * N .. of the quantized matrix
+ *   workspace at least b12x_b200_gemm_grouped_workspace_bytes(kind, decode, ...) bytes (decode =
+ *             1 for the _smallm_grouped entry point), same rules as for the ungrouped calls
+ * groups = 1 is exactly the ungrouped call.
+ */
+int64_t b12x_b200_gemm_grouped_workspace_bytes(int kind, int decode, int64_t m, int64_t n,
+                                               int64_t k, int64_t groups, int block_n,
+                                               int sm_count);
+int b12x_b200_gemm_blockscaled_grouped(int kind, const void* a, const void* sfa, const void* b,
+                                       const void* sfb, void* c, int c_dtype, const float* alpha,
+                                       int64_t m, int64_t n, int64_t k, int64_t ldc,
+                                       int64_t groups, int block_n, int sm_count, void* workspace,
+                                       int64_t workspace_bytes,
+                                       const b12x_b200_epilogue_t* epilogue, int* status,
+                                       b12x_b200_stream_t stream);
+int b12x_b200_gemm_blockscaled_smallm_grouped(int kind, const void* x, const void* sf_x,
+                                              const void* w, const void* sf_w, void* c,
+                                              int c_dtype, const float* alpha, int64_t m,
+                                              int64_t n, int64_t k, int64_t ldc, int64_t groups,
+                                              void* workspace, int64_t workspace_bytes,
+                                              const b12x_b200_epilogue_t* epilogue, int sm_count,
+                                              int* status, b12x_b200_stream_t stream);
+
+/*
  * Decode-shape (1 <= M <= 128) variant of b12x_b200_gemm_blockscaled: the weight matrix is
  * streamed once, split evenly over all SMs along N and K (stream-K), and partial sums meet in
  * a caller-owned FP32 workspace. Stands in for the reference's small-M split-K policy and its

@@ -133,15 +133,16 @@ def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int,
     sfa_base = torch.as_strided(sfa_flat, (l * sfa_group,), (1,))
     sfb_base = torch.as_strided(sfb_flat, (l * sfb_group,), (1,))
     ldc = c.stride(0) if m > 1 else n
-    for g in range(l):
-        # Quantized C: group g fills columns [g * N, (g + 1) * N) of the [M, N * L] MXFP8 matrix.
-        qc = None if quantized_c is None else launch.QuantizedC(
-            quantized_c[0], quantized_c[1], quantized_c[2], col0=g * n, total_cols=n * l)
-        launch.gemm_blockscaled(
-            kind, a.select(2, g), sfa_base[g * sfa_group:], b.select(2, g),
-            sfb_base[g * sfb_group:], c.select(2, g), None if alpha_is_one else alpha,
-            m, n, k, ldc=ldc, block_n=block_n, sm_count=sm_count, stream_int=stream_int,
-            quantized_c=qc)
+    if l > 1 and ldc != n:
+        raise ValueError("a grouped output must be dense [L, M, N] storage")
+    # One launch for all L groups: the operands are physical [L, rows, K] stacks, and the tiles
+    # of every group go into one work list on the device. Quantized C: group g fills columns
+    # [g * N, (g + 1) * N) of the [M, N * L] MXFP8 matrix.
+    qc = None if quantized_c is None else launch.QuantizedC(
+        quantized_c[0], quantized_c[1], quantized_c[2], col0=0, total_cols=n * l)
+    launch.gemm_blockscaled(
+        kind, a, sfa_base, b, sfb_base, c, None if alpha_is_one else alpha, m, n, k, ldc=ldc,
+        block_n=block_n, sm_count=sm_count, stream_int=stream_int, quantized_c=qc, groups=l)
 
 
 @torch.library.custom_op("b12x::dense_gemm_launch", mutates_args=("c_tensor_gpu",))

@@ -211,9 +211,12 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
                      m: int, n: int, k: int, *, ldc: int | None = None, block_n: int = 0,
                      sm_count: int = 0, stream_int: int | None = None,
                      small_m: bool | None = None, bias: torch.Tensor | None = None,
-                     quantized_c: QuantizedC | None = None) -> None:
-    """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)`` for one group. ``a``/``b`` are row
-    pointers to K-major code matrices, ``sfa``/``sfb`` point at the first scale atom.
+                     quantized_c: QuantizedC | None = None, groups: int = 1) -> None:
+    """``c[M, ldc] = cvt(alpha * (a . sfa)(b . sfb)^T)``. ``a``/``b`` are row pointers to K-major
+    code matrices, ``sfa``/``sfb`` point at the first scale atom. With ``groups > 1`` the
+    tensors hold that many problems of the same shape group after group (operands ``[L, rows,
+    K]``, each group's dense scale atoms, outputs ``[L, M, ldc]``) and all of them run in one
+    launch.
 
     Decode shapes (see :func:`route_to_decode_kernel`; never when a tile width is forced, always
     with ``small_m=True``) go to the weight-streaming stream-K kernel, everything else to the
@@ -227,31 +230,33 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     if small_m is None:
         small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and (
             quantized_c is not None or route_to_decode_kernel(m, n, dev, sm_count))
-    if small_m and 0 < m <= SMALL_M_MAX and n > 0:
-        work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
-        with torch.cuda.device(dev):
-            rc = _native.load().b12x_b200_gemm_blockscaled_smallm_ex(
-                kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
-                _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
-                m, n, k, ldc if ldc is not None else n, work.data_ptr(), work.numel(),
-                ctypes.byref(ep) if ep is not None else None, sm_count,
-                status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-        _native.check(rc, "b12x_b200_gemm_blockscaled_smallm_ex")
-        return
     lib = _native.load()
+    decode = bool(small_m and 0 < m <= SMALL_M_MAX and n > 0)
     with torch.cuda.device(dev):
-        # Scratch for the CTA-pair kernel's split last round (0 when the shape has none).
-        need = int(lib.b12x_b200_gemm_blockscaled_workspace_bytes(kind, m, n, k, block_n, sm_count))
+        # Decode kernel: counters and partial tiles. Tiled kernels: scratch for the CTA-pair
+        # kernel's split last round (0 when the shape has none).
+        need = int(lib.b12x_b200_gemm_grouped_workspace_bytes(
+            kind, int(decode), m, n, k, groups, 0 if decode else block_n, sm_count))
+    if need < 0:
+        raise _native.NativeLibraryError(f"no kernel plan for M={m}, N={n}, K={k}, groups={groups}")
     work = stream_workspace(need, dev, stream_int) if need > 0 else None
-    with torch.cuda.device(dev):
-        rc = lib.b12x_b200_gemm_blockscaled_ex(
-            kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+    common_tail = (work.data_ptr() if work is not None else None,
+                   work.numel() if work is not None else 0,
+                   ctypes.byref(ep) if ep is not None else None)
+    head = (kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
             _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
-            m, n, k, ldc if ldc is not None else n, block_n, sm_count,
-            work.data_ptr() if work is not None else None, work.numel() if work is not None else 0,
-            ctypes.byref(ep) if ep is not None else None,
-            status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-    _native.check(rc, "b12x_b200_gemm_blockscaled_ex")
+            m, n, k, ldc if ldc is not None else n, groups)
+    with torch.cuda.device(dev):
+        if decode:
+            rc = lib.b12x_b200_gemm_blockscaled_smallm_grouped(
+                *head, *common_tail, sm_count, status_buffer(dev).data_ptr(),
+                _stream_ptr(stream_int, dev))
+        else:
+            rc = lib.b12x_b200_gemm_blockscaled_grouped(
+                *head, block_n, sm_count, *common_tail, status_buffer(dev).data_ptr(),
+                _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_blockscaled_smallm_grouped" if decode
+                  else "b12x_b200_gemm_blockscaled_grouped")
 
 
 def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tensor | None,

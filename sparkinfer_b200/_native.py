@@ -54,6 +54,20 @@ SIGNATURES = {
          _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_i64, _c_epilogue_p,
          _c_void_p, _c_void_p],
     ),
+    "b12x_b200_gemm_grouped_workspace_bytes": (
+        _c_i64, [_c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
+    "b12x_b200_gemm_blockscaled_grouped": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_i64, _c_epilogue_p,
+         _c_void_p, _c_void_p],
+    ),
+    "b12x_b200_gemm_blockscaled_smallm_grouped": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+         _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_epilogue_p, _c_int,
+         _c_void_p, _c_void_p],
+    ),
     "b12x_b200_gemm_blockscaled_smallm_ex": (
         _c_int,
         [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,

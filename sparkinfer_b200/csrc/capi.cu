@@ -80,8 +80,8 @@ int check_epilogue(const b12x_b200_epilogue_t* e, int c_dtype, int64_t n, bool a
 }
 
 // K-major byte matrix [rows, row_bytes] -> boxes of 128 bytes x box_rows, 128-byte swizzle.
-int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                     uint32_t box_rows) {
+int make_operand_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                        uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
   const cuuint64_t dims[2] = {row_bytes, rows};
@@ -99,18 +99,40 @@ int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return B12X_B200_OK;
 }
 
+// Stack of `groups` K-major byte matrices [groups, rows, row_bytes] -> boxes of 128 bytes x
+// box_rows x 1 group, 128-byte swizzle. A box never crosses into the next group: rows at or
+// beyond `rows` are out of bounds and read as zeros.
+int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                     uint32_t box_rows, uint64_t groups = 1) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[3] = {row_bytes, rows, groups};
+  const cuuint64_t strides[2] = {row_bytes, rows * row_bytes};
+  const cuuint32_t box[3] = {128, box_rows, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed (%d)", int(r));
+    return B12X_B200_ERR_CUDA;
+  }
+  return B12X_B200_OK;
+}
+
 // Row-major BF16 matrix [rows, cols] with row pitch `ld` elements -> unswizzled boxes of
 // box_cols x box_rows elements (the raw activation rows of the fused-quantizer decode GEMM).
 int make_raw_rows_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                      uint32_t box_cols, uint32_t box_rows) {
+                      uint32_t box_cols, uint32_t box_rows, uint64_t groups = 1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {ld * 2};
-  const cuuint32_t box[2] = {box_cols, box_rows};
-  const cuuint32_t elem_strides[2] = {1, 1};
+  const cuuint64_t dims[3] = {cols, rows, groups};
+  const cuuint64_t strides[2] = {ld * 2, rows * ld * 2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r =
-      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box,
          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -122,8 +144,8 @@ int make_raw_rows_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 
 // Row-major 2-byte matrix [rows, cols] with row pitch `ld` elements -> boxes of 64 columns
 // (128 bytes) x 128 rows, 128-byte swizzle; used for TMA stores of BF16/FP16 outputs.
-int make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                    uint64_t ld) {
+int make_output_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                       uint64_t ld) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
   const cuuint64_t dims[2] = {cols, rows};
@@ -132,6 +154,27 @@ int make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r =
       fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
+         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(C) failed (%d)", int(r));
+    return B12X_B200_ERR_CUDA;
+  }
+  return B12X_B200_OK;
+}
+
+// The same for a stack of `groups` outputs [groups, rows, ld] (a store never spills into the
+// next group: rows at or beyond `rows` are clipped).
+int make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint64_t groups = 1) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[3] = {cols, rows, groups};
+  const cuuint64_t strides[2] = {ld * 2, rows * ld * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box,
          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -327,9 +370,9 @@ struct PairTailPlan {
   size_t bytes = 0;
 };
 
-PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int sms) {
+PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int64_t groups, int sms) {
   PairTailPlan t;
-  const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256) * groups;
   t.pairs = int(tiles < sms / 2 ? tiles : sms / 2);
   if (t.pairs < 1 || !switches().pair_tail_split) return t;
   const int64_t rounds = tiles / t.pairs;
@@ -366,9 +409,11 @@ namespace {
 
 int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* b, const void* sfb,
                           void* c, int c_dtype, const float* alpha, int64_t m, int64_t n, int64_t k,
-                          int64_t ldc, int block_n, int sm_count, void* workspace,
+                          int64_t ldc, int64_t groups, int block_n, int sm_count, void* workspace,
                           int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue,
                           int* status, b12x_b200_stream_t stream) {
+  if (groups < 1 || groups > 65535)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be in [1, 65535]");
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
@@ -405,15 +450,15 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   // Problems with enough 256 x 256 pair tiles go to the CTA-pair kernel unless a tile width was
   // forced. "Enough" is two thirds of the pairs: measured on 148 SMs the pair kernel wins from
   // 56 tiles up (512 x 7168, 1024 x 4096, 256 x 18432) and loses at 28-32 tiles.
-  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256) * groups;
   const bool use_pair = (block_n == B12X_B200_BLOCK_N_PAIR) ||
                         ((block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms));
 
   CUtensorMap map_a, map_b;
-  rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(row_bytes), 128);
+  rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(row_bytes), 128, uint64_t(groups));
   if (rc != B12X_B200_OK) return rc;
   rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(row_bytes),
-                        use_pair ? 128u : uint32_t(bn));
+                        use_pair ? 128u : uint32_t(bn), uint64_t(groups));
   if (rc != B12X_B200_OK) return rc;
 
   GemmParams p;
@@ -432,8 +477,13 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
   p.group_m = 16;
   p.bias = epilogue ? epilogue->bias : nullptr;
+  p.groups = int(groups);
+  p.sfa_group_bytes = ((m + 127) / 128) * int64_t(p.k_atoms_total) * 512;
+  p.sfb_group_bytes = ((n + 127) / 128) * int64_t(p.k_atoms_total) * 512;
+  p.c_group_elems = m * ldc;
   p.num_stages = 0;  // filled per instantiation
-  const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+  const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * groups;
+  if (tiles > INT32_MAX) return fail(B12X_B200_ERR_UNSUPPORTED, "too many tiles");
   const int grid = int(tiles < sms ? tiles : sms);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // Output through TMA when rows of C are 16-byte aligned 2-byte values; otherwise the
@@ -442,7 +492,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   memset(&map_c, 0, sizeof(map_c));
   p.use_tma_store = 0;
   if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0) {
-    rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
+    rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc), uint64_t(groups));
     if (rc != B12X_B200_OK) return rc;
     p.use_tma_store = 1;
   }
@@ -456,7 +506,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
     tail.counters = nullptr;
     tail.partials = nullptr;
     tail.segments = 0;
-    const PairTailPlan tp = plan_pair_tail(kind, m, n, k, sms);
+    const PairTailPlan tp = plan_pair_tail(kind, m, n, k, groups, sms);
     if (workspace && tp.segments >= 2 && workspace_bytes >= int64_t(tp.bytes) &&
         aligned16(workspace)) {
       tail.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kPairCounterOffset);
@@ -480,7 +530,7 @@ extern "C" int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* s
                                           const float* alpha, int64_t m, int64_t n, int64_t k,
                                           int64_t ldc, int block_n, int sm_count, int* status,
                                           b12x_b200_stream_t stream) {
-  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, 1, block_n,
                                sm_count, nullptr, 0, nullptr, status, stream);
 }
 
@@ -491,23 +541,45 @@ extern "C" int b12x_b200_gemm_blockscaled_ex(int kind, const void* a, const void
                                              void* workspace, int64_t workspace_bytes,
                                              const b12x_b200_epilogue_t* epilogue, int* status,
                                              b12x_b200_stream_t stream) {
-  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, block_n,
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, 1, block_n,
                                sm_count, workspace, workspace_bytes, epilogue, status, stream);
 }
 
-extern "C" int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n,
-                                                              int64_t k, int block_n, int sm_count) {
+extern "C" int b12x_b200_gemm_blockscaled_grouped(int kind, const void* a, const void* sfa,
+                                                  const void* b, const void* sfb, void* c,
+                                                  int c_dtype, const float* alpha, int64_t m,
+                                                  int64_t n, int64_t k, int64_t ldc,
+                                                  int64_t groups, int block_n, int sm_count,
+                                                  void* workspace, int64_t workspace_bytes,
+                                                  const b12x_b200_epilogue_t* epilogue,
+                                                  int* status, b12x_b200_stream_t stream) {
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, c, c_dtype, alpha, m, n, k, ldc, groups,
+                               block_n, sm_count, workspace, workspace_bytes, epilogue, status,
+                               stream);
+}
+
+namespace {
+
+int64_t tiled_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k, int64_t groups,
+                              int block_n, int sm_count) {
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
-  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (m <= 0 || n <= 0 || k <= 0 || groups < 1) return 0;
   DeviceInfo info;
   if (device_info(&info) != B12X_B200_OK) return -1;
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
-  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256) * groups;
   const bool use_pair = (block_n == B12X_B200_BLOCK_N_PAIR) ||
                         ((block_n == 0) && (sms >= 2) && (pair_tiles * 3 >= sms));
   if (!use_pair || sms < 2) return 0;
-  const PairTailPlan tp = plan_pair_tail(kind, m, n, k, sms);
+  const PairTailPlan tp = plan_pair_tail(kind, m, n, k, groups, sms);
   return tp.segments >= 2 ? int64_t(tp.bytes) : 0;
+}
+
+}  // namespace
+
+extern "C" int64_t b12x_b200_gemm_blockscaled_workspace_bytes(int kind, int64_t m, int64_t n,
+                                                              int64_t k, int block_n, int sm_count) {
+  return tiled_workspace_bytes(kind, m, n, k, 1, block_n, sm_count);
 }
 
 extern "C" int b12x_b200_quantize_mxfp8_rows(const void* src, int src_dtype, int64_t ld_src,
@@ -613,9 +685,9 @@ int gemm_block_fp8_impl(const void* a, const float* sfa, const void* b, const fl
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
 
   CUtensorMap map_a, map_b;
-  rc = make_operand_map(&map_a, a, uint64_t(m), uint64_t(k), BlockFp8Tile::BM);
+  rc = make_operand_map_2d(&map_a, a, uint64_t(m), uint64_t(k), BlockFp8Tile::BM);
   if (rc != B12X_B200_OK) return rc;
-  rc = make_operand_map(&map_b, b, uint64_t(n), uint64_t(k), BlockFp8Tile::BN);
+  rc = make_operand_map_2d(&map_b, b, uint64_t(n), uint64_t(k), BlockFp8Tile::BN);
   if (rc != B12X_B200_OK) return rc;
 
   BlockFp8Params p;
@@ -655,7 +727,7 @@ int gemm_block_fp8_impl(const void* a, const float* sfa, const void* b, const fl
   memset(&map_c, 0, sizeof(map_c));
   p.use_tma_store = 0;
   if (c_dtype != B12X_B200_FP32 && aligned16(c) && (ldc * 2) % 16 == 0) {
-    rc = make_output_map(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
+    rc = make_output_map_2d(&map_c, c, uint64_t(m), uint64_t(n), uint64_t(ldc));
     if (rc != B12X_B200_OK) return rc;
     p.use_tma_store = 1;
   }
@@ -694,7 +766,7 @@ extern "C" int b12x_b200_gemm_block_fp8_ex(const void* a, const float* sfa, cons
 namespace {
 
 struct SmallMPlan {
-  int m_pad, tiles, k_tiles, k_atoms, grid, max_segments, stages, stage_bytes;
+  int m_pad, tiles, tiles_per_group, k_tiles, k_atoms, grid, max_segments, stages, stage_bytes;
   int issuers, sf_col0, tmem_cols, raw_rows;
   size_t partial_bytes, total_bytes;
 };
@@ -702,7 +774,8 @@ struct SmallMPlan {
 // Geometry of the decode-shape kernel for (kind, m, n, k) on `sms` SMs; `fused` adds the raw
 // BF16 activation rows (8 or 16 of them) to every stage. The workspace need does not depend on
 // `fused`.
-int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, SmallMPlan* out) {
+int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, int64_t groups,
+                SmallMPlan* out) {
   if (m < 1 || m > 128) return fail(B12X_B200_ERR_UNSUPPORTED, "decode kernel needs 1 <= M <= 128");
   if (n < 1 || k < 1 || n > INT32_MAX || k > INT32_MAX)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
@@ -711,7 +784,10 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
   SmallMPlan pl;
   pl.m_pad = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
-  pl.tiles = int((n + 127) / 128);
+  if (groups < 1 || groups > 65535 || ((n + 127) / 128) * groups > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be in [1, 65535]");
+  pl.tiles_per_group = int((n + 127) / 128);
+  pl.tiles = int(pl.tiles_per_group * groups);  // the tiles of all groups form one list
   pl.k_tiles = int((k + elems_per_stage - 1) / elems_per_stage);
   pl.k_atoms = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
   const int64_t units = int64_t(pl.tiles) * pl.k_tiles;
@@ -832,6 +908,7 @@ struct SmallMCall {
   unsigned long long* timeline;
   cudaStream_t stream;
   const b12x_b200_epilogue_t* epilogue = nullptr;
+  int64_t groups = 1;
 };
 
 // Argument checks shared by the decode-shape entry points. On success *empty is set when there
@@ -876,7 +953,7 @@ int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empt
   if (rc != B12X_B200_OK) return rc;
   if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
   *sms_out = (a.sm_count > 0 && a.sm_count < info.sm_count) ? a.sm_count : info.sm_count;
-  return plan_smallm(a.kind, a.m, a.n, a.k, *sms_out, fused, plan);
+  return plan_smallm(a.kind, a.m, a.n, a.k, *sms_out, fused, a.groups, plan);
 }
 
 int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
@@ -889,15 +966,16 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "workspace smaller than b12x_b200_gemm_smallm_workspace_bytes");
   const int64_t row_bytes = (a.kind == B12X_B200_KIND_MXFP8) ? a.k : a.k / 2;
   CUtensorMap map_w, map_x;
-  int rc = make_operand_map(&map_w, a.w, uint64_t(a.n), uint64_t(row_bytes), 128);
+  int rc = make_operand_map(&map_w, a.w, uint64_t(a.n), uint64_t(row_bytes), 128, uint64_t(a.groups));
   if (rc != B12X_B200_OK) return rc;
   if (fused) {
     const uint32_t elems = (a.kind == B12X_B200_KIND_MXFP8) ? 128u : 256u;
     rc = make_raw_rows_map(&map_x, a.x_src, uint64_t(a.m), uint64_t(a.k), uint64_t(a.ld_x), elems,
-                           uint32_t(pl.raw_rows));
+                           uint32_t(pl.raw_rows), uint64_t(a.groups));
     if (rc != B12X_B200_OK) return rc;
   } else {
-    rc = make_operand_map(&map_x, a.x, uint64_t(a.m), uint64_t(row_bytes), uint32_t(pl.m_pad));
+    rc = make_operand_map(&map_x, a.x, uint64_t(a.m), uint64_t(row_bytes), uint32_t(pl.m_pad),
+                          uint64_t(a.groups));
     if (rc != B12X_B200_OK) return rc;
   }
 
@@ -917,6 +995,10 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.out_dtype = a.c_dtype;
   p.m_pad = pl.m_pad;
   p.tiles = pl.tiles;
+  p.tiles_per_group = pl.tiles_per_group;
+  p.sf_w_group_bytes = int64_t(pl.tiles_per_group) * pl.k_atoms * 512;
+  p.sf_x_group_bytes = int64_t(pl.k_atoms) * 512;  // one row tile of activations per group
+  p.c_group_elems = a.m * a.ldc;
   p.k_tiles = pl.k_tiles;
   p.k_atoms_total = pl.k_atoms;
   p.max_segments = pl.max_segments;
@@ -966,7 +1048,7 @@ extern "C" int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, in
   if (device_info(&info) != B12X_B200_OK) return -1;
   const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
   SmallMPlan pl;
-  if (plan_smallm(kind, m, n, k, sms, false, &pl) != B12X_B200_OK) return -1;
+  if (plan_smallm(kind, m, n, k, sms, false, 1, &pl) != B12X_B200_OK) return -1;
   return int64_t(pl.total_bytes);
 }
 
@@ -996,6 +1078,33 @@ extern "C" int b12x_b200_gemm_blockscaled_smallm_ex(int kind, const void* x, con
                   reinterpret_cast<cudaStream_t>(stream)};
   a.epilogue = epilogue;
   return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int b12x_b200_gemm_blockscaled_smallm_grouped(
+    int kind, const void* x, const void* sf_x, const void* w, const void* sf_w, void* c, int c_dtype,
+    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
+    void* workspace, int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue, int sm_count,
+    int* status, b12x_b200_stream_t stream) {
+  SmallMCall a = {kind, x,     sf_x, nullptr, 0,   nullptr,  w,      sf_w,    c, c_dtype,
+                  alpha, m,    n,    k,       ldc, sm_count, status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  a.epilogue = epilogue;
+  a.groups = groups;
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int64_t b12x_b200_gemm_grouped_workspace_bytes(int kind, int decode, int64_t m,
+                                                          int64_t n, int64_t k, int64_t groups,
+                                                          int block_n, int sm_count) {
+  if (!decode) return tiled_workspace_bytes(kind, m, n, k, groups, block_n, sm_count);
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (n <= 0 || k <= 0) return -1;
+  DeviceInfo info;
+  if (device_info(&info) != B12X_B200_OK) return -1;
+  const int sms = (sm_count > 0 && sm_count < info.sm_count) ? sm_count : info.sm_count;
+  SmallMPlan pl;
+  if (plan_smallm(kind, m, n, k, sms, false, groups, &pl) != B12X_B200_OK) return -1;
+  return int64_t(pl.total_bytes);
 }
 
 extern "C" int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x,

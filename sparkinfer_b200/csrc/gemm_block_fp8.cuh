@@ -273,6 +273,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
         continue;
       }
       GemmParams gp;
+      gp.c_group_elems = 0;
       gp.c = p.c;
       gp.m = p.m;
       gp.n = p.n;
@@ -284,7 +285,7 @@ gemm_block_fp8_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = acc[c * 32 + i] * alpha;
         if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, col0 + c * 32, p.n);
-        store_row_chunk(gp, row, col0 + c * 32, vals);
+        store_row_chunk(gp, 0, row, col0 + c * 32, vals);
       }
     }
     if (p.use_tma_store && quarter == 2 && lane == 0) tma_store_wait_all<0>();

@@ -81,7 +81,19 @@ struct GemmParams {
   int num_stages;        // shared-memory ring depth actually used (<= GemmTile::kStages)
   int use_tma_store;     // 2-byte outputs with 16-byte aligned rows: stage in smem, TMA store
   const void* bias;      // [N] values of the output dtype added to every row, or null
+  // Grouped (batched) GEMM: `groups` independent problems of the same shape, operands stacked
+  // as [groups, rows, K], scale atoms and outputs group after group. Tiles of all groups form
+  // one list for the persistent scheduler.
+  int groups;
+  long long sfa_group_bytes, sfb_group_bytes;  // scale atoms of one group
+  long long c_group_elems;                     // output elements between groups
 };
+
+// Tile index of the whole (grouped) problem -> group and tile inside the group.
+__device__ __forceinline__ void split_group(int tile, int tiles_per_group, int& group, int& local) {
+  group = tile / tiles_per_group;
+  local = tile - group * tiles_per_group;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
                                             int& tm, int& tn) {
@@ -168,11 +180,12 @@ __device__ __forceinline__ float add_bias_1(float v, const void* bias, int out_d
   return __fadd_rn(__half2float(__float2half_rn(v)), __half2float(__half(hr)));
 }
 
-// Writes 32 consecutive output columns of one row. `vals` already carry alpha.
-__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col0,
+// Writes 32 consecutive output columns of one row of group `group`. `vals` already carry alpha.
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int group, int row, int col0,
                                                 const float (&vals)[32]) {
   if (row >= p.m || col0 >= p.n) return;
-  const size_t base = static_cast<size_t>(row) * p.ldc + col0;
+  const size_t base = static_cast<size_t>(group) * p.c_group_elems +
+                      static_cast<size_t>(row) * p.ldc + col0;
   const bool full = (col0 + 32 <= p.n);
   if (p.out_dtype == kOutFp32) {
     float* out = static_cast<float*>(p.c) + base;
@@ -265,7 +278,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     return;
   }
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_group = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_group * p.groups;
   const int k_tiles = (p.k + T::kElemsPerStage - 1) / T::kElemsPerStage;
   const int n_row_atoms_b = (p.n + 127) / 128;
   const uint32_t smem_u32 = smem_addr_u32(smem);
@@ -279,14 +293,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int m0 = tm * T::BM;
       const int n0 = tn * BN;
       const int sfb_atom0 = n0 / 128;
       const int sfb_atoms = min((n0 % 128 + BN + 127) / 128, n_row_atoms_b - sfb_atom0);
-      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(tm) * p.k_atoms_total * 512;
-      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
+      const uint8_t* sfa_src = p.sfa + grp * p.sfa_group_bytes + static_cast<size_t>(tm) * p.k_atoms_total * 512;
+      const uint8_t* sfb_src = p.sfb + grp * p.sfb_group_bytes + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
       for (int kt = 0; kt < k_tiles; ++kt) {
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
@@ -301,8 +316,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
           const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
           const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
           mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
-          tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
-          tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0);
+          tma_load_3d(st, &map_a, bar, kt * T::kRowBytes, m0, grp);
+          tma_load_3d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0, grp);
           bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
                     sf_bytes, bar);
           for (int ra = 0; ra < sfb_atoms; ++ra)
@@ -323,8 +338,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     int iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const uint32_t sfb_col_shift = static_cast<uint32_t>(((tn * BN) % 128) / 32);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
@@ -404,8 +420,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     int iter = 0;
     bool store_pending = false;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++iter) {
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       // The epilogue warps meet at barriers in the TMA-store path, so they agree on the
@@ -476,7 +493,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
           if (store_thread) {
             for (int sub = 0; sub < (chunks + 1) / 2; ++sub) {
               const int col = tn * BN + pass * 128 + sub * 64;
-              if (col < p.n) tma_store_2d(&map_c, c_stage + sub * (128 * 128), col, tm * T::BM);
+              if (col < p.n) tma_store_3d(&map_c, c_stage + sub * (128 * 128), col, tm * T::BM, grp);
             }
             tma_store_commit();
           }
@@ -493,7 +510,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
         if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
-        store_row_chunk(p, row, tn * BN + c * 32, vals);
+        store_row_chunk(p, grp, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();
       __syncwarp();

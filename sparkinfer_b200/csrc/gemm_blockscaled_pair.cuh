@@ -166,8 +166,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const bool tmem_ok = (tmem_base == 0);
   if (!tmem_ok && threadIdx.x == 0 && p.status) atomicMax(p.status, kStatusTmemLayout);
 
-  // tiles_m counts 256-row pair tiles here.
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  // tiles_m counts 256-row pair tiles here; the tiles of all groups form one list.
+  const int tiles_per_group = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_group * p.groups;
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int k_tiles = (p.k + T::kElemsPerStage - 1) / T::kElemsPerStage;
@@ -184,8 +185,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     PairWork w;
     for (int it = 0; ok && pair_work(it, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++it) {
-      int tm, tn;
-      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(w.tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int m0 = tm * 256 + static_cast<int>(rank) * 128;
       const int n0 = tn * BN;
       for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
@@ -199,9 +201,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           uint8_t* st = smem + stage * T::kStageBytes;
           uint64_t* bar = &full_bar[stage];
           mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes);
-          tma_load_2d(st, &map_a, bar, kt * T::kRowBytes, m0);
-          tma_load_2d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes,
-                      n0 + static_cast<int>(rank) * (BN / 2));
+          tma_load_3d(st, &map_a, bar, kt * T::kRowBytes, m0, grp);
+          tma_load_3d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes,
+                      n0 + static_cast<int>(rank) * (BN / 2), grp);
         }
         __syncwarp();
         if (++stage == T::kStages) { stage = 0; phase ^= 1; }
@@ -216,15 +218,18 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     PairWork w;
     for (int it = 0; ok && pair_work(it, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++it) {
-      int tm, tn;
-      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(w.tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int n0 = tn * BN;
       const int sfa_atom = tm * 2 + static_cast<int>(rank);
       const bool sfa_ok = sfa_atom < m_row_atoms;
       const int sfb_atom0 = n0 / 128;
       const int sfb_atoms = min(T::kSfbRowAtoms, n_row_atoms - sfb_atom0);
-      const uint8_t* sfa_src = p.sfa + static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
-      const uint8_t* sfb_src = p.sfb + static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
+      const uint8_t* sfa_src = p.sfa + grp * p.sfa_group_bytes +
+                               static_cast<size_t>(sfa_ok ? sfa_atom : 0) * p.k_atoms_total * 512;
+      const uint8_t* sfb_src = p.sfb + grp * p.sfb_group_bytes +
+                               static_cast<size_t>(sfb_atom0) * p.k_atoms_total * 512;
       for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
         if (!mbar_wait_bounded_cluster(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
@@ -345,8 +350,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     bool store_pending = false;
     PairWork w;
     for (int iter = 0; pair_work(iter, pair, num_pairs, num_tiles, k_tiles, tail.segments, w); ++iter) {
-      int tm, tn;
-      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int tm, tn, grp, local;
+      split_group(w.tile, tiles_per_group, grp, local);
+      tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       if (!epilogue_bar_and(mbar_wait_bounded_cluster(&acc_full_bar[acc], acc_phase, abort_flag))) {
@@ -458,7 +464,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o[j] = add_bias_1(o[j], p.bias, p.out_dtype, col + j, p.n);
               }
-              const size_t idx = static_cast<size_t>(row) * p.ldc + col;
+              const size_t idx = static_cast<size_t>(grp) * p.c_group_elems +
+                                 static_cast<size_t>(row) * p.ldc + col;
               if (p.out_dtype != kOutFp32 && col + 4 <= p.n &&
                   ((reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(p.c) + idx) & 7) == 0)) {
                 const bool bf = p.out_dtype == kOutBf16;
@@ -549,7 +556,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             epilogue_bar_sync();
             if (store_thread) {
               const int col = tn * BN + pass * 128 + sub * 64;
-              if (col < p.n && m0 < p.m) tma_store_2d(&map_c, c_stage, col, m0);
+              if (col < p.n && m0 < p.m) tma_store_3d(&map_c, c_stage, col, m0, grp);
               tma_store_commit();
             }
             store_pending = true;
@@ -584,7 +591,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
         if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
-        store_row_chunk(p, row, tn * BN + c * 32, vals);
+        store_row_chunk(p, grp, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();
       __syncwarp();

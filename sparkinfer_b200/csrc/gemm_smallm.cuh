@@ -73,7 +73,12 @@ struct SmallMParams {
   int* counters;
   int m, n, k, ldc, out_dtype;
   int m_pad;               // MMA N: 16, 32, 64 or 128
-  int tiles;               // ceil(N / 128)
+  int tiles;               // weight tiles of all groups: groups * ceil(N / 128)
+  int tiles_per_group;     // ceil(N / 128)
+  // Grouped GEMM: operands stacked as [groups, rows, K]; scale atoms and outputs group after
+  // group (bytes / elements between groups). Group g of the quantized-C output, if any, starts
+  // at column quant_col0 + g * N.
+  long long sf_w_group_bytes, sf_x_group_bytes, c_group_elems;
   int k_tiles;             // ceil(K / elems per stage)
   int k_atoms_total;
   int max_segments;        // scratch slots per tile
@@ -321,7 +326,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
     if (p.wait_for_weights) grid_dependency_wait();
     int stage = 0;
     uint32_t phase = 0;
-    int tile = u_begin / p.k_tiles;
+    int tile = u_begin / p.k_tiles;  // over all groups
     int kt = u_begin - tile * p.k_tiles;
     for (int u = u_begin; u < u_end; ++u) {
       if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
@@ -332,13 +337,16 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       if (elect_one()) {
         uint8_t* st = smem + stage * p.stage_bytes;
         uint64_t* bar = &full_bar[stage];
+        const int grp = tile / p.tiles_per_group;
+        const int local = tile - grp * p.tiles_per_group;
         const int katom0 = kt * T::kKAtoms;
         const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
         const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
         mbar_arrive_expect_tx(bar, T::kWBytes + sf_bytes);
-        tma_load_2d(st, &map_w, bar, kt * 128, tile * 128);
+        tma_load_3d(st, &map_w, bar, kt * 128, local * 128, grp);
         bulk_load(st + T::kWBytes,
-                  p.sf_w + (static_cast<size_t>(tile) * p.k_atoms_total + katom0) * 512,
+                  p.sf_w + grp * p.sf_w_group_bytes +
+                      (static_cast<size_t>(local) * p.k_atoms_total + katom0) * 512,
                   sf_bytes, bar);
       }
       __syncwarp();
@@ -381,7 +389,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       grid_dependency_wait();  // activations may come from the previous grid
       int stage = 0;
       uint32_t phase = 0;
-      int kt = u_begin % p.k_tiles;
+      int tile = u_begin / p.k_tiles;
+      int kt = u_begin - tile * p.k_tiles;
       for (int u = u_begin; u < u_end; ++u) {
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
@@ -391,23 +400,25 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         if (elect_one()) {
           uint8_t* st = smem + stage * p.stage_bytes;
           uint64_t* bar = &full_bar[stage];
+          const int grp = tile / p.tiles_per_group;
           const int katom0 = kt * T::kKAtoms;
           const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
           const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
           if (FUSED) {
             mbar_arrive_expect_tx(bar, raw_bytes);
-            tma_load_2d(st + FusedQuant<KIND>::raw_offset(p.m_pad), &map_x, bar,
-                        kt * T::kElemsPerStage, 0);
+            tma_load_3d(st + FusedQuant<KIND>::raw_offset(p.m_pad), &map_x, bar,
+                        kt * T::kElemsPerStage, 0, grp);
           } else {
             mbar_arrive_expect_tx(bar, x_bytes + sf_bytes);
-            tma_load_2d(st + T::kXOffset, &map_x, bar, kt * 128, 0);
-            bulk_load(st + T::kWBytes + T::kSfBytes, p.sf_x + static_cast<size_t>(katom0) * 512,
+            tma_load_3d(st + T::kXOffset, &map_x, bar, kt * 128, 0, grp);
+            bulk_load(st + T::kWBytes + T::kSfBytes,
+                      p.sf_x + grp * p.sf_x_group_bytes + static_cast<size_t>(katom0) * 512,
                       sf_bytes, bar);
           }
         }
         __syncwarp();
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
-        if (++kt == p.k_tiles) kt = 0;
+        if (++kt == p.k_tiles) { kt = 0; ++tile; }
       }
     } else if (FUSED && warp >= 8) {
       // ------------------------------ activation quantizers ------------------------------
@@ -552,9 +563,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       // warp holds 32 consecutive columns of the row, which is exactly one scale block, so the
       // block maximum is one warp-wide integer max of the magnitudes' bit patterns. Called by
       // whole warps.
-      auto emit = [&](int mrow, int n_global, bool n_ok, float acc_value) {
+      auto emit = [&](int grp, int mrow, int n_global, bool n_ok, float acc_value) {
         float v = acc_value * alpha;
-        const size_t idx = static_cast<size_t>(mrow) * p.ldc + n_global;
+        const size_t idx = static_cast<size_t>(grp) * p.c_group_elems +
+                           static_cast<size_t>(mrow) * p.ldc + n_global;
         if constexpr (!EPI) {
           if (n_ok) {
             if (p.out_dtype == kOutBf16)
@@ -585,7 +597,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           const uint32_t byte = ue8m0_from_amax(amax);
           const float inv = ue8m0_reciprocal(byte);
           if (n_ok) {
-            const int qcol = p.quant_col0 + n_global;
+            const int qcol = p.quant_col0 + grp * p.n + n_global;
             p.quant_values[static_cast<size_t>(mrow) * p.quant_ld + qcol] =
                 static_cast<uint8_t>(e4m3x4(__fmul_rn(stored, inv), 0.0f, 0.0f, 0.0f) & 0xFFu);
             if (lane == 0) {
@@ -624,7 +636,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         const uint32_t taddr0 =
             lane_base + static_cast<uint32_t>((acc * p.issuers + (both ? 0 : first_issuer)) * p.m_pad);
         const uint32_t taddr1 = lane_base + static_cast<uint32_t>((acc * p.issuers + 1) * p.m_pad);
-        const int n_global = tile * 128 + n_local;
+        const int grp = tile / p.tiles_per_group;
+        const int n_global = (tile - grp * p.tiles_per_group) * 128 + n_local;  // inside the group
         const bool n_ok = n_global < p.n;
         int first_cta = 0, segments = 1, slot = 0;
         if (!whole) {
@@ -650,7 +663,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int mrow = c0 + i;
-              if (mrow < p.m) emit(mrow, n_global, n_ok, __uint_as_float(raw[i]));
+              if (mrow < p.m) emit(grp, mrow, n_global, n_ok, __uint_as_float(raw[i]));
             }
           } else {
 #pragma unroll
@@ -691,7 +704,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int mrow = m0 + i;
-                if (mrow < p.m) emit(mrow, n_global, n_ok, sum[i]);
+                if (mrow < p.m) emit(grp, mrow, n_global, n_ok, sum[i]);
               }
             }
           }

@@ -159,6 +159,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Three-dimensional form: (x = bytes along K, y = row, z = group). Operands of a grouped GEMM
+// are described by one map over [groups, rows, K], so a tile never reads across a group edge:
+// rows at or beyond the group's row count are out of bounds and arrive as zeros.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_addr_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)),
+      "r"(smem_addr_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map,
                                                  uint64_t* bar, int32_t x, int32_t y,
                                                  uint64_t policy) {
@@ -185,6 +198,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
   asm volatile(
       "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
       ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr_u32(smem_src)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src,
+                                             int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr_u32(smem_src)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 

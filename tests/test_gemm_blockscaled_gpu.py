@@ -869,3 +869,41 @@ def test_quantized_c_equals_row_quantization_of_the_bf16_output(kind, m, n, k, g
                        _quantized_c=(q.values, q.scale_rows[0], q.scale_mma), **kw)
     from sparkinfer_b200._lib.launch import check_kernel_status
     check_kernel_status(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,groups,tile", [
+    (4, 384, 512, 5, None),          # decode kernel: 15 weight tiles of 5 groups in one work list
+    (33, 200, 256, 3, None),         # decode kernel, ragged N, K split over CTAs
+    (130, 264, 384, 2, (128, 64)),   # single-CTA tiled kernel, ragged edges inside each group
+    (256, 512, 256, 3, (128, 128)),
+    (300, 504, 640, 2, (256, 256)),  # CTA-pair kernel, rows of a group end inside a pair tile
+    (512, 1024, 512, 4, None),       # automatic choice
+])
+def test_mm_grouped_batches_run_in_one_launch(m, n, k, groups, tile):
+    """``L`` problems stacked as ``[M, K, L]`` / ``[N, K, L]`` go through ONE kernel launch (the
+    tiles of all groups form one work list); every group against the oracle, and group edges
+    must not leak: the operands of group g + 1 follow those of group g directly in memory."""
+    from gpu_util import DEV, assert_gemm_close, to_dev
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200.gemm import blockscaled
+
+    a_vals, a_sw, b_vals, b_sw, refs = [], [], [], [], []
+    for g in range(groups):
+        a = seeded_bf16(500 + g, (m, k), 0.25 * (1 + g)).float().numpy()
+        b = seeded_bf16(600 + g, (n, k), 0.03 / (1 + g)).float().numpy()
+        av, asr = O.quantize_mxfp8_rows(a)
+        bv, bsr = O.quantize_mxfp8_rows(b)
+        a_vals.append(av); b_vals.append(bv)
+        a_sw.append(O.swizzle_scales(asr, 127)); b_sw.append(O.swizzle_scales(bsr, 127))
+        refs.append(O.dequantize_mxfp8(av, asr) @ O.dequantize_mxfp8(bv, bsr).T)
+    a_t = to_dev(np.stack(a_vals)).view(torch.float8_e4m3fn).as_strided((m, k, groups), (k, 1, m * k))
+    b_t = to_dev(np.stack(b_vals)).view(torch.float8_e4m3fn).as_strided((n, k, groups), (k, 1, n * k))
+    sfa = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(a_sw)), m, k, groups, 32)
+    sfb = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(b_sw)), n, k, groups, 32)
+    out = torch.full((groups, m, n), float("nan"), dtype=torch.bfloat16, device=DEV).permute(1, 2, 0)
+    blockscaled.mm((a_t, sfa), (b_t, sfb), out, c_dtype="bfloat16", mma_tiler_mn=tile, **MXFP8)
+    torch.cuda.synchronize()
+    for g in range(groups):
+        assert_gemm_close(out[:, :, g], refs[g])
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
