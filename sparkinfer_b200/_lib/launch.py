@@ -34,6 +34,19 @@ _COUNTER_BYTES = 64 << 10  # counter block at the start of a decode workspace
 _DTYPE_CODE = {torch.bfloat16: _native.DT_BF16, torch.float16: _native.DT_FP16,
                torch.float32: _native.DT_FP32}
 
+import os as _os
+
+# Debug aid, off by default: B12X_B200_CHECK_STATUS=1 makes every launcher synchronise and call
+# check_kernel_status() after its kernel, so that a kernel that gave up a bounded wait (and left
+# its output unwritten) raises at the call that launched it instead of going unnoticed. It
+# serialises the host with the device and cannot be used under CUDA-graph capture.
+_CHECK_AFTER_LAUNCH = _os.getenv("B12X_B200_CHECK_STATUS", "0") == "1"
+
+
+def _after_launch(device: torch.device) -> None:
+    if _CHECK_AFTER_LAUNCH and not torch.cuda.is_current_stream_capturing():
+        check_kernel_status(device)
+
 KERNEL_STATUS_TEXT = {
     1: "TMA producer timed out waiting for a free pipeline stage",
     2: "MMA issuer timed out waiting for operands or a free accumulator",
@@ -257,6 +270,7 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
                 _stream_ptr(stream_int, dev))
     _native.check(rc, "b12x_b200_gemm_blockscaled_smallm_grouped" if decode
                   else "b12x_b200_gemm_blockscaled_grouped")
+    _after_launch(dev)
 
 
 def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tensor | None,
@@ -286,6 +300,7 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
             ctypes.byref(ep) if ep is not None else None, sm_count,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
     _native.check(rc, "b12x_b200_gemm_smallm_fused_quant")
+    _after_launch(dev)
 
 
 def gemm_smallm_timeline(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
@@ -329,6 +344,7 @@ def gemm_block_fp8(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: tor
             ldc if ldc is not None else n, sm_count, ctypes.byref(ep) if ep is not None else None,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
     _native.check(rc, "b12x_b200_gemm_block_fp8_ex")
+    _after_launch(dev)
 
 
 def quantize_mxfp8_rows(src: torch.Tensor, values: torch.Tensor, scale_rows: torch.Tensor | None,
