@@ -44,14 +44,14 @@ L2_FLUSH_BYTES = 256 << 20
 
 # DRAM bytes (read + write) of ONE launch of each workload's GEMM kernel on one GPU at the full
 # size, from `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` captures of
-# `python -m sparkinfer_b200.profile_case <op> M N K 3` (summaries under profiles/). Output
+# `python profile_case.py <op> M N K 3` (summaries under profiles/). Output
 # bytes still held in the 126 MB L2 when the kernel ends are not in the write figure.
 NCU_TRAFFIC_BYTES = {
-    "cfg0_nvfp4_128x4096x4096": 9_763_584 + 0,
-    "cfg1_nvfp4_decode_m16": 33_144_832 + 0,
-    "cfg2_mxfp8_prefill": 268_549_632 + 98_470_400,
-    "cfg3_block_fp8_colpar": 297_408_768 + 129_085_696,
-    "cfg4_nvfp4_rowpar": 205_381_120 + 43_779_584,
+    "cfg0_nvfp4_128x4096x4096": 9_762_816 + 0,
+    "cfg1_nvfp4_decode_m16": 33_144_320 + 0,
+    "cfg2_mxfp8_prefill": 270_284_800 + 98_234_368,
+    "cfg3_block_fp8_colpar": 298_083_840 + 131_562_752,
+    "cfg4_nvfp4_rowpar": 206_371_840 + 50_135_808,
 }
 
 
