@@ -14,6 +14,7 @@ Reference functions used (path:line in the b12x tree):
   _scale_u8_from_max_abs                                  b12x/gemm/_shared/wo_mxfp8.py:844-851
   ref_fp4_quant, dequantize_grouped_nvfp4,
   compute_global_scale, recover_grouped_e4m3_scales       tests/_reference/helpers.py:224-363
+  _block_fp8_reference                                    tests/gemm/test_gemm_stack.py:98-113
   pack_fp8_block_scaled_weight_mxfp8 (re-quantization to UE8M0 block scales, expansion to
   per-row scales, MMA layout)                             b12x/gemm/_shared/wo_mxfp8.py:873-1187
     (these insist on CUDA tensors; the generator swaps the module's device check for a no-op
@@ -141,7 +142,12 @@ def main() -> None:
     gm["nv_a"], gm["nv_b"] = _bf16_bits(a), _bf16_bits(b)
     gm["nv_gsa"], gm["nv_gsb"] = gsa.numpy(), gsb.numpy()
     gm["nv_out"] = (da @ db.T).numpy()
-    # Block-FP8 with FP32 scales, tests/gemm/test_gemm_stack.py:98-113 restated with torch ops.
+    # Block-FP8 with FP32 scales: the reference's own test reference
+    # (tests/gemm/test_gemm_stack.py:98-113, BF16 out), imported, plus the same dequantized
+    # product kept in FP32 for the tight error bound.
+    import importlib
+
+    block_fp8_reference = importlib.import_module("tests.gemm.test_gemm_stack")._block_fp8_reference
     m, n, k = 64, 256, 256
     gen = torch.Generator().manual_seed(3042)
     a8 = torch.randn((m, k), generator=gen).clamp(-3, 3).to(torch.float8_e4m3fn)
@@ -150,6 +156,7 @@ def main() -> None:
     sb = torch.rand((n // 128, k // 128), generator=gen) + 0.5
     a_d = (a8.float().view(m, k // 128, 128) * sa[:, :, None]).reshape(m, k)
     b_d = (b8.float().view(n // 128, 128, k // 128, 128) * sb[:, None, :, None]).reshape(n, k)
+    gm["bf8_out_bf16_bits"] = _bf16_bits(block_fp8_reference(a8, b8, sa, sb))
     gm["bf8_a"] = a8.view(torch.uint8).numpy()
     gm["bf8_b"] = b8.view(torch.uint8).numpy()
     gm["bf8_sa"], gm["bf8_sb"] = sa.numpy(), sb.numpy()

@@ -96,6 +96,8 @@ def test_gemm_references_match_reference():
     assert np.array_equal(O.gemm_nvfp4(pa, sa, gsa, pb, sb, gsb), g["nv_out"])
     out = O.gemm_block_fp8(g["bf8_a"], g["bf8_sa"], g["bf8_b"], g["bf8_sb"])
     assert np.array_equal(out, g["bf8_out"])
+    # the reference's own _block_fp8_reference (tests/gemm/test_gemm_stack.py:98-113), BF16 out
+    assert np.array_equal(O.bf16_round(out), bf16_bits_to_f32(g["bf8_out_bf16_bits"]))
 
 
 def test_e4m3_codec_matches_torch_in_domain():
