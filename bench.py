@@ -41,6 +41,9 @@ sys.path.insert(0, str(ROOT))
 NOMINAL = {"hbm_gbs": 8000.0, "fp8_tflops": 4500.0, "fp4_tflops": 9000.0}
 DEFAULT_WORKLOAD = "cfg3_block_fp8_colpar"
 L2_FLUSH_BYTES = 256 << 20
+# Collective of the K-split (row-parallel) step on several GPUs: "peer" = this package's own
+# all-reduce kernel over NVLink peer memory, "nccl" = torch.distributed all_reduce.
+COLLECTIVE = os.environ.get("B12X_BENCH_COLLECTIVE", "peer")
 
 # DRAM bytes (read + write) of ONE launch of each workload's GEMM kernel on one GPU at the full
 # size, from `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` captures of
@@ -255,7 +258,7 @@ class Step:
         self.xq = nvfp4.allocate_outputs(self.xplan, device=self.device)
         nvfp4.run(plan=self.xplan, x=x, global_scale=gs_x, outputs=self.xq)
         self.alpha = (1.0 / (gs_x * gs_w)).float()
-        self.out = torch.empty((m, n, 1), dtype=torch.bfloat16, device=self.device)
+        self.out = self._output_buffer(m, n)
         lhs = (self.xq.packed_a_view, self.xq.scale_mma_view(m, kl))
         kw = dict(ab_dtype="float4_e2m1fn", sf_dtype="float8_e4m3fn", sf_vec_size=16,
                   c_dtype="bfloat16", alpha=self.alpha)
@@ -309,6 +312,43 @@ class Step:
         self.h2d_bytes = x.numel() * 2
         self.d2h_bytes = self.out.numel() * 2
 
+    def _output_buffer(self, m: int, n: int) -> torch.Tensor:
+        """Output of a K-split step on several GPUs: the peer-mapped buffer of this package's
+        all-reduce kernel, so that the GEMM writes its partial where the kernel sums it. All
+        ranks agree on whether the peer mapping came up; if it did not on any of them, the
+        step uses NCCL and the line says so."""
+        self.reducer = None
+        self.collective = "none"
+        if self.w["shard"] == "k" and self.world > 1:
+            import torch.distributed as dist
+
+            from sparkinfer_b200.parallel import PeerAllReduce
+
+            self.collective = "nccl all_reduce"
+            reducer, why = None, ""
+            if COLLECTIVE == "peer":
+                try:
+                    reducer = PeerAllReduce(m, n, torch.bfloat16, device=self.device)
+                except Exception as exc:  # no symmetric memory on this box
+                    why = f"{type(exc).__name__}: {str(exc)[:120]}"
+            ok = torch.tensor([1 if reducer is not None else 0], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 1:
+                self.reducer = reducer
+                self.collective = "b12x_b200_allreduce_peer (own kernel, NVLink peer memory)"
+                return reducer.partial.view(m, n, 1)
+            if COLLECTIVE == "peer":
+                self.collective += f" (peer memory unavailable: {why or 'on another rank'})"
+        return torch.empty((m, n, 1), dtype=torch.bfloat16, device=self.device)
+
+    def all_reduce(self):
+        if self.reducer is not None:
+            self.reducer()
+        else:
+            import torch.distributed as dist
+
+            dist.all_reduce(self.out)
+
     def _setup_block_fp8(self, x, wt, n_shard, k_shard):
         from sparkinfer_b200.gemm import blockscaled
 
@@ -340,9 +380,7 @@ class Step:
             self.quant()
         self.gemm()
         if self.w["shard"] == "k" and self.world > 1:
-            import torch.distributed as dist
-
-            dist.all_reduce(self.out)
+            self.all_reduce()
 
     def flops(self) -> float:
         return 2.0 * self.w["m"] * self.w["n"] * self.w["k"]  # whole job, all ranks
@@ -589,7 +627,7 @@ def config_dict(name: str, w: dict, world: int, steps: int) -> dict:
     group = replicas_for(w, steps)
     return {"workload": name, "m": w["m"], "n": w["n"], "k": w["k"],
             "sharding": {"n": "column-parallel N/gpus, no communication",
-                         "k": "row-parallel K/gpus + NCCL BF16 all-reduce",
+                         "k": "row-parallel K/gpus + BF16 all-reduce (own peer-memory kernel; NCCL timed beside it)",
                          None: "single GPU"}[w["shard"]],
             "step": ("activation quantize_rows + " if w["quant"] else "") + "GEMM"
                     + (" (one fused kernel)" if w.get("fused") else "")
@@ -697,8 +735,14 @@ def time_components(step: Step, flush, sync_ranks, reduce_max) -> dict:
     if step.w["shard"] == "k" and step.world > 1:
         import torch.distributed as dist
 
+        out["collective"] = step.collective
         out["allreduce_ms"] = reduce_max(float(np.mean(
-            time_steps(lambda: dist.all_reduce(step.out), 20, 3, flush, sync_ranks, use_graph=False))))
+            time_steps(step.all_reduce, 20, 3, flush, sync_ranks, use_graph=False))))
+        if step.reducer is not None:  # the library collective on the same bytes, for comparison
+            scratch = torch.empty_like(step.out)
+            out["nccl_allreduce_ms"] = reduce_max(float(np.mean(
+                time_steps(lambda: dist.all_reduce(scratch), 20, 3, flush, sync_ranks, use_graph=False))))
+            del scratch
     return out
 
 

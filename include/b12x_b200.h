@@ -345,6 +345,37 @@ int b12x_b200_quantize_nvfp4_rows(const void* src, int src_dtype, int64_t ld_src
  */
 int b12x_b200_selftest_wait_timeout(int* status, int max_polls, b12x_b200_stream_t stream);
 
+/*
+ * Sum of the per-rank partial outputs of a row-parallel (K-split) linear over peer memory: the
+ * all-reduce that follows the GEMM when the serving stack shards K across the GPUs of a node.
+ * The reference's GEMM is single-GPU and leaves this step to the caller's torch.distributed
+ * all_reduce; it has no counterpart there. Every rank calls this with the same shapes, one
+ * kernel per rank and call: rank s pulls the rows of slab s (rows * s / world up to
+ * rows * (s + 1) / world) of every rank's partial, adds them in FP32 in rank order, rounds once
+ * and pushes the result into all ranks' buffers, in place. When the call's kernel has finished
+ * on a rank's stream, that rank's buffer holds the complete sum, identical on every rank.
+ *
+ *   buffers  host array of `world` device pointers: rank r's [rows, ld] partial as mapped in
+ *            THIS process (own allocation for r == rank, peer mappings otherwise), 16-byte aligned
+ *   signals  host array of `world` device pointers to each rank's signal block
+ *            (b12x_b200_allreduce_peer_signal_bytes() bytes, zeroed once before the first call
+ *            and before any peer can call), mapped the same way
+ *   rank     this process's rank in [0, world). rank < 0 runs ALL ranks in one cooperative grid
+ *            on the current device (every pointer local): a single-GPU rehearsal for tests;
+ *            blocks * world must then be resident at once (<= SMs)
+ *   dtype    B12X_B200_BF16 or B12X_B200_FP16; cols % 8 == 0, ld % 8 == 0
+ *   blocks   thread blocks of 512 threads per rank, 0 = library default
+ *   max_polls  limit of each wait for another rank's flag (one poll is a system-scope load plus
+ *            a 200 ns back-off), 0 = 2^21 (a few seconds). When a wait runs out *status is
+ *            raised to 6, the data phase is skipped and the kernel returns.
+ * Waits on other GPUs' kernels: the ranks must be on different devices (rank >= 0), launched
+ * by their own processes or threads; never launch two ranks' calls on one device.
+ */
+int64_t b12x_b200_allreduce_peer_signal_bytes(void);
+int b12x_b200_allreduce_peer(void* const* buffers, void* const* signals, int world, int rank,
+                             int dtype, int64_t rows, int64_t cols, int64_t ld, int blocks,
+                             int64_t max_polls, int* status, b12x_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

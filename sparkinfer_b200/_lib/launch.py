@@ -53,6 +53,7 @@ KERNEL_STATUS_TEXT = {
     3: "epilogue timed out waiting for a finished accumulator",
     4: "split-K reduction timed out waiting for its peers",
     5: "tensor memory was not allocated from column 0",
+    6: "all-reduce over peer memory timed out waiting for another rank",
 }
 
 
@@ -373,8 +374,31 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
     _native.check(rc, "b12x_b200_quantize_nvfp4_rows")
 
 
+def allreduce_peer_signal_bytes() -> int:
+    return int(_native.load().b12x_b200_allreduce_peer_signal_bytes())
+
+
+def allreduce_peer(buffer_ptrs: list[int], signal_ptrs: list[int], rank: int, dtype: torch.dtype,
+                   rows: int, cols: int, ld: int, device: torch.device, *, blocks: int = 0,
+                   max_polls: int = 0, stream_int: int | None = None) -> None:
+    """Sum of all ranks' ``[rows, ld]`` partials over peer memory, in place in every rank's
+    buffer. ``buffer_ptrs`` / ``signal_ptrs``: every rank's buffer and signal block as mapped in
+    this process. ``rank = -1`` rehearses all ranks in one grid on ``device`` (tests)."""
+    world = len(buffer_ptrs)
+    if len(signal_ptrs) != world:
+        raise ValueError("one signal block per buffer")
+    bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
+    sigs = (ctypes.c_void_p * world)(*signal_ptrs)
+    with torch.cuda.device(device):
+        rc = _native.load().b12x_b200_allreduce_peer(
+            bufs, sigs, world, rank, _DTYPE_CODE[dtype], rows, cols, ld, blocks, max_polls,
+            status_buffer(device).data_ptr(), _stream_ptr(stream_int, device))
+    _native.check(rc, "b12x_b200_allreduce_peer")
+    _after_launch(device)
+
+
 __all__ = [
-    "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
+    "allreduce_peer", "allreduce_peer_signal_bytes", "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
     "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
     "route_to_decode_kernel", "smallm_workspace", "stream_workspace", "quantize_mxfp8_rows",
     "quantize_nvfp4_rows",

@@ -15,6 +15,7 @@
 #include "gemm_blockscaled_pair.cuh"
 #include "gemm_smallm.cuh"
 #include "quantize.cuh"
+#include "allreduce_peer.cuh"
 
 namespace b12x_b200 {
 namespace {
@@ -1251,5 +1252,92 @@ extern "C" int b12x_b200_selftest_wait_timeout(int* status, int max_polls,
       status, uint32_t(max_polls));
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "selftest launch");
+  return B12X_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// All-reduce of row-parallel partial outputs over peer memory
+// ------------------------------------------------------------------------------------------
+namespace b12x_b200 {
+namespace {
+
+template <int G, bool BF16>
+cudaError_t launch_allreduce_peer(const PeerAllReduceParams& p, int blocks, bool rehearsal,
+                                  cudaStream_t stream) {
+  if (!rehearsal) {
+    allreduce_peer_kernel<G, BF16><<<blocks, 512, 0, stream>>>(p);
+    return cudaGetLastError();
+  }
+  // All ranks in one grid: its blocks wait on each other, so they must all be resident.
+  PeerAllReduceParams copy = p;
+  void* args[] = {&copy};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&allreduce_peer_kernel<G, BF16>),
+                                     dim3(blocks, p.world), dim3(512), args, 0, stream);
+}
+
+template <bool BF16>
+cudaError_t launch_allreduce_peer_any(const PeerAllReduceParams& p, int blocks, bool rehearsal,
+                                      cudaStream_t stream) {
+  switch (p.world) {
+    case 2: return launch_allreduce_peer<2, BF16>(p, blocks, rehearsal, stream);
+    case 4: return launch_allreduce_peer<4, BF16>(p, blocks, rehearsal, stream);
+    case 8: return launch_allreduce_peer<8, BF16>(p, blocks, rehearsal, stream);
+    default: return launch_allreduce_peer<0, BF16>(p, blocks, rehearsal, stream);
+  }
+}
+
+}  // namespace
+}  // namespace b12x_b200
+
+extern "C" int64_t b12x_b200_allreduce_peer_signal_bytes(void) {
+  return int64_t(b12x_b200::kSigWords) * 4;
+}
+
+extern "C" int b12x_b200_allreduce_peer(void* const* buffers, void* const* signals, int world,
+                                        int rank, int dtype, int64_t rows, int64_t cols,
+                                        int64_t ld, int blocks, int64_t max_polls, int* status,
+                                        b12x_b200_stream_t stream) {
+  if (!buffers || !signals) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (world < 1 || world > kMaxPeers)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "world must be in [1, 8]");
+  if (rank >= world) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rank outside the world");
+  if (dtype != B12X_B200_BF16 && dtype != B12X_B200_FP16)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "all-reduce works on BF16 or FP16 partials");
+  if (rows < 0 || cols < 0 || ld < cols || cols % 8 != 0 || ld % 8 != 0)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "cols and ld must be multiples of 8 with ld >= cols");
+  if (max_polls < 0 || max_polls > (int64_t(1) << 31) - 1)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "max_polls outside [0, 2^31)");
+  for (int r = 0; r < world; ++r) {
+    if (!buffers[r] || !signals[r]) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(buffers[r]) & 15) || (reinterpret_cast<uintptr_t>(signals[r]) & 15))
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "buffers and signal blocks must be 16-byte aligned");
+  }
+  DeviceInfo info;
+  const int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  if (world == 1 || rows == 0 || cols == 0) return B12X_B200_OK;  // one rank: the partial is the sum
+  const bool rehearsal = rank < 0;
+  if (blocks <= 0) blocks = rehearsal ? std::max(1, info.sm_count / (2 * world)) : 2 * info.sm_count;
+  if (rehearsal && int64_t(blocks) * world > int64_t(info.sm_count))
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rehearsal grid would not be resident at once");
+  PeerAllReduceParams p{};
+  for (int r = 0; r < world; ++r) {
+    p.buf[r] = buffers[r];
+    p.sig[r] = static_cast<uint32_t*>(signals[r]);
+  }
+  p.world = world;
+  p.rank = rank;
+  p.rows = rows;
+  p.cols = cols;
+  p.ld = ld;
+  p.out_dtype = dtype == B12X_B200_BF16 ? kOutBf16 : kOutFp16;
+  p.max_polls = max_polls ? uint32_t(max_polls) : (1u << 21);
+  p.status = status;
+  const cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const cudaError_t err = dtype == B12X_B200_BF16
+                              ? launch_allreduce_peer_any<true>(p, blocks, rehearsal, s)
+                              : launch_allreduce_peer_any<false>(p, blocks, rehearsal, s);
+  if (err != cudaSuccess) return fail_cuda(err, "all-reduce launch");
   return B12X_B200_OK;
 }

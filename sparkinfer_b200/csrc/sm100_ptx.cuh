@@ -22,6 +22,7 @@ enum KernelStatus : int {
   kStatusEpilogueTimeout = 3,   // epilogue waited too long for a finished accumulator
   kStatusReduceTimeout = 4,     // split-K reduction waited too long for its peers
   kStatusTmemLayout = 5,        // tensor memory was not handed out from column 0
+  kStatusPeerTimeout = 6,       // all-reduce over peer memory waited too long for another rank
 };
 
 // Polls allowed on one mbarrier phase before a wait gives up. Legitimate waits on this

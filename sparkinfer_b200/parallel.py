@@ -7,7 +7,8 @@ both keep the per-GPU work a plain call into the ops of this package:
   rank holds the full activation and writes its ``[M, N/g]`` slab. No communication.
 * row-parallel: K is split (whole 128-column blocks); each rank quantizes its slice of the
   activation with the *same* caller-supplied global scale, multiplies, and the BF16 partial
-  outputs are summed with one all-reduce (NCCL over NVLink on GPUs, gloo in CPU tests).
+  outputs are summed with one all-reduce: :class:`PeerAllReduce` (this package's own kernel
+  over NVLink peer memory) on GPUs, or ``torch.distributed`` (NCCL; gloo in CPU tests).
 
 One process per GPU, ``torch.distributed`` for the plumbing.
 """
@@ -73,6 +74,66 @@ def all_reduce_partials(partial: torch.Tensor, group=None) -> torch.Tensor:
     return partial
 
 
+def slab_rows(rows: int, world_size: int, rank: int) -> tuple[int, int]:
+    """Rows ``[begin, end)`` of the output that ``rank`` sums and broadcasts in
+    :class:`PeerAllReduce` (the split the kernel uses: ``rows * rank // world_size``)."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    return rows * rank // world_size, rows * (rank + 1) // world_size
+
+
+class PeerAllReduce:
+    """All-reduce of the row-parallel partial outputs by this package's own kernel over peer
+    memory (``b12x_b200_allreduce_peer``).
+
+    Owns a ``[rows, cols]`` BF16/FP16 buffer in symmetric memory (every rank of the node maps
+    every other rank's buffer) and a small signal block. The GEMM writes its partial straight
+    into :attr:`partial`; calling the object sums the partials of all ranks in place: when the
+    call's kernel has finished on this rank's stream, :attr:`partial` holds the full sum,
+    bit-identical on every rank. Collective: every rank must construct it and call it the same
+    number of times. One rank per GPU."""
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, group=None,
+                 device: torch.device | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from ._lib import launch
+
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("PeerAllReduce needs an initialised process group")
+        if dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError(f"partials must be bf16/fp16, got {dtype}")
+        if cols % 8 != 0:
+            raise ValueError(f"cols={cols} must be a multiple of 8")
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world_size > 8:
+            raise ValueError("at most 8 ranks (one NVLink node)")
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.rows, self.cols, self.dtype = int(rows), int(cols), dtype
+        self.partial = symm_mem.empty((self.rows, self.cols), dtype=dtype, device=self.device)
+        self._signal = symm_mem.empty((launch.allreduce_peer_signal_bytes() // 4,),
+                                      dtype=torch.int32, device=self.device)
+        self._signal.zero_()
+        self._handles = (symm_mem.rendezvous(self.partial, group),
+                         symm_mem.rendezvous(self._signal, group))
+        self.buffer_ptrs = [int(p) for p in self._handles[0].buffer_ptrs]
+        self.signal_ptrs = [int(p) for p in self._handles[1].buffer_ptrs]
+        # Every rank's signal block is zero before any rank can send a flag into it.
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)
+
+    def __call__(self, stream: object | None = None) -> torch.Tensor:
+        from ._lib import launch
+
+        launch.allreduce_peer(self.buffer_ptrs, self.signal_ptrs, self.rank, self.dtype, self.rows,
+                              self.cols, self.cols, self.device,
+                              stream_int=launch.cuda_stream_to_int(stream))
+        return self.partial
+
+
 def gather_columns(slab: torch.Tensor, group=None) -> torch.Tensor:
     """Concatenate the ``[M, N/g]`` slabs of a column-parallel linear along N (not on the timed
     path; equal slab widths)."""
@@ -84,4 +145,4 @@ def gather_columns(slab: torch.Tensor, group=None) -> torch.Tensor:
 
 
 __all__ = ["Shard", "shard_range", "column_parallel_weight", "row_parallel_slices",
-           "all_reduce_partials", "gather_columns"]
+           "all_reduce_partials", "gather_columns", "slab_rows", "PeerAllReduce"]

@@ -112,3 +112,19 @@ def test_column_and_row_parallel_on_two_gloo_ranks():
         assert col_ok, "gathered column-parallel slabs differ from the unsharded product"
         assert slice_ok, "a K-slice quantized differently from the same columns of the full tensor"
         assert row_ok, f"row-parallel sum off by {err}"
+
+
+def test_slab_rows_partition_the_output_like_the_kernel():
+    """`slab_rows` mirrors the kernel's split (rows * rank // world): contiguous, complete,
+    non-overlapping, also when the world does not divide the rows."""
+    from sparkinfer_b200.parallel import slab_rows
+
+    for rows, world in [(4096, 2), (4096, 8), (203, 3), (5, 8), (0, 4)]:
+        edges = [slab_rows(rows, world, r) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+        assert all(b <= e for b, e in edges)
+    import pytest
+
+    with pytest.raises(ValueError):
+        slab_rows(16, 2, 2)
