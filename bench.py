@@ -41,9 +41,11 @@ sys.path.insert(0, str(ROOT))
 NOMINAL = {"hbm_gbs": 8000.0, "fp8_tflops": 4500.0, "fp4_tflops": 9000.0}
 DEFAULT_WORKLOAD = "cfg3_block_fp8_colpar"
 L2_FLUSH_BYTES = 256 << 20
-# Collective of the K-split (row-parallel) step on several GPUs: "peer" = this package's own
-# all-reduce kernel over NVLink peer memory, "nccl" = torch.distributed all_reduce.
-COLLECTIVE = os.environ.get("B12X_BENCH_COLLECTIVE", "peer")
+# Collective of the K-split (row-parallel) step on several GPUs: "fused" = the GEMM scatters its
+# output tiles to the slab owners over NVLink peer memory while it runs and this package's
+# reduction kernel adds and broadcasts the slabs; "peer" = plain GEMM, then this package's
+# all-reduce kernel over peer memory; "nccl" = plain GEMM, then torch.distributed all_reduce.
+COLLECTIVE = os.environ.get("B12X_BENCH_COLLECTIVE", "fused")
 
 # DRAM bytes (read + write) of ONE launch of each workload's GEMM kernel on one GPU at the full
 # size, from `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` captures of
@@ -231,6 +233,7 @@ class Step:
         x, wt = x_cpu.to(device), wt_cpu.to(device)
         del x_cpu, wt_cpu
         self.kernels_per_step = 1
+        self.reducer, self.collective = None, "none"
         self.h2d_bytes = self.d2h_bytes = 0
         self.group = 1          # consecutive steps captured together (HBM-bound workloads)
         self.replicas = replicas
@@ -281,6 +284,12 @@ class Step:
             self.gemms = [(lambda rhs=rhs: blockscaled.mm(lhs, rhs, self.out, **kw))
                           for rhs in rhs_list]
         self.gemm = lambda: [g() for g in self.gemms]
+        if self.reducer is not None and self.reducer.scatter:
+            from sparkinfer_b200 import _native
+
+            self.gemm = lambda: self.reducer.gemm(
+                _native.KIND_NVFP4, self.xq.packed_a_storage, self.xq.scale_storage,
+                wq.packed_a_storage, wq.scale_storage, self.alpha, kl)
         self.quant = (lambda: nvfp4.run(plan=self.xplan, x=self.x, global_scale=self.gs_x,
                                         outputs=self.xq)) if (self.w["quant"] and not self.fused) else None
         self.kernels_per_step = 2 if self.quant is not None else 1
@@ -326,18 +335,23 @@ class Step:
 
             self.collective = "nccl all_reduce"
             reducer, why = None, ""
-            if COLLECTIVE == "peer":
+            if COLLECTIVE in ("peer", "fused"):
+                scatter = COLLECTIVE == "fused" and m % (256 * self.world) == 0
                 try:
-                    reducer = PeerAllReduce(m, n, torch.bfloat16, device=self.device)
+                    reducer = PeerAllReduce(m, n, torch.bfloat16, device=self.device, scatter=scatter)
                 except Exception as exc:  # no symmetric memory on this box
                     why = f"{type(exc).__name__}: {str(exc)[:120]}"
             ok = torch.tensor([1 if reducer is not None else 0], device=self.device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if int(ok.item()) == 1:
                 self.reducer = reducer
-                self.collective = "b12x_b200_allreduce_peer (own kernel, NVLink peer memory)"
-                return reducer.partial.view(m, n, 1)
-            if COLLECTIVE == "peer":
+                self.collective = (
+                    "b12x_b200_gemm_blockscaled_scatter + b12x_b200_allreduce_peer_scattered "
+                    "(GEMM tiles scattered to slab owners over NVLink peer memory, own reduction kernel)"
+                    if reducer.scatter else
+                    "b12x_b200_allreduce_peer (own kernel, NVLink peer memory)")
+                return reducer.result.view(m, n, 1)
+            if COLLECTIVE in ("peer", "fused"):
                 self.collective += f" (peer memory unavailable: {why or 'on another rank'})"
         return torch.empty((m, n, 1), dtype=torch.bfloat16, device=self.device)
 

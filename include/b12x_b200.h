@@ -376,6 +376,36 @@ int b12x_b200_allreduce_peer(void* const* buffers, void* const* signals, int wor
                              int dtype, int64_t rows, int64_t cols, int64_t ld, int blocks,
                              int64_t max_polls, int* status, b12x_b200_stream_t stream);
 
+/*
+ * The two halves of the fused row-parallel step (no counterpart in the reference either).
+ *
+ * b12x_b200_gemm_blockscaled_scatter: the CTA-pair GEMM of b12x_b200_gemm_blockscaled whose
+ * output tiles are not written to one C but scattered by row slab: M is cut into `world` slabs
+ * of M / world rows (M must be a multiple of 256 * world); a tile in slab s is stored, while the
+ * main loop carries on with the next tile, into destinations[s] at rows
+ * rank * (M / world) + (row - s * (M / world)). destinations[s] is rank s's [M, ld] receive
+ * buffer as mapped in this process (peer memory for s != rank): when all ranks' GEMMs have
+ * finished, rank s holds every rank's partial of its slab, in slot order. BF16 or FP16; the
+ * optional workspace is that of b12x_b200_gemm_blockscaled_ex (split last round).
+ *
+ * b12x_b200_allreduce_peer_scattered: the reduction that follows. Rank s adds the `world` slots
+ * of its own receive buffer (buffers[s], local reads only) in FP32 in slot order, rounds once,
+ * and pushes the rows of slab s into outputs[t] of every rank t ([M, ld] result buffers, peer
+ * mapped). Flags, limits, status and the rehearsal mode (rank < 0) are those of
+ * b12x_b200_allreduce_peer; rows % world == 0. When the kernel has finished on a rank's stream,
+ * that rank's output holds the complete sum.
+ */
+int b12x_b200_gemm_blockscaled_scatter(int kind, const void* a, const void* sfa, const void* b,
+                                       const void* sfb, void* const* destinations, int world,
+                                       int rank, int c_dtype, const float* alpha, int64_t m,
+                                       int64_t n, int64_t k, int64_t ld, int sm_count,
+                                       void* workspace, int64_t workspace_bytes, int* status,
+                                       b12x_b200_stream_t stream);
+int b12x_b200_allreduce_peer_scattered(void* const* buffers, void* const* outputs,
+                                       void* const* signals, int world, int rank, int dtype,
+                                       int64_t rows, int64_t cols, int64_t ld, int blocks,
+                                       int64_t max_polls, int* status, b12x_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

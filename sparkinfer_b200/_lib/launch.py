@@ -374,31 +374,72 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
     _native.check(rc, "b12x_b200_quantize_nvfp4_rows")
 
 
+def gemm_blockscaled_scatter(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
+                             sfb: torch.Tensor, destination_ptrs: list[int], rank: int,
+                             dtype: torch.dtype, alpha: torch.Tensor | None, m: int, n: int, k: int,
+                             *, ld: int | None = None, sm_count: int = 0,
+                             stream_int: int | None = None) -> None:
+    """The CTA-pair GEMM with its output scattered by row slab over ``destination_ptrs`` (every
+    rank's ``[M, ld]`` receive buffer as mapped in this process): this rank's partial of slab
+    ``s`` lands in slot ``rank`` of destination ``s``. ``M % (256 * world) == 0``."""
+    for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb)):
+        _require_cuda(name, t)
+    dev = a.device
+    world = len(destination_ptrs)
+    lib = _native.load()
+    with torch.cuda.device(dev):
+        need = int(lib.b12x_b200_gemm_grouped_workspace_bytes(kind, 0, m, n, k, 1,
+                                                              _native.BLOCK_N_PAIR, sm_count))
+    work = stream_workspace(need, dev, stream_int) if need > 0 else None
+    dsts = (ctypes.c_void_p * world)(*destination_ptrs)
+    with torch.cuda.device(dev):
+        rc = lib.b12x_b200_gemm_blockscaled_scatter(
+            kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), dsts, world, rank,
+            _DTYPE_CODE[dtype], alpha.data_ptr() if alpha is not None else None, m, n, k,
+            ld if ld is not None else n, sm_count, work.data_ptr() if work is not None else None,
+            work.numel() if work is not None else 0, status_buffer(dev).data_ptr(),
+            _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_gemm_blockscaled_scatter")
+    _after_launch(dev)
+
+
 def allreduce_peer_signal_bytes() -> int:
     return int(_native.load().b12x_b200_allreduce_peer_signal_bytes())
 
 
 def allreduce_peer(buffer_ptrs: list[int], signal_ptrs: list[int], rank: int, dtype: torch.dtype,
                    rows: int, cols: int, ld: int, device: torch.device, *, blocks: int = 0,
-                   max_polls: int = 0, stream_int: int | None = None) -> None:
-    """Sum of all ranks' ``[rows, ld]`` partials over peer memory, in place in every rank's
-    buffer. ``buffer_ptrs`` / ``signal_ptrs``: every rank's buffer and signal block as mapped in
-    this process. ``rank = -1`` rehearses all ranks in one grid on ``device`` (tests)."""
+                   max_polls: int = 0, stream_int: int | None = None,
+                   output_ptrs: list[int] | None = None) -> None:
+    """Sum of all ranks' ``[rows, ld]`` partials over peer memory. ``buffer_ptrs`` /
+    ``signal_ptrs``: every rank's buffer and signal block as mapped in this process. Without
+    ``output_ptrs`` every rank's buffer holds its whole partial and receives the sum in place;
+    with them the buffers hold scattered partials (see :func:`gemm_blockscaled_scatter`) and the
+    sum goes to every rank's output. ``rank = -1`` rehearses all ranks in one grid on ``device``
+    (tests)."""
     world = len(buffer_ptrs)
-    if len(signal_ptrs) != world:
-        raise ValueError("one signal block per buffer")
+    if len(signal_ptrs) != world or (output_ptrs is not None and len(output_ptrs) != world):
+        raise ValueError("one signal block (and one output) per buffer")
     bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
     sigs = (ctypes.c_void_p * world)(*signal_ptrs)
+    tail = (world, rank, _DTYPE_CODE[dtype], rows, cols, ld, blocks, max_polls)
     with torch.cuda.device(device):
-        rc = _native.load().b12x_b200_allreduce_peer(
-            bufs, sigs, world, rank, _DTYPE_CODE[dtype], rows, cols, ld, blocks, max_polls,
-            status_buffer(device).data_ptr(), _stream_ptr(stream_int, device))
-    _native.check(rc, "b12x_b200_allreduce_peer")
+        if output_ptrs is None:
+            name = "b12x_b200_allreduce_peer"
+            rc = _native.load().b12x_b200_allreduce_peer(
+                bufs, sigs, *tail, status_buffer(device).data_ptr(), _stream_ptr(stream_int, device))
+        else:
+            name = "b12x_b200_allreduce_peer_scattered"
+            outs = (ctypes.c_void_p * world)(*output_ptrs)
+            rc = _native.load().b12x_b200_allreduce_peer_scattered(
+                bufs, outs, sigs, *tail, status_buffer(device).data_ptr(),
+                _stream_ptr(stream_int, device))
+    _native.check(rc, name)
     _after_launch(device)
 
 
 __all__ = [
-    "allreduce_peer", "allreduce_peer_signal_bytes", "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
+    "allreduce_peer", "allreduce_peer_signal_bytes", "gemm_blockscaled_scatter", "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
     "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
     "route_to_decode_kernel", "smallm_workspace", "stream_workspace", "quantize_mxfp8_rows",
     "quantize_nvfp4_rows",

@@ -99,6 +99,17 @@ SIGNATURES = {
     ),
     "b12x_b200_selftest_wait_timeout": (_c_int, [_c_void_p, _c_int, _c_void_p]),
     "b12x_b200_allreduce_peer_signal_bytes": (_c_i64, []),
+    "b12x_b200_gemm_blockscaled_scatter": (
+        _c_int,
+        [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+         _c_void_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_void_p, _c_i64, _c_void_p,
+         _c_void_p],
+    ),
+    "b12x_b200_allreduce_peer_scattered": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int,
+         _c_i64, _c_void_p, _c_void_p],
+    ),
     "b12x_b200_allreduce_peer": (
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_i64,

@@ -20,6 +20,12 @@
 // bounded: when it runs out the status word is raised, the data phase is skipped and the kernel
 // returns.
 //
+// SCATTERED variant (after a GEMM that scattered its output, see ScatterOut in
+// gemm_blockscaled_pair.cuh): every rank's partial of slab s already lies in rank s's own buffer,
+// in slot r = rows [r * slab, (r + 1) * slab). Rank s then reads only local memory, and pushes
+// the sum of its slab into a second buffer (`out`, rows [s * slab, (s + 1) * slab)) of every
+// rank: the pull half of the traffic has been hidden under the GEMM's main loop.
+//
 // rank < 0 selects the single-GPU rehearsal used by the tests: blockIdx.y is the rank and all
 // ranks run in one cooperative grid (kernels that wait on each other must not be separate
 // launches on one GPU).
@@ -44,6 +50,7 @@ constexpr int kSigWords = 32;
 
 struct PeerAllReduceParams {
   void* buf[kMaxPeers];      // rank r's [rows][ld] buffer as mapped in this process
+  void* out[kMaxPeers];      // SCATTERED: rank r's [rows][ld] result buffer as mapped here
   uint32_t* sig[kMaxPeers];  // rank r's signal block as mapped in this process
   int world;
   int rank;                  // this process's rank; < 0: blockIdx.y (single-GPU rehearsal)
@@ -107,7 +114,7 @@ __device__ __forceinline__ uint4 pack_sum(const float (&acc)[8]) {
 }
 
 // G: number of ranks when known at compile time (2, 4, 8), 0 for any other count.
-template <int G, bool BF16>
+template <int G, bool BF16, bool SCATTERED>
 __global__ void __launch_bounds__(512)
 allreduce_peer_kernel(const PeerAllReduceParams p) {
   constexpr int kUnroll = (G == 2) ? 4 : 2;
@@ -135,21 +142,25 @@ allreduce_peer_kernel(const PeerAllReduceParams p) {
     const long long nvec = (r1 - r0) * vec_per_row;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     const bool dense = (p.ld == p.cols);
+    const long long slab_elems = (p.rows / world) * p.ld;  // SCATTERED: rows % world == 0
     for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + t; base < nvec;
          base += stride * kUnroll) {
-      long long off[kUnroll];  // element offset of each vector inside a rank's buffer
+      long long off[kUnroll];  // element offset of each vector from the start of a slab
       uint4 v[kUnroll][G ? G : kMaxPeers];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         const long long i = base + u * stride;
         if (i < nvec) {
-          off[u] = dense ? (r0 * p.ld + i * 8)
-                         : ((r0 + i / vec_per_row) * p.ld + (i % vec_per_row) * 8);
+          off[u] = dense ? i * 8 : ((i / vec_per_row) * p.ld + (i % vec_per_row) * 8);
 #pragma unroll
           for (int r = 0; r < (G ? G : kMaxPeers); ++r) {
-            if (r < world)
-              v[u][r] = ld_peer_16(reinterpret_cast<const uint4*>(
-                  static_cast<const uint16_t*>(p.buf[r]) + off[u]));
+            if (r < world) {
+              // rank r's contribution: slot r of my own buffer, or my slab of rank r's buffer
+              const uint16_t* src = SCATTERED
+                                        ? static_cast<const uint16_t*>(p.buf[me]) + slab_elems * r
+                                        : static_cast<const uint16_t*>(p.buf[r]) + r0 * p.ld;
+              v[u][r] = ld_peer_16(reinterpret_cast<const uint4*>(src + off[u]));
+            }
           }
         }
       }
@@ -165,8 +176,10 @@ allreduce_peer_kernel(const PeerAllReduceParams p) {
           const uint4 out = pack_sum<BF16>(acc);
 #pragma unroll
           for (int r = 0; r < (G ? G : kMaxPeers); ++r) {
-            if (r < world)
-              st_peer_16(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.buf[r]) + off[u]), out);
+            if (r < world) {
+              uint16_t* dst = static_cast<uint16_t*>(SCATTERED ? p.out[r] : p.buf[r]) + r0 * p.ld;
+              st_peer_16(reinterpret_cast<uint4*>(dst + off[u]), out);
+            }
           }
         }
       }

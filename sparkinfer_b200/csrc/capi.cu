@@ -281,17 +281,18 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
 }
 
 // CTA-pair kernel: clusters of two CTAs, one 256 x BN tile per pair.
-template <int KIND, int BN, bool BIAS>
+template <int KIND, int BN, bool BIAS, bool SCATTER = false>
 int launch_gemm_pair_impl(const CUtensorMap& map_a, const CUtensorMap& map_b,
                           const CUtensorMap& map_c, const GemmParams& p, const PairTail& tail,
-                          int pairs, cudaStream_t stream) {
+                          int pairs, cudaStream_t stream,
+                          const ScatterOut<SCATTER>& sc = ScatterOut<SCATTER>{}) {
   using T = PairTile<KIND, BN>;
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err =
-        cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, BN, BIAS>,
+        cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, BN, BIAS, SCATTER>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
@@ -310,7 +311,8 @@ int launch_gemm_pair_impl(const CUtensorMap& map_a, const CUtensorMap& map_b,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t err =
-      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN, BIAS>, map_a, map_b, map_c, p, tail);
+      cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, BN, BIAS, SCATTER>, map_a, map_b,
+                         map_c, p, tail, sc);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_blockscaled_pair launch");
   return B12X_B200_OK;
 }
@@ -366,6 +368,13 @@ constexpr size_t kWorkspaceHeaderBytes = kPairCounterOffset + kPairCounterBytes;
 
 // Whether (and how) the CTA-pair kernel splits its last, partial round along K: `segments` per
 // leftover tile (0 = no split) and the scratch it needs.
+// Destinations of a row-parallel scatter (see ScatterOut in gemm_blockscaled_pair.cuh).
+struct ScatterPlan {
+  void* const* dst;
+  int world;
+  int rank;
+};
+
 struct PairTailPlan {
   int pairs = 0, left = 0, segments = 0;
   size_t bytes = 0;
@@ -412,7 +421,8 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
                           void* c, int c_dtype, const float* alpha, int64_t m, int64_t n, int64_t k,
                           int64_t ldc, int64_t groups, int block_n, int sm_count, void* workspace,
                           int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue,
-                          int* status, b12x_b200_stream_t stream) {
+                          int* status, b12x_b200_stream_t stream,
+                          const ScatterPlan* scatter = nullptr) {
   if (groups < 1 || groups > 65535)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be in [1, 65535]");
   if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
@@ -425,6 +435,22 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       block_n != 192 && block_n != 256)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT,
                 "block_n must be 0, 64, 128, 192, 256 or B12X_B200_BLOCK_N_PAIR");
+  if (scatter) {
+    if (scatter->world < 1 || scatter->world > kMaxScatter || scatter->rank < 0 ||
+        scatter->rank >= scatter->world || !scatter->dst)
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "scatter: world in [1, 8], rank inside it");
+    if (groups != 1 || epilogue || c_dtype == B12X_B200_FP32)
+      return fail(B12X_B200_ERR_UNSUPPORTED,
+                  "scatter: one group, no epilogue, BF16 or FP16 partials");
+    if (m % (int64_t(scatter->world) * 256) != 0)
+      return fail(B12X_B200_ERR_UNSUPPORTED, "scatter: M must be a multiple of 256 * world");
+    if ((ldc * 2) % 16 != 0) return fail(B12X_B200_ERR_ALIGNMENT, "scatter: ld must be a multiple of 8");
+    for (int r = 0; r < scatter->world; ++r)
+      if (!scatter->dst[r] || !aligned16(scatter->dst[r]))
+        return fail(B12X_B200_ERR_ALIGNMENT, "scatter: destinations must be 16-byte aligned");
+    block_n = B12X_B200_BLOCK_N_PAIR;
+    c = scatter->dst[scatter->rank];
+  }
   if (m == 0 || n == 0) return B12X_B200_OK;
   if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
@@ -514,6 +540,20 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       tail.partials =
           reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kWorkspaceHeaderBytes);
       tail.segments = tp.segments;
+    }
+    if (scatter) {
+      ScatterOut<true> sc;
+      memset(&sc, 0, sizeof(sc));
+      sc.slab_rows = int(m / scatter->world);
+      sc.rank = scatter->rank;
+      for (int r = 0; r < scatter->world; ++r) {
+        sc.base[r] = scatter->dst[r];
+        rc = make_output_map(&sc.map[r], scatter->dst[r], uint64_t(m), uint64_t(n), uint64_t(ldc), 1);
+        if (rc != B12X_B200_OK) return rc;
+      }
+      if (kind == B12X_B200_KIND_MXFP8)
+        return launch_gemm_pair_impl<kMxfp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
+      return launch_gemm_pair_impl<kNvfp4, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
     }
     if (kind == B12X_B200_KIND_MXFP8)
       return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
@@ -1261,29 +1301,89 @@ extern "C" int b12x_b200_selftest_wait_timeout(int* status, int max_polls,
 namespace b12x_b200 {
 namespace {
 
-template <int G, bool BF16>
+template <int G, bool BF16, bool SCATTERED>
 cudaError_t launch_allreduce_peer(const PeerAllReduceParams& p, int blocks, bool rehearsal,
                                   cudaStream_t stream) {
   if (!rehearsal) {
-    allreduce_peer_kernel<G, BF16><<<blocks, 512, 0, stream>>>(p);
+    allreduce_peer_kernel<G, BF16, SCATTERED><<<blocks, 512, 0, stream>>>(p);
     return cudaGetLastError();
   }
   // All ranks in one grid: its blocks wait on each other, so they must all be resident.
   PeerAllReduceParams copy = p;
   void* args[] = {&copy};
-  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&allreduce_peer_kernel<G, BF16>),
-                                     dim3(blocks, p.world), dim3(512), args, 0, stream);
+  return cudaLaunchCooperativeKernel(
+      reinterpret_cast<const void*>(&allreduce_peer_kernel<G, BF16, SCATTERED>),
+      dim3(blocks, p.world), dim3(512), args, 0, stream);
 }
 
-template <bool BF16>
+template <bool BF16, bool SCATTERED>
 cudaError_t launch_allreduce_peer_any(const PeerAllReduceParams& p, int blocks, bool rehearsal,
                                       cudaStream_t stream) {
   switch (p.world) {
-    case 2: return launch_allreduce_peer<2, BF16>(p, blocks, rehearsal, stream);
-    case 4: return launch_allreduce_peer<4, BF16>(p, blocks, rehearsal, stream);
-    case 8: return launch_allreduce_peer<8, BF16>(p, blocks, rehearsal, stream);
-    default: return launch_allreduce_peer<0, BF16>(p, blocks, rehearsal, stream);
+    case 2: return launch_allreduce_peer<2, BF16, SCATTERED>(p, blocks, rehearsal, stream);
+    case 4: return launch_allreduce_peer<4, BF16, SCATTERED>(p, blocks, rehearsal, stream);
+    case 8: return launch_allreduce_peer<8, BF16, SCATTERED>(p, blocks, rehearsal, stream);
+    default: return launch_allreduce_peer<0, BF16, SCATTERED>(p, blocks, rehearsal, stream);
   }
+}
+
+int allreduce_peer_impl(void* const* buffers, void* const* outputs, void* const* signals, int world,
+                        int rank, int dtype, int64_t rows, int64_t cols, int64_t ld, int blocks,
+                        int64_t max_polls, int* status, b12x_b200_stream_t stream) {
+  if (!buffers || !signals) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (world < 1 || world > kMaxPeers)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "world must be in [1, 8]");
+  if (rank >= world) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rank outside the world");
+  if (dtype != B12X_B200_BF16 && dtype != B12X_B200_FP16)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "all-reduce works on BF16 or FP16 partials");
+  if (rows < 0 || cols < 0 || ld < cols || cols % 8 != 0 || ld % 8 != 0)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "cols and ld must be multiples of 8 with ld >= cols");
+  if (outputs && rows % world != 0)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "scattered partials: rows must be a multiple of world");
+  if (max_polls < 0 || max_polls > (int64_t(1) << 31) - 1)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "max_polls outside [0, 2^31)");
+  for (int r = 0; r < world; ++r) {
+    if (!buffers[r] || !signals[r] || (outputs && !outputs[r]))
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(buffers[r]) & 15) || (reinterpret_cast<uintptr_t>(signals[r]) & 15) ||
+        (outputs && (reinterpret_cast<uintptr_t>(outputs[r]) & 15)))
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "buffers and signal blocks must be 16-byte aligned");
+  }
+  DeviceInfo info;
+  const int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  if (rows == 0 || cols == 0) return B12X_B200_OK;
+  if (world == 1 && !outputs) return B12X_B200_OK;  // one rank: the partial is the sum
+  const bool rehearsal = rank < 0;
+  if (blocks <= 0) blocks = rehearsal ? std::max(1, info.sm_count / (2 * world)) : 2 * info.sm_count;
+  if (rehearsal && int64_t(blocks) * world > int64_t(info.sm_count))
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rehearsal grid would not be resident at once");
+  PeerAllReduceParams p{};
+  for (int r = 0; r < world; ++r) {
+    p.buf[r] = buffers[r];
+    p.out[r] = outputs ? outputs[r] : nullptr;
+    p.sig[r] = static_cast<uint32_t*>(signals[r]);
+  }
+  p.world = world;
+  p.rank = rank;
+  p.rows = rows;
+  p.cols = cols;
+  p.ld = ld;
+  p.out_dtype = dtype == B12X_B200_BF16 ? kOutBf16 : kOutFp16;
+  p.max_polls = max_polls ? uint32_t(max_polls) : (1u << 21);
+  p.status = status;
+  const cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool bf = dtype == B12X_B200_BF16;
+  cudaError_t err;
+  if (outputs)
+    err = bf ? launch_allreduce_peer_any<true, true>(p, blocks, rehearsal, s)
+             : launch_allreduce_peer_any<false, true>(p, blocks, rehearsal, s);
+  else
+    err = bf ? launch_allreduce_peer_any<true, false>(p, blocks, rehearsal, s)
+             : launch_allreduce_peer_any<false, false>(p, blocks, rehearsal, s);
+  if (err != cudaSuccess) return fail_cuda(err, "all-reduce launch");
+  return B12X_B200_OK;
 }
 
 }  // namespace
@@ -1297,47 +1397,32 @@ extern "C" int b12x_b200_allreduce_peer(void* const* buffers, void* const* signa
                                         int rank, int dtype, int64_t rows, int64_t cols,
                                         int64_t ld, int blocks, int64_t max_polls, int* status,
                                         b12x_b200_stream_t stream) {
-  if (!buffers || !signals) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
-  if (world < 1 || world > kMaxPeers)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "world must be in [1, 8]");
-  if (rank >= world) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rank outside the world");
-  if (dtype != B12X_B200_BF16 && dtype != B12X_B200_FP16)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "all-reduce works on BF16 or FP16 partials");
-  if (rows < 0 || cols < 0 || ld < cols || cols % 8 != 0 || ld % 8 != 0)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "cols and ld must be multiples of 8 with ld >= cols");
-  if (max_polls < 0 || max_polls > (int64_t(1) << 31) - 1)
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "max_polls outside [0, 2^31)");
-  for (int r = 0; r < world; ++r) {
-    if (!buffers[r] || !signals[r]) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
-    if ((reinterpret_cast<uintptr_t>(buffers[r]) & 15) || (reinterpret_cast<uintptr_t>(signals[r]) & 15))
-      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "buffers and signal blocks must be 16-byte aligned");
-  }
-  DeviceInfo info;
-  const int rc = device_info(&info);
-  if (rc != B12X_B200_OK) return rc;
-  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
-  if (world == 1 || rows == 0 || cols == 0) return B12X_B200_OK;  // one rank: the partial is the sum
-  const bool rehearsal = rank < 0;
-  if (blocks <= 0) blocks = rehearsal ? std::max(1, info.sm_count / (2 * world)) : 2 * info.sm_count;
-  if (rehearsal && int64_t(blocks) * world > int64_t(info.sm_count))
-    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rehearsal grid would not be resident at once");
-  PeerAllReduceParams p{};
-  for (int r = 0; r < world; ++r) {
-    p.buf[r] = buffers[r];
-    p.sig[r] = static_cast<uint32_t*>(signals[r]);
-  }
-  p.world = world;
-  p.rank = rank;
-  p.rows = rows;
-  p.cols = cols;
-  p.ld = ld;
-  p.out_dtype = dtype == B12X_B200_BF16 ? kOutBf16 : kOutFp16;
-  p.max_polls = max_polls ? uint32_t(max_polls) : (1u << 21);
-  p.status = status;
-  const cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const cudaError_t err = dtype == B12X_B200_BF16
-                              ? launch_allreduce_peer_any<true>(p, blocks, rehearsal, s)
-                              : launch_allreduce_peer_any<false>(p, blocks, rehearsal, s);
-  if (err != cudaSuccess) return fail_cuda(err, "all-reduce launch");
-  return B12X_B200_OK;
+  return allreduce_peer_impl(buffers, nullptr, signals, world, rank, dtype, rows, cols, ld, blocks,
+                             max_polls, status, stream);
+}
+
+extern "C" int b12x_b200_allreduce_peer_scattered(void* const* buffers, void* const* outputs,
+                                                  void* const* signals, int world, int rank,
+                                                  int dtype, int64_t rows, int64_t cols,
+                                                  int64_t ld, int blocks, int64_t max_polls,
+                                                  int* status, b12x_b200_stream_t stream) {
+  if (!outputs) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  return allreduce_peer_impl(buffers, outputs, signals, world, rank, dtype, rows, cols, ld, blocks,
+                             max_polls, status, stream);
+}
+
+extern "C" int b12x_b200_gemm_blockscaled_scatter(int kind, const void* a, const void* sfa,
+                                                  const void* b, const void* sfb,
+                                                  void* const* destinations, int world, int rank,
+                                                  int c_dtype, const float* alpha, int64_t m,
+                                                  int64_t n, int64_t k, int64_t ld, int sm_count,
+                                                  void* workspace, int64_t workspace_bytes,
+                                                  int* status, b12x_b200_stream_t stream) {
+  ScatterPlan plan;
+  plan.dst = destinations;
+  plan.world = world;
+  plan.rank = rank;
+  return gemm_blockscaled_impl(kind, a, sfa, b, sfb, nullptr, c_dtype, alpha, m, n, k, ld, 1,
+                               B12X_B200_BLOCK_N_PAIR, sm_count, workspace, workspace_bytes,
+                               nullptr, status, stream, &plan);
 }

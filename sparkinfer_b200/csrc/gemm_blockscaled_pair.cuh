@@ -111,16 +111,35 @@ struct PairTail {
   int segments;  // S, or <= 1 when the tail is not split
 };
 
+// Row-parallel scatter of the output (SCATTER instantiation): the M rows are cut into `world`
+// slabs of `slab_rows` (a multiple of the 256-row pair tile); a tile whose rows lie in slab s is
+// stored into destination s, a [world * slab_rows][ld] buffer that may live on another GPU
+// (peer-mapped), at rows rank * slab_rows + (row - s * slab_rows): slot `rank` of the owner of
+// slab s, where that owner's reduction kernel expects this rank's partial.
+constexpr int kMaxScatter = 8;
+template <bool ON>
+struct ScatterOut {};
+template <>
+struct ScatterOut<true> {
+  CUtensorMap map[kMaxScatter];  // destination s as a [1][world * slab_rows][n] tensor
+  void* base[kMaxScatter];
+  int slab_rows;
+  int rank;
+};
+
 constexpr int kPairPartialFloats = 128 * 256;
 constexpr uint32_t kPairReducePolls = 1u << 20;
 
 // BIAS: the instantiation with the bias epilogue (the plain one carries none of its code).
-template <int KIND, int BN, bool BIAS>
+// SCATTER: the instantiation whose output tiles go to per-slab destinations (see ScatterOut).
+template <int KIND, int BN, bool BIAS, bool SCATTER = false>
 __global__ void __launch_bounds__(224, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                              const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_c, const GemmParams p,
-                             const PairTail tail) {
+                             const PairTail tail,
+                             const __grid_constant__ ScatterOut<SCATTER> sc) {
+  static_assert(!(BIAS && SCATTER), "the scattered output is a partial sum: no bias on it");
   using T = PairTile<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -366,6 +385,15 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row = m0 + row_in_tile;
       const uint32_t taddr = (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const uint32_t acc_empty_leader = map_to_cta(smem_addr_u32(&acc_empty_bar[acc]), 0);
+      // Where this CTA's 128 rows go: the caller's C, or (SCATTER) the slab owner's buffer.
+      void* c_base = p.c;
+      int dst = 0;          // destination index (SCATTER)
+      int row_shift = 0;    // destination row = row + row_shift (SCATTER)
+      if constexpr (SCATTER) {
+        dst = m0 / sc.slab_rows;
+        row_shift = (sc.rank - dst) * sc.slab_rows;
+        c_base = sc.base[dst];
+      }
       if (w.segments > 1) {
         // ---- segment of a leftover tile: FP32 partial to scratch, then the shared reduction ----
         const int s_count = w.segments;
@@ -464,12 +492,13 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o[j] = add_bias_1(o[j], p.bias, p.out_dtype, col + j, p.n);
               }
-              const size_t idx = static_cast<size_t>(grp) * p.c_group_elems +
-                                 static_cast<size_t>(row) * p.ldc + col;
+              const size_t idx = SCATTER ? static_cast<size_t>(row + row_shift) * p.ldc + col
+                                         : static_cast<size_t>(grp) * p.c_group_elems +
+                                               static_cast<size_t>(row) * p.ldc + col;
               if (p.out_dtype != kOutFp32 && col + 4 <= p.n &&
-                  ((reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(p.c) + idx) & 7) == 0)) {
+                  ((reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(c_base) + idx) & 7) == 0)) {
                 const bool bf = p.out_dtype == kOutBf16;
-                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.c) + idx) =
+                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(c_base) + idx) =
                     make_uint2(bf ? pack_bf16x2(o[0], o[1]) : pack_f16x2(o[0], o[1]),
                                bf ? pack_bf16x2(o[2], o[3]) : pack_f16x2(o[2], o[3]));
                 continue;
@@ -478,11 +507,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               for (int j = 0; j < 4; ++j) {
                 if (col + j < p.n) {
                   if (p.out_dtype == kOutBf16)
-                    static_cast<__nv_bfloat16*>(p.c)[idx + j] = __float2bfloat16_rn(o[j]);
+                    static_cast<__nv_bfloat16*>(c_base)[idx + j] = __float2bfloat16_rn(o[j]);
                   else if (p.out_dtype == kOutFp16)
-                    static_cast<__half*>(p.c)[idx + j] = __float2half_rn(o[j]);
+                    static_cast<__half*>(c_base)[idx + j] = __float2half_rn(o[j]);
                   else
-                    static_cast<float*>(p.c)[idx + j] = o[j];
+                    static_cast<float*>(c_base)[idx + j] = o[j];
                 }
               }
             }
@@ -556,7 +585,12 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             epilogue_bar_sync();
             if (store_thread) {
               const int col = tn * BN + pass * 128 + sub * 64;
-              if (col < p.n && m0 < p.m) tma_store_3d(&map_c, c_stage, col, m0, grp);
+              if (col < p.n && m0 < p.m) {
+                if constexpr (SCATTER)
+                  tma_store_3d(&sc.map[dst], c_stage, col, m0 + row_shift, 0);
+                else
+                  tma_store_3d(&map_c, c_stage, col, m0, grp);
+              }
               tma_store_commit();
             }
             store_pending = true;
@@ -591,13 +625,15 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(raw[i]) * alpha;
         if constexpr (BIAS) add_bias_32(vals, p.bias, p.out_dtype, tn * BN + c * 32, p.n);
-        store_row_chunk(p, grp, row, tn * BN + c * 32, vals);
+        if constexpr (!SCATTER) store_row_chunk(p, grp, row, tn * BN + c * 32, vals);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
     }
     if (p.use_tma_store && threadIdx.x == 64) tma_store_wait_all<0>();
+    // Stores that went to another GPU are fenced at system scope before the kernel ends.
+    if constexpr (SCATTER) __threadfence_system();
   }
 
   // Neither CTA may leave (or give back tensor memory) while the pair's tensor core can still

@@ -83,18 +83,27 @@ def slab_rows(rows: int, world_size: int, rank: int) -> tuple[int, int]:
 
 
 class PeerAllReduce:
-    """All-reduce of the row-parallel partial outputs by this package's own kernel over peer
-    memory (``b12x_b200_allreduce_peer``).
+    """All-reduce of the row-parallel partial outputs by this package's own kernels over peer
+    memory, in two forms.
 
-    Owns a ``[rows, cols]`` BF16/FP16 buffer in symmetric memory (every rank of the node maps
-    every other rank's buffer) and a small signal block. The GEMM writes its partial straight
-    into :attr:`partial`; calling the object sums the partials of all ranks in place: when the
-    call's kernel has finished on this rank's stream, :attr:`partial` holds the full sum,
-    bit-identical on every rank. Collective: every rank must construct it and call it the same
+    *Plain* (``scatter=False``): the GEMM writes its whole ``[rows, cols]`` partial into
+    :attr:`partial`; calling the object sums all ranks' partials in place
+    (``b12x_b200_allreduce_peer``: pull the own slab from every rank, add, push to every rank),
+    and :attr:`result` is :attr:`partial`.
+
+    *Fused with the GEMM* (``scatter=True``, ``rows % (256 * world) == 0``): :meth:`gemm` runs the
+    CTA-pair GEMM with its output tiles scattered to the owners of their row slabs while the
+    main loop runs (``b12x_b200_gemm_blockscaled_scatter``), so that the call only adds the
+    local slots and pushes the result slab (``b12x_b200_allreduce_peer_scattered``) into
+    :attr:`result`, a second buffer.
+
+    Buffers live in symmetric memory (every rank of the node maps every other rank's). When the
+    call's kernel has finished on this rank's stream, :attr:`result` holds the full sum,
+    bit-identical on every rank. Collective: every rank constructs it and calls it the same
     number of times. One rank per GPU."""
 
     def __init__(self, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, group=None,
-                 device: torch.device | None = None):
+                 device: torch.device | None = None, scatter: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
 
         from ._lib import launch
@@ -111,27 +120,49 @@ class PeerAllReduce:
         self.rank = dist.get_rank(group)
         if self.world_size > 8:
             raise ValueError("at most 8 ranks (one NVLink node)")
+        if scatter and rows % (256 * self.world_size) != 0:
+            raise ValueError(f"scatter needs rows={rows} to be a multiple of 256 * world")
+        self.scatter = bool(scatter)
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.rows, self.cols, self.dtype = int(rows), int(cols), dtype
         self.partial = symm_mem.empty((self.rows, self.cols), dtype=dtype, device=self.device)
         self._signal = symm_mem.empty((launch.allreduce_peer_signal_bytes() // 4,),
                                       dtype=torch.int32, device=self.device)
         self._signal.zero_()
-        self._handles = (symm_mem.rendezvous(self.partial, group),
-                         symm_mem.rendezvous(self._signal, group))
+        self._handles = [symm_mem.rendezvous(self.partial, group),
+                         symm_mem.rendezvous(self._signal, group)]
         self.buffer_ptrs = [int(p) for p in self._handles[0].buffer_ptrs]
         self.signal_ptrs = [int(p) for p in self._handles[1].buffer_ptrs]
+        self.result = self.partial
+        self.output_ptrs = None
+        if self.scatter:
+            self.result = symm_mem.empty((self.rows, self.cols), dtype=dtype, device=self.device)
+            self._handles.append(symm_mem.rendezvous(self.result, group))
+            self.output_ptrs = [int(p) for p in self._handles[2].buffer_ptrs]
         # Every rank's signal block is zero before any rank can send a flag into it.
         torch.cuda.synchronize(self.device)
         dist.barrier(group)
+
+    def gemm(self, kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
+             sfb: torch.Tensor, alpha: torch.Tensor | None, k: int,
+             stream: object | None = None) -> None:
+        """This rank's partial GEMM ``[rows, K_local] x [cols, K_local]^T`` with the output
+        scattered to the slab owners (``scatter=True`` only)."""
+        from ._lib import launch
+
+        if not self.scatter:
+            raise RuntimeError("gemm() belongs to the scatter form; write into .partial instead")
+        launch.gemm_blockscaled_scatter(kind, a, sfa, b, sfb, self.buffer_ptrs, self.rank,
+                                        self.dtype, alpha, self.rows, self.cols, k,
+                                        stream_int=launch.cuda_stream_to_int(stream))
 
     def __call__(self, stream: object | None = None) -> torch.Tensor:
         from ._lib import launch
 
         launch.allreduce_peer(self.buffer_ptrs, self.signal_ptrs, self.rank, self.dtype, self.rows,
-                              self.cols, self.cols, self.device,
+                              self.cols, self.cols, self.device, output_ptrs=self.output_ptrs,
                               stream_int=launch.cuda_stream_to_int(stream))
-        return self.partial
+        return self.result
 
 
 def gather_columns(slab: torch.Tensor, group=None) -> torch.Tensor:

@@ -127,3 +127,68 @@ def test_a_peer_that_never_arrives_ends_in_a_status_word_not_a_hang():
         launch.check_kernel_status(DEV)
     assert bool((bufs[0] == 1).all()) and bool((bufs[1] == 2).all())   # nothing was summed
     launch.check_kernel_status(DEV)
+
+
+# --------------------------------------------------------------------------------------
+# The fused form: GEMM output scattered to the slab owners, then the scattered reduction
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind,world,m,n,k_local", [
+    ("nvfp4", 2, 512, 512, 512), ("mxfp8", 2, 1024, 768, 256), ("nvfp4", 4, 1024, 520, 384),
+    ("mxfp8", 8, 2048, 256, 128),
+    ("nvfp4", 2, 2048, 2560, 2048),      # 80 pair tiles on 74 pairs: the split last round scatters too
+])
+def test_scattered_gemm_then_reduction_equals_the_sum_of_plain_partials(kind, world, m, n, k_local):
+    """Each "rank" multiplies its K slice (separate launches that do not wait on each other:
+    every receive buffer is local here). Slot r of receive buffer s must equal rows of slab s of
+    rank r's plain partial bit for bit, the reduced output must equal the rank-ordered FP32 sum
+    rounded once, and that sum must meet the GEMM's error bound against the FP32
+    dequantize-matmul over the whole K."""
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import BLOCK_N_PAIR, KIND_MXFP8, KIND_NVFP4
+    from test_gemm_fuzz_gpu import _operand
+
+    code = KIND_MXFP8 if kind == "mxfp8" else KIND_NVFP4
+    gen = torch.Generator(device=DEV).manual_seed(500 + world + m)
+    alpha = torch.tensor([0.5], dtype=torch.float32, device=DEV)
+    slab = m // world
+    recv = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    outs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    partials, ref = [], torch.zeros((m, n), dtype=torch.float32, device=DEV)
+    for r in range(world):
+        a, sfa, a_deq = _operand(kind, m, k_local, gen, DEV)
+        b, sfb, b_deq = _operand(kind, n, k_local, gen, DEV)
+        ref += 0.5 * (a_deq @ b_deq.T)
+        plain = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        launch.gemm_blockscaled(code, a, sfa, b, sfb, plain, alpha, m, n, k_local, block_n=BLOCK_N_PAIR)
+        launch.gemm_blockscaled_scatter(code, a, sfa, b, sfb, [t.data_ptr() for t in recv], r,
+                                        torch.bfloat16, alpha, m, n, k_local)
+        partials.append(plain)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(DEV)
+    for s in range(world):
+        for r in range(world):
+            got = recv[s][r * slab:(r + 1) * slab]
+            want = partials[r][s * slab:(s + 1) * slab]
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (s, r)
+    launch.allreduce_peer([t.data_ptr() for t in recv], [t.data_ptr() for t in _signals(world)], -1,
+                          torch.bfloat16, m, n, n, DEV, output_ptrs=[t.data_ptr() for t in outs])
+    torch.cuda.synchronize()
+    launch.check_kernel_status(DEV)
+    want = _expected(partials, n)
+    for t in outs:
+        assert torch.equal(t.view(torch.int16), want.view(torch.int16))
+    scale = float(ref.abs().max())
+    err = float((outs[0].float() - ref).abs().max())
+    assert err <= (world * 2.0 ** -8 + 2.0 ** -16) * scale, (err, scale)
+
+
+def test_scatter_refuses_shapes_it_cannot_cut_into_whole_tiles():
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import KIND_MXFP8
+
+    z = torch.zeros(1 << 20, dtype=torch.uint8, device=DEV)
+    dst = [z.data_ptr(), z.data_ptr()]
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        launch.gemm_blockscaled_scatter(KIND_MXFP8, z, z, z, z, dst, 0, torch.bfloat16, None, 384, 256, 128)
+    with pytest.raises(RuntimeError, match="BF16 or FP16"):
+        launch.gemm_blockscaled_scatter(KIND_MXFP8, z, z, z, z, dst, 0, torch.float32, None, 512, 256, 128)
