@@ -68,6 +68,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Data accesses at system scope (plain .cg accesses measured the same over NVLink).
 __device__ __forceinline__ uint4 ld_peer_16(const uint4* p) {
   uint4 v;
   asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"

@@ -546,6 +546,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       memset(&sc, 0, sizeof(sc));
       sc.slab_rows = int(m / scatter->world);
       sc.rank = scatter->rank;
+      sc.world = scatter->world;
       for (int r = 0; r < scatter->world; ++r) {
         sc.base[r] = scatter->dst[r];
         rc = make_output_map(&sc.map[r], scatter->dst[r], uint64_t(m), uint64_t(n), uint64_t(ldc), 1);
@@ -1356,7 +1357,9 @@ int allreduce_peer_impl(void* const* buffers, void* const* outputs, void* const*
   if (rows == 0 || cols == 0) return B12X_B200_OK;
   if (world == 1 && !outputs) return B12X_B200_OK;  // one rank: the partial is the sum
   const bool rehearsal = rank < 0;
-  if (blocks <= 0) blocks = rehearsal ? std::max(1, info.sm_count / (2 * world)) : 2 * info.sm_count;
+  // One block of 512 threads per SM measured best on two GPUs (74: 72 us, 148: 70, 296: 71,
+  // 592: 80 for a 58.7 MB matrix).
+  if (blocks <= 0) blocks = rehearsal ? std::max(1, info.sm_count / (2 * world)) : info.sm_count;
   if (rehearsal && int64_t(blocks) * world > int64_t(info.sm_count))
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "rehearsal grid would not be resident at once");
   PeerAllReduceParams p{};

@@ -125,7 +125,19 @@ struct ScatterOut<true> {
   void* base[kMaxScatter];
   int slab_rows;
   int rank;
+  int world;
 };
+
+// The scheduler's consecutive tile rows alternate between the slabs (row i of the schedule is
+// tile row (i % world) * tiles_m / world + i / world), so that at any moment the tiles being
+// finished are spread over all destinations instead of all going to one peer: a round of 74
+// pair tiles stores 9.5 MB at once, and with every tile of a round bound for the same GPU that
+// burst waited for the link (two GPUs: 133 us, against 124 us once spread and 107 us for the
+// plain GEMM). Dealing the rows out by twos, so that a pair's own consecutive tiles alternate
+// between destinations as well, measured the same as this simple form.
+__device__ __forceinline__ int scatter_tile_row(int tm, int tiles_m, int world) {
+  return (tm % world) * (tiles_m / world) + tm / world;
+}
 
 constexpr int kPairPartialFloats = 128 * 256;
 constexpr uint32_t kPairReducePolls = 1u << 20;
@@ -207,6 +219,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       int tm, tn, grp, local;
       split_group(w.tile, tiles_per_group, grp, local);
       tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      if constexpr (SCATTER) tm = scatter_tile_row(tm, p.tiles_m, sc.world);
       const int m0 = tm * 256 + static_cast<int>(rank) * 128;
       const int n0 = tn * BN;
       for (int kt = w.kt_begin; kt < w.kt_end; ++kt) {
@@ -240,6 +253,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       int tm, tn, grp, local;
       split_group(w.tile, tiles_per_group, grp, local);
       tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      if constexpr (SCATTER) tm = scatter_tile_row(tm, p.tiles_m, sc.world);
       const int n0 = tn * BN;
       const int sfa_atom = tm * 2 + static_cast<int>(rank);
       const bool sfa_ok = sfa_atom < m_row_atoms;
@@ -372,6 +386,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       int tm, tn, grp, local;
       split_group(w.tile, tiles_per_group, grp, local);
       tile_coords(local, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      if constexpr (SCATTER) tm = scatter_tile_row(tm, p.tiles_m, sc.world);
       const int acc = iter % T::kAccStages;
       const uint32_t acc_phase = (iter / T::kAccStages) & 1;
       if (!epilogue_bar_and(mbar_wait_bounded_cluster(&acc_full_bar[acc], acc_phase, abort_flag))) {
