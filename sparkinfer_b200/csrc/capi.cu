@@ -286,7 +286,7 @@ int launch_gemm_pair_impl(const CUtensorMap& map_a, const CUtensorMap& map_b,
                           const CUtensorMap& map_c, const GemmParams& p, const PairTail& tail,
                           int pairs, cudaStream_t stream,
                           const ScatterOut<SCATTER>& sc = ScatterOut<SCATTER>{}) {
-  using T = PairTile<KIND, BN>;
+  using T = PairTile<KIND, BN, SCATTER ? 2 : 1>;
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
   int dev = 0;
   cudaGetDevice(&dev);
@@ -549,8 +549,6 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       sc.world = scatter->world;
       for (int r = 0; r < scatter->world; ++r) {
         sc.base[r] = scatter->dst[r];
-        rc = make_output_map(&sc.map[r], scatter->dst[r], uint64_t(m), uint64_t(n), uint64_t(ldc), 1);
-        if (rc != B12X_B200_OK) return rc;
       }
       if (kind == B12X_B200_KIND_MXFP8)
         return launch_gemm_pair_impl<kMxfp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);

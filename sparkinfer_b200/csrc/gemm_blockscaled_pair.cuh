@@ -36,7 +36,9 @@
 
 namespace b12x_b200 {
 
-template <int KIND, int BN>
+// CSLOTS: 16 KiB output staging slots (one 64-column sub-tile each). The ordinary kernels use
+// one; the scatter kernel alternates between two.
+template <int KIND, int BN, int CSLOTS = 1>
 struct PairTile {
   static_assert(BN == 128 || BN == 256, "pair tiles are 128 or 256 columns wide");
   static constexpr int BM = 128;                               // rows per CTA (256 per pair)
@@ -57,7 +59,9 @@ struct PairTile {
   static constexpr int kAccStages = (2 * BN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
   static constexpr int kSfaCol0 = kAccStages * BN;
   static constexpr int kSfbCol0 = kSfaCol0 + kSfaCols;
-  static constexpr int kCStageBytes = 128 * 64 * 2;          // one 64-column output sub-tile
+  static constexpr int kCSlots = CSLOTS;
+  static constexpr int kCSlotBytes = 128 * 64 * 2;           // one 64-column output sub-tile
+  static constexpr int kCStageBytes = CSLOTS * kCSlotBytes;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kStagesRaw =
       (227 * 1024 - kBarrierBytes - 1024 - kCStageBytes) / kStageBytes;
@@ -121,8 +125,7 @@ template <bool ON>
 struct ScatterOut {};
 template <>
 struct ScatterOut<true> {
-  CUtensorMap map[kMaxScatter];  // destination s as a [1][world * slab_rows][n] tensor
-  void* base[kMaxScatter];
+  void* base[kMaxScatter];       // destination s: a [world * slab_rows][ld] buffer
   int slab_rows;
   int rank;
   int world;
@@ -152,7 +155,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                              const PairTail tail,
                              const __grid_constant__ ScatterOut<SCATTER> sc) {
   static_assert(!(BIAS && SCATTER), "the scattered output is a partial sum: no bias on it");
-  using T = PairTile<KIND, BN>;
+  using T = PairTile<KIND, BN, SCATTER ? 2 : 1>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -582,6 +585,40 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         // for the previous store to have read the slot are off the critical path, and the small
         // slot leaves room for one more pipeline stage.
         auto stage_and_store = [&](int pass) {
+          if constexpr (SCATTER) {
+            // Scattered tiles may cross NVLink. The 128 epilogue threads stage the pass's 128
+            // columns (256-byte rows; 16-byte piece q of row r at position q ^ (r % 8)) in the
+            // 32 KiB slot and copy it out with ordinary 16-byte stores, two whole 256-byte rows
+            // per warp instruction. Measured on 4 GPUs (4096 x 7168 x 4608 per rank, 44 MB of it
+            // bound for peers): 104-107 us whichever way the tiles leave (TMA stores of 64-column
+            // sub-tiles through one or four slots, ordinary stores of 128- or 256-byte row
+            // pieces), against 78 us with every destination local: the kernel is bound by what
+            // the links carry in a many-to-many pattern (0.45-0.5 TB/s per GPU, the rate NCCL's
+            // all-reduce reaches there too), not by how the stores are issued.
+            static_assert(T::kCSlots == 2, "the scatter epilogue stages 128 columns at a time");
+            epilogue_bar_sync();  // everyone has finished reading the previous pass
+            uint8_t* row_ptr = c_stage + row_in_tile * 256;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const int j = q ^ (row_in_tile & 7);
+              *reinterpret_cast<uint4*>(row_ptr + j * 16) = make_uint4(
+                  packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+            }
+            epilogue_bar_sync();
+            const int col0 = tn * BN + pass * 128;
+            uint16_t* out_rows = static_cast<uint16_t*>(c_base) +
+                                 static_cast<size_t>(m0 + row_shift) * p.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int idx = i * 128 + row_in_tile;   // 128 rows x 16 pieces of 16 bytes
+              const int r = idx >> 4;
+              const int j = idx & 15;
+              const uint4 v = *reinterpret_cast<const uint4*>(c_stage + r * 256 + ((j ^ (r & 7)) * 16));
+              if (m0 + r < p.m && col0 + j * 8 + 8 <= p.n)
+                st_global_v4_sys(out_rows + static_cast<size_t>(r) * p.ldc + j * 8, v);
+            }
+            return;
+          }
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub) {
             if (store_pending) {
@@ -600,12 +637,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             epilogue_bar_sync();
             if (store_thread) {
               const int col = tn * BN + pass * 128 + sub * 64;
-              if (col < p.n && m0 < p.m) {
-                if constexpr (SCATTER)
-                  tma_store_3d(&sc.map[dst], c_stage, col, m0 + row_shift, 0);
-                else
-                  tma_store_3d(&map_c, c_stage, col, m0, grp);
-              }
+              if (col < p.n && m0 < p.m) tma_store_3d(&map_c, c_stage, col, m0, grp);
               tma_store_commit();
             }
             store_pending = true;
