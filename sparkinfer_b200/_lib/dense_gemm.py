@@ -214,6 +214,39 @@ def _select_default_mma_tiler_mn(m: int, n: int, sm_count: int) -> Tuple[int, in
 _UNIT_SCALE_CACHE: dict = {}
 
 
+def _plain_fp8_launch(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor],
+                      alpha: Optional[torch.Tensor], *, m: int, n: int, k: int, l: int,
+                      c_dtype: str, mma_tiler_mn, sm_count: int, stream) -> torch.Tensor:
+    """``dense_gemm(plain_fp8=True)`` on the tiled kernels: E4M3 x E4M3 with FP32 accumulation
+    and ``alpha`` as the only scale (b12x/_lib/dense_gemm.py:7140-7189 in the reference)."""
+    _check_operand("A", a, m, k, l)
+    _check_operand("B", b, n, k, l)
+    if out is None:
+        out = _empty_dense_gemm_output(m, n, l, dtype=_C_DTYPES[c_dtype], device=a.device)
+    elif out.dtype != _C_DTYPES[c_dtype]:
+        raise ValueError(f"out dtype {out.dtype} does not match c_dtype={c_dtype!r}")
+    if tuple(out.shape) != (m, n, l):
+        raise ValueError(f"out must have shape {(m, n, l)}, got {tuple(out.shape)}")
+    if out.stride(1) != 1 or (l > 1 and out.stride(2) != m * n) or (m > 1 and out.stride(0) < n):
+        raise ValueError(f"out must be backed by physical [L, M, N] storage, got strides {out.stride()}")
+    if alpha is not None and (alpha.dtype != torch.float32 or alpha.numel() != 1):
+        raise ValueError("alpha must be a float32 tensor with one element")
+    if m == 0 or n == 0:
+        return out
+    block_n = 0
+    if mma_tiler_mn is not None:
+        tile_m, tile_n = int(mma_tiler_mn[0]), int(mma_tiler_mn[1])
+        block_n = _native.BLOCK_N_PAIR if (tile_m, tile_n) == (256, 256) else (
+            tile_n if tile_n in _KERNEL_BLOCK_N else 0)
+    ldc = out.stride(0) if m > 1 else n
+    if l > 1 and ldc != n:
+        raise ValueError("a grouped output must be dense [L, M, N] storage")
+    launch.gemm_blockscaled(_native.KIND_FP8, a, None, b, None, out, alpha, m, n, k, ldc=ldc,
+                            block_n=block_n, sm_count=sm_count,
+                            stream_int=cuda_stream_to_int(stream), groups=l)
+    return out
+
+
 def _unit_mxfp8_scales(device: torch.device, rows: int, k: int, groups: int) -> torch.Tensor:
     """Cached MMA-layout scale view with every UE8M0 byte at 127 (2^0), for plain FP8."""
     from .mxfp8_rows import pack_mxfp8_scales_for_dense_gemm
@@ -308,7 +341,16 @@ def dense_gemm(
         # the one real scale as alpha (dense_gemm.py:7137-7139 in the reference).
         raise ValueError("plain_fp8 requires float8_e4m3fn operands with float8_e8m0fnu/32 scales")
     if plain_fp8:
-        # The caller's scale storage is not read in this mode: every block scale is 2^0.
+        # The caller's scale storage is not read in this mode. Shapes of the tiled kernels run
+        # the unscaled FP8 MMA (no scale bytes move at all); decode shapes stay on the
+        # weight-streaming kernel, which is written for block scales, with every scale 2^0
+        # (1/32 of the weight bytes on top).
+        forced = mma_tiler_mn is not None and int(mma_tiler_mn[1]) in _KERNEL_BLOCK_N
+        if _quantized_c is None and (forced or not launch.route_to_decode_kernel(
+                m, n, a_torch.device, int(sm_count))):
+            return _plain_fp8_launch(a_torch, b_torch, out, alpha, m=m, n=n, k=k, l=l,
+                                     c_dtype=c_dtype, mma_tiler_mn=mma_tiler_mn,
+                                     sm_count=int(sm_count), stream=stream)
         sfa_torch = _unit_mxfp8_scales(a_torch.device, m, k, l)
         sfb_torch = _unit_mxfp8_scales(a_torch.device, n, k, l)
     _kind_of(ab_dtype, sf_dtype, sf_vec_size)

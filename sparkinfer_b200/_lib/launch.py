@@ -220,8 +220,8 @@ def _epilogue(c: torch.Tensor, n: int, bias: torch.Tensor | None,
     return ep
 
 
-def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
-                     sfb: torch.Tensor, c: torch.Tensor, alpha: torch.Tensor | None,
+def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor | None, b: torch.Tensor,
+                     sfb: torch.Tensor | None, c: torch.Tensor, alpha: torch.Tensor | None,
                      m: int, n: int, k: int, *, ldc: int | None = None, block_n: int = 0,
                      sm_count: int = 0, stream_int: int | None = None,
                      small_m: bool | None = None, bias: torch.Tensor | None = None,
@@ -235,12 +235,17 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     Decode shapes (see :func:`route_to_decode_kernel`; never when a tile width is forced, always
     with ``small_m=True``) go to the weight-streaming stream-K kernel, everything else to the
     persistent tiled kernels; ``block_n=_native.BLOCK_N_PAIR`` forces the CTA-pair kernel."""
-    for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb), ("c", c)):
+    plain = kind == _native.KIND_FP8      # no block scales: sfa / sfb are not read
+    for name, t in (("a", a), ("b", b), ("c", c)) + (() if plain else (("sfa", sfa), ("sfb", sfb))):
         _require_cuda(name, t)
     if c.dtype not in _DTYPE_CODE:
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = a.device
     ep = _epilogue(c, n, bias, quantized_c)
+    if plain:
+        if small_m or quantized_c is not None:
+            raise ValueError("the unscaled FP8 recipe runs on the tiled kernels only")
+        small_m = False
     if small_m is None:
         small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and (
             quantized_c is not None or route_to_decode_kernel(m, n, dev, sm_count))
@@ -257,7 +262,8 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Ten
     common_tail = (work.data_ptr() if work is not None else None,
                    work.numel() if work is not None else 0,
                    ctypes.byref(ep) if ep is not None else None)
-    head = (kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+    head = (kind, a.data_ptr(), None if plain else sfa.data_ptr(), b.data_ptr(),
+            None if plain else sfb.data_ptr(), c.data_ptr(),
             _DTYPE_CODE[c.dtype], alpha.data_ptr() if alpha is not None else None,
             m, n, k, ldc if ldc is not None else n, groups)
     with torch.cuda.device(dev):

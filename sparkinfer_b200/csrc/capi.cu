@@ -387,7 +387,7 @@ PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int64_t g
   if (t.pairs < 1 || !switches().pair_tail_split) return t;
   const int64_t rounds = tiles / t.pairs;
   t.left = int(tiles - rounds * t.pairs);
-  const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
+  const int elems_per_stage = (kind == B12X_B200_KIND_NVFP4) ? 256 : 128;
   const int64_t k_tiles = (k + elems_per_stage - 1) / elems_per_stage;
   // Split only when the leftover tiles would keep at most a tenth of the pairs busy, and never
   // below two k-tiles per segment. The split round is not free: it ends when the slowest pair
@@ -425,8 +425,9 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
                           const ScatterPlan* scatter = nullptr) {
   if (groups < 1 || groups > 65535)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be in [1, 65535]");
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4)
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
+  const bool scaled = kind != B12X_B200_KIND_FP8;
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
   if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
@@ -452,17 +453,18 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
     c = scatter->dst[scatter->rank];
   }
   if (m == 0 || n == 0) return B12X_B200_OK;
-  if (!a || !b || !sfa || !sfb || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (!a || !b || !c || (scaled && (!sfa || !sfb)))
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
   if (ldc < n) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "ldc < n");
   {
     const int erc = check_epilogue(epilogue, c_dtype, n, false);
     if (erc != B12X_B200_OK) return erc;
   }
-  const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
+  const int sf_vec = (kind == B12X_B200_KIND_NVFP4) ? 16 : 32;
   if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
-  const int64_t row_bytes = (kind == B12X_B200_KIND_MXFP8) ? k : k / 2;
+  const int64_t row_bytes = (kind == B12X_B200_KIND_NVFP4) ? k / 2 : k;
   if (row_bytes % 16 != 0) return fail(B12X_B200_ERR_ALIGNMENT, "operand rows must be 16-byte multiples");
-  if (!aligned16(a) || !aligned16(b) || !aligned16(sfa) || !aligned16(sfb))
+  if (!aligned16(a) || !aligned16(b) || (scaled && (!aligned16(sfa) || !aligned16(sfb))))
     return fail(B12X_B200_ERR_ALIGNMENT, "operand and scale pointers must be 16-byte aligned");
 
   DeviceInfo info;
@@ -501,7 +503,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   p.out_dtype = c_dtype;
   p.tiles_m = int((m + 127) / 128);
   p.tiles_n = int((n + bn - 1) / bn);
-  p.k_atoms_total = int((k + sf_vec * 4 - 1) / (sf_vec * 4));
+  p.k_atoms_total = scaled ? int((k + sf_vec * 4 - 1) / (sf_vec * 4)) : 0;
   p.group_m = 16;
   p.bias = epilogue ? epilogue->bias : nullptr;
   p.groups = int(groups);
@@ -552,14 +554,20 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       }
       if (kind == B12X_B200_KIND_MXFP8)
         return launch_gemm_pair_impl<kMxfp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
+      if (kind == B12X_B200_KIND_FP8)
+        return launch_gemm_pair_impl<kFp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
       return launch_gemm_pair_impl<kNvfp4, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
     }
     if (kind == B12X_B200_KIND_MXFP8)
       return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
+    if (kind == B12X_B200_KIND_FP8)
+      return launch_gemm_pair<kFp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
     return launch_gemm_pair<kNvfp4, 256>(map_a, map_b, map_c, p, tail, pairs, s);
   }
   if (kind == B12X_B200_KIND_MXFP8)
     return dispatch_block_n<kMxfp8>(bn, map_a, map_b, map_c, p, grid, s);
+  if (kind == B12X_B200_KIND_FP8)
+    return dispatch_block_n<kFp8>(bn, map_a, map_b, map_c, p, grid, s);
   return dispatch_block_n<kNvfp4>(bn, map_a, map_b, map_c, p, grid, s);
 }
 
@@ -602,7 +610,8 @@ namespace {
 
 int64_t tiled_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k, int64_t groups,
                               int block_n, int sm_count) {
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8)
+    return -1;
   if (m <= 0 || n <= 0 || k <= 0 || groups < 1) return 0;
   DeviceInfo info;
   if (device_info(&info) != B12X_B200_OK) return -1;

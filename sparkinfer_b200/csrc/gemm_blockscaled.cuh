@@ -5,6 +5,9 @@
 // A and B are K-major. Two operand recipes share one kernel template:
 //   kMxfp8 : E4M3 codes, one UE8M0 scale per 32 elements of K  (tcgen05 kind::mxf8f6f4)
 //   kNvfp4 : packed E2M1 codes (low nibble = even k), one UE4M3 scale per 16 elements
+//   kFp8   : E4M3 codes without block scales (tcgen05 kind::f8f6f4); alpha is the only scale.
+//            No scale bytes are loaded or copied to tensor memory, and the columns they would
+//            take hold a second accumulator instead.
 //            (tcgen05 kind::mxf4nvf4, scale_vec::4X)
 // Scale factors live in global memory as 512-byte atoms covering 128 rows x 4 scale columns,
 // atom order [row_tile][k_tile], byte (r%32)*16 + ((r/32)%4)*4 + (kb%4) inside an atom. That is
@@ -25,7 +28,7 @@
 
 namespace b12x_b200 {
 
-enum OperandKind : int { kMxfp8 = 0, kNvfp4 = 1 };
+enum OperandKind : int { kMxfp8 = 0, kNvfp4 = 1, kFp8 = 2 };
 enum OutDtype : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
 
 template <int KIND, int BN>
@@ -36,11 +39,13 @@ struct GemmTile {
   static constexpr int BM = 128;
   static constexpr int kRowBytes = 128;                       // bytes of K per stage and row
   static constexpr int kMmasPerStage = 4;                     // 32 bytes of K per instruction
-  static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
+  static constexpr bool kScaled = (KIND != kFp8);
+  static constexpr int kElemsPerMma = (KIND == kNvfp4) ? 64 : 32;
   static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
-  static constexpr int kSfVec = (KIND == kMxfp8) ? 32 : 16;
+  static constexpr int kSfVec = (KIND == kNvfp4) ? 16 : 32;
   static constexpr int kElemsPerAtom = kSfVec * 4;            // K covered by one scale atom
-  static constexpr int kKAtoms = kElemsPerStage / kElemsPerAtom;  // 1 (MXFP8) or 4 (NVFP4)
+  // scale atoms per stage: 1 (MXFP8), 4 (NVFP4), none (plain FP8)
+  static constexpr int kKAtoms = kScaled ? kElemsPerStage / kElemsPerAtom : 0;
   // Row atoms of SFB a tile can touch: tiles that are not multiples of 128 start inside an atom.
   static constexpr int kSfbRowAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
   static constexpr int kABytes = BM * kRowBytes;
@@ -315,15 +320,18 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
           const int katom0 = kt * T::kKAtoms;
           const int katoms = min(T::kKAtoms, p.k_atoms_total - katom0);
           const uint32_t sf_bytes = static_cast<uint32_t>(katoms) * 512u;
-          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes + sf_bytes * (1 + sfb_atoms));
+          mbar_arrive_expect_tx(bar, T::kABytes + T::kBBytes +
+                                         (T::kScaled ? sf_bytes * (1 + sfb_atoms) : 0u));
           tma_load_3d(st, &map_a, bar, kt * T::kRowBytes, m0, grp);
           tma_load_3d(st + T::kABytes, &map_b, bar, kt * T::kRowBytes, n0, grp);
-          bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
-                    sf_bytes, bar);
-          for (int ra = 0; ra < sfb_atoms; ++ra)
-            bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
-                      sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
+          if constexpr (T::kScaled) {
+            bulk_load(st + T::kABytes + T::kBBytes, sfa_src + static_cast<size_t>(katom0) * 512,
                       sf_bytes, bar);
+            for (int ra = 0; ra < sfb_atoms; ++ra)
+              bulk_load(st + T::kABytes + T::kBBytes + T::kSfaBytes + ra * T::kKAtoms * 512,
+                        sfb_src + (static_cast<size_t>(ra) * p.k_atoms_total + katom0) * 512,
+                        sf_bytes, bar);
+          }
         }
         __syncwarp();
         if (++stage == p.num_stages) { stage = 0; phase ^= 1; }
@@ -331,8 +339,10 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    constexpr uint32_t idesc_base = make_idesc_block_scaled(
-        128, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    constexpr uint32_t idesc_base =
+        KIND == kFp8 ? make_idesc_f8(128, BN)
+                     : make_idesc_block_scaled(128, BN, KIND == kMxfp8 ? 0u : 1u,
+                                               KIND == kMxfp8 ? 1u : 0u);
     int stage = 0;
     uint32_t phase = 0;
     int iter = 0;
@@ -366,7 +376,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
         if (elect_one()) {
           // Scale atoms of this stage -> TMEM. Every atom slot of the stage is copied; slots the
           // producer did not fill (edge of N or K) only feed masked columns or skipped MMAs.
-          {
+          if constexpr (T::kScaled) {
             const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
 #pragma unroll
             for (int ka = 0; ka < T::kKAtoms; ++ka) {
@@ -385,7 +395,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
               for (int j = 0; j < T::kMmasPerStage; ++j) {
                 const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
-                if (KIND == kMxfp8)
+                if constexpr (KIND == kFp8)
+                  tc_mma_f8(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate);
+                else if (KIND == kMxfp8)
                   tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                               idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                               sfb_taddr);
@@ -396,7 +408,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
             } else {
               for (int j = 0; j < mmas; ++j) {
                 const uint32_t accumulate = (kt > 0 || j > 0) ? 1u : 0u;
-                if (KIND == kMxfp8)
+                if constexpr (KIND == kFp8)
+                  tc_mma_f8(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate);
+                else if (KIND == kMxfp8)
                   tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                               idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                               sfb_taddr);

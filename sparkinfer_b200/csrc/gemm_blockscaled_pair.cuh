@@ -44,9 +44,10 @@ struct PairTile {
   static constexpr int BM = 128;                               // rows per CTA (256 per pair)
   static constexpr int kRowBytes = 128;
   static constexpr int kMmasPerStage = 4;
-  static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
+  static constexpr bool kScaled = (KIND != kFp8);
+  static constexpr int kElemsPerMma = (KIND == kNvfp4) ? 64 : 32;
   static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
-  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : 4;
+  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : (KIND == kNvfp4 ? 4 : 0);
   static constexpr int kSfbRowAtoms = BN / 128;
   static constexpr int kABytes = BM * kRowBytes;
   static constexpr int kBBytes = (BN / 2) * kRowBytes;         // this CTA's half of B
@@ -175,7 +176,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::kStages; ++s) {
-      mbar_init(&full_bar[s], 2);  // operand producer + scale producer
+      mbar_init(&full_bar[s], T::kScaled ? 2 : 1);  // operand producer (+ scale producer)
       mbar_init(&peer_full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -244,6 +245,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++stage == T::kStages) { stage = 0; phase ^= 1; }
       }
     }
+  } else if (warp == 6 && !T::kScaled) {
+    // plain FP8: there are no scale factors to bring in
   } else if (warp == 6) {
     // ------------------------- scale-factor producer (both CTAs) -------------------------
     // A second producer warp so that the five copies of a stage are issued by two warps in
@@ -314,8 +317,10 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA) ------------------------------
-    constexpr uint32_t idesc_base = make_idesc_block_scaled(
-        256, BN, KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+    constexpr uint32_t idesc_base =
+        KIND == kFp8 ? make_idesc_f8(256, BN)
+                     : make_idesc_block_scaled(256, BN, KIND == kMxfp8 ? 0u : 1u,
+                                               KIND == kMxfp8 ? 1u : 0u);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -344,20 +349,24 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const int mmas = min(T::kMmasPerStage,
                              (p.k - kt * T::kElemsPerStage + T::kElemsPerMma - 1) / T::kElemsPerMma);
         if (elect_one()) {
-          const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
+          if constexpr (T::kScaled) {
+            const uint64_t sf_desc = make_sf_chunk_desc(st + T::kABytes + T::kBBytes);
 #pragma unroll
-          for (int ka = 0; ka < T::kKAtoms; ++ka) {
-            tc_copy_sf_atom_pair(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
+            for (int ka = 0; ka < T::kKAtoms; ++ka) {
+              tc_copy_sf_atom_pair(T::kSfaCol0 + ka * 4, sf_desc + ((ka * 512) >> 4));
 #pragma unroll
-            for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
-              tc_copy_sf_atom_pair(T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
-                                   sf_desc + ((T::kSfaBytes + (ra * T::kKAtoms + ka) * 512) >> 4));
+              for (int ra = 0; ra < T::kSfbRowAtoms; ++ra)
+                tc_copy_sf_atom_pair(T::kSfbCol0 + ka * T::kSfbRowAtoms * 4 + ra * 4,
+                                     sf_desc + ((T::kSfaBytes + (ra * T::kKAtoms + ka) * 512) >> 4));
+            }
           }
           const uint64_t adesc = make_kmajor_sw128_desc(st);
           const uint64_t bdesc = make_kmajor_sw128_desc(st + T::kABytes);
           for (int j = 0; j < mmas; ++j) {
             const uint32_t accumulate = (kt > w.kt_begin || j > 0) ? 1u : 0u;
-            if (KIND == kMxfp8)
+            if constexpr (KIND == kFp8)
+              tc_mma_f8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate);
+            else if (KIND == kMxfp8)
               tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                                idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                                T::kSfbCol0);

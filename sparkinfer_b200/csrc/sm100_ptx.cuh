@@ -442,6 +442,19 @@ __device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t d_taddr, uint64_t ades
       : "memory");
 }
 
+// Unscaled E4M3 x E4M3 over the pair (256 rows), K = 32 per instruction.
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
                                                  uint32_t idesc, uint32_t accumulate,
                                                  uint32_t sfa_taddr, uint32_t sfb_taddr) {

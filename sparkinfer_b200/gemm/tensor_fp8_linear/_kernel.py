@@ -2,8 +2,9 @@
 ``output_scale * (x_e4m3 @ W_e4m3^T) (+ bias)``.
 
 Both operands arrive already in E4M3, so there is nothing to quantize: a call is one GEMM with
-``alpha = output_scale``. The GEMM is the MXFP8 kernel fed with block scales of exactly 1.0
-(UE8M0 byte 127) on both sides, taken from a per-device, per-shape cache: as in the reference
+``alpha = output_scale``. Shapes of the tiled kernels run the unscaled E4M3 MMA (no scale bytes
+move); decode shapes run the weight-streaming MXFP8 kernel fed with block scales of exactly 1.0
+(UE8M0 byte 127) on both sides, taken from a per-device, per-shape cache. As in the reference
 (``plain_fp8``), the scale storage a packed weight carries is never read.
 """
 
@@ -109,10 +110,18 @@ def _forward(source_2d: torch.Tensor, weight_values: torch.Tensor, weight_scale_
     out = torch.empty((tokens, out_features), dtype=out_dtype, device=source_2d.device)
     del weight_scale_mma  # plain FP8: every block scale is 1.0 whatever the weight carries
     device = source_2d.device
-    launch.gemm_blockscaled(
-        _native.KIND_MXFP8, codes, _cached_unit_atoms(tokens, padded_in, device).view(torch.uint8),
-        weight_values, _cached_unit_atoms(out_features, padded_in, device).view(torch.uint8), out,
-        output_scale, tokens, out_features, padded_in, stream_int=stream_int, bias=bias)
+    if launch.route_to_decode_kernel(tokens, out_features, device, 0):
+        # Decode shapes: the weight-streaming kernel, which is written for block scales, fed
+        # with cached scales of exactly 1.0 on both sides.
+        launch.gemm_blockscaled(
+            _native.KIND_MXFP8, codes, _cached_unit_atoms(tokens, padded_in, device).view(torch.uint8),
+            weight_values, _cached_unit_atoms(out_features, padded_in, device).view(torch.uint8), out,
+            output_scale, tokens, out_features, padded_in, stream_int=stream_int, bias=bias)
+    else:
+        # Everything else: the unscaled E4M3 MMA, no scale bytes at all.
+        launch.gemm_blockscaled(_native.KIND_FP8, codes, None, weight_values, None, out,
+                                output_scale, tokens, out_features, padded_in,
+                                stream_int=stream_int, bias=bias)
     return out
 
 

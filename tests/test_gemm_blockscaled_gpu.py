@@ -70,6 +70,36 @@ def test_mm_mxfp8_matches_oracle(m, n, k, c_dtype, tile_n):
     assert_gemm_close(out[:, :, 0], a_deq @ b_deq.T, out_dtype=out.dtype)
 
 
+@pytest.mark.parametrize("m,n,k,tile", [
+    (16, 512, 512, None),           # decode kernel, unit block scales
+    (256, 512, 384, None),          # tiled kernel, unscaled E4M3 MMA
+    (300, 504, 640, (128, 192)), (1024, 2048, 1024, (256, 256)),
+    (2048, 2560, 2048, None),       # CTA-pair kernel
+])
+def test_mm_plain_fp8_ignores_the_scale_tensors(m, n, k, tile):
+    """dense_gemm(plain_fp8=True): E4M3 codes times alpha, whatever the scale storage holds
+    (here: bytes that would scale by 2^-127 if they were read)."""
+    from gpu_util import DEV
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200.gemm import blockscaled
+
+    gen = torch.Generator(device=DEV).manual_seed(m + n + k)
+    a = (torch.randint(0, 256, (m, k), dtype=torch.uint8, device=DEV, generator=gen) & 0xBF)
+    b = (torch.randint(0, 256, (n, k), dtype=torch.uint8, device=DEV, generator=gen) & 0xBF)
+    zeros_a = torch.zeros((-(-m // 128)) * (-(-k // 128)) * 512, dtype=torch.uint8, device=DEV)
+    zeros_b = torch.zeros((-(-n // 128)) * (-(-k // 128)) * 512, dtype=torch.uint8, device=DEV)
+    sfa = layout.convert_sf_to_mma_layout(zeros_a, m, k, 1, 32).view(torch.float8_e8m0fnu)
+    sfb = layout.convert_sf_to_mma_layout(zeros_b, n, k, 1, 32).view(torch.float8_e8m0fnu)
+    alpha = torch.tensor([0.25], dtype=torch.float32, device=DEV)
+    out = blockscaled.mm((a.view(torch.float8_e4m3fn).view(m, k, 1), sfa),
+                         (b.view(torch.float8_e4m3fn).view(n, k, 1), sfb), alpha=alpha,
+                         c_dtype="bfloat16", plain_fp8=True, mma_tiler_mn=tile, **MXFP8)
+    torch.cuda.synchronize()
+    ref = 0.25 * (a.view(torch.float8_e4m3fn).float() @ b.view(torch.float8_e4m3fn).float().T)
+    err = float((out[:, :, 0].float() - ref).abs().max())
+    assert err <= (2.0 ** -8 + 2.0 ** -16) * float(ref.abs().max()), err
+
+
 def test_mm_nvfp4_matches_reference_fixture():
     """Operands and FP32 result produced by the reference's own torch code."""
     from gpu_util import assert_gemm_close, nvfp4_operand

@@ -178,3 +178,69 @@ def test_cta_pair_split_tail_matches_fp32_reference(kind, m, n, k, dtype):
     torch.cuda.synchronize()
     assert float((unsplit.float() - ref).abs().max()) <= (eps + 2.0 ** -16) * scale
     assert float((unsplit.float() - outs[0].float()).abs().max()) <= 2 * eps * scale + 1e-30
+
+
+# --------------------------------------------------------------------------------------
+# The unscaled FP8 recipe (dense_gemm(plain_fp8=True) on the tiled kernels): E4M3 x E4M3,
+# alpha the only scale, no scale tensors at all
+# --------------------------------------------------------------------------------------
+def _plain_fp8_cases():
+    rng = np.random.default_rng(4242)
+    cases = []
+    for i in range(20):
+        m = int(rng.choice([65, 128, 129, 255, 256, 300, 512, 777, 1024]))
+        n = int(rng.choice([64, 128, 200, 256, 384, 640, 1152, 2048]))
+        k = 32 * int(rng.integers(1, 40))
+        if k % 16:
+            k += 16
+        route = str(rng.choice(["auto", "bn64", "bn128", "bn192", "bn256", "pair"]))
+        dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
+        cases.append((i, m, n, k, route, dtype, bool(rng.integers(0, 2))))
+    cases.append((20, 2048, 2560, 2048, "auto", torch.bfloat16, False))   # pair kernel, split last round
+    cases.append((21, 4096, 4096, 4096, "auto", torch.bfloat16, True))    # several rounds, two accumulators
+    return cases
+
+
+@pytest.mark.parametrize("index,m,n,k,route,dtype,with_bias", _plain_fp8_cases())
+def test_plain_fp8_matches_fp32_reference(index, m, n, k, route, dtype, with_bias):
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import BLOCK_N_PAIR, KIND_FP8
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(9000 + index)
+    a = torch.randint(0, 256, (m, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    b = torch.randint(0, 256, (n, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    a_deq, b_deq = a.view(torch.float8_e4m3fn).float(), b.view(torch.float8_e4m3fn).float()
+    alpha = torch.tensor([0.375], dtype=torch.float32, device=dev)
+    bias = None
+    if with_bias and dtype != torch.float32:
+        bias = torch.randn(n, device=dev, generator=gen).to(dtype)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=dev)
+    kwargs = {}
+    if route.startswith("bn"):
+        kwargs["block_n"] = int(route[2:])
+    elif route == "pair":
+        kwargs["block_n"] = BLOCK_N_PAIR
+    launch.gemm_blockscaled(KIND_FP8, a, None, b, None, out, alpha, m, n, k, bias=bias, **kwargs)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(dev)
+    ref = 0.375 * (a_deq @ b_deq.T)
+    if bias is not None:
+        ref = (ref.to(dtype).float() + bias.float())
+    got = out.float()
+    assert not torch.isnan(got).any()
+    scale = float(ref.abs().max())
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -20}[dtype]
+    err = float((got - ref).abs().max())
+    assert err <= ((2 if bias is not None else 1) * eps + 2.0 ** -16) * scale + 1e-30, (err, scale)
+
+
+def test_plain_fp8_refuses_the_decode_kernel():
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import KIND_FP8
+
+    dev = torch.device("cuda:0")
+    z = torch.zeros((64, 128), dtype=torch.uint8, device=dev)
+    out = torch.empty((8, 64), dtype=torch.bfloat16, device=dev)
+    with pytest.raises(ValueError, match="tiled kernels only"):
+        launch.gemm_blockscaled(KIND_FP8, z, None, z, None, out, None, 8, 64, 128, small_m=True)
