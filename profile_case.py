@@ -29,7 +29,7 @@ from sparkinfer_b200 import _native  # noqa: E402
 from sparkinfer_b200._lib import launch  # noqa: E402
 
 OPS = ("mxfp8", "nvfp4", "pair_mxfp8", "pair_nvfp4", "decode_nvfp4", "decode_mxfp8",
-       "fused_nvfp4", "fused_mxfp8", "block_fp8", "quant_mxfp8", "quant_nvfp4")
+       "fused_nvfp4", "fused_mxfp8", "fp8", "pair_fp8", "block_fp8", "quant_mxfp8", "quant_nvfp4")
 
 
 def build_case(op: str, m: int, n: int, k: int, device: torch.device):
@@ -69,6 +69,12 @@ def build_case(op: str, m: int, n: int, k: int, device: torch.device):
         block_n = _native.BLOCK_N_PAIR if op.startswith("pair") else 0
         return lambda: launch.gemm_blockscaled(kind, a, sfa, b, sfb, c, None, m, n, k,
                                                block_n=block_n, small_m=small)
+    if op in ("fp8", "pair_fp8"):
+        a, b = codes((m, k)), codes((n, k))
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        block_n = _native.BLOCK_N_PAIR if op.startswith("pair") else 0
+        return lambda: launch.gemm_blockscaled(_native.KIND_FP8, a, None, b, None, c, None, m, n, k,
+                                               block_n=block_n)
     if op == "block_fp8":
         a, b = codes((m, k)), codes((n, k))
         sa = torch.rand((m, k // 128), device=device, generator=g) + 0.5

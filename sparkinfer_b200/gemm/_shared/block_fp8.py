@@ -16,7 +16,7 @@ import logging
 import os
 import time
 from collections.abc import Mapping
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Iterable, Sequence
 
 import torch
@@ -68,6 +68,10 @@ class BlockFP8LinearBinding:
     output: torch.Tensor
     bias: torch.Tensor | None = None
     expected_m: int | None = None
+    # Set by build_block_fp8_linear_binding, which has validated every tensor against the
+    # packed weight: a bound run then goes straight to the two launches. A binding made by
+    # hand (this constructor) is validated on every run.
+    prechecked_rows: SourceRows | None = field(default=None, repr=False, compare=False)
 
     def run(self, *, stream: object = None) -> torch.Tensor:
         return block_fp8_linear_mxfp8(binding=self, stream=stream)
@@ -114,9 +118,12 @@ def build_block_fp8_linear_binding(*, source: torch.Tensor, packed_weight: Block
                                    expected_m: int | None = None) -> BlockFP8LinearBinding:
     if not isinstance(packed_weight, BlockFP8LinearWeight):
         raise TypeError("packed_weight must be a BlockFP8LinearWeight")
-    _check_bound_tensors(x_q, output, _source_rows(source, packed_weight), packed_weight)
+    rows = _source_rows(source, packed_weight)
+    _check_bound_tensors(x_q, output, rows, packed_weight)
+    on_gpu = isinstance(source, torch.Tensor) and source.is_cuda
     return BlockFP8LinearBinding(source=source, packed_weight=packed_weight, x_q=x_q,
-                                 output=output, bias=bias, expected_m=expected_m)
+                                 output=output, bias=bias, expected_m=expected_m,
+                                 prechecked_rows=rows if on_gpu else None)
 
 
 @dataclass(frozen=True)
@@ -267,6 +274,16 @@ def block_fp8_linear_mxfp8(source: torch.Tensor | None = None,
                 f"do not also pass {', '.join(clashing)}")
         source, packed_weight, bias = binding.source, binding.packed_weight, binding.bias
         expected_m = binding.expected_m
+        rows = binding.prechecked_rows
+        if rows is not None and rows.rows.data_ptr() == source.data_ptr():
+            # Validated when it was built and frozen since: quantize, multiply, done.
+            output = quantize_then_gemm(rows.rows, packed_weight.weight.values,
+                                        packed_weight.weight.scale_mma,
+                                        padded_k=packed_weight.in_features,
+                                        out_features=packed_weight.out_features, x_q=binding.x_q,
+                                        out=binding.output, bias=bias, stream=stream,
+                                        bias_in_place=True)
+            return rows.restore(output, packed_weight.out_features)
     if source is None or packed_weight is None:
         raise TypeError("block_fp8_linear_mxfp8 requires source and packed_weight or binding")
     _check_gpu_tensor("source", source)
