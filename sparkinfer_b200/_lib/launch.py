@@ -380,15 +380,16 @@ def quantize_nvfp4_rows(src: torch.Tensor, global_scale: torch.Tensor, packed: t
     _native.check(rc, "b12x_b200_quantize_nvfp4_rows")
 
 
-def gemm_blockscaled_scatter(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor,
-                             sfb: torch.Tensor, destination_ptrs: list[int], rank: int,
+def gemm_blockscaled_scatter(kind: int, a: torch.Tensor, sfa: torch.Tensor | None, b: torch.Tensor,
+                             sfb: torch.Tensor | None, destination_ptrs: list[int], rank: int,
                              dtype: torch.dtype, alpha: torch.Tensor | None, m: int, n: int, k: int,
                              *, ld: int | None = None, sm_count: int = 0,
                              stream_int: int | None = None) -> None:
     """The CTA-pair GEMM with its output scattered by row slab over ``destination_ptrs`` (every
     rank's ``[M, ld]`` receive buffer as mapped in this process): this rank's partial of slab
     ``s`` lands in slot ``rank`` of destination ``s``. ``M % (256 * world) == 0``."""
-    for name, t in (("a", a), ("b", b), ("sfa", sfa), ("sfb", sfb)):
+    plain = kind == _native.KIND_FP8
+    for name, t in (("a", a), ("b", b)) + (() if plain else (("sfa", sfa), ("sfb", sfb))):
         _require_cuda(name, t)
     dev = a.device
     world = len(destination_ptrs)
@@ -400,7 +401,8 @@ def gemm_blockscaled_scatter(kind: int, a: torch.Tensor, sfa: torch.Tensor, b: t
     dsts = (ctypes.c_void_p * world)(*destination_ptrs)
     with torch.cuda.device(dev):
         rc = lib.b12x_b200_gemm_blockscaled_scatter(
-            kind, a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), dsts, world, rank,
+            kind, a.data_ptr(), None if plain else sfa.data_ptr(), b.data_ptr(),
+            None if plain else sfb.data_ptr(), dsts, world, rank,
             _DTYPE_CODE[dtype], alpha.data_ptr() if alpha is not None else None, m, n, k,
             ld if ld is not None else n, sm_count, work.data_ptr() if work is not None else None,
             work.numel() if work is not None else 0, status_buffer(dev).data_ptr(),
