@@ -411,6 +411,24 @@ int b12x_b200_allreduce_peer_scattered(void* const* buffers, void* const* output
                                        int64_t rows, int64_t cols, int64_t ld, int blocks,
                                        int64_t max_polls, int* status, b12x_b200_stream_t stream);
 
+/*
+ * Load-time conversion of a block-scaled FP8 checkpoint weight (E4M3 codes [groups, M, K], one
+ * FP32 scale per 128 x 128 block, [groups, ceil(M/128), K/128]) into the MXFP8 rows the GEMM
+ * reads. Replaces pack_fp8_block_scaled_weight_mxfp8 and its helpers
+ * (b12x/gemm/_shared/wo_mxfp8.py:873-1187), byte for byte:
+ *   requantize != 0: v = code * scale in FP32, block amax, byte = 127 + clamp(ceil(log2(amax /
+ *     448)), -127, 127) (127 for an all-zero block), new code = E4M3(v / 2^(byte - 127));
+ *   requantize == 0 (every scale already a power of two): codes are copied, byte is the
+ *     scale's exponent.
+ * out_codes [groups, M, K]; scale_rows (optional) [groups, M, K/32] row-major bytes; scale_mma
+ * (optional) the 512-byte atoms [groups][ceil(M/128)][K/128], rows beyond M set to 127.
+ * K % 128 == 0. In place (out_codes == codes) is allowed.
+ */
+int b12x_b200_pack_block_fp8_weight_mxfp8(const void* codes, const float* scale, void* out_codes,
+                                          void* scale_rows, void* scale_mma, int64_t m, int64_t k,
+                                          int64_t groups, int requantize,
+                                          b12x_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

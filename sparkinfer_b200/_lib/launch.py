@@ -411,6 +411,26 @@ def gemm_blockscaled_scatter(kind: int, a: torch.Tensor, sfa: torch.Tensor | Non
     _after_launch(dev)
 
 
+def pack_block_fp8_weight_mxfp8(codes: torch.Tensor, scale: torch.Tensor, out_codes: torch.Tensor,
+                                scale_rows: torch.Tensor | None, scale_mma: torch.Tensor | None,
+                                m: int, k: int, groups: int, requantize: bool, *,
+                                stream_int: int | None = None) -> None:
+    """Block-scaled FP8 checkpoint weight ``[groups, M, K]`` + FP32 128x128 block scales ->
+    MXFP8 codes, row-major UE8M0 bytes and scale atoms (one launch, load time)."""
+    for name, t in (("codes", codes), ("scale", scale), ("out_codes", out_codes)):
+        _require_cuda(name, t)
+    if scale.dtype != torch.float32 or not scale.is_contiguous():
+        raise ValueError("block scales must be contiguous float32")
+    dev = codes.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_pack_block_fp8_weight_mxfp8(
+            codes.data_ptr(), scale.data_ptr(), out_codes.data_ptr(),
+            scale_rows.data_ptr() if scale_rows is not None else None,
+            scale_mma.data_ptr() if scale_mma is not None else None, m, k, groups,
+            1 if requantize else 0, _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_pack_block_fp8_weight_mxfp8")
+
+
 def allreduce_peer_signal_bytes() -> int:
     return int(_native.load().b12x_b200_allreduce_peer_signal_bytes())
 
@@ -447,7 +467,7 @@ def allreduce_peer(buffer_ptrs: list[int], signal_ptrs: list[int], rank: int, dt
 
 
 __all__ = [
-    "allreduce_peer", "allreduce_peer_signal_bytes", "gemm_blockscaled_scatter", "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
+    "allreduce_peer", "allreduce_peer_signal_bytes", "pack_block_fp8_weight_mxfp8", "gemm_blockscaled_scatter", "cuda_stream_to_int", "status_buffer", "check_kernel_status", "gemm_blockscaled", "QuantizedC",
     "gemm_block_fp8", "gemm_smallm_fused_quant", "gemm_smallm_timeline", "selftest_wait_timeout",
     "route_to_decode_kernel", "smallm_workspace", "stream_workspace", "quantize_mxfp8_rows",
     "quantize_nvfp4_rows",

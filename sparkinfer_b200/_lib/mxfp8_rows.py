@@ -300,6 +300,10 @@ def pack_fp8_block_scaled_weight_mxfp8(weight: torch.Tensor, scale: torch.Tensor
     if min(m, k, num_groups) <= 0:
         raise ValueError("m, k, and num_groups must be positive")
     _check_mxfp8_k(k)
+    if weight.is_cuda:
+        return _pack_block_fp8_weight_on_device(weight, scale, m=m, k=k, num_groups=num_groups)
+    # Host tensors (only reachable with the device check lifted, as the CPU tests do): the same
+    # arithmetic in torch ops, which is what pins the kernel's bytes.
     if not _scale_is_exact_ue8m0(scale):
         _check_gpu_tensor("scale", scale)
         weight, scale = _requantize_block_fp8_to_ue8m0(weight, scale, m=m, k=k, num_groups=num_groups)
@@ -315,6 +319,35 @@ def pack_fp8_block_scaled_weight_mxfp8(weight: torch.Tensor, scale: torch.Tensor
     return MXFP8Rows(values=values, scale_rows=scale_rows,
                      scale_mma=pack_mxfp8_scales_for_dense_gemm(scale_rows, m=m, k=k,
                                                                 num_groups=num_groups))
+
+
+def _pack_block_fp8_weight_on_device(weight: torch.Tensor, scale: torch.Tensor, *, m: int, k: int,
+                                     num_groups: int) -> MXFP8Rows:
+    """The conversion above as one kernel launch (``b12x_b200_pack_block_fp8_weight_mxfp8``)."""
+    from . import launch
+
+    row_tiles, k_blocks = _ceil_div(m, 128), k // 128
+    if scale.numel() != num_groups * row_tiles * k_blocks:
+        raise ValueError(f"block scale must have shape {(num_groups * row_tiles, k_blocks)}; "
+                         f"got {tuple(scale.shape)}")
+    requantize = not _scale_is_exact_ue8m0(scale)
+    if requantize:
+        _check_gpu_tensor("scale", scale)
+    if scale.dtype in (torch.uint8, torch.float8_e8m0fnu):
+        block_scale = torch.exp2(scale.view(torch.uint8).to(torch.float32) - 127.0)
+    elif scale.is_floating_point():
+        block_scale = scale.to(torch.float32)
+    else:
+        raise ValueError(f"scale must be e8m0, uint8, or floating-point, got {scale.dtype}")
+    block_scale = block_scale.to(weight.device).reshape(num_groups, row_tiles, k_blocks).contiguous()
+    codes = _groups_first(weight, m=m, k=k, num_groups=num_groups).contiguous()
+    out = empty_mxfp8_rows_for_dense_gemm(m, k, num_groups=num_groups, device=weight.device)
+    # The packed values come back in the layout the torch path produces: [M, K] for one group,
+    # the [M, K, L] view over [L, M, K] storage otherwise.
+    values_storage = out.values if num_groups == 1 else out.values.permute(2, 0, 1)
+    launch.pack_block_fp8_weight_mxfp8(codes.view(torch.uint8), block_scale, values_storage,
+                                       out.scale_rows, out.scale_mma, m, k, num_groups, requantize)
+    return out
 
 
 def dequantize_mxfp8_rows_torch(values: torch.Tensor, scale_rows: torch.Tensor) -> torch.Tensor:

@@ -16,6 +16,7 @@
 #include "gemm_smallm.cuh"
 #include "quantize.cuh"
 #include "allreduce_peer.cuh"
+#include "pack_weight.cuh"
 
 namespace b12x_b200 {
 namespace {
@@ -1435,4 +1436,41 @@ extern "C" int b12x_b200_gemm_blockscaled_scatter(int kind, const void* a, const
   return gemm_blockscaled_impl(kind, a, sfa, b, sfb, nullptr, c_dtype, alpha, m, n, k, ld, 1,
                                B12X_B200_BLOCK_N_PAIR, sm_count, workspace, workspace_bytes,
                                nullptr, status, stream, &plan);
+}
+
+// ------------------------------------------------------------------------------------------
+// Load-time weight packing
+// ------------------------------------------------------------------------------------------
+extern "C" int b12x_b200_pack_block_fp8_weight_mxfp8(const void* codes, const float* scale,
+                                                     void* out_codes, void* scale_rows,
+                                                     void* scale_mma, int64_t m, int64_t k,
+                                                     int64_t groups, int requantize,
+                                                     b12x_b200_stream_t stream) {
+  if (m <= 0 || k <= 0 || groups <= 0 || m > INT32_MAX - 128 || k > INT32_MAX || groups > 65535)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad size");
+  if (k % 128 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 128");
+  if (!codes || !scale || !out_codes) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (!aligned16(codes) || !aligned16(out_codes) || (scale_rows && (uintptr_t(scale_rows) & 3)) ||
+      (scale_mma && !aligned16(scale_mma)))
+    return fail(B12X_B200_ERR_ALIGNMENT, "codes and atoms must be 16-byte aligned");
+  const int64_t row_tiles = (m + 127) / 128;
+  if (row_tiles > 65535) return fail(B12X_B200_ERR_UNSUPPORTED, "too many rows");
+  DeviceInfo info;
+  const int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  PackWeightParams p;
+  p.codes = static_cast<const uint8_t*>(codes);
+  p.scale = scale;
+  p.out_codes = static_cast<uint8_t*>(out_codes);
+  p.scale_rows = static_cast<uint8_t*>(scale_rows);
+  p.scale_mma = static_cast<uint8_t*>(scale_mma);
+  p.m = int(m);
+  p.k = int(k);
+  p.requantize = requantize ? 1 : 0;
+  pack_block_fp8_weight_kernel<<<dim3(unsigned(k / 128), unsigned(row_tiles), unsigned(groups)), 256, 0,
+                                 reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "pack_block_fp8_weight launch");
+  return B12X_B200_OK;
 }

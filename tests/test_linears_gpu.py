@@ -222,3 +222,64 @@ def test_tensor_fp8_linear_ignores_scale_storage_bias_leading_dims_graph_and_err
         tensor_fp8_linear.pack_weight(weight, torch.ones(2, device=DEV))
     with pytest.raises(ValueError, match="multiple of 32"):
         tensor_fp8_linear.pack_weight(weight[:, :48], scale)
+
+
+# --------------------------------------------------------------------------------------
+# Weight packing on the device (one kernel) against the reference's outputs and the torch
+# restatement of the same arithmetic
+# --------------------------------------------------------------------------------------
+def _packed_bytes(rows):
+    values = rows.values if rows.values.ndim == 2 else rows.values.permute(2, 0, 1)
+    physical = rows.scale_mma.permute(5, 2, 4, 0, 1, 3).contiguous().view(torch.uint8)
+    return (values.contiguous().view(torch.uint8).cpu().numpy(),
+            rows.scale_rows.contiguous().view(torch.uint8).cpu().numpy(),
+            physical.cpu().numpy().reshape(-1))
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2, 3])
+def test_device_weight_packer_matches_reference_fixture(idx):
+    """Same fixture as the CPU test of the torch restatement: outputs of the reference's own
+    pack_fp8_block_scaled_weight_mxfp8 (re-quantized codes, per-row scale bytes, scale atoms;
+    one and two groups, ragged row count, power-of-two scales passed through)."""
+    from conftest import GOLDEN
+    from sparkinfer_b200._lib import mxfp8_rows as mr
+
+    g = np.load(GOLDEN / "weight_pack.npz")
+    m, k, groups = (int(v) for v in g[f"shape{idx}"])
+    weight = torch.from_numpy(g[f"w{idx}"]).view(torch.float8_e4m3fn).to("cuda:0")
+    scale = torch.from_numpy(g[f"scale{idx}"]).to("cuda:0")
+    values, scale_rows, atoms = _packed_bytes(
+        mr.pack_fp8_block_scaled_weight_mxfp8(weight, scale, m=m, k=k, num_groups=groups))
+    assert np.array_equal(values, g[f"values{idx}"])
+    assert np.array_equal(scale_rows, g[f"scale_rows{idx}"])
+    assert np.array_equal(atoms, g[f"scale_mma{idx}"])
+
+
+@pytest.mark.parametrize("m,k,groups,spread", [
+    (384, 512, 1, 1.0), (200, 256, 3, 1e-3), (1000, 1024, 1, 1e4), (128, 128, 2, 1e-30),
+    (77, 384, 1, 1e30),
+])
+def test_device_weight_packer_equals_torch_restatement(monkeypatch, m, k, groups, spread):
+    """Random checkpoint-style weights with scales over a wide range (down to values whose
+    blocks land on the smallest UE8M0 bytes, up to the largest), and blocks of zeros."""
+    from sparkinfer_b200._lib import mxfp8_rows as mr
+
+    gen = torch.Generator().manual_seed(m * 7 + k)
+    w = (torch.randn((groups * m, k), generator=gen) * 60).clamp(-448, 448).to(torch.float8_e4m3fn)
+    w[: min(m, 128), :128] = 0                       # one all-zero block
+    blocks = (groups * -(-m // 128), k // 128)
+    scale = (torch.rand(blocks, generator=gen) + 0.25) * spread * torch.exp2(
+        torch.randint(-6, 7, blocks, generator=gen).float())
+    got = _packed_bytes(mr.pack_fp8_block_scaled_weight_mxfp8(
+        w.to("cuda:0"), scale.to("cuda:0"), m=m, k=k, num_groups=groups))
+    monkeypatch.setattr(mr, "_check_gpu_tensor", lambda name, tensor: None)
+    want = _packed_bytes(mr.pack_fp8_block_scaled_weight_mxfp8(w, scale, m=m, k=k, num_groups=groups))
+    for a, b, what in zip(got, want, ("codes", "scale rows", "scale atoms")):
+        assert np.array_equal(a, b), what
+    # power-of-two scales: codes pass through untouched
+    pow2 = torch.exp2(torch.randint(-20, 20, blocks, generator=gen).float())
+    got = _packed_bytes(mr.pack_fp8_block_scaled_weight_mxfp8(
+        w.to("cuda:0"), pow2.to("cuda:0"), m=m, k=k, num_groups=groups))
+    want = _packed_bytes(mr.pack_fp8_block_scaled_weight_mxfp8(w, pow2, m=m, k=k, num_groups=groups))
+    for a, b, what in zip(got, want, ("codes", "scale rows", "scale atoms")):
+        assert np.array_equal(a, b), what
