@@ -806,6 +806,7 @@ def main() -> None:
         return float(t.item())
 
     def parity_over_ranks(step: Step) -> dict:
+        sync_ranks()  # ranks leave the set-up of a step at different times
         step.run()
         torch.cuda.synchronize()
         par = step.parity()

@@ -371,7 +371,7 @@ int b12x_b200_selftest_wait_timeout(int* status, int max_polls, b12x_b200_stream
  *   dtype    B12X_B200_BF16 or B12X_B200_FP16; cols % 8 == 0, ld % 8 == 0
  *   blocks   thread blocks of 512 threads per rank, 0 = library default
  *   max_polls  limit of each wait for another rank's flag (one poll is a system-scope load plus
- *            a 200 ns back-off), 0 = 2^21 (a few seconds). When a wait runs out *status is
+ *            a 200 ns back-off), 0 = 2^24 (tens of seconds). When a wait runs out *status is
  *            raised to 6, the data phase is skipped and the kernel returns.
  * Waits on other GPUs' kernels: the ranks must be on different devices (rank >= 0), launched
  * by their own processes or threads; never launch two ranks' calls on one device.

@@ -1382,7 +1382,9 @@ int allreduce_peer_impl(void* const* buffers, void* const* outputs, void* const*
   p.cols = cols;
   p.ld = ld;
   p.out_dtype = dtype == B12X_B200_BF16 ? kOutBf16 : kOutFp16;
-  p.max_polls = max_polls ? uint32_t(max_polls) : (1u << 21);
+  // Default: 2^24 polls of a system-scope load plus a 200 ns back-off, tens of seconds. Ranks
+  // of a serving process can be a second apart at the first call (host-side set-up).
+  p.max_polls = max_polls ? uint32_t(max_polls) : (1u << 24);
   p.status = status;
   const cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == B12X_B200_BF16;
