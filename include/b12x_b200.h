@@ -241,6 +241,21 @@ int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x
                                       int* status, b12x_b200_stream_t stream);
 
 /*
+ * The same for `groups` problems of one shape in one launch: the reference's
+ * dense_gemm_fused_quant_a_grouped without its inverse-RoPE option
+ * (b12x/_lib/dense_gemm.py:5803-5944; WO-A of the MLA output projection). Row r of group g of
+ * the activation starts at x + r * ld_x + g * x_group_stride elements (the reference's source
+ * [M, groups, K] has ld_x = groups * K and x_group_stride = K); weights, their scale atoms and
+ * the output are group-major as in b12x_b200_gemm_blockscaled_grouped.
+ */
+int b12x_b200_gemm_smallm_fused_quant_grouped(
+    int kind, const void* x_bf16, int64_t ld_x, int64_t x_group_stride,
+    const float* x_global_scale, const void* w, const void* sf_w, void* c, int c_dtype,
+    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
+    void* workspace, int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue, int sm_count,
+    int* status, b12x_b200_stream_t stream);
+
+/*
  * b12x_b200_gemm_blockscaled_smallm that also records, per CTA, eight 64-bit values in
  * `stamps` (global-timer nanoseconds at entry, after set-up, after the dependency wait, at the
  * first full pipeline stage, at the last finished accumulator and at the end of the epilogue,

@@ -465,6 +465,65 @@ def dense_gemm_fused_quant_a(
     return out
 
 
+def dense_gemm_fused_quant_a_grouped(
+    source: torch.Tensor,
+    b: torch.Tensor,
+    sfb: torch.Tensor,
+    *,
+    groups: int,
+    out: Optional[torch.Tensor] = None,
+    positions: Optional[torch.Tensor] = None,
+    cos_sin_cache: Optional[torch.Tensor] = None,
+    head_dim: int = 0,
+    nope_dim: int = 0,
+    rope_dim: int = 0,
+    expected_m: Optional[int] = None,
+    sfb_k_replicated: bool = False,
+    mma_tiler_mn: Optional[Tuple[int, int]] = None,
+    stream: object = None,
+) -> torch.Tensor:
+    """Grouped small-M BF16 activations -> MXFP8 GEMM in ONE launch
+    (b12x/_lib/dense_gemm.py:5803-5944, the WO-A shape): ``source [M, groups, K]`` BF16 (rows
+    may be strided, ``[groups, K]`` contiguous inside a row), per group ``[M, K] x [N, K]^T``
+    into ``out [M, N, groups]``. Every group's rows are quantized inside the decode kernel,
+    bit for bit as ``quantize_rows`` would. The inverse-RoPE rotation the reference can apply to
+    the rows before quantizing (``positions`` / ``cos_sin_cache``) belongs to the attention
+    side of that projection and is not built."""
+    if source.dtype != torch.bfloat16 or source.ndim != 3:
+        raise ValueError("fused grouped MXFP8 quantization requires BF16 [M, groups, K]")
+    m, k = int(source.shape[0]), int(source.shape[2])
+    if int(source.shape[1]) != groups:
+        raise ValueError(f"source groups {int(source.shape[1])} != weight groups {groups}")
+    if source.stride(2) != 1 or source.stride(1) != k:
+        raise ValueError(
+            f"fused grouped MXFP8 A needs contiguous [groups, K] rows, got strides {source.stride()}")
+    row_stride = int(source.stride(0))
+    if m < 1 or m > 8 or k % 128 != 0 or row_stride % 8 != 0:
+        raise ValueError(
+            f"fused grouped MXFP8 quantization requires 1<=M<=8, K%128=0, row stride%8=0; "
+            f"got M={m}, K={k}, row_stride={row_stride}")
+    if b.ndim != 3 or int(b.shape[1]) != k or int(b.shape[2]) != groups:
+        raise ValueError(f"B must have shape [N,{k},{groups}], got {tuple(b.shape)}")
+    if positions is not None or cos_sin_cache is not None:
+        raise NotImplementedError(
+            "the inverse-RoPE prologue belongs to the MLA output projection and is not built")
+    n = int(b.shape[0])
+    _check_operand("B", b, n, k, groups)
+    if not mma_view_is_canonical(sfb, n, k, 32, groups):
+        raise ValueError("SFB must be the (32,4,n_tiles,4,k_tiles,L) view over dense atom storage")
+    if out is None:
+        out = _empty_dense_gemm_output(m, n, groups, dtype=torch.bfloat16, device=source.device)
+    if out.shape != (m, n, groups) or out.dtype != torch.bfloat16:
+        raise ValueError(
+            f"out must be BF16 with shape {(m, n, groups)}, got {out.dtype} {tuple(out.shape)}")
+    if out.stride(1) != 1 or (groups > 1 and out.stride(2) != m * n) or (m > 1 and out.stride(0) != n):
+        raise ValueError(f"out must be backed by physical [L, M, N] storage, got strides {out.stride()}")
+    sfb_flat = sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb
+    launch.gemm_smallm_fused_quant(_native.KIND_MXFP8, source, None, b, sfb_flat, out, None, m, n, k,
+                                   ldc=n, stream_int=cuda_stream_to_int(stream), groups=groups)
+    return out
+
+
 def dense_gemm_fused_quant_a_nvfp4(
     source: torch.Tensor,
     global_scale: torch.Tensor,
@@ -507,4 +566,5 @@ def dense_gemm_fused_quant_a_nvfp4(
     return out
 
 
-__all__ = ["dense_gemm", "dense_gemm_fused_quant_a", "dense_gemm_fused_quant_a_nvfp4", "get_num_sm"]
+__all__ = ["dense_gemm", "dense_gemm_fused_quant_a", "dense_gemm_fused_quant_a_grouped",
+           "dense_gemm_fused_quant_a_nvfp4", "get_num_sm"]

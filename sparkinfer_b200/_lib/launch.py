@@ -285,9 +285,11 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
                             alpha: torch.Tensor | None, m: int, n: int, k: int, *,
                             ldc: int | None = None, sm_count: int = 0,
                             stream_int: int | None = None, bias: torch.Tensor | None = None,
-                            quantized_c: QuantizedC | None = None) -> None:
+                            quantized_c: QuantizedC | None = None, groups: int = 1) -> None:
     """Decode GEMM that quantizes its BF16 activation rows ``x [M, K]`` (M <= 16) inside the
-    kernel; bit for bit ``quantize rows`` followed by :func:`gemm_blockscaled`."""
+    kernel; bit for bit ``quantize rows`` followed by :func:`gemm_blockscaled`. With
+    ``groups > 1``: ``x [M, groups, K]``, weights / scale atoms / output group-major, one
+    launch."""
     for name, t in (("x", x), ("w", w), ("sfw", sfw), ("c", c)):
         _require_cuda(name, t)
     if x.dtype != torch.bfloat16 or x.stride(-1) != 1:
@@ -296,17 +298,29 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
         raise TypeError(f"unsupported output dtype {c.dtype}")
     dev = x.device
     ep = _epilogue(c, n, bias, quantized_c)
-    work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
+    if groups == 1:
+        work = smallm_workspace(kind, m, n, k, dev, sm_count, stream_int)
+        row_stride, group_stride = (x.stride(0) if m > 1 else k), 0
+    else:
+        # x is [M, groups, K]: rows `x.stride(0)` apart, groups `x.stride(1)` apart.
+        with torch.cuda.device(dev):
+            need = int(_native.load().b12x_b200_gemm_grouped_workspace_bytes(
+                kind, 1, m, n, k, groups, 0, sm_count))
+        if need < 0:
+            raise _native.NativeLibraryError(
+                f"no decode-shape plan for M={m}, N={n}, K={k}, groups={groups}")
+        work = stream_workspace(need, dev, stream_int)
+        row_stride, group_stride = (x.stride(0) if m > 1 else groups * k), x.stride(1)
     with torch.cuda.device(dev):
-        rc = _native.load().b12x_b200_gemm_smallm_fused_quant(
-            kind, x.data_ptr(), x.stride(0) if m > 1 else k,
+        rc = _native.load().b12x_b200_gemm_smallm_fused_quant_grouped(
+            kind, x.data_ptr(), row_stride, group_stride,
             global_scale.data_ptr() if global_scale is not None else None, w.data_ptr(),
             sfw.data_ptr(), c.data_ptr(), _DTYPE_CODE[c.dtype],
             alpha.data_ptr() if alpha is not None else None, m, n, k,
-            ldc if ldc is not None else n, work.data_ptr(), work.numel(),
+            ldc if ldc is not None else n, groups, work.data_ptr(), work.numel(),
             ctypes.byref(ep) if ep is not None else None, sm_count,
             status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
-    _native.check(rc, "b12x_b200_gemm_smallm_fused_quant")
+    _native.check(rc, "b12x_b200_gemm_smallm_fused_quant_grouped")
     _after_launch(dev)
 
 

@@ -126,11 +126,13 @@ int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 // Row-major BF16 matrix [rows, cols] with row pitch `ld` elements -> unswizzled boxes of
 // box_cols x box_rows elements (the raw activation rows of the fused-quantizer decode GEMM).
 int make_raw_rows_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                      uint32_t box_cols, uint32_t box_rows, uint64_t groups = 1) {
+                      uint32_t box_cols, uint32_t box_rows, uint64_t groups = 1,
+                      uint64_t group_stride = 0) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(B12X_B200_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
   const cuuint64_t dims[3] = {cols, rows, groups};
-  const cuuint64_t strides[2] = {ld * 2, rows * ld * 2};
+  // Elements between the same row of consecutive groups: group-major [L][rows][ld] by default.
+  const cuuint64_t strides[2] = {ld * 2, (group_stride ? group_stride : rows * ld) * 2};
   const cuuint32_t box[3] = {box_cols, box_rows, 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r =
@@ -962,6 +964,7 @@ struct SmallMCall {
   cudaStream_t stream;
   const b12x_b200_epilogue_t* epilogue = nullptr;
   int64_t groups = 1;
+  int64_t x_group_stride = 0;  // fused rows: elements between groups (0: group-major rows)
 };
 
 // Argument checks shared by the decode-shape entry points. On success *empty is set when there
@@ -1024,7 +1027,7 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   if (fused) {
     const uint32_t elems = (a.kind == B12X_B200_KIND_MXFP8) ? 128u : 256u;
     rc = make_raw_rows_map(&map_x, a.x_src, uint64_t(a.m), uint64_t(a.k), uint64_t(a.ld_x), elems,
-                           uint32_t(pl.raw_rows), uint64_t(a.groups));
+                           uint32_t(pl.raw_rows), uint64_t(a.groups), uint64_t(a.x_group_stride));
     if (rc != B12X_B200_OK) return rc;
   } else {
     rc = make_operand_map(&map_x, a.x, uint64_t(a.m), uint64_t(row_bytes), uint32_t(pl.m_pad),
@@ -1174,6 +1177,25 @@ extern "C" int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, i
                   alpha, m,       n,       k,      ldc,  sm_count,       status, nullptr,
                   reinterpret_cast<cudaStream_t>(stream)};
   a.epilogue = epilogue;
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int b12x_b200_gemm_smallm_fused_quant_grouped(
+    int kind, const void* x_bf16, int64_t ld_x, int64_t x_group_stride,
+    const float* x_global_scale, const void* w, const void* sf_w, void* c, int c_dtype,
+    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
+    void* workspace, int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue, int sm_count,
+    int* status, b12x_b200_stream_t stream) {
+  if (!x_bf16) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (groups < 1) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be positive");
+  if (groups > 1 && (x_group_stride < k || x_group_stride % 8 != 0))
+    return fail(B12X_B200_ERR_ALIGNMENT, "activation groups must be 16-byte aligned and K apart at least");
+  SmallMCall a = {kind,  nullptr, nullptr, x_bf16, ld_x, x_global_scale, w,      sf_w,    c, c_dtype,
+                  alpha, m,       n,       k,      ldc,  sm_count,       status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  a.epilogue = epilogue;
+  a.groups = groups;
+  a.x_group_stride = groups > 1 ? x_group_stride : 0;
   return smallm_entry(a, workspace, workspace_bytes);
 }
 

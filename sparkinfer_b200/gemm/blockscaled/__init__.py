@@ -25,7 +25,8 @@ META = OpMeta(
     name="blockscaled",
     group="gemm",
     api_style="oneshot",
-    entry_points=("mm", "mm_fused_quant_a", "mm_fused_quant_a_nvfp4", "is_supported"),
+    entry_points=("mm", "mm_fused_quant_a", "mm_fused_quant_a_grouped", "mm_fused_quant_a_nvfp4",
+                  "is_supported"),
     dtypes=("bf16", "fp16", "fp32", "fp8_e4m3", "fp4_e2m1"),
     recipes=("nvfp4", "mxfp8", "block_fp8"),
     provenance=Provenance(
@@ -38,6 +39,7 @@ META = OpMeta(
 )
 
 if TYPE_CHECKING:  # static analysis only; runtime resolution is lazy
-    from .api import is_supported, mm, mm_fused_quant_a, mm_fused_quant_a_nvfp4  # noqa: F401
+    from .api import (is_supported, mm, mm_fused_quant_a, mm_fused_quant_a_grouped,  # noqa: F401
+                      mm_fused_quant_a_nvfp4)
 
 install_lazy_api(globals(), META)

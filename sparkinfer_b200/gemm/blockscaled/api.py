@@ -4,6 +4,7 @@ from __future__ import annotations
 
 from ..._lib.dense_gemm import dense_gemm as mm
 from ..._lib.dense_gemm import dense_gemm_fused_quant_a as mm_fused_quant_a
+from ..._lib.dense_gemm import dense_gemm_fused_quant_a_grouped as mm_fused_quant_a_grouped
 from ..._lib.dense_gemm import dense_gemm_fused_quant_a_nvfp4 as mm_fused_quant_a_nvfp4
 from ..._lib.gating import default_is_supported
 from . import META
@@ -14,4 +15,5 @@ def is_supported(device=None) -> bool:
     return default_is_supported(device, requires=META.requires)
 
 
-__all__ = ["mm", "mm_fused_quant_a", "mm_fused_quant_a_nvfp4", "is_supported"]
+__all__ = ["mm", "mm_fused_quant_a", "mm_fused_quant_a_grouped", "mm_fused_quant_a_nvfp4",
+           "is_supported"]

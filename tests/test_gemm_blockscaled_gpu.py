@@ -630,6 +630,51 @@ def test_mm_fused_quant_a_mxfp8_equals_quantize_then_mm_bit_for_bit(m, n, k):
     check_kernel_status(DEV)
 
 
+@pytest.mark.parametrize("m,n,k,groups,row_pad", [
+    (1, 128, 256, 2, 0), (4, 512, 512, 5, 0), (8, 1536, 1024, 3, 64), (3, 200, 384, 4, 8),
+    (8, 4096, 512, 16, 0),      # 512 weight tiles in one work list (more than SMs: stream-K)
+])
+def test_mm_fused_quant_a_grouped_equals_the_groups_one_by_one(m, n, k, groups, row_pad):
+    """``source [M, groups, K]`` (rows strided when ``row_pad`` > 0), weights ``[N, K, groups]``:
+    one launch for all groups must give, per group, exactly what ``mm_fused_quant_a`` gives for
+    that group alone, and meet the oracle."""
+    from gpu_util import DEV, assert_gemm_close, to_dev
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200.gemm import blockscaled
+
+    backing = torch.zeros((m, groups * k + row_pad), dtype=torch.bfloat16)
+    source = backing[:, :groups * k].view(m, groups, k)
+    b_vals, b_sw, refs = [], [], []
+    for g in range(groups):
+        source[:, g] = seeded_bf16(700 + g + m, (m, k), 0.25 * (1 + g))
+        b = seeded_bf16(800 + g + n, (n, k), 0.03 / (1 + g)).float().numpy()
+        bv, bsr = O.quantize_mxfp8_rows(b)
+        b_vals.append(bv); b_sw.append(O.swizzle_scales(bsr, 127))
+        av, asr = O.quantize_mxfp8_rows(source[:, g].float().numpy())
+        refs.append(O.dequantize_mxfp8(av, asr) @ O.dequantize_mxfp8(bv, bsr).T)
+    src_dev = backing.to(DEV)[:, :groups * k].view(m, groups, k)
+    b_t = to_dev(np.stack(b_vals)).view(torch.float8_e4m3fn).as_strided((n, k, groups), (k, 1, n * k))
+    sfb = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(b_sw)), n, k, groups, 32)
+    out = torch.full((groups, m, n), float("nan"), dtype=torch.bfloat16, device=DEV).permute(1, 2, 0)
+    got = blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups, out=out)
+    torch.cuda.synchronize()
+    assert got is out
+    for g in range(groups):
+        assert_gemm_close(out[:, :, g], refs[g])
+        one_sfb = layout.convert_sf_to_mma_layout(to_dev(b_sw[g]), n, k, 1, 32)
+        alone = blockscaled.mm_fused_quant_a(
+            src_dev[:, g].contiguous(), to_dev(b_vals[g]).view(torch.float8_e4m3fn).view(n, k, 1), one_sfb)
+        assert torch.equal(alone[:, :, 0].view(torch.int16), out[:, :, g].contiguous().view(torch.int16)), g
+    with pytest.raises(NotImplementedError, match="inverse-RoPE"):
+        blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups,
+                                             positions=torch.zeros(m, dtype=torch.int64, device=DEV),
+                                             cos_sin_cache=torch.zeros((4, 64), device=DEV))
+    with pytest.raises(ValueError, match="source groups"):
+        blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups + 1)
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 128, 256), (4, 512, 512), (16, 14336, 4096), (13, 1024, 2048),
                                    (9, 24064, 1024), (16, 200, 320), (2, 4096, 7168)])
 def test_mm_fused_quant_a_nvfp4_equals_quantize_then_mm_bit_for_bit(m, n, k):

@@ -263,3 +263,29 @@ def test_tensor_fp8_linear_fake_op_and_host_validation():
         tensor_fp8_linear.mm(w_cpu, object())  # the device check comes first, as in the reference
     assert isinstance(tensor_fp8_linear.is_supported(), bool)
     assert "tensor_fp8_linear" in {m.name for m in __import__("sparkinfer_b200").list_ops()}
+
+
+def test_grouped_fused_quant_host_checks_fire_before_any_launch():
+    """Argument errors of mm_fused_quant_a_grouped (b12x/_lib/dense_gemm.py:5803-5944) are host
+    checks: they need no GPU and raise the reference's messages."""
+    from sparkinfer_b200.gemm import blockscaled
+
+    k, groups, n = 256, 3, 128
+    src = torch.zeros((4, groups, k), dtype=torch.bfloat16)
+    b = torch.zeros((groups, n, k), dtype=torch.uint8).permute(1, 2, 0)
+    sfb = torch.zeros(1, dtype=torch.uint8)
+    with pytest.raises(ValueError, match=r"requires BF16 \[M, groups, K\]"):
+        blockscaled.mm_fused_quant_a_grouped(src.float(), b, sfb, groups=groups)
+    with pytest.raises(ValueError, match="source groups 3 != weight groups 4"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=4)
+    with pytest.raises(ValueError, match="1<=M<=8"):
+        blockscaled.mm_fused_quant_a_grouped(torch.zeros((9, groups, k), dtype=torch.bfloat16), b, sfb,
+                                             groups=groups)
+    with pytest.raises(ValueError, match="contiguous \\[groups, K\\] rows"):
+        blockscaled.mm_fused_quant_a_grouped(
+            torch.zeros((4, groups, 2 * k), dtype=torch.bfloat16)[:, :, :k], b, sfb, groups=groups)
+    with pytest.raises(ValueError, match=r"B must have shape \[N,256,3\]"):
+        blockscaled.mm_fused_quant_a_grouped(src, b[:, :128], sfb, groups=groups)
+    with pytest.raises(NotImplementedError, match="inverse-RoPE"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups,
+                                             positions=torch.zeros(4, dtype=torch.int64))
