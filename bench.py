@@ -17,8 +17,12 @@ Workloads (the reference's configurations):
   cfg1_nvfp4_decode_m{1,4,16}_fused  the same step as one kernel (quantizer fused in)
   cfg2_mxfp8_prefill               quantize_rows + MXFP8 GEMM, 8192 x 7168 x 7168
   cfg3_block_fp8_colpar            E4M3 + FP32 block scales, 4096 x 18432 x 7168, N / gpus
-  cfg4_nvfp4_rowpar                quantize_rows + NVFP4 GEMM + BF16 all-reduce,
-                                   4096 x 7168 x 18432, K / gpus
+  cfg4_nvfp4_rowpar                quantize_rows + NVFP4 GEMM + BF16 sum over the ranks,
+                                   4096 x 7168 x 18432, K / gpus. The sum is this package's
+                                   own code over NVLink peer memory, fused into the GEMM's
+                                   epilogue (B12X_BENCH_COLLECTIVE=fused, the default), or its
+                                   stand-alone all-reduce kernel (=peer), or NCCL (=nccl);
+                                   NCCL's time on the same bytes is reported beside it.
 """
 
 from __future__ import annotations
