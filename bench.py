@@ -884,7 +884,19 @@ def main() -> None:
 
     from sparkinfer_b200._lib.launch import check_kernel_status
 
-    check_kernel_status(device)
+    def kernel_status_over_ranks() -> str | None:
+        """Highest kernel status word over the ranks (None when every bounded wait was met);
+        every rank gets the same answer, so nobody leaves the others inside a collective."""
+        try:
+            check_kernel_status(device)
+            code, text = 0.0, ""
+        except RuntimeError as exc:
+            code, text = 1.0, str(exc)
+        if reduce_max(code) == 0.0:
+            return None
+        return text or "a kernel on another rank reported a timed-out wait"
+
+    headline_status = kernel_status_over_ranks()
 
     tensor_peak = peaks["bf16_tflops"] * (4 if w["kind"] == "nvfp4" else 2)
     nominal_tensor = NOMINAL["fp4_tflops"] if w["kind"] == "nvfp4" else NOMINAL["fp8_tflops"]
@@ -935,7 +947,9 @@ def main() -> None:
                 torch.cuda.empty_cache()
             except Exception as exc:  # keep the headline line even if a side config fails
                 extra[name] = {"error": str(exc)[:160]}
-        check_kernel_status(device)
+            status = kernel_status_over_ranks()
+            if status is not None:
+                extra.setdefault(name, {})["kernel_status"] = status
 
     if rank == 0:
         baseline = cpu_baseline(w, args.workload) if world == 1 else None
@@ -954,6 +968,7 @@ def main() -> None:
             "config": config_dict(args.workload, w, world, args.steps),
             "roofline": roofline,
             "parity": parity,
+            "kernel_status": headline_status or "ok",
             "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d_d2h[0], "d2h_bytes_per_step": h2d_d2h[1],
                     "ms_per_step": e2e_ms, "row_pieces": e2e_pieces},
