@@ -40,7 +40,7 @@ enum {
   B12X_B200_KIND_MXFP8 = 0, /* E4M3 codes, UE8M0 scale per 32 elements of K              */
   B12X_B200_KIND_NVFP4 = 1, /* packed E2M1 codes, UE4M3 (E4M3) scale per 16 elements     */
   /* E4M3 codes without block scales: alpha is the only scale (the reference's
-   * dense_gemm(plain_fp8=True), b12x/_lib/dense_gemm.py:7140-7189, per-tensor FP8 linears).
+   * dense_gemm(plain_fp8=True), b12x/_lib/dense_gemm.py:7096-7139, 7225-7233; MMA :268-330, per-tensor FP8 linears).
    * sfa / sfb are ignored and may be NULL. Accepted by b12x_b200_gemm_blockscaled, _ex,
    * _grouped and _scatter (tiled and CTA-pair kernels); the decode entry points refuse it. */
   B12X_B200_KIND_FP8 = 2

@@ -218,7 +218,7 @@ def _plain_fp8_launch(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tens
                       alpha: Optional[torch.Tensor], *, m: int, n: int, k: int, l: int,
                       c_dtype: str, mma_tiler_mn, sm_count: int, stream) -> torch.Tensor:
     """``dense_gemm(plain_fp8=True)`` on the tiled kernels: E4M3 x E4M3 with FP32 accumulation
-    and ``alpha`` as the only scale (b12x/_lib/dense_gemm.py:7140-7189 in the reference)."""
+    and ``alpha`` as the only scale (b12x/_lib/dense_gemm.py:7096-7139, 7225-7233; MMA :268-330 in the reference)."""
     _check_operand("A", a, m, k, l)
     _check_operand("B", b, n, k, l)
     if out is None:
@@ -340,6 +340,8 @@ def dense_gemm(
         # Per-tensor FP8 rides on the MXFP8 kernel: the caller passes unit block scales and
         # the one real scale as alpha (dense_gemm.py:7137-7139 in the reference).
         raise ValueError("plain_fp8 requires float8_e4m3fn operands with float8_e8m0fnu/32 scales")
+    if plain_fp8 and (_quantized_c is not None or sfb_k_replicated):
+        raise ValueError("plain_fp8 does not support tiled/quantized output or replicated scales")
     if plain_fp8:
         # The caller's scale storage is not read in this mode. Shapes of the tiled kernels run
         # the unscaled FP8 MMA (no scale bytes move at all); decode shapes stay on the
