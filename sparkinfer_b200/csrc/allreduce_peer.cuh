@@ -65,8 +65,10 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Flag store without a fence of its own: every use below follows either a kernel boundary or an
+// explicit __threadfence_system(), which is what orders the data before the flag.
+__device__ __forceinline__ void st_flag_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Data accesses at system scope (plain .cg accesses measured the same over NVLink).
 __device__ __forceinline__ uint4 ld_peer_16(const uint4* p) {
@@ -124,12 +126,15 @@ allreduce_peer_kernel(const PeerAllReduceParams p) {
   uint32_t* mine = p.sig[me];
   __shared__ uint32_t s_call;
   __shared__ int s_last;
-  if (threadIdx.x == 0) s_call = ld_acquire_sys(mine + kSigCall) + 1;
+  // Written by this rank's previous call (an earlier kernel on this device): a plain load.
+  if (threadIdx.x == 0) s_call = *reinterpret_cast<volatile uint32_t*>(mine + kSigCall) + 1;
   __syncthreads();
   const uint32_t call = s_call;
 
   const int t = static_cast<int>(threadIdx.x);
-  if (blockIdx.x == 0 && t < world && t != me) st_release_sys(p.sig[t] + kSigStart + me, call);
+  // "My partial is complete": it was written (and, where it went to peers, fenced at system
+  // scope) by the GEMM kernel that precedes this one in the stream, so the flag needs no fence.
+  if (blockIdx.x == 0 && t < world && t != me) st_flag_sys(p.sig[t] + kSigStart + me, call);
   bool ok = true;
   if (t < world && t != me) ok = wait_flag(mine + kSigStart + t, call, p.max_polls);
   ok = __syncthreads_and(ok);
@@ -196,18 +201,20 @@ allreduce_peer_kernel(const PeerAllReduceParams p) {
   }
   __syncthreads();
   if (!s_last) return;
+  // Every block fenced its pushes at system scope before it was counted; this fence makes those
+  // counts (and with them the pushes) precede the end flags.
   __threadfence_system();
   bool done = true;
   if (ok && t < world && t != me) {
-    st_release_sys(p.sig[t] + kSigEnd + me, call);
+    st_flag_sys(p.sig[t] + kSigEnd + me, call);
     done = wait_flag(mine + kSigEnd + t, call, p.max_polls);
   }
   done = __syncthreads_and(done);
   if (t == 0) {
     if (!done && p.status) atomicMax(p.status, kStatusPeerTimeout);
+    // Read next by this rank's next call, a later kernel on this device.
     mine[kSigBlocksDone] = 0;
-    __threadfence_system();
-    st_release_sys(mine + kSigCall, call);
+    mine[kSigCall] = call;
   }
 }
 
