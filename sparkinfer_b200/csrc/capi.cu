@@ -881,7 +881,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   const int cols = pl.sf_col0 + 2 * SmallMTile<kMxfp8>::kSfColsPerIssuer;
   pl.tmem_cols = cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
   const int smem_limit = 227 * 1024;
-  int stages = (smem_limit - 2048) / pl.stage_bytes;
+  int stages = (smem_limit - kSmallMTailBytes) / pl.stage_bytes;
   if (stages > SmallMTile<kMxfp8>::kMaxStages) stages = SmallMTile<kMxfp8>::kMaxStages;
   // With two issuing warps taking alternate units, a stage must always come back to the same
   // warp: with an odd ring a warp would skip every other phase of a stage's barrier, and a
@@ -1076,7 +1076,9 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   }
   p.wait_for_weights = a.n <= kEarlyReleaseRows ? 1 : 0;
   p.timeline = a.timeline;
-  const int smem_bytes = pl.stages * pl.stage_bytes + 2048;
+  p.packed_store = (a.c_dtype != B12X_B200_FP32 && aligned16(a.c) && a.ldc % 8 == 0) ? 1 : 0;
+  p.smem_bytes = pl.stages * pl.stage_bytes + kSmallMTailBytes;
+  const int smem_bytes = pl.stages * pl.stage_bytes + kSmallMTailBytes;
   if (a.kind == B12X_B200_KIND_MXFP8)
     return fused ? launch_smallm<kMxfp8, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
                  : launch_smallm<kMxfp8, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);

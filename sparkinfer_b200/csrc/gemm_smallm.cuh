@@ -104,9 +104,18 @@ struct SmallMParams {
   // Non-zero: the weight stream too waits for the previous grid (weights of few rows may be a
   // predecessor's fresh output, see the header comment).
   int wait_for_weights;
+  // Non-zero: whole tiles of 2-byte outputs leave through a small shared-memory staging area as
+  // 16-byte stores (rows of C 16-byte aligned); zero: every lane stores its own 2-byte values.
+  int packed_store;
+  int smem_bytes;          // dynamic shared memory of the launch
   // Optional per-CTA time stamps (8 x uint64 per CTA, see kTimeline*); null in normal use.
   unsigned long long* timeline;
 };
+
+// Bytes after the ring: barriers and flags (first 512), then the output staging area.
+constexpr int kSmallMTailBytes = 3072;
+constexpr int kSmallMStagingOffset = 512;
+constexpr int kSmallMStagingBytes = 2048;  // per epilogue warp: eight output rows x 32 columns x 2 bytes
 
 // Slots of SmallMParams::timeline per CTA (global timer, nanoseconds).
 enum : int {
@@ -320,6 +329,33 @@ __device__ __forceinline__ void emit_output(const SmallMParams& p, float alpha, 
 
 // EPI: the instantiation whose epilogue can add a bias and re-quantize the output rows; the
 // plain one carries none of that code.
+// Eight consecutive output rows x this warp's 32 columns, one value per row in each lane:
+// turned around in the warp's 512 bytes of staging memory and stored as 16 bytes per lane (lane
+// l: row l / 4, columns (l % 4) * 8 .. + 7). `vals` are final values (scaled); rows from
+// `row0 + 8` on or beyond `m`, and columns beyond `n`, are not written.
+__device__ __forceinline__ void store_rows8_packed(const SmallMParams& p, uint16_t* buf, int lane,
+                                                   size_t c_group0, int row0, int col0,
+                                                   const float (&vals)[8]) {
+  __syncwarp();  // the previous eight rows have been read
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    buf[r * 32 + lane] = (p.out_dtype == kOutBf16) ? __bfloat16_as_ushort(__float2bfloat16_rn(vals[r]))
+                                                   : __half_as_ushort(__float2half_rn(vals[r]));
+  __syncwarp();
+  const int r8 = lane >> 2;
+  const int j4 = lane & 3;
+  const int mrow = row0 + r8;
+  const int col = col0 + j4 * 8;
+  if (mrow < p.m && col < p.n) {
+    uint16_t* dst = static_cast<uint16_t*>(p.c) + c_group0 + static_cast<size_t>(mrow) * p.ldc + col;
+    if (col + 8 <= p.n) {
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(buf + r8 * 32 + j4 * 8);
+    } else {
+      for (int e = 0; col + e < p.n; ++e) dst[e] = buf[r8 * 32 + j4 * 8 + e];
+    }
+  }
+}
+
 template <int KIND, bool FUSED, bool EPI>
 __global__ void __launch_bounds__(FUSED ? 512 : 256, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -336,6 +372,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
+  // Output staging (see packed_store); used only if it lies inside the launch's shared memory
+  // (the ring's base is rounded up to 1 KiB, which may take up to 1023 bytes of the tail).
+  uint8_t* staging = reinterpret_cast<uint8_t*>(full_bar) + kSmallMStagingOffset;
+  const bool staging_fits = (staging + kSmallMStagingBytes) <= (smem_raw + p.smem_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -659,6 +699,45 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           slot = static_cast<int>(blockIdx.x) - first_cta;
         }
         float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
+        if (!EPI && whole && p.packed_store && staging_fits) {
+          // A lane holds one output column of every row, so storing from registers means one
+          // 2-byte store per row and lane (64 bytes per warp instruction), and those stores
+          // measured 75 ns apiece per warp: 1 us of a 16-row tile's epilogue and 4 us of a
+          // 64-row one. Instead each warp turns eight rows x its 32 columns around in its own
+          // 512 bytes of shared memory and stores 16 bytes per lane: one instruction per
+          // eight rows, no barrier between the warps.
+          const int tile_n0 = (tile - grp * p.tiles_per_group) * 128;
+          uint16_t* buf = reinterpret_cast<uint16_t*>(staging) + quarter * 256;
+          const int col0 = tile_n0 + quarter * 32;
+          for (int c0 = 0; c0 < p.m_pad && c0 < p.m; c0 += 16) {
+            uint32_t raw[16];
+            tmem_load_16cols(taddr0 + c0, raw);
+            if (both) {
+              uint32_t other[16];
+              tmem_load_16cols(taddr1 + c0, other);
+              tmem_load_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                raw[i] = __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(other[i])));
+            } else {
+              tmem_load_wait();
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (c0 + 8 * h >= p.m) break;  // uniform: nothing but padding rows from here on
+              float vals[8];
+#pragma unroll
+              for (int r = 0; r < 8; ++r) vals[r] = __uint_as_float(raw[8 * h + r]) * alpha;
+              store_rows8_packed(p, buf, lane, c_group0, c0 + 8 * h, col0, vals);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+          u = seg_end;
+          ++seg;
+          continue;
+        }
         for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
           uint32_t raw[16];
           tmem_load_16cols(taddr0 + c0, raw);
@@ -725,6 +804,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                 for (int i = 0; i < 8; ++i) v[i] = (m0 + i < p.m) ? __ldcg(src + i * 128) : 0.0f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) sum[i] += v[i];
+              }
+              if (!EPI && p.packed_store && staging_fits) {
+                float vals[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vals[i] = sum[i] * alpha;
+                store_rows8_packed(p, reinterpret_cast<uint16_t*>(staging) + quarter * 256, lane,
+                                   c_group0, m0,
+                                   (tile - grp * p.tiles_per_group) * 128 + quarter * 32, vals);
+                continue;
               }
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
