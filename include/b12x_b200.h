@@ -259,7 +259,8 @@ int b12x_b200_gemm_smallm_fused_quant_grouped(
  * b12x_b200_gemm_blockscaled_smallm that also records, per CTA, eight 64-bit values in
  * `stamps` (global-timer nanoseconds at entry, after set-up, after the dependency wait, at the
  * first full pipeline stage, at the last finished accumulator and at the end of the epilogue,
- * then the SM id and a spare). For the timeline summaries of the decode GEMM; it has no
+ * then the SM id and the time at which the last accumulator had been read out of tensor
+ * memory). For the timeline summaries of the decode GEMM; it has no
  * counterpart in the reference. stamps_len (in 64-bit words) must be at least 8 x the grid
  * size, for which 8 x the SM count always suffices.
  */

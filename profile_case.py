@@ -142,12 +142,13 @@ def timeline(m: int, n: int, k: int, chain: int, device: torch.device) -> int:
 
     print("per GEMM i >= 1 (microseconds, medians over CTAs; 'first'/'last' over the whole grid):")
     print("  i  grid_start-prev_grid_end  entry->setup  setup->deps_done  entry->first_stage  "
-          "first_stage->last_acc  last_acc->exit  grid_span")
+          "first_stage->last_acc  last_acc->drained  drained->exit  grid_span")
     for i in range(1, chain):
         e, su, dd, fs, la, ex = (t[i, :, j][live[i]] for j in range(6))
+        dr = t[i, :, 7][live[i]]
         prev_end = t[i - 1, :, 5][live[i - 1]].max()
         print(f"  {i}  {float(e.min() - prev_end) / 1e3:+8.2f}  {med(su - e):8.2f}  {med(dd - su):8.2f}  "
-              f"{med(fs - e):8.2f}  {med(la - fs):8.2f}  {med(ex - la):8.2f}  "
+              f"{med(fs - e):8.2f}  {med(la - fs):8.2f}  {med(dr - la):8.2f}  {med(ex - dr):8.2f}  "
               f"{float(ex.max() - e.min()) / 1e3:8.2f}")
     e_all = [t[i, :, 0][live[i]].min() for i in range(chain)]
     period = [(float(e_all[i + 1] - e_all[i]) / 1e3) for i in range(chain - 1)]

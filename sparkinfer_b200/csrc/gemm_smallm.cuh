@@ -126,6 +126,7 @@ enum : int {
   kTimelineLastAcc = 4,     // epilogue saw the last accumulator of the CTA complete
   kTimelineExit = 5,        // epilogue done
   kTimelineSm = 6,          // SM id
+  kTimelineDrained = 7,     // the last accumulator of the CTA has been read out of tensor memory
   kTimelineSlots = 8,
 };
 
@@ -722,6 +723,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
             } else {
               tmem_load_wait();
             }
+            if (stamps && threadIdx.x == 64 && seg_end == u_end && (c0 + 16 >= p.m_pad || c0 + 16 >= p.m))
+              stamps[kTimelineDrained] = global_timer_ns();
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               if (c0 + 8 * h >= p.m) break;  // uniform: nothing but padding rows from here on
@@ -751,6 +754,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           } else {
             tmem_load_wait();
           }
+          if (stamps && threadIdx.x == 64 && seg_end == u_end && c0 + 16 >= p.m_pad)
+            stamps[kTimelineDrained] = global_timer_ns();
           if (whole) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
