@@ -122,8 +122,8 @@ int b12x_b200_gemm_blockscaled(int kind, const void* a, const void* sfa, const v
  * b12x_b200_gemm_blockscaled with caller-owned scratch and an optional epilogue (bias only;
  * see b12x_b200_epilogue_t). The CTA-pair kernel (chosen for large
  * problems, or with B12X_B200_BLOCK_N_PAIR) runs whole rounds of 256 x 256 tiles over the SM
- * pairs; when the tiles left for the last round would occupy at most a tenth of the pairs, it cuts
- * them along K over all pairs instead and adds the FP32 partial tiles up through this scratch
+ * pairs; when the tiles left over would occupy at most half of the pairs, it cuts them along K
+ * over the pairs instead (as the first thing the pairs do) and adds the FP32 partial tiles up through this scratch
  * (in a fixed order: results do not depend on timing). Without scratch, or where no split
  * applies, the call is exactly b12x_b200_gemm_blockscaled. Plays the role of the reference's
  * split-K / stream-K policy (b12x/_lib/dense_gemm.py:387-454, 6671-6894) for large M.

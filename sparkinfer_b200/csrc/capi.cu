@@ -392,13 +392,15 @@ PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int64_t g
   t.left = int(tiles - rounds * t.pairs);
   const int elems_per_stage = (kind == B12X_B200_KIND_NVFP4) ? 256 : 128;
   const int64_t k_tiles = (k + elems_per_stage - 1) / elems_per_stage;
-  // Split only when the leftover tiles would keep at most a tenth of the pairs busy, and never
-  // below two k-tiles per segment. The split round is not free: it ends when the slowest pair
-  // of each tile has delivered (the pairs drift apart by several microseconds over a dozen
-  // rounds) and then pays for the partial tiles' round trip through L2, together about half a
-  // tile time on 4096 x 7168 x 18432 (4 tiles left on 74 pairs: 213 -> 200 us) and a whole one
-  // on 8192 x 7168 x 7168 (8 left: 294 -> 296 us).
-  if (t.left == 0 || t.left * 10 > t.pairs || size_t(t.left) * 2 * sizeof(int) > kPairCounterBytes)
+  // Split when the leftover tiles would keep at most half of the pairs busy, and never below two
+  // k-tiles per segment. The split tiles are done FIRST, while all pairs are still in step: a
+  // segment's epilogue waits for the other segments of its tile, and by the end of the kernel
+  // the pairs have drifted apart by several microseconds. Done last, the split paid for that
+  // drift (it saved nothing on 8192 x 7168 x 7168 and was restricted to a leftover of a tenth
+  // of the pairs). Warm caches, split last -> split first: 4096 x 7168 x 18432 (4 tiles left on
+  // 74 pairs) 179.1 -> 175.1-177.1 us; 4096 x 7168 x 9216 107.5 -> 101.2 us; 8192 x 7168 x 7168
+  // (8 left, whole tiles under the old rule) 289.8 -> 285.7 us.
+  if (t.left == 0 || t.left * 2 > t.pairs || size_t(t.left) * 2 * sizeof(int) > kPairCounterBytes)
     return t;
   int64_t seg = t.pairs / t.left;
   if (seg > k_tiles / 2) seg = k_tiles / 2;
@@ -544,7 +546,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
       tail.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + kPairCounterOffset);
       tail.partials =
           reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kWorkspaceHeaderBytes);
-      tail.segments = tp.segments;
+      tail.segments = -tp.segments;  // negative: the split tiles come first (see pair_work)
     }
     if (scatter) {
       ScatterOut<true> sc;

@@ -17,10 +17,11 @@
 //                          128 x 256 accumulator into registers -> arrive on the leader's
 //                          acc_empty -> convert, stage in swizzled shared memory, TMA store
 //
-// Last, partial round. With T tiles on P pairs the first T / P rounds keep every pair busy; the
-// T % P tiles left would occupy a few pairs for a whole tile time while the rest idle (448 tiles
-// on 74 pairs: 4 tiles, a seventh round at 5 % occupancy). When at most a tenth of the pairs
-// would be busy, each leftover tile is instead cut along K into S = P / (T % P) segments, one per pair.
+// Partial round. With T tiles on P pairs, T / P rounds keep every pair busy; the T % P tiles
+// left would occupy a few pairs for a whole tile time while the rest idle (448 tiles on 74
+// pairs: 4 tiles, a seventh round at 5 % occupancy). When at most half of the pairs would be
+// busy, each leftover tile is instead cut along K into S = P / (T % P) segments, one per pair,
+// and these segments are the FIRST thing the pairs do (while they are still in step).
 // A pair multiplies its segment as usual, writes its FP32 partial tile to scratch, and counts
 // itself in on the tile's counter; once all 2S CTAs of the tile have arrived (a bounded wait on
 // the counter: all pairs of the grid are resident, one CTA per SM), every CTA adds up the S
@@ -77,6 +78,8 @@ struct PairWork {
 };
 
 // it-th piece of work of `pair` (P pairs, T tiles, tail_segments = S or <= 1 for no split).
+// tail_segments < -1: S = -tail_segments and the split tiles come FIRST (it = 0 of the pairs that
+// have a segment), when all pairs are still in step, instead of after the whole rounds.
 __device__ __forceinline__ bool pair_work(int it, int pair, int num_pairs, int num_tiles,
                                           int k_tiles, int tail_segments, PairWork& w) {
   const int rounds = num_tiles / num_pairs;
@@ -85,6 +88,25 @@ __device__ __forceinline__ bool pair_work(int it, int pair, int num_pairs, int n
   w.seg = 0;
   w.segments = 1;
   w.tail_index = 0;
+  if (tail_segments < -1) {
+    const int s_count = -tail_segments;
+    const int first = rounds * num_pairs;
+    const int left = num_tiles - first;
+    const bool has_unit = pair < left * s_count;
+    if (has_unit && it == 0) {
+      w.tail_index = pair / s_count;
+      w.tile = first + w.tail_index;
+      w.seg = pair - w.tail_index * s_count;
+      w.segments = s_count;
+      w.kt_begin = static_cast<int>(static_cast<long long>(k_tiles) * w.seg / s_count);
+      w.kt_end = static_cast<int>(static_cast<long long>(k_tiles) * (w.seg + 1) / s_count);
+      return true;
+    }
+    const int whole = has_unit ? it - 1 : it;
+    if (whole >= rounds) return false;
+    w.tile = pair + whole * num_pairs;
+    return true;
+  }
   if (it < rounds) {
     w.tile = pair + it * num_pairs;
     return true;
