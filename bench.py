@@ -60,10 +60,10 @@ E2E_ROW_CHUNKS = max(1, int(os.environ.get("B12X_BENCH_E2E_CHUNKS", "8")))
 # bytes still held in the 126 MB L2 when the kernel ends are not in the write figure.
 NCU_TRAFFIC_BYTES = {
     "cfg0_nvfp4_128x4096x4096": 9_762_816 + 0,
-    "cfg1_nvfp4_decode_m16": 33_144_320 + 0,
-    "cfg2_mxfp8_prefill": 270_284_800 + 98_234_368,
+    "cfg1_nvfp4_decode_m16": 33_151_232 + 256,
+    "cfg2_mxfp8_prefill": 286_378_496 + 115_882_496,
     "cfg3_block_fp8_colpar": 298_083_840 + 131_562_752,
-    "cfg4_nvfp4_rowpar": 206_371_840 + 50_135_808,
+    "cfg4_nvfp4_rowpar": 223_142_656 + 62_427_648,
 }
 
 
