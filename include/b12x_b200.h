@@ -407,7 +407,7 @@ int b12x_b200_allreduce_peer(void* const* buffers, void* const* signals, int wor
  * rank * (M / world) + (row - s * (M / world)). destinations[s] is rank s's [M, ld] receive
  * buffer as mapped in this process (peer memory for s != rank): when all ranks' GEMMs have
  * finished, rank s holds every rank's partial of its slab, in slot order. BF16 or FP16; the
- * optional workspace is that of b12x_b200_gemm_blockscaled_ex (split last round).
+ * optional workspace is that of b12x_b200_gemm_blockscaled_ex (split leftover tiles).
  *
  * b12x_b200_allreduce_peer_scattered: the reduction that follows. Rank s adds the `world` slots
  * of its own receive buffer (buffers[s], local reads only) in FP32 in slot order, rounds once,

@@ -253,7 +253,7 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor | None, b: to
     decode = bool(small_m and 0 < m <= SMALL_M_MAX and n > 0)
     with torch.cuda.device(dev):
         # Decode kernel: counters and partial tiles. Tiled kernels: scratch for the CTA-pair
-        # kernel's split last round (0 when the shape has none).
+        # kernel's split leftover tiles (0 when the shape has none).
         need = int(lib.b12x_b200_gemm_grouped_workspace_bytes(
             kind, int(decode), m, n, k, groups, 0 if decode else block_n, sm_count))
     if need < 0:

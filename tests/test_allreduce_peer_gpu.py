@@ -135,7 +135,7 @@ def test_a_peer_that_never_arrives_ends_in_a_status_word_not_a_hang():
 @pytest.mark.parametrize("kind,world,m,n,k_local", [
     ("nvfp4", 2, 512, 512, 512), ("mxfp8", 2, 1024, 768, 256), ("nvfp4", 4, 1024, 520, 384),
     ("mxfp8", 8, 2048, 256, 128),
-    ("nvfp4", 2, 2048, 2560, 2048),      # 80 pair tiles on 74 pairs: the split last round scatters too
+    ("nvfp4", 2, 2048, 2560, 2048),      # 80 pair tiles on 74 pairs: the split leftover tiles scatter too
 ])
 def test_scattered_gemm_then_reduction_equals_the_sum_of_plain_partials(kind, world, m, n, k_local):
     """Each "rank" multiplies its K slice (separate launches that do not wait on each other:

@@ -845,7 +845,7 @@ def test_a_timed_out_wait_is_reported_and_the_next_gemm_is_correct():
     ("decode", 5, 200, 384, torch.float32), ("bn64", 130, 264, 384, torch.bfloat16),
     ("bn128", 256, 512, 256, torch.float32), ("bn256", 300, 504, 640, torch.float16),
     ("pair", 768, 1280, 1024, torch.bfloat16), ("pair", 300, 504, 640, torch.float32),
-    ("auto", 2048, 2560, 2048, torch.bfloat16),    # CTA-pair kernel with a split last round
+    ("auto", 2048, 2560, 2048, torch.bfloat16),    # CTA-pair kernel with split leftover tiles
 ])
 def test_fused_bias_equals_a_bias_add_on_the_stored_output(route, m, n, k, dtype):
     """The bias epilogue of every GEMM kernel must give, bit for bit, what adding the bias

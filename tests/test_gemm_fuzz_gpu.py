@@ -196,7 +196,7 @@ def _plain_fp8_cases():
         route = str(rng.choice(["auto", "bn64", "bn128", "bn192", "bn256", "pair"]))
         dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
         cases.append((i, m, n, k, route, dtype, bool(rng.integers(0, 2))))
-    cases.append((20, 2048, 2560, 2048, "auto", torch.bfloat16, False))   # pair kernel, split last round
+    cases.append((20, 2048, 2560, 2048, "auto", torch.bfloat16, False))   # pair kernel, split leftover tiles
     cases.append((21, 4096, 4096, 4096, "auto", torch.bfloat16, True))    # several rounds, two accumulators
     return cases
 
