@@ -700,7 +700,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
           slot = static_cast<int>(blockIdx.x) - first_cta;
         }
         float* my_slot = p.partials + (static_cast<size_t>(tile) * p.max_segments + slot) * slot_floats;
-        if (!EPI && whole && p.packed_store && staging_fits) {
+        if ((!EPI || p.quant_values == nullptr) && whole && p.packed_store && staging_fits) {
           // A lane holds one output column of every row, so storing from registers means one
           // 2-byte store per row and lane (64 bytes per warp instruction), and those stores
           // measured 75 ns apiece per warp: 1 us of a 16-row tile's epilogue and 4 us of a
@@ -730,7 +730,12 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
               if (c0 + 8 * h >= p.m) break;  // uniform: nothing but padding rows from here on
               float vals[8];
 #pragma unroll
-              for (int r = 0; r < 8; ++r) vals[r] = __uint_as_float(raw[8 * h + r]) * alpha;
+              for (int r = 0; r < 8; ++r) {
+                vals[r] = __uint_as_float(raw[8 * h + r]) * alpha;
+                if constexpr (EPI) {  // bias only (a quantized output keeps the per-lane path)
+                  if (p.bias != nullptr) vals[r] = add_bias_1(vals[r], p.bias, p.out_dtype, n_global, p.n);
+                }
+              }
               store_rows8_packed(p, buf, lane, c_group0, c0 + 8 * h, col0, vals);
             }
           }
@@ -810,10 +815,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                 for (int i = 0; i < 8; ++i) sum[i] += v[i];
               }
-              if (!EPI && p.packed_store && staging_fits) {
+              if ((!EPI || p.quant_values == nullptr) && p.packed_store && staging_fits) {
                 float vals[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) vals[i] = sum[i] * alpha;
+                for (int i = 0; i < 8; ++i) {
+                  vals[i] = sum[i] * alpha;
+                  if constexpr (EPI) {
+                    if (p.bias != nullptr) vals[i] = add_bias_1(vals[i], p.bias, p.out_dtype, n_global, p.n);
+                  }
+                }
                 store_rows8_packed(p, reinterpret_cast<uint16_t*>(staging) + quarter * 256, lane,
                                    c_group0, m0,
                                    (tile - grp * p.tiles_per_group) * 128 + quarter * 32, vals);
