@@ -397,7 +397,20 @@ def dense_gemm(
         load_path or "tma", bool(swap_ab), bool(sfb_k_replicated), alpha_is_one, stream_int,
     )
     t0 = time.perf_counter() if _B12X_TIMING else 0.0
-    if out is None:
+    if _direct_launch_ok(a_torch):
+        # Plain eager call on real CUDA tensors: what the custom op's body would do, without the
+        # dispatcher round trip of a 33-argument op (about half of the host time of a call).
+        # Tracing (torch.compile), fake tensors and meta tensors go through the ops below.
+        if out is None:
+            out = _empty_dense_gemm_output(m, n, l, dtype=_C_DTYPES[c_dtype], device=a_torch.device)
+        elif out.dtype != _C_DTYPES[c_dtype]:
+            raise ValueError(f"out dtype {out.dtype} does not match c_dtype={c_dtype!r}")
+        _dense_gemm_launch_flat(
+            a_torch, b_torch, sfa_torch, sfb_torch, out, alpha, n=n, k=k, l=l, ab_dtype=ab_dtype,
+            sf_dtype=sf_dtype, sf_vec_size=sf_vec_size, mma_tile_n=int(mma_tiler_mn[1]),
+            sm_count=int(sm_count), alpha_is_one=alpha_is_one, stream_int=stream_int,
+            mma_tile_m=int(mma_tiler_mn[0]))
+    elif out is None:
         out = torch.ops.b12x.dense_gemm_launch_functional(
             a_torch, b_torch, sfa_torch, sfb_torch, alpha, n, k, l, l, ab_dtype, sf_dtype,
             c_dtype, c_dtype, *op_tail)
@@ -413,6 +426,15 @@ def dense_gemm(
             logger.warning("b12x_dense_gemm timing m=%d n=%d k=%d l=%d enqueue=%.3fms",
                            m, n, k, l, ms)
     return out
+
+
+_DIRECT_LAUNCH = os.environ.get("B12X_B200_DIRECT_LAUNCH", "1") != "0"
+
+
+def _direct_launch_ok(t: torch.Tensor) -> bool:
+    """True for an ordinary eager call: a real CUDA tensor, nothing tracing."""
+    return (_DIRECT_LAUNCH and type(t) is torch.Tensor and t.is_cuda
+            and not torch.compiler.is_compiling())
 
 
 def _fused_quant_rhs(name: str, b: torch.Tensor, sfb: torch.Tensor, row_bytes: int):
