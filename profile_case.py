@@ -29,7 +29,8 @@ from sparkinfer_b200 import _native  # noqa: E402
 from sparkinfer_b200._lib import launch  # noqa: E402
 
 OPS = ("mxfp8", "nvfp4", "pair_mxfp8", "pair_nvfp4", "decode_nvfp4", "decode_mxfp8",
-       "fused_nvfp4", "fused_mxfp8", "fp8", "pair_fp8", "block_fp8", "quant_mxfp8", "quant_nvfp4")
+       "fused_nvfp4", "fused_mxfp8", "fp8", "pair_fp8", "scatter2_nvfp4", "scatter4_nvfp4",
+       "scatter8_nvfp4", "block_fp8", "quant_mxfp8", "quant_nvfp4")
 
 
 def build_case(op: str, m: int, n: int, k: int, device: torch.device):
@@ -75,6 +76,21 @@ def build_case(op: str, m: int, n: int, k: int, device: torch.device):
         block_n = _native.BLOCK_N_PAIR if op.startswith("pair") else 0
         return lambda: launch.gemm_blockscaled(_native.KIND_FP8, a, None, b, None, c, None, m, n, k,
                                                block_n=block_n)
+    if op in ("scatter2_nvfp4", "scatter4_nvfp4", "scatter8_nvfp4"):
+        # The row-parallel GEMM of one rank with every slab owner's receive buffer on this GPU
+        # (the scatter itself, without the links).
+        world = int(op[7])
+        k_atoms = (k + 63) // 64
+        a, b = codes((m, k // 2)), codes((n, k // 2))
+        sfa = torch.full((((m + 127) // 128) * k_atoms * 512,), 0x38, dtype=torch.uint8, device=device)
+        sfb = torch.full((((n + 127) // 128) * k_atoms * 512,), 0x38, dtype=torch.uint8, device=device)
+        recv = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(world)]
+        ptrs = [t.data_ptr() for t in recv]
+
+        def run(recv=recv):  # the closure keeps the receive buffers alive
+            launch.gemm_blockscaled_scatter(1, a, sfa, b, sfb, ptrs, 0, torch.bfloat16, None, m, n, k)
+
+        return run
     if op == "block_fp8":
         a, b = codes((m, k)), codes((n, k))
         sa = torch.rand((m, k // 128), device=device, generator=g) + 0.5
