@@ -986,3 +986,26 @@ def test_mm_grouped_batches_run_in_one_launch(m, n, k, groups, tile):
         assert_gemm_close(out[:, :, g], refs[g])
     from sparkinfer_b200._lib.launch import check_kernel_status
     check_kernel_status(DEV)
+
+
+def test_mm_through_the_custom_ops_equals_the_direct_launch(monkeypatch):
+    """A plain eager call launches directly; tracing goes through b12x::dense_gemm_launch and
+    b12x::dense_gemm_launch_functional. Both routes must run the same kernel on the same
+    arguments: identical bytes, with and without a caller-owned output."""
+    from gpu_util import DEV, mxfp8_operand
+    from sparkinfer_b200._lib import dense_gemm as dg
+    from sparkinfer_b200.gemm import blockscaled
+
+    m, n, k = 48, 384, 512
+    lhs, _ = mxfp8_operand(seeded_bf16(901, (m, k), 0.25))
+    rhs, _ = mxfp8_operand(seeded_bf16(902, (n, k), 0.03))
+    direct = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **MXFP8)
+    direct_out = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm(lhs, rhs, direct_out, c_dtype="bfloat16", **MXFP8)
+    monkeypatch.setattr(dg, "_DIRECT_LAUNCH", False)
+    via_functional = blockscaled.mm(lhs, rhs, c_dtype="bfloat16", **MXFP8)
+    via_op = torch.full((m, n, 1), float("nan"), dtype=torch.bfloat16, device=DEV)
+    blockscaled.mm(lhs, rhs, via_op, c_dtype="bfloat16", **MXFP8)
+    torch.cuda.synchronize()
+    for t in (direct_out, via_functional, via_op):
+        assert torch.equal(t.view(torch.int16), direct.view(torch.int16))
