@@ -43,7 +43,12 @@ enum {
    * dense_gemm(plain_fp8=True), b12x/_lib/dense_gemm.py:7096-7139, 7225-7233; MMA :268-330, per-tensor FP8 linears).
    * sfa / sfb are ignored and may be NULL. Accepted by b12x_b200_gemm_blockscaled, _ex,
    * _grouped and _scatter (tiled and CTA-pair kernels); the decode entry points refuse it. */
-  B12X_B200_KIND_FP8 = 2
+  B12X_B200_KIND_FP8 = 2,
+  /* MXFP4: packed E2M1 codes (as NVFP4) with one UE8M0 scale per 32 elements of K, scale atoms
+   * of 128 rows x 4 scale columns = 128 elements of K (the reference's float4_e2m1fn operands
+   * with sf_dtype float8_e8m0fnu / sf_vec_size 32, b12x/_lib/dense_gemm.py:7225-7260). Tiled
+   * and CTA-pair kernels; the decode entry points refuse it. */
+  B12X_B200_KIND_MXFP4 = 3
 };
 
 /* Element types of dense tensors. */

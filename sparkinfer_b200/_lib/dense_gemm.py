@@ -73,9 +73,12 @@ def _kind_of(ab_dtype: str, sf_dtype: str, sf_vec_size: int) -> int:
     if ab_dtype == "float4_e2m1fn":
         if sf_dtype == "float8_e4m3fn" and sf_vec_size == 16:
             return _native.KIND_NVFP4
+        if sf_dtype == "float8_e8m0fnu" and sf_vec_size == 32:
+            return _native.KIND_MXFP4
         raise ValueError(
-            "float4_e2m1fn operands are supported as NVFP4 only (sf_dtype='float8_e4m3fn', "
-            f"sf_vec_size=16); got sf_dtype={sf_dtype!r}, sf_vec_size={sf_vec_size}")
+            "float4_e2m1fn operands need sf_dtype='float8_e4m3fn' with sf_vec_size=16 (NVFP4) or "
+            f"sf_dtype='float8_e8m0fnu' with sf_vec_size=32 (MXFP4); got sf_dtype={sf_dtype!r}, "
+            f"sf_vec_size={sf_vec_size}")
     if sf_dtype == "float8_e8m0fnu" and sf_vec_size == 32:
         return _native.KIND_MXFP8
     raise ValueError(
@@ -107,7 +110,7 @@ def _dense_gemm_launch_flat(a, b, sfa, sfb, c, alpha, *, n: int, k: int, l: int,
                             ) -> None:
     kind = _kind_of(ab_dtype, sf_dtype, sf_vec_size)
     m = int(a.shape[0])
-    row_bytes = k // 2 if kind == _native.KIND_NVFP4 else k
+    row_bytes = k // 2 if kind in (_native.KIND_NVFP4, _native.KIND_MXFP4) else k
     _check_operand("A", a, m, row_bytes, l)
     _check_operand("B", b, n, row_bytes, l)
     if not mma_view_is_canonical(sfa, m, k, sf_vec_size, l):

@@ -390,7 +390,8 @@ PairTailPlan plan_pair_tail(int kind, int64_t m, int64_t n, int64_t k, int64_t g
   if (t.pairs < 1 || !switches().pair_tail_split) return t;
   const int64_t rounds = tiles / t.pairs;
   t.left = int(tiles - rounds * t.pairs);
-  const int elems_per_stage = (kind == B12X_B200_KIND_NVFP4) ? 256 : 128;
+  const int elems_per_stage =
+      (kind == B12X_B200_KIND_NVFP4 || kind == B12X_B200_KIND_MXFP4) ? 256 : 128;
   const int64_t k_tiles = (k + elems_per_stage - 1) / elems_per_stage;
   // Split when the leftover tiles would keep at most half of the pairs busy, and never below two
   // k-tiles per segment. The split tiles are done FIRST, while all pairs are still in step: a
@@ -430,9 +431,11 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
                           const ScatterPlan* scatter = nullptr) {
   if (groups < 1 || groups > 65535)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be in [1, 65535]");
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8)
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8 &&
+      kind != B12X_B200_KIND_MXFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
   const bool scaled = kind != B12X_B200_KIND_FP8;
+  const bool fp4 = kind == B12X_B200_KIND_NVFP4 || kind == B12X_B200_KIND_MXFP4;
   if (c_dtype < B12X_B200_BF16 || c_dtype > B12X_B200_FP32)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
   if (m < 0 || n < 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX)
@@ -467,7 +470,7 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
   }
   const int sf_vec = (kind == B12X_B200_KIND_NVFP4) ? 16 : 32;
   if (k % 32 != 0) return fail(B12X_B200_ERR_UNSUPPORTED, "K must be a multiple of 32");
-  const int64_t row_bytes = (kind == B12X_B200_KIND_NVFP4) ? k / 2 : k;
+  const int64_t row_bytes = fp4 ? k / 2 : k;
   if (row_bytes % 16 != 0) return fail(B12X_B200_ERR_ALIGNMENT, "operand rows must be 16-byte multiples");
   if (!aligned16(a) || !aligned16(b) || (scaled && (!aligned16(sfa) || !aligned16(sfb))))
     return fail(B12X_B200_ERR_ALIGNMENT, "operand and scale pointers must be 16-byte aligned");
@@ -563,18 +566,24 @@ int gemm_blockscaled_impl(int kind, const void* a, const void* sfa, const void* 
         return launch_gemm_pair_impl<kMxfp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
       if (kind == B12X_B200_KIND_FP8)
         return launch_gemm_pair_impl<kFp8, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
+      if (kind == B12X_B200_KIND_MXFP4)
+        return launch_gemm_pair_impl<kMxfp4, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
       return launch_gemm_pair_impl<kNvfp4, 256, false, true>(map_a, map_b, map_c, p, tail, pairs, s, sc);
     }
     if (kind == B12X_B200_KIND_MXFP8)
       return launch_gemm_pair<kMxfp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
     if (kind == B12X_B200_KIND_FP8)
       return launch_gemm_pair<kFp8, 256>(map_a, map_b, map_c, p, tail, pairs, s);
+    if (kind == B12X_B200_KIND_MXFP4)
+      return launch_gemm_pair<kMxfp4, 256>(map_a, map_b, map_c, p, tail, pairs, s);
     return launch_gemm_pair<kNvfp4, 256>(map_a, map_b, map_c, p, tail, pairs, s);
   }
   if (kind == B12X_B200_KIND_MXFP8)
     return dispatch_block_n<kMxfp8>(bn, map_a, map_b, map_c, p, grid, s);
   if (kind == B12X_B200_KIND_FP8)
     return dispatch_block_n<kFp8>(bn, map_a, map_b, map_c, p, grid, s);
+  if (kind == B12X_B200_KIND_MXFP4)
+    return dispatch_block_n<kMxfp4>(bn, map_a, map_b, map_c, p, grid, s);
   return dispatch_block_n<kNvfp4>(bn, map_a, map_b, map_c, p, grid, s);
 }
 
@@ -617,7 +626,8 @@ namespace {
 
 int64_t tiled_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k, int64_t groups,
                               int block_n, int sm_count) {
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8)
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_FP8 &&
+      kind != B12X_B200_KIND_MXFP4)
     return -1;
   if (m <= 0 || n <= 0 || k <= 0 || groups < 1) return 0;
   DeviceInfo info;

@@ -5,6 +5,8 @@
 // A and B are K-major. Two operand recipes share one kernel template:
 //   kMxfp8 : E4M3 codes, one UE8M0 scale per 32 elements of K  (tcgen05 kind::mxf8f6f4)
 //   kNvfp4 : packed E2M1 codes (low nibble = even k), one UE4M3 scale per 16 elements
+//   kMxfp4 : packed E2M1 codes, one UE8M0 scale per 32 elements (kind::mxf4nvf4, scale_vec::2X):
+//            a 512-byte scale atom covers 128 elements of K, i.e. two K = 64 instructions
 //   kFp8   : E4M3 codes without block scales (tcgen05 kind::f8f6f4); alpha is the only scale.
 //            No scale bytes are loaded or copied to tensor memory, and the columns they would
 //            take hold a second accumulator instead.
@@ -28,7 +30,7 @@
 
 namespace b12x_b200 {
 
-enum OperandKind : int { kMxfp8 = 0, kNvfp4 = 1, kFp8 = 2 };
+enum OperandKind : int { kMxfp8 = 0, kNvfp4 = 1, kFp8 = 2, kMxfp4 = 3 };
 enum OutDtype : int { kOutBf16 = 0, kOutFp16 = 1, kOutFp32 = 2 };
 
 template <int KIND, int BN>
@@ -40,7 +42,7 @@ struct GemmTile {
   static constexpr int kRowBytes = 128;                       // bytes of K per stage and row
   static constexpr int kMmasPerStage = 4;                     // 32 bytes of K per instruction
   static constexpr bool kScaled = (KIND != kFp8);
-  static constexpr int kElemsPerMma = (KIND == kNvfp4) ? 64 : 32;
+  static constexpr int kElemsPerMma = (KIND == kNvfp4 || KIND == kMxfp4) ? 64 : 32;
   static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
   static constexpr int kSfVec = (KIND == kNvfp4) ? 16 : 32;
   static constexpr int kElemsPerAtom = kSfVec * 4;            // K covered by one scale atom
@@ -342,7 +344,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t idesc_base =
         KIND == kFp8 ? make_idesc_f8(128, BN)
                      : make_idesc_block_scaled(128, BN, KIND == kMxfp8 ? 0u : 1u,
-                                               KIND == kMxfp8 ? 1u : 0u);
+                                               KIND == kNvfp4 ? 0u : 1u);
     int stage = 0;
     uint32_t phase = 0;
     int iter = 0;
@@ -401,6 +403,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
                   tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                               idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                               sfb_taddr);
+                else if (KIND == kMxfp4)
+                  tc_mma_mxf4(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, (j & 1) * 2, (j & 1) * 2), accumulate,
+                              T::kSfaCol0 + (j >> 1) * 4,
+                              sfb_taddr + (j >> 1) * T::kSfbRowAtoms * 4);
                 else
                   tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
                               T::kSfaCol0 + j * 4, sfb_taddr + j * T::kSfbRowAtoms * 4);
@@ -414,6 +421,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
                   tc_mma_mxf8(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                               idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                               sfb_taddr);
+                else if (KIND == kMxfp4)
+                  tc_mma_mxf4(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, (j & 1) * 2, (j & 1) * 2), accumulate,
+                              T::kSfaCol0 + (j >> 1) * 4,
+                              sfb_taddr + (j >> 1) * T::kSfbRowAtoms * 4);
                 else
                   tc_mma_nvf4(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
                               T::kSfaCol0 + j * 4, sfb_taddr + j * T::kSfbRowAtoms * 4);

@@ -46,9 +46,9 @@ struct PairTile {
   static constexpr int kRowBytes = 128;
   static constexpr int kMmasPerStage = 4;
   static constexpr bool kScaled = (KIND != kFp8);
-  static constexpr int kElemsPerMma = (KIND == kNvfp4) ? 64 : 32;
+  static constexpr int kElemsPerMma = (KIND == kNvfp4 || KIND == kMxfp4) ? 64 : 32;
   static constexpr int kElemsPerStage = kElemsPerMma * kMmasPerStage;
-  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : (KIND == kNvfp4 ? 4 : 0);
+  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : (KIND == kNvfp4 ? 4 : (KIND == kMxfp4 ? 2 : 0));
   static constexpr int kSfbRowAtoms = BN / 128;
   static constexpr int kABytes = BM * kRowBytes;
   static constexpr int kBBytes = (BN / 2) * kRowBytes;         // this CTA's half of B
@@ -342,7 +342,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t idesc_base =
         KIND == kFp8 ? make_idesc_f8(256, BN)
                      : make_idesc_block_scaled(256, BN, KIND == kMxfp8 ? 0u : 1u,
-                                               KIND == kMxfp8 ? 1u : 0u);
+                                               KIND == kNvfp4 ? 0u : 1u);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -392,6 +392,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               tc_mma_mxf8_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
                                idesc_with_sf_ids(idesc_base, j, j), accumulate, T::kSfaCol0,
                                T::kSfbCol0);
+            else if (KIND == kMxfp4)
+              tc_mma_mxf4_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j,
+                               idesc_with_sf_ids(idesc_base, (j & 1) * 2, (j & 1) * 2), accumulate,
+                               T::kSfaCol0 + (j >> 1) * 4,
+                               T::kSfbCol0 + (j >> 1) * T::kSfbRowAtoms * 4);
             else
               tc_mma_nvf4_pair(d_taddr, adesc + 2 * j, bdesc + 2 * j, idesc_base, accumulate,
                                T::kSfaCol0 + j * 4, T::kSfbCol0 + j * T::kSfbRowAtoms * 4);

@@ -302,6 +302,23 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_taddr, uint64_t adesc, ui
       : "memory");
 }
 
+// MXFP4: E2M1 codes with one UE8M0 scale per 32 elements, K = 64 per instruction (two scale
+// bytes of each operand's 4-byte scale word, chosen by the scale ids in the descriptor: 0 or 2).
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate,
+                                            uint32_t sfa_taddr, uint32_t sfb_taddr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n"
+      ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_taddr),
+      "r"(sfb_taddr)
+      : "memory");
+}
+
 // Unscaled E4M3 x E4M3 -> FP32, K = 32 per instruction.
 __device__ __forceinline__ void tc_mma_f8(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
                                           uint32_t idesc, uint32_t accumulate) {
@@ -435,6 +452,21 @@ __device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t d_taddr, uint64_t ades
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n"
+      ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_taddr),
+      "r"(sfb_taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_mxf4_pair(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate,
+                                                 uint32_t sfa_taddr, uint32_t sfb_taddr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::2X "
       "[%0], %1, %2, %3, [%5], [%6], p;\n"
       "}\n"
       ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_taddr),

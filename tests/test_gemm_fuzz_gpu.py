@@ -34,9 +34,13 @@ def _operand(kind: str, rows: int, k: int, gen, dev):
             scales.float() - 127.0).repeat_interleave(32, dim=1)
         return codes, _atoms(scales, 127), deq
     packed = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev, generator=gen)
-    scales = torch.randint(0x18, 0x31, (rows, k // 16), dtype=torch.uint8, device=dev, generator=gen)
     lut = torch.tensor(E2M1, dtype=torch.float32, device=dev)
     vals = torch.stack((lut[(packed & 0xF).long()], lut[(packed >> 4).long()]), dim=-1).view(rows, k)
+    if kind == "mxfp4":
+        scales = torch.randint(121, 129, (rows, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+        deq = vals * torch.exp2(scales.float() - 127.0).repeat_interleave(32, dim=1)
+        return packed, _atoms(scales, 127), deq
+    scales = torch.randint(0x18, 0x31, (rows, k // 16), dtype=torch.uint8, device=dev, generator=gen)
     deq = vals * scales.view(torch.float8_e4m3fn).float().repeat_interleave(16, dim=1)
     return packed, _atoms(scales, 0), deq
 
@@ -244,3 +248,69 @@ def test_plain_fp8_refuses_the_decode_kernel():
     out = torch.empty((8, 64), dtype=torch.bfloat16, device=dev)
     with pytest.raises(ValueError, match="tiled kernels only"):
         launch.gemm_blockscaled(KIND_FP8, z, None, z, None, out, None, 8, 64, 128, small_m=True)
+
+
+def _mxfp4_cases():
+    rng = np.random.default_rng(4321)
+    cases = []
+    for i in range(20):
+        m = int(rng.choice([1, 17, 64, 128, 129, 200, 256, 300, 511, 640, 1024]))
+        n = int(rng.choice([8, 64, 72, 128, 192, 200, 256, 264, 512, 776, 1024, 1288]))
+        k = 64 * int(rng.integers(1, 40))
+        route = str(rng.choice(["auto", "bn64", "bn128", "bn192", "bn256", "pair", "pair"]))
+        dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
+        cases.append((i, m, n, k, route, dtype))
+    cases.append((20, 2048, 4608, 2048, "auto", torch.bfloat16))
+    cases.append((21, 4096, 2304, 1600, "pair", torch.bfloat16))   # leftover tiles split along K
+    return cases
+
+
+@pytest.mark.parametrize("index,m,n,k,route,dtype", _mxfp4_cases())
+def test_mxfp4_matches_fp32_reference(index, m, n, k, route, dtype):
+    """E2M1 codes with UE8M0 scales per 32 elements (scale_vec::2X of the FP4 MMA): every tile
+    width of the tiled kernel and the CTA-pair kernel, K with a half-filled scale atom."""
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._native import BLOCK_N_PAIR, KIND_MXFP4
+    from tests.gpu_util import assert_whole_output_close
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(7000 + index)
+    a, sfa, a_deq = _operand("mxfp4", m, k, gen, dev)
+    b, sfb, b_deq = _operand("mxfp4", n, k, gen, dev)
+    alpha = torch.tensor([0.5], dtype=torch.float32, device=dev)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=dev)
+    kwargs = {}
+    if route.startswith("bn"):
+        kwargs["block_n"] = int(route[2:])
+    elif route == "pair":
+        kwargs["block_n"] = BLOCK_N_PAIR
+    launch.gemm_blockscaled(KIND_MXFP4, a, sfa, b, sfb, out, alpha, m, n, k, **kwargs)
+    torch.cuda.synchronize()
+    launch.check_kernel_status(dev)
+    assert_whole_output_close(out, a_deq, b_deq, 0.5, out_dtype=dtype)
+
+
+def test_mxfp4_refuses_the_decode_kernel_and_runs_through_mm():
+    """The public ``blockscaled.mm`` accepts float4_e2m1fn with float8_e8m0fnu / 32 scales (the
+    reference's MXF4 mode, b12x/_lib/dense_gemm.py:580-582) and never routes it to the decode
+    kernel; forcing that kernel is an error."""
+    from sparkinfer_b200._lib import launch
+    from sparkinfer_b200._lib.layout import convert_sf_to_mma_layout as mma_view
+    from sparkinfer_b200._native import KIND_MXFP4
+    from sparkinfer_b200.gemm import blockscaled
+    from tests.gpu_util import assert_whole_output_close
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(99)
+    m, n, k = 16, 4096, 1024        # a decode shape for the other recipes
+    a, sfa, a_deq = _operand("mxfp4", m, k, gen, dev)
+    b, sfb, b_deq = _operand("mxfp4", n, k, gen, dev)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    with pytest.raises(ValueError, match="tiled kernels only"):
+        launch.gemm_blockscaled(KIND_MXFP4, a, sfa, b, sfb, out, None, m, n, k, small_m=True)
+    got = blockscaled.mm(
+        (a.view(m, k // 2, 1), mma_view(sfa.view(torch.float8_e8m0fnu), m, k, 1, 32)),
+        (b.view(n, k // 2, 1), mma_view(sfb.view(torch.float8_e8m0fnu), n, k, 1, 32)),
+        ab_dtype="float4_e2m1fn", sf_dtype="float8_e8m0fnu", c_dtype="bfloat16", sf_vec_size=32)
+    torch.cuda.synchronize()
+    assert_whole_output_close(got[:, :, 0], a_deq, b_deq, 1.0)

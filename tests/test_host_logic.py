@@ -156,9 +156,9 @@ def test_blockscaled_mm_validates_before_launch():
     with pytest.raises(ValueError, match="mutually exclusive"):
         blockscaled.mm((a, sf), (a, sf), ab_dtype="float4_e2m1fn", b_packed=True,
                        b_preexpanded=True, **kw)
-    with pytest.raises(ValueError, match="NVFP4 only"):
+    with pytest.raises(ValueError, match=r"\(NVFP4\) or"):
         blockscaled.mm((a, sf), (a, sf), ab_dtype="float4_e2m1fn", sf_dtype="float8_e8m0fnu",
-                       c_dtype="bfloat16", sf_vec_size=32, sm_count=148)
+                       c_dtype="bfloat16", sf_vec_size=16, sm_count=148)
     with pytest.raises(ValueError, match="CUDA"):
         blockscaled.mm((a, sf), (a, sf), ab_dtype="float4_e2m1fn", **kw)
 
