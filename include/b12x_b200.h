@@ -450,6 +450,26 @@ int b12x_b200_pack_block_fp8_weight_mxfp8(const void* codes, const float* scale,
                                           int64_t groups, int requantize,
                                           b12x_b200_stream_t stream);
 
+/*
+ * Batched C[b] = A[b] @ dequant(W[b]) for b < batch: A BF16 [batch, M, K] with 1 <= M <= 32, W
+ * rowwise MXFP8 (E4M3 codes and one UE8M0 byte per 32 codes of the contiguous axis), C BF16
+ * [batch, M, N], FP32 accumulation. Replaces the launch of the MXFP8 backend of b12x.gemm.bmm
+ * (b12x/gemm/_shared/mxfp8_bmm.py:1771-1834, kernel :446-1040; public contract
+ * b12x/gemm/_bmm/api.py:41-83).
+ *   n_major == 0: codes [batch, N, K], scales [batch, N, K/32]; K % 32 == 0.
+ *   n_major != 0: codes [batch, K, N], scales [batch, K, N/32]; N % 32 == 0, K % 8 == 0.
+ * Every tensor is given by its base and the strides (in elements) of its two outer axes; the
+ * inner axis is contiguous. A rows and weight rows start on 16-byte boundaries, C rows on
+ * 4-byte boundaries. A weight is dequantized as BF16(code * 2^(byte - 127)) (byte 255 is NaN).
+ * No workspace, no allocation, no status word (the kernel waits on nothing); safe to capture in
+ * a CUDA graph. Each output is a fixed-order sum, so repeated launches give identical bits.
+ */
+int b12x_b200_bmm_mxfp8(const void* a, int64_t a_stride_b, int64_t a_stride_m,
+                        const void* w_values, int64_t w_stride_b, int64_t w_stride_r,
+                        const void* w_scales, int64_t sf_stride_b, int64_t sf_stride_r, void* c,
+                        int64_t c_stride_b, int64_t c_stride_m, int n_major, int64_t batch,
+                        int64_t m, int64_t n, int64_t k, b12x_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,18 +33,23 @@ __version__ = "0.1.0"
 
 # group -> op names; one directory per op, checked by tests/test_registry.py.
 _OPS: dict[str, tuple[str, ...]] = {
-    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear", "tensor_fp8_linear"),
+    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear", "tensor_fp8_linear", "bmm"),
     "quantization": ("nvfp4", "mxfp8"),
 }
+
+# A group-level function cannot share its name with a child module: ``gemm.bmm`` is a function,
+# its metadata and implementation live in a private package (b12x/__init__.py:64-72).
+_OP_MODULE_OVERRIDES: dict[str, str] = {"gemm.bmm": "gemm._bmm"}
+
+
+def _op_module(group: str, name: str):
+    path = _OP_MODULE_OVERRIDES.get(f"{group}.{name}", f"{group}.{name}")
+    return importlib.import_module(f"{__name__}.{path}")
 
 
 def list_ops() -> list[OpMeta]:
     """META of every op, in registry order."""
-    return [
-        importlib.import_module(f"{__name__}.{group}.{name}").META
-        for group, names in _OPS.items()
-        for name in names
-    ]
+    return [_op_module(group, name).META for group, names in _OPS.items() for name in names]
 
 
 def find_op(qualname: str) -> OpMeta:
@@ -52,7 +57,7 @@ def find_op(qualname: str) -> OpMeta:
     group, _, name = qualname.partition(".")
     if name not in _OPS.get(group, ()):
         raise KeyError(f"unknown op {qualname!r}")
-    return importlib.import_module(f"{__name__}.{group}.{name}").META
+    return _op_module(group, name).META
 
 
 def clear_all_caches() -> None:

@@ -449,6 +449,25 @@ def pack_block_fp8_weight_mxfp8(codes: torch.Tensor, scale: torch.Tensor, out_co
     _native.check(rc, "b12x_b200_pack_block_fp8_weight_mxfp8")
 
 
+def bmm_mxfp8(a: torch.Tensor, w_values: torch.Tensor, w_scales: torch.Tensor, out: torch.Tensor,
+              *, n_major: bool, batch: int, m: int, n: int, k: int,
+              stream_int: int | None = None) -> None:
+    """``out[b] = a[b] @ dequant(w[b])``: BF16 ``a [B, M, K]`` (M <= 32), rowwise-MXFP8 weights
+    (``[B, N, K]`` K-major or ``[B, K, N]`` N-major, one UE8M0 byte per 32 codes of the inner
+    axis), BF16 ``out [B, M, N]``. The tensors may be strided views; inner axes are contiguous."""
+    for name, t in (("a", a), ("w_values", w_values), ("w_scales", w_scales), ("out", out)):
+        _require_cuda(name, t)
+    dev = a.device
+    with torch.cuda.device(dev):
+        rc = _native.load().b12x_b200_bmm_mxfp8(
+            a.data_ptr(), a.stride(0), a.stride(1),
+            w_values.data_ptr(), w_values.stride(0), w_values.stride(1),
+            w_scales.data_ptr(), w_scales.stride(0), w_scales.stride(1),
+            out.data_ptr(), out.stride(0), out.stride(1), 1 if n_major else 0,
+            batch, m, n, k, _stream_ptr(stream_int, dev))
+    _native.check(rc, "b12x_b200_bmm_mxfp8")
+
+
 def allreduce_peer_signal_bytes() -> int:
     return int(_native.load().b12x_b200_allreduce_peer_signal_bytes())
 

@@ -111,6 +111,11 @@ SIGNATURES = {
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_i64, _c_int,
          _c_void_p],
     ),
+    "b12x_b200_bmm_mxfp8": (
+        _c_int,
+        [_c_void_p, _c_i64, _c_i64, _c_void_p, _c_i64, _c_i64, _c_void_p, _c_i64, _c_i64,
+         _c_void_p, _c_i64, _c_i64, _c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p],
+    ),
     "b12x_b200_allreduce_peer_signal_bytes": (_c_i64, []),
     "b12x_b200_gemm_blockscaled_scatter": (
         _c_int,

@@ -17,6 +17,7 @@
 #include "quantize.cuh"
 #include "allreduce_peer.cuh"
 #include "pack_weight.cuh"
+#include "bmm_mxfp8.cuh"
 
 namespace b12x_b200 {
 namespace {
@@ -1518,4 +1519,90 @@ extern "C" int b12x_b200_pack_block_fp8_weight_mxfp8(const void* codes, const fl
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(err, "pack_block_fp8_weight launch");
   return B12X_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Batched BF16 x rowwise-MXFP8 product (the MLA absorb projections)
+// ------------------------------------------------------------------------------------------
+namespace {
+
+template <int MAJOR, int MT>
+int launch_bmm(const BmmParams& p, int batch, cudaStream_t stream) {
+  using S = BmmShape<MAJOR, MT>;
+  if (S::kSmemBytes > 48 * 1024) {
+    static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !set_for[dev]) {
+      const cudaError_t attr_err =
+          cudaFuncSetAttribute(bmm_mxfp8_kernel<MAJOR, MT>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+      if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+      set_for[dev] = true;
+    }
+  }
+  const dim3 grid(unsigned((p.n + S::kTileN - 1) / S::kTileN), unsigned(batch), 1);
+  bmm_mxfp8_kernel<MAJOR, MT><<<grid, kBmmThreads, S::kSmemBytes, stream>>>(p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "bmm_mxfp8 launch");
+  return B12X_B200_OK;
+}
+
+template <int MAJOR>
+int dispatch_bmm_rows(const BmmParams& p, int batch, cudaStream_t stream) {
+  if (p.m <= 8) return launch_bmm<MAJOR, 8>(p, batch, stream);
+  if (p.m <= 16) return launch_bmm<MAJOR, 16>(p, batch, stream);
+  return launch_bmm<MAJOR, 32>(p, batch, stream);
+}
+
+}  // namespace
+
+extern "C" int b12x_b200_bmm_mxfp8(const void* a, int64_t a_stride_b, int64_t a_stride_m,
+                                   const void* w_values, int64_t w_stride_b, int64_t w_stride_r,
+                                   const void* w_scales, int64_t sf_stride_b, int64_t sf_stride_r,
+                                   void* c, int64_t c_stride_b, int64_t c_stride_m, int n_major,
+                                   int64_t batch, int64_t m, int64_t n, int64_t k,
+                                   b12x_b200_stream_t stream) {
+  if (batch <= 0 || batch > 65535 || m <= 0 || n <= 0 || k <= 0 || n > INT32_MAX - 64 ||
+      k > INT32_MAX)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad size");
+  if (m > 32) return fail(B12X_B200_ERR_UNSUPPORTED, "the batched product takes at most 32 rows");
+  if (!a || !w_values || !w_scales || !c) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (n_major) {
+    if (n % 32 != 0 || k % 8 != 0)
+      return fail(B12X_B200_ERR_UNSUPPORTED, "N-major weights need N % 32 == 0 and K % 8 == 0");
+  } else if (k % 32 != 0) {
+    return fail(B12X_B200_ERR_UNSUPPORTED, "K-major weights need K % 32 == 0");
+  }
+  if (!aligned16(a) || a_stride_b % 8 != 0 || a_stride_m % 8 != 0)
+    return fail(B12X_B200_ERR_ALIGNMENT, "A rows must start on 16-byte boundaries");
+  if (!aligned16(w_values) || w_stride_b % 16 != 0 || w_stride_r % 16 != 0)
+    return fail(B12X_B200_ERR_ALIGNMENT, "weight rows must start on 16-byte boundaries");
+  if ((uintptr_t(c) & 3) || c_stride_b % 2 != 0 || c_stride_m % 2 != 0)
+    return fail(B12X_B200_ERR_ALIGNMENT, "C rows must start on 4-byte boundaries");
+  if (a_stride_b < 0 || a_stride_m < 0 || w_stride_b < 0 || w_stride_r < 0 || sf_stride_b < 0 ||
+      sf_stride_r < 0 || c_stride_b < 0 || c_stride_m < 0)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "negative stride");
+  DeviceInfo info;
+  const int rc = device_info(&info);
+  if (rc != B12X_B200_OK) return rc;
+  if (info.cc_major != 10) return fail(B12X_B200_ERR_NO_DEVICE_CODE, "device is not sm_100");
+  BmmParams p;
+  p.a = static_cast<const __nv_bfloat16*>(a);
+  p.a_stride_b = a_stride_b;
+  p.a_stride_m = a_stride_m;
+  p.w = static_cast<const uint8_t*>(w_values);
+  p.w_stride_b = w_stride_b;
+  p.w_stride_r = w_stride_r;
+  p.sf = static_cast<const uint8_t*>(w_scales);
+  p.sf_stride_b = sf_stride_b;
+  p.sf_stride_r = sf_stride_r;
+  p.c = static_cast<__nv_bfloat16*>(c);
+  p.c_stride_b = c_stride_b;
+  p.c_stride_m = c_stride_m;
+  p.m = int(m);
+  p.n = int(n);
+  p.k = int(k);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return n_major ? dispatch_bmm_rows<1>(p, int(batch), s) : dispatch_bmm_rows<0>(p, int(batch), s);
 }

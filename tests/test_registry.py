@@ -18,15 +18,19 @@ def test_ops_table_matches_directories():
         group_dir = ROOT / "sparkinfer_b200" / group
         on_disk = {p.name for p in group_dir.iterdir()
                    if p.is_dir() and not p.name.startswith("_")}
-        assert on_disk == set(names), (group, on_disk, names)
+        private = {q.split(".")[1] for q in pkg._OP_MODULE_OVERRIDES if q.startswith(group + ".")}
+        assert on_disk == set(names) - private, (group, on_disk, names)
+        for qualname, path in pkg._OP_MODULE_OVERRIDES.items():
+            assert (ROOT / "sparkinfer_b200" / path.replace(".", "/")).is_dir(), qualname
 
 
 @pytest.mark.parametrize("meta", pkg.list_ops(), ids=lambda m: m.qualname)
 def test_meta_shape_and_entry_points(meta):
     assert meta.archs == ("sm100a",)
     assert meta.api_style in ("planned", "oneshot")
-    assert meta.entry_points and "is_supported" in meta.entry_points
-    module = importlib.import_module(f"sparkinfer_b200.{meta.group}.{meta.name}")
+    assert meta.entry_points and any(e in meta.entry_points
+                                     for e in ("is_supported", f"is_{meta.name}_supported"))
+    module = pkg._op_module(meta.group, meta.name)
     for name in meta.entry_points:
         assert getattr(module, name) is not None
     assert sorted(dir(module)) == sorted([*meta.entry_points, "META"])
@@ -92,3 +96,55 @@ def test_graft_entry_build_runs_without_a_gpu():
     import __graft_entry__ as entry
 
     entry.build()
+
+
+def test_gemm_group_exposes_flat_functions():
+    """``gemm.mm`` is ``blockscaled.mm``; ``gemm.bmm`` is a function, not an op package
+    (the reference's tests/gemm/test_bmm.py:116-140)."""
+    from sparkinfer_b200 import gemm
+
+    pkg.list_ops()
+    flat = gemm.bmm
+    assert callable(flat) and not hasattr(flat, "mm")
+    pkg.list_ops()
+    assert gemm.bmm is flat
+    assert gemm.mm is gemm.blockscaled.mm
+    meta = pkg.find_op("gemm.bmm")
+    assert meta.qualname == "gemm.bmm"
+    assert set(meta.entry_points) == {"bmm", "prewarm_bmm", "can_implement_bmm", "is_bmm_supported"}
+    assert not hasattr(gemm, "Weight")
+    with pytest.raises(AttributeError):
+        gemm.no_such_function
+
+
+def test_bmm_host_checks_need_no_gpu():
+    import torch
+
+    from sparkinfer_b200 import gemm
+
+    spec = dict(a_dtype="bfloat16", b_dtype="float8_e4m3fn", sf_dtype="float8_e8m0fnu",
+                c_dtype="bfloat16", sf_vec_size=32)
+    lhs = torch.zeros(16, 1, 192, dtype=torch.bfloat16)
+    values = torch.zeros(16, 192, 512, dtype=torch.float8_e4m3fn)
+    scales = torch.zeros(16, 192, 16, dtype=torch.uint8)
+    out = torch.empty(16, 1, 512, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError, match="supports only"):
+        gemm.bmm(lhs, (values, scales), out, **{**spec, "b_dtype": "bfloat16"},
+                 b_major="n", sf_axis="n")
+    with pytest.raises(NotImplementedError, match="sf_axis to match b_major"):
+        gemm.bmm(lhs, (values, scales), out, **spec, b_major="n", sf_axis="k")
+    with pytest.raises(TypeError, match="tensor tuple"):
+        gemm.bmm(lhs, [values, scales], out, **spec, b_major="n", sf_axis="n")
+    with pytest.raises(ValueError, match="rhs scales must have shape"):
+        gemm.bmm(lhs, (values, scales[:, :, :8]), out, **spec, b_major="n", sf_axis="n")
+    with pytest.raises(ValueError, match="rhs values must be float8_e4m3fn"):
+        gemm.bmm(lhs, (values.to(torch.bfloat16), scales), out, **spec, b_major="n", sf_axis="n")
+    overlapped = torch.as_strided(torch.empty(1024, dtype=torch.bfloat16), (16, 2, 512), (2, 2, 1))
+    with pytest.raises(ValueError, match="internal storage overlap"):
+        gemm.bmm(torch.zeros(16, 2, 192, dtype=torch.bfloat16), (values, scales), overlapped,
+                 **spec, b_major="n", sf_axis="n")
+    with pytest.raises(ValueError, match="CUDA"):
+        gemm.bmm(lhs, (values, scales), out, **spec, b_major="n", sf_axis="n")
+    kwargs = dict(batch=16, max_m=32, n=512, k=192, **spec, b_major="n", sf_axis="n")
+    assert not gemm.can_implement_bmm(**kwargs)            # no sm_100 device here
+    assert not gemm.can_implement_bmm(**{**kwargs, "b_dtype": "bfloat16"})
