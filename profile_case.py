@@ -8,7 +8,9 @@ by the library), ``pair_mxfp8``, ``pair_nvfp4`` (the CTA-pair kernel forced), ``
 ``pair_mxfp4`` (E2M1 codes with UE8M0 scales per 32 elements), ``decode_nvfp4``,
 ``decode_mxfp8`` (the small-M stream-K kernel), ``fused_nvfp4``, ``fused_mxfp8`` (the same with
 the activation quantizer fused in, M <= 16), ``block_fp8``, ``quant_mxfp8``, ``quant_nvfp4`` (row
-quantizers; N is ignored). The program is what a profiler is pointed at: few launches, nothing
+quantizers; N is ignored), ``bmm_k``, ``bmm_n`` (the batched BF16 x MXFP8 product over 16 heads,
+K-major or N-major weights, a different weight set each call). ``graph_<op>`` captures the
+launches in one CUDA graph and prints the device time per call. The program is what a profiler is pointed at: few launches, nothing
 else on the device, operands sized by the caller. It prints the CUDA-event time of the last
 launch and exits non-zero if a kernel reported a timed-out wait.
 
@@ -31,7 +33,7 @@ from sparkinfer_b200._lib import launch  # noqa: E402
 
 OPS = ("mxfp8", "nvfp4", "pair_mxfp8", "pair_nvfp4", "decode_nvfp4", "decode_mxfp8",
        "fused_nvfp4", "fused_mxfp8", "fp8", "pair_fp8", "scatter2_nvfp4", "scatter4_nvfp4",
-       "scatter8_nvfp4", "block_fp8", "quant_mxfp8", "quant_nvfp4", "mxfp4", "pair_mxfp4")
+       "scatter8_nvfp4", "block_fp8", "quant_mxfp8", "quant_nvfp4", "mxfp4", "pair_mxfp4", "bmm_k", "bmm_n")
 
 
 def build_case(op: str, m: int, n: int, k: int, device: torch.device):
@@ -71,6 +73,23 @@ def build_case(op: str, m: int, n: int, k: int, device: torch.device):
         block_n = _native.BLOCK_N_PAIR if op.startswith("pair") else 0
         return lambda: launch.gemm_blockscaled(kind, a, sfa, b, sfb, c, None, m, n, k,
                                                block_n=block_n, small_m=small)
+    if op in ("bmm_k", "bmm_n"):
+        # 16 heads; 80 weight sets (160 MB, more than L2) taken in turn, as the layers of a
+        # model would be.
+        batch, sets, n_major = 16, 80, op == "bmm_n"
+        rows, inner = (k, n) if n_major else (n, k)
+        values = codes((sets, batch, rows, inner)).view(torch.float8_e4m3fn)
+        scales = torch.full((sets, batch, rows, inner // 32), 127, dtype=torch.uint8, device=device)
+        lhs = torch.randn((batch, m, k), device=device, generator=g).to(torch.bfloat16)
+        out = torch.empty((batch, m, n), dtype=torch.bfloat16, device=device)
+        turn = [0]
+
+        def run():
+            i = turn[0] = (turn[0] + 1) % sets
+            launch.bmm_mxfp8(lhs, values[i], scales[i], out, n_major=n_major, batch=batch, m=m,
+                             n=n, k=k)
+
+        return run
     if op in ("mxfp4", "pair_mxfp4"):
         k_atoms = (k + 127) // 128
         a, b = codes((m, k // 2)), codes((n, k // 2))
@@ -192,7 +211,30 @@ def main(argv=None) -> int:
     device = torch.device("cuda:0")
     if op == "timeline_nvfp4":
         return timeline(m, n, k, max(launches, 2), device)
-    fn = build_case(op, m, n, k, device)
+    graphed = op.startswith("graph_")
+    fn = build_case(op[6:] if graphed else op, m, n, k, device)
+    if graphed:
+        # `launches` calls captured in one CUDA graph, replayed five times: device time per
+        # call without the host's launch cost, for kernels of a few microseconds.
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(launches):
+                fn()
+        times = []
+        for _ in range(5):
+            start = torch.cuda.Event(enable_timing=True)
+            stop = torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / launches)
+        launch.check_kernel_status(device)
+        print(f"{op} {m}x{n}x{k} us_per_call={sorted(times)[2]:.2f} (median of 5 replays of "
+              f"{launches} calls)")
+        return 0
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     for i in range(launches):

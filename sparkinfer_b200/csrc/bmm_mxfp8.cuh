@@ -8,7 +8,9 @@
 // the reference does) and multiplied with FP32 accumulation.
 //
 // Shape of the problem: 16 x 256 x 512 or 16 x 192 x 512 weight bytes (2 MB), at most 32 rows.
-// It is bound by launch and memory latency, not by bytes or math, so the kernel is laid out to
+// It is bound by launch and memory latency, not by bytes or math. Two kernels: the tensor-core
+// one at the end of this file (both operand blocks of a CTA resident in shared memory; taken
+// whenever they fit) and the CUDA-core one that follows (any K), which is laid out to
 // put every global load of a warp in flight before the first use and to finish in one pass:
 //   grid = (N / columns per CTA, B), 8 warps per CTA; the warps split K (chunk c goes to warp
 //   c % 8), a lane owns one (K-major) or two (N-major) output columns and all M rows of them;
@@ -264,6 +266,221 @@ bmm_mxfp8_kernel(const BmmParams p) {
       *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(s0, s1);
     } else {
       *dst = __float2bfloat16_rn(s0);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor-core variant: the same product with the whole [MT x K] activation block and the whole
+// dequantized [columns x K] weight tile of a CTA in shared memory as BF16 and warp-level BF16
+// MMAs (m16n8k16, FP32 accumulation) over them. Used whenever the two blocks fit in shared
+// memory; the CUDA-core kernel above remains for longer K. A 2 MB problem with at most 32 rows
+// is far too small for the tcgen05 pipeline (its set-up alone costs more than this kernel's
+// math), so the warp-level MMA is the right tool here.
+//   phase 1: all 256 threads load their share of A and W (every global load of a round in
+//            flight before the first use), dequantize W, store BF16 rows [row][K + 8] (the
+//            8-element pad makes every fragment load conflict-free);
+//   phase 2: warp w owns the 8 columns (w % blocks) of the tile and, when the tile has fewer
+//            than 8 such blocks, one part of K; fragments are 32-bit shared loads;
+//   phase 3: the K parts of a block are added in part order, rounded once, stored.
+template <int MAJOR, int MT>
+struct BmmMmaShape {
+  static constexpr int kTileN = MAJOR == 1 ? 64 : 32;
+  static constexpr int kBlocks = kTileN / 8;              // n8 blocks per CTA
+  static constexpr int kParts = kBmmWarps / kBlocks;      // K parts per block (1 or 2)
+  static constexpr int kRoundA = 8, kRoundW = 4;          // 16-byte loads per thread, round
+  static __host__ __device__ int k_padded(int k) { return (k + 15) & ~15; }
+  static __host__ __device__ int ld(int k) { return k_padded(k) + 8; }
+  static __host__ __device__ int smem_bytes(int k) {
+    return (kTileN + MT) * ld(k) * 2 + (kParts - 1) * kBlocks * (MT / 16) * 32 * 16;
+  }
+};
+
+__device__ __forceinline__ void bmm_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 16 E4M3 codes times one scale -> 16 BF16 (as 8 packed words).
+__device__ __forceinline__ void bmm_dequant16(const uint4& codes, float scale, uint32_t (&out)[8]) {
+  const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float lo, hi;
+    bmm_e4m3x2(w[i >> 1] >> ((i & 1) * 16), lo, hi);
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo * scale, hi * scale);
+    out[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+template <int MAJOR, int MT>
+__global__ void __launch_bounds__(kBmmThreads)
+bmm_mxfp8_mma_kernel(const BmmParams p) {
+  using S = BmmMmaShape<MAJOR, MT>;
+  constexpr int TN = S::kTileN, RA = S::kRoundA, RW = S::kRoundW;
+  extern __shared__ __align__(16) float bmm_smem[];
+  const int kp = S::k_padded(p.k), ld = S::ld(p.k);
+  __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(bmm_smem);   // [MT][ld]
+  __nv_bfloat16* w_s = a_s + MT * ld;                                // [TN][ld]
+  float* red = reinterpret_cast<float*>(w_s + TN * ld);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.y;
+  const int n0 = blockIdx.x * TN;
+  const uint8_t* w_b = p.w + (int64_t)b * p.w_stride_b;
+  const uint8_t* sf_b = p.sf + (int64_t)b * p.sf_stride_b;
+  const __nv_bfloat16* a_b = p.a + (int64_t)b * p.a_stride_b;
+
+  // ---- phase 1: weights (loads of a round first, then dequantize and store) -------------
+  if constexpr (MAJOR == 0) {
+    const int segs_per_row = p.k >> 4, segs = TN * segs_per_row;
+    for (int base = 0; base < segs; base += kBmmThreads * RW) {
+      uint4 codes[RW];
+      uint32_t sbyte[RW];
+#pragma unroll
+      for (int j = 0; j < RW; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        const int row = idx / segs_per_row, seg = idx - row * segs_per_row;
+        codes[j] = make_uint4(0u, 0u, 0u, 0u);
+        sbyte[j] = 127u;
+        if (idx < segs && n0 + row < p.n) {
+          codes[j] = *reinterpret_cast<const uint4*>(w_b + (int64_t)(n0 + row) * p.w_stride_r + seg * 16);
+          sbyte[j] = sf_b[(int64_t)(n0 + row) * p.sf_stride_r + (seg >> 1)];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < RW; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        if (idx >= segs) break;
+        const int row = idx / segs_per_row, seg = idx - row * segs_per_row;
+        uint32_t v[8];
+        bmm_dequant16(codes[j], bmm_ue8m0(sbyte[j]), v);
+        uint4* dst = reinterpret_cast<uint4*>(w_s + row * ld + seg * 16);
+        dst[0] = make_uint4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_uint4(v[4], v[5], v[6], v[7]);
+      }
+    }
+  } else {
+    constexpr int kSegsPerRow = TN / 16;
+    const int segs = p.k * kSegsPerRow;
+    for (int base = 0; base < segs; base += kBmmThreads * RW) {
+      uint4 codes[RW];
+      uint32_t sbyte[RW];
+#pragma unroll
+      for (int j = 0; j < RW; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        const int row = idx / kSegsPerRow, col = n0 + (idx % kSegsPerRow) * 16;
+        codes[j] = make_uint4(0u, 0u, 0u, 0u);
+        sbyte[j] = 127u;
+        if (idx < segs && col < p.n) {
+          codes[j] = *reinterpret_cast<const uint4*>(w_b + (int64_t)row * p.w_stride_r + col);
+          sbyte[j] = sf_b[(int64_t)row * p.sf_stride_r + (col >> 5)];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < RW; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        if (idx >= segs) break;
+        const int row = idx / kSegsPerRow, c0 = (idx % kSegsPerRow) * 16;
+        uint32_t v[8];
+        bmm_dequant16(codes[j], bmm_ue8m0(sbyte[j]), v);
+        uint16_t* dst = reinterpret_cast<uint16_t*>(w_s) + c0 * ld + row;   // transposed: [n][k]
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dst[(2 * i) * ld] = (uint16_t)(v[i] & 0xFFFFu);
+          dst[(2 * i + 1) * ld] = (uint16_t)(v[i] >> 16);
+        }
+      }
+    }
+    // K rounded up to the MMA's 16: the extra weight columns are zero.
+    for (int idx = tid; idx < TN * (kp - p.k); idx += kBmmThreads) {
+      const int row = idx / (kp - p.k), c = p.k + idx % (kp - p.k);
+      w_s[row * ld + c] = __float2bfloat16_rn(0.f);
+    }
+  }
+  // ---- phase 1: activations (rows beyond M and columns beyond K are zero) --------------
+  {
+    const int segs_per_row = kp >> 3, segs = MT * segs_per_row;
+    for (int base = 0; base < segs; base += kBmmThreads * RA) {
+      uint4 v[RA];
+#pragma unroll
+      for (int j = 0; j < RA; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        const int row = idx / segs_per_row, seg = idx - row * segs_per_row;
+        v[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (idx < segs && row < p.m && seg * 8 < p.k)
+          v[j] = *reinterpret_cast<const uint4*>(a_b + (int64_t)row * p.a_stride_m + seg * 8);
+      }
+#pragma unroll
+      for (int j = 0; j < RA; ++j) {
+        const int idx = base + j * kBmmThreads + tid;
+        if (idx >= segs) break;
+        const int row = idx / segs_per_row, seg = idx - row * segs_per_row;
+        *reinterpret_cast<uint4*>(a_s + row * ld + seg * 8) = v[j];
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 2: MMAs -------------------------------------------------------------------
+  const int block = warp % S::kBlocks, part = warp / S::kBlocks;
+  const int g = lane >> 2, q = lane & 3;
+  const int steps = kp >> 4;
+  const int s_begin = steps * part / S::kParts, s_end = steps * (part + 1) / S::kParts;
+  float acc[MT / 16][4];
+#pragma unroll
+  for (int t = 0; t < MT / 16; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+  const uint32_t* w_words = reinterpret_cast<const uint32_t*>(w_s + (block * 8 + g) * ld) + q;
+  const uint32_t* a_words = reinterpret_cast<const uint32_t*>(a_s + g * ld) + q;
+  const int row_words = ld >> 1;
+#pragma unroll 4
+  for (int s = s_begin; s < s_end; ++s) {
+    const uint32_t b0 = w_words[s * 8], b1 = w_words[s * 8 + 4];
+#pragma unroll
+    for (int t = 0; t < MT / 16; ++t) {
+      const uint32_t* ar = a_words + t * 16 * row_words + s * 8;
+      const uint32_t a[4] = {ar[0], ar[8 * row_words], ar[4], ar[8 * row_words + 4]};
+      bmm_mma_bf16(acc[t], a, b0, b1);
+    }
+  }
+
+  // ---- phase 3: add the K parts in order, round, store -----------------------------------
+  if constexpr (S::kParts > 1) {
+    float4* slot = reinterpret_cast<float4*>(red) + (block * (MT / 16)) * 32 + lane;
+    if (part == 1) {
+#pragma unroll
+      for (int t = 0; t < MT / 16; ++t)
+        slot[t * 32] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    }
+    __syncthreads();
+    if (part == 1) return;
+#pragma unroll
+    for (int t = 0; t < MT / 16; ++t) {
+      const float4 other = slot[t * 32];
+      acc[t][0] += other.x; acc[t][1] += other.y; acc[t][2] += other.z; acc[t][3] += other.w;
+    }
+  }
+  const int col = n0 + block * 8 + 2 * q;
+  if (col >= p.n) return;
+  __nv_bfloat16* c_b = p.c + (int64_t)b * p.c_stride_b + col;
+#pragma unroll
+  for (int t = 0; t < MT / 16; ++t) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = t * 16 + h * 8 + g;
+      if (row >= p.m) continue;
+      __nv_bfloat16* dst = c_b + (int64_t)row * p.c_stride_m;
+      if (col + 1 < p.n) {
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc[t][2 * h], acc[t][2 * h + 1]);
+      } else {
+        *dst = __float2bfloat16_rn(acc[t][2 * h]);
+      }
     }
   }
 }

@@ -221,6 +221,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 struct Switches {
   bool decode_overlap = true;   // programmatic stream serialization for decode GEMMs / quantizers
   bool pair_tail_split = true;  // split-K the last partial round of the CTA-pair kernel
+  bool bmm_tensor_core = true;  // batched BF16 x MXFP8 product on warp-level MMAs when it fits
 };
 
 const Switches& switches() {
@@ -228,6 +229,7 @@ const Switches& switches() {
     Switches v;
     if (const char* e = getenv("B12X_B200_DECODE_OVERLAP")) v.decode_overlap = atoi(e) != 0;
     if (const char* e = getenv("B12X_B200_PAIR_TAIL_SPLIT")) v.pair_tail_split = atoi(e) != 0;
+    if (const char* e = getenv("B12X_B200_BMM_TENSOR_CORE")) v.bmm_tensor_core = atoi(e) != 0;
     return v;
   }();
   return sw;
@@ -1548,8 +1550,35 @@ int launch_bmm(const BmmParams& p, int batch, cudaStream_t stream) {
   return B12X_B200_OK;
 }
 
+constexpr int kBmmMmaSmemLimit = 200 * 1024;
+
+template <int MAJOR, int MT>
+int launch_bmm_mma(const BmmParams& p, int batch, cudaStream_t stream) {
+  using S = BmmMmaShape<MAJOR, MT>;
+  static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !set_for[dev]) {
+    const cudaError_t attr_err =
+        cudaFuncSetAttribute(bmm_mxfp8_mma_kernel<MAJOR, MT>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kBmmMmaSmemLimit);
+    if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
+    set_for[dev] = true;
+  }
+  const dim3 grid(unsigned((p.n + S::kTileN - 1) / S::kTileN), unsigned(batch), 1);
+  bmm_mxfp8_mma_kernel<MAJOR, MT><<<grid, kBmmThreads, S::smem_bytes(p.k), stream>>>(p);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(err, "bmm_mxfp8 launch");
+  return B12X_B200_OK;
+}
+
 template <int MAJOR>
 int dispatch_bmm_rows(const BmmParams& p, int batch, cudaStream_t stream) {
+  // Both blocks of a CTA in shared memory: the tensor-core kernel. Longer K: the CUDA-core one.
+  if (switches().bmm_tensor_core && BmmMmaShape<MAJOR, 32>::smem_bytes(p.k) <= kBmmMmaSmemLimit) {
+    if (p.m <= 16) return launch_bmm_mma<MAJOR, 16>(p, batch, stream);
+    return launch_bmm_mma<MAJOR, 32>(p, batch, stream);
+  }
   if (p.m <= 8) return launch_bmm<MAJOR, 8>(p, batch, stream);
   if (p.m <= 16) return launch_bmm<MAJOR, 16>(p, batch, stream);
   return launch_bmm<MAJOR, 32>(p, batch, stream);

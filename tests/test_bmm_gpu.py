@@ -268,6 +268,9 @@ def _launcher_cases():
             n = int(rng.choice([1, 7, 32, 100, 256, 515]))
             k = 32 * int(rng.integers(1, 30))
         cases.append((i, n_major, batch, m, n, k))
+    # K too long for the shared-memory-resident tensor-core kernel: the CUDA-core kernel.
+    cases += [(16, False, 4, 5, 100, 2048), (17, True, 3, 32, 96, 1600), (18, False, 2, 19, 64, 4096),
+              (19, True, 8, 12, 64, 2056)]
     return cases
 
 
