@@ -15,6 +15,7 @@ Reference functions used (path:line in the b12x tree):
   ref_fp4_quant, dequantize_grouped_nvfp4,
   compute_global_scale, recover_grouped_e4m3_scales       tests/_reference/helpers.py:224-363
   _block_fp8_reference                                    tests/gemm/test_gemm_stack.py:98-113
+  _dequant_physical, _logical_b (gemm.bmm's reference)    tests/gemm/test_bmm.py:74-84
   pack_fp8_block_scaled_weight_mxfp8 (re-quantization to UE8M0 block scales, expansion to
   per-row scales, MMA layout)                             b12x/gemm/_shared/wo_mxfp8.py:873-1187
     (these insist on CUDA tensors; the generator swaps the module's device check for a no-op
@@ -192,7 +193,31 @@ def main() -> None:
                                  .view(torch.uint8).numpy().reshape(-1))
     np.savez_compressed(HERE / "weight_pack.npz", **pk)
 
-    for name in ("nvfp4_quant.npz", "mxfp8_quant.npz", "gemm_ref.npz", "weight_pack.npz"):
+    # ---------------- gemm.bmm: the reference test module's own torch reference ----------------
+    import importlib
+
+    tb = importlib.import_module("tests.gemm.test_bmm")
+    bm = {}
+    for idx, (major, batch, m, n, k, seed) in enumerate([
+            ("k", 3, 5, 48, 96, 5101), ("n", 2, 7, 64, 40, 5102), ("k", 2, 32, 40, 64, 5103)]):
+        gen = torch.Generator().manual_seed(seed)
+        rows, inner = (k, n) if major == "n" else (n, k)
+        values = (torch.randn((batch, rows, inner), generator=gen) * 0.3).to(torch.float8_e4m3fn)
+        scales = torch.randint(100, 150, (batch, rows, inner // 32), generator=gen, dtype=torch.uint8)
+        scales[0, 0, 0], scales[0, 1, 0], scales[1, 0, 0] = 0, 1, 254
+        lhs = _bf16_inputs(seed + 50, (batch, m, k))
+        physical = tb._dequant_physical((values, scales))
+        logical = tb._logical_b((values, scales), major)
+        bm[f"major{idx}"] = np.array([major == "n"])
+        bm[f"values{idx}"] = values.view(torch.uint8).numpy()
+        bm[f"scales{idx}"] = scales.numpy()
+        bm[f"lhs_bits{idx}"] = _bf16_bits(lhs)
+        bm[f"dequant_bits{idx}"] = _bf16_bits(physical)
+        bm[f"product{idx}"] = torch.bmm(lhs.double(), logical.double()).numpy()
+    np.savez_compressed(HERE / "bmm_ref.npz", **bm)
+
+    for name in ("nvfp4_quant.npz", "mxfp8_quant.npz", "gemm_ref.npz", "weight_pack.npz",
+                 "bmm_ref.npz"):
         print(name, (HERE / name).stat().st_size, "bytes")
 
 

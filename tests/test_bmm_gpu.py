@@ -254,6 +254,42 @@ def test_envelope_and_argument_errors(rhs_by_major):
     assert not gemm.can_implement_bmm(**{**kwargs, "b_dtype": "bfloat16"})
 
 
+@pytest.mark.parametrize("idx", range(3))
+def test_kernel_matches_the_oracle_on_the_golden_fixture(idx):
+    """Inputs and FP64 product from the fixture generated with the reference test module's own
+    torch reference; the oracle restates it; the kernel is the oracle's product accumulated in
+    FP32 and rounded once to BF16."""
+    from conftest import GOLDEN, bf16_bits_to_f32
+    from oracle import blockscaled_oracle as O
+    from sparkinfer_b200._lib import launch
+
+    g = np.load(GOLDEN / "bmm_ref.npz")
+    n_major = bool(g[f"major{idx}"][0])
+    values = torch.from_numpy(g[f"values{idx}"]).cuda()
+    scales = torch.from_numpy(g[f"scales{idx}"]).cuda()
+    lhs = torch.from_numpy(g[f"lhs_bits{idx}"].view(np.int16)).cuda().view(torch.bfloat16)
+    batch, m, k = lhs.shape
+    n = values.shape[2] if n_major else values.shape[1]
+    out = torch.full((batch, m, n), torch.nan, device="cuda", dtype=torch.bfloat16)
+    launch.bmm_mxfp8(lhs, values.view(torch.float8_e4m3fn), scales, out, n_major=n_major,
+                     batch=batch, m=m, n=n, k=k)
+    torch.cuda.synchronize()
+    exact = O.bmm_mxfp8(bf16_bits_to_f32(g[f"lhs_bits{idx}"]), g[f"values{idx}"],
+                        g[f"scales{idx}"], n_major)
+    np.testing.assert_allclose(exact, g[f"product{idx}"], rtol=1e-12, atol=0)
+    got = out.float().cpu().numpy().astype(np.float64)
+    # FP32 accumulation of exact products and one rounding to BF16: per output, 2^-8 of the
+    # result plus 2^-20 of the sum of the products' magnitudes. Outputs whose partial sums can
+    # leave the FP32 range (the fixture holds a 2^127 scale) are only required to be non-NaN.
+    w = np.abs(O.dequantize_rowwise_mxfp8_bf16(g[f"values{idx}"], g[f"scales{idx}"])).astype(np.float64)
+    magnitude = np.matmul(np.abs(bf16_bits_to_f32(g[f"lhs_bits{idx}"])).astype(np.float64),
+                          w if n_major else np.swapaxes(w, -1, -2))
+    safe = magnitude < 1.0e37
+    assert safe.mean() > 0.75 and not np.isnan(got).any()
+    bound = np.abs(exact) * 2.0 ** -8 + magnitude * 2.0 ** -20
+    assert (np.abs(got - exact)[safe] <= bound[safe]).all()
+
+
 def _launcher_cases():
     rng = np.random.default_rng(77)
     cases = []

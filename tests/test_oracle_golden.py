@@ -145,3 +145,23 @@ def test_weight_requantization_matches_reference(idx):
     assert np.array_equal(new_codes, g[f"values{idx}"])
     assert np.array_equal(rows, g[f"scale_rows{idx}"].reshape(m, k // 32))
     assert np.array_equal(O.swizzle_scales(rows, 127), g[f"scale_mma{idx}"])
+
+
+@pytest.mark.parametrize("idx", range(3))
+def test_bmm_oracle_matches_the_reference_tests_torch_reference(idx):
+    """Dequantization bit for bit (bytes 0, 1 and 254 included) and the FP64 product."""
+    g = np.load(GOLDEN / "bmm_ref.npz")
+    values, scales = g[f"values{idx}"], g[f"scales{idx}"]
+    deq = O.dequantize_rowwise_mxfp8_bf16(values, scales)
+    want = bf16_bits_to_f32(g[f"dequant_bits{idx}"])
+    assert np.array_equal(deq.view(np.uint32), want.view(np.uint32))
+    got = O.bmm_mxfp8(bf16_bits_to_f32(g[f"lhs_bits{idx}"]), values, scales, bool(g[f"major{idx}"][0]))
+    assert got.shape == g[f"product{idx}"].shape
+    np.testing.assert_allclose(got, g[f"product{idx}"], rtol=1e-12, atol=0)
+
+
+def test_bmm_oracle_scale_byte_255_is_nan():
+    values = np.full((1, 2, 32), 0x38, dtype=np.uint8)       # 1.0
+    scales = np.array([[[255], [127]]], dtype=np.uint8)
+    deq = O.dequantize_rowwise_mxfp8_bf16(values, scales)
+    assert np.isnan(deq[0, 0]).all() and (deq[0, 1] == 1.0).all()
