@@ -46,8 +46,9 @@ enum {
   B12X_B200_KIND_FP8 = 2,
   /* MXFP4: packed E2M1 codes (as NVFP4) with one UE8M0 scale per 32 elements of K, scale atoms
    * of 128 rows x 4 scale columns = 128 elements of K (the reference's float4_e2m1fn operands
-   * with sf_dtype float8_e8m0fnu / sf_vec_size 32, b12x/_lib/dense_gemm.py:7225-7260). Tiled
-   * and CTA-pair kernels; the decode entry points refuse it. */
+   * with sf_dtype float8_e8m0fnu / sf_vec_size 32, b12x/_lib/dense_gemm.py:7225-7260). Every
+   * GEMM entry point takes it except the two with fused activation quantization (no quantizer
+   * produces MXFP4). */
   B12X_B200_KIND_MXFP4 = 3
 };
 

@@ -246,10 +246,6 @@ def gemm_blockscaled(kind: int, a: torch.Tensor, sfa: torch.Tensor | None, b: to
         if small_m or quantized_c is not None:
             raise ValueError("the unscaled FP8 recipe runs on the tiled kernels only")
         small_m = False
-    if kind == _native.KIND_MXFP4:
-        if small_m or quantized_c is not None:
-            raise ValueError("the MXFP4 recipe runs on the tiled kernels only")
-        small_m = False
     if small_m is None:
         small_m = block_n == 0 and 0 < m <= SMALL_M_MAX and (
             quantized_c is not None or route_to_decode_kernel(m, n, dev, sm_count))

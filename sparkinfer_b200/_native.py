@@ -18,7 +18,7 @@ _LIB: ctypes.CDLL | None = None
 KIND_MXFP8 = 0
 KIND_NVFP4 = 1
 KIND_FP8 = 2      # E4M3 without block scales (tiled and CTA-pair kernels only)
-KIND_MXFP4 = 3    # E2M1 codes with UE8M0 scales per 32 elements (tiled and CTA-pair kernels only)
+KIND_MXFP4 = 3    # E2M1 codes with UE8M0 scales per 32 elements (no fused activation quantizer)
 DT_BF16 = 0
 DT_FP16 = 1
 DT_FP32 = 2

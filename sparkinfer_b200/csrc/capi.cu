@@ -851,7 +851,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   if (n < 1 || k < 1 || n > INT32_MAX || k > INT32_MAX)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "bad problem size");
   if (sms < 1) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "no SMs");
-  const int sf_vec = (kind == B12X_B200_KIND_MXFP8) ? 32 : 16;
+  const int sf_vec = (kind == B12X_B200_KIND_NVFP4) ? 16 : 32;
   const int elems_per_stage = (kind == B12X_B200_KIND_MXFP8) ? 128 : 256;
   SmallMPlan pl;
   pl.m_pad = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
@@ -879,8 +879,9 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   int64_t seg = (pl.k_tiles + units_per_cta - 1) / units_per_cta + 1;
   if (seg > pl.grid) seg = pl.grid;
   pl.max_segments = int(seg);
-  pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8) ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
-                                                  : SmallMTile<kNvfp4>::stage_bytes(pl.m_pad);
+  pl.stage_bytes = (kind == B12X_B200_KIND_MXFP8)   ? SmallMTile<kMxfp8>::stage_bytes(pl.m_pad)
+                   : (kind == B12X_B200_KIND_NVFP4) ? SmallMTile<kNvfp4>::stage_bytes(pl.m_pad)
+                                                    : SmallMTile<kMxfp4>::stage_bytes(pl.m_pad);
   pl.raw_rows = 0;
   if (fused) {
     pl.raw_rows = m <= 8 ? 8 : 16;
@@ -991,7 +992,10 @@ struct SmallMCall {
 int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empty) {
   *empty = false;
   const bool fused = a.x_src != nullptr;
-  if (a.kind != B12X_B200_KIND_MXFP8 && a.kind != B12X_B200_KIND_NVFP4)
+  if (a.kind == B12X_B200_KIND_MXFP4 && fused)
+    return fail(B12X_B200_ERR_UNSUPPORTED, "no activation quantizer produces MXFP4");
+  if (a.kind != B12X_B200_KIND_MXFP8 && a.kind != B12X_B200_KIND_NVFP4 &&
+      a.kind != B12X_B200_KIND_MXFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
   if (a.c_dtype < B12X_B200_BF16 || a.c_dtype > B12X_B200_FP32)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown output dtype");
@@ -1101,6 +1105,8 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   if (a.kind == B12X_B200_KIND_MXFP8)
     return fused ? launch_smallm<kMxfp8, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
                  : launch_smallm<kMxfp8, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
+  if (a.kind == B12X_B200_KIND_MXFP4)
+    return launch_smallm<kMxfp4, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
   return fused ? launch_smallm<kNvfp4, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
                : launch_smallm<kNvfp4, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
 }
@@ -1118,7 +1124,8 @@ int smallm_entry(const SmallMCall& a, void* workspace, int64_t workspace_bytes) 
 
 extern "C" int64_t b12x_b200_gemm_smallm_workspace_bytes(int kind, int64_t m, int64_t n, int64_t k,
                                                          int sm_count) {
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_MXFP4)
+    return -1;
   if (n <= 0 || k <= 0) return -1;
   // Same SM count as the launch will use: the caller's limit, capped by the device.
   DeviceInfo info;
@@ -1174,7 +1181,8 @@ extern "C" int64_t b12x_b200_gemm_grouped_workspace_bytes(int kind, int decode, 
                                                           int64_t n, int64_t k, int64_t groups,
                                                           int block_n, int sm_count) {
   if (!decode) return tiled_workspace_bytes(kind, m, n, k, groups, block_n, sm_count);
-  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4) return -1;
+  if (kind != B12X_B200_KIND_MXFP8 && kind != B12X_B200_KIND_NVFP4 && kind != B12X_B200_KIND_MXFP4)
+    return -1;
   if (n <= 0 || k <= 0) return -1;
   DeviceInfo info;
   if (device_info(&info) != B12X_B200_OK) return -1;

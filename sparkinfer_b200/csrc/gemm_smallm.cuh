@@ -159,7 +159,7 @@ template <int KIND>
 struct SmallMTile {
   static constexpr int kElemsPerMma = (KIND == kMxfp8) ? 32 : 64;
   static constexpr int kElemsPerStage = kElemsPerMma * 4;
-  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : 4;
+  static constexpr int kKAtoms = (KIND == kMxfp8) ? 1 : (KIND == kNvfp4 ? 4 : 2);
   static constexpr int kWBytes = 128 * 128;
   static constexpr int kSfBytes = kKAtoms * 512;
   // Stage = weights | weight scales | activation scales | activation rows (m_pad * 128 B).
@@ -580,7 +580,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
       // accumulator barrier, through a commit if it issued anything there, plainly otherwise.
       const int me = (warp == 1) ? 0 : 1;
       const uint32_t idesc_base = make_idesc_block_scaled(
-          128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kMxfp8 ? 1u : 0u);
+          128, static_cast<uint32_t>(p.m_pad), KIND == kMxfp8 ? 0u : 1u, KIND == kNvfp4 ? 0u : 1u);
       const uint32_t sfw_col = tmem_base + p.sf_col0 + me * T::kSfColsPerIssuer;
       const uint32_t sfx_col = sfw_col + 16;
       int stage = 0;
@@ -638,6 +638,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                 if (KIND == kMxfp8)
                   tc_mma_mxf8(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
                               idesc_with_sf_ids(idesc_base, j, j), accumulate, sfw_col, sfx_col);
+                else if (KIND == kMxfp4)   // two UE8M0 bytes per MMA: bytes 0-1 or 2-3 of atom j / 2
+                  tc_mma_mxf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j,
+                              idesc_with_sf_ids(idesc_base, (j & 1) * 2, (j & 1) * 2), accumulate,
+                              sfw_col + (j >> 1) * 4, sfx_col + (j >> 1) * 4);
                 else
                   tc_mma_nvf4(d_taddr, wdesc + 2 * j, xdesc + 2 * j, idesc_base, accumulate,
                               sfw_col + j * 4, sfx_col + j * 4);

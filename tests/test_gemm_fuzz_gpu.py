@@ -257,11 +257,17 @@ def _mxfp4_cases():
         m = int(rng.choice([1, 17, 64, 128, 129, 200, 256, 300, 511, 640, 1024]))
         n = int(rng.choice([8, 64, 72, 128, 192, 200, 256, 264, 512, 776, 1024, 1288]))
         k = 64 * int(rng.integers(1, 40))
-        route = str(rng.choice(["auto", "bn64", "bn128", "bn192", "bn256", "pair", "pair"]))
+        route = str(rng.choice(["auto", "bn64", "bn128", "bn192", "bn256", "pair", "pair", "decode",
+                                "decode"]))
+        if route == "decode" and m > 128:
+            m = int(rng.choice([1, 4, 16, 33, 64, 100]))
         dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
         cases.append((i, m, n, k, route, dtype))
     cases.append((20, 2048, 4608, 2048, "auto", torch.bfloat16))
     cases.append((21, 4096, 2304, 1600, "pair", torch.bfloat16))   # leftover tiles split along K
+    cases.append((22, 16, 14336, 4096, "decode", torch.bfloat16))  # decode shape, stream-K
+    cases.append((23, 64, 4096, 1984, "decode", torch.float32))    # two issuers, half-filled atom
+    cases.append((24, 128, 1032, 320, "decode", torch.bfloat16))
     return cases
 
 
@@ -284,16 +290,18 @@ def test_mxfp4_matches_fp32_reference(index, m, n, k, route, dtype):
         kwargs["block_n"] = int(route[2:])
     elif route == "pair":
         kwargs["block_n"] = BLOCK_N_PAIR
+    elif route == "decode":
+        kwargs["small_m"] = True
     launch.gemm_blockscaled(KIND_MXFP4, a, sfa, b, sfb, out, alpha, m, n, k, **kwargs)
     torch.cuda.synchronize()
     launch.check_kernel_status(dev)
     assert_whole_output_close(out, a_deq, b_deq, 0.5, out_dtype=dtype)
 
 
-def test_mxfp4_refuses_the_decode_kernel_and_runs_through_mm():
+def test_mxfp4_runs_through_mm_and_has_no_fused_activation_quantizer():
     """The public ``blockscaled.mm`` accepts float4_e2m1fn with float8_e8m0fnu / 32 scales (the
-    reference's MXF4 mode, b12x/_lib/dense_gemm.py:580-582) and never routes it to the decode
-    kernel; forcing that kernel is an error."""
+    reference's MXF4 mode, b12x/_lib/dense_gemm.py:580-582); a decode shape goes to the decode
+    kernel like the other recipes. The fused-quantization entry refuses the kind."""
     from sparkinfer_b200._lib import launch
     from sparkinfer_b200._lib.layout import convert_sf_to_mma_layout as mma_view
     from sparkinfer_b200._native import KIND_MXFP4
@@ -306,8 +314,11 @@ def test_mxfp4_refuses_the_decode_kernel_and_runs_through_mm():
     a, sfa, a_deq = _operand("mxfp4", m, k, gen, dev)
     b, sfb, b_deq = _operand("mxfp4", n, k, gen, dev)
     out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    with pytest.raises(ValueError, match="tiled kernels only"):
-        launch.gemm_blockscaled(KIND_MXFP4, a, sfa, b, sfb, out, None, m, n, k, small_m=True)
+    from sparkinfer_b200 import _native
+
+    x = torch.zeros((m, k), dtype=torch.bfloat16, device=dev)
+    with pytest.raises(_native.NativeLibraryError, match="MXFP4"):
+        launch.gemm_smallm_fused_quant(KIND_MXFP4, x, None, b, sfb, out, None, m, n, k)
     got = blockscaled.mm(
         (a.view(m, k // 2, 1), mma_view(sfa.view(torch.float8_e8m0fnu), m, k, 1, 32)),
         (b.view(n, k // 2, 1), mma_view(sfb.view(torch.float8_e8m0fnu), n, k, 1, 32)),
