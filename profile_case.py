@@ -5,7 +5,7 @@
 
 ``op`` is one of ``mxfp8``, ``nvfp4`` (the tiled block-scaled GEMM, kernel and tile width chosen
 by the library), ``pair_mxfp8``, ``pair_nvfp4`` (the CTA-pair kernel forced), ``mxfp4``,
-``pair_mxfp4`` (E2M1 codes with UE8M0 scales per 32 elements), ``decode_nvfp4``,
+``pair_mxfp4``, ``decode_mxfp4`` (E2M1 codes with UE8M0 scales per 32 elements), ``decode_nvfp4``,
 ``decode_mxfp8`` (the small-M stream-K kernel), ``fused_nvfp4``, ``fused_mxfp8`` (the same with
 the activation quantizer fused in, M <= 16), ``block_fp8``, ``quant_mxfp8``, ``quant_nvfp4`` (row
 quantizers; N is ignored), ``bmm_k``, ``bmm_n`` (the batched BF16 x MXFP8 product over 16 heads,
@@ -33,7 +33,7 @@ from sparkinfer_b200._lib import launch  # noqa: E402
 
 OPS = ("mxfp8", "nvfp4", "pair_mxfp8", "pair_nvfp4", "decode_nvfp4", "decode_mxfp8",
        "fused_nvfp4", "fused_mxfp8", "fp8", "pair_fp8", "scatter2_nvfp4", "scatter4_nvfp4",
-       "scatter8_nvfp4", "block_fp8", "quant_mxfp8", "quant_nvfp4", "mxfp4", "pair_mxfp4", "bmm_k", "bmm_n")
+       "scatter8_nvfp4", "block_fp8", "quant_mxfp8", "quant_nvfp4", "mxfp4", "pair_mxfp4", "decode_mxfp4", "bmm_k", "bmm_n")
 
 
 def build_case(op: str, m: int, n: int, k: int, device: torch.device):
@@ -90,7 +90,7 @@ def build_case(op: str, m: int, n: int, k: int, device: torch.device):
                              n=n, k=k)
 
         return run
-    if op in ("mxfp4", "pair_mxfp4"):
+    if op in ("mxfp4", "pair_mxfp4", "decode_mxfp4"):
         k_atoms = (k + 127) // 128
         a, b = codes((m, k // 2)), codes((n, k // 2))
         sfa = torch.full((((m + 127) // 128) * k_atoms * 512,), 127, dtype=torch.uint8, device=device)
@@ -98,7 +98,7 @@ def build_case(op: str, m: int, n: int, k: int, device: torch.device):
         c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
         block_n = _native.BLOCK_N_PAIR if op.startswith("pair") else 0
         return lambda: launch.gemm_blockscaled(_native.KIND_MXFP4, a, sfa, b, sfb, c, None, m, n, k,
-                                               block_n=block_n)
+                                               block_n=block_n, small_m=op.startswith("decode"))
     if op in ("fp8", "pair_fp8"):
         a, b = codes((m, k)), codes((n, k))
         c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
