@@ -248,7 +248,7 @@ int b12x_b200_gemm_smallm_fused_quant(int kind, const void* x_bf16, int64_t ld_x
 
 /*
  * The same for `groups` problems of one shape in one launch: the reference's
- * dense_gemm_fused_quant_a_grouped without its inverse-RoPE option
+ * dense_gemm_fused_quant_a_grouped without its inverse-RoPE option (next entry point)
  * (b12x/_lib/dense_gemm.py:5803-5944; WO-A of the MLA output projection). Row r of group g of
  * the activation starts at x + r * ld_x + g * x_group_stride elements (the reference's source
  * [M, groups, K] has ld_x = groups * K and x_group_stride = K); weights, their scale atoms and
@@ -260,6 +260,27 @@ int b12x_b200_gemm_smallm_fused_quant_grouped(
     const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
     void* workspace, int64_t workspace_bytes, const b12x_b200_epilogue_t* epilogue, int sm_count,
     int* status, b12x_b200_stream_t stream);
+
+/*
+ * The grouped call with the reference's inverse-RoPE option (MXFP8 only,
+ * b12x/_lib/dense_gemm.py:5849-5882 host contract, :3505-3530 device arithmetic): before a
+ * 32-element block of an activation row is quantized, the trailing rope_dim elements of every
+ * head_dim-wide slice of the group's K are rotated back in FP32. Row r is the token at
+ * positions[r] (int32, or int64 when positions_are_int64); for the interleaved pair (even, odd)
+ * number j of the rotary part, with cos = cache[pos * rope_dim + j] and
+ * sin = cache[pos * rope_dim + rope_dim / 2 + j] (BF16, or FP32 when cache_is_fp32):
+ *   even' = fma(even, cos, odd * sin),   odd' = fma(odd, cos, -(even * sin)).
+ * head_dim = nope_dim + rope_dim, all multiples of 32, head_dim dividing K. positions and the
+ * cache are read on the device at run time (no bounds check on positions, as in the reference).
+ * No epilogue. Everything else as b12x_b200_gemm_smallm_fused_quant_grouped with kind MXFP8.
+ */
+int b12x_b200_gemm_smallm_fused_quant_grouped_inv_rope(
+    const void* x_bf16, int64_t ld_x, int64_t x_group_stride, const void* positions,
+    int positions_are_int64, const void* cos_sin_cache, int cache_is_fp32, int head_dim,
+    int nope_dim, int rope_dim, const void* w, const void* sf_w, void* c, int c_dtype,
+    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
+    void* workspace, int64_t workspace_bytes, int sm_count, int* status,
+    b12x_b200_stream_t stream);
 
 /*
  * b12x_b200_gemm_blockscaled_smallm that also records, per CTA, eight 64-bit values in

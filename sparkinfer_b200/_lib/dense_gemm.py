@@ -513,9 +513,10 @@ def dense_gemm_fused_quant_a_grouped(
     (b12x/_lib/dense_gemm.py:5803-5944, the WO-A shape): ``source [M, groups, K]`` BF16 (rows
     may be strided, ``[groups, K]`` contiguous inside a row), per group ``[M, K] x [N, K]^T``
     into ``out [M, N, groups]``. Every group's rows are quantized inside the decode kernel,
-    bit for bit as ``quantize_rows`` would. The inverse-RoPE rotation the reference can apply to
-    the rows before quantizing (``positions`` / ``cos_sin_cache``) belongs to the attention
-    side of that projection and is not built."""
+    bit for bit as ``quantize_rows`` would. With ``positions`` / ``cos_sin_cache`` the trailing
+    ``rope_dim`` elements of every ``head_dim`` block of a row are inverse-RoPE-rotated in FP32
+    before quantization (``:5849-5882``; interleaved pairs, ``cos = cache[pos, j]``,
+    ``sin = cache[pos, rope_dim / 2 + j]``)."""
     if source.dtype != torch.bfloat16 or source.ndim != 3:
         raise ValueError("fused grouped MXFP8 quantization requires BF16 [M, groups, K]")
     m, k = int(source.shape[0]), int(source.shape[2])
@@ -531,9 +532,28 @@ def dense_gemm_fused_quant_a_grouped(
             f"got M={m}, K={k}, row_stride={row_stride}")
     if b.ndim != 3 or int(b.shape[1]) != k or int(b.shape[2]) != groups:
         raise ValueError(f"B must have shape [N,{k},{groups}], got {tuple(b.shape)}")
+    inv_rope = None
     if positions is not None or cos_sin_cache is not None:
-        raise NotImplementedError(
-            "the inverse-RoPE prologue belongs to the MLA output projection and is not built")
+        if positions is None or cos_sin_cache is None:
+            raise ValueError("inverse-RoPE needs both positions and cos_sin_cache")
+        if positions.shape != (m,):
+            raise ValueError(f"positions must have shape {(m,)}, got {tuple(positions.shape)}")
+        if not positions.is_contiguous() or not cos_sin_cache.is_contiguous():
+            raise ValueError("positions and cos_sin_cache must be contiguous")
+        if cos_sin_cache.ndim != 2 or int(cos_sin_cache.shape[1]) != rope_dim:
+            raise ValueError(
+                f"cos_sin_cache must have shape [max_pos, {rope_dim}], got {tuple(cos_sin_cache.shape)}")
+        if (head_dim <= 0 or nope_dim + rope_dim != head_dim or head_dim % 32 or nope_dim % 32
+                or rope_dim % 32 or k % head_dim):
+            raise ValueError(
+                "fused inverse-RoPE requires 32-aligned head_dim = nope_dim + rope_dim "
+                f"dividing K, got head={head_dim}, nope={nope_dim}, rope={rope_dim}, K={k}")
+        if positions.dtype not in (torch.int32, torch.int64):
+            raise ValueError(f"fused inv-RoPE positions must be int32/int64, got {positions.dtype}")
+        if cos_sin_cache.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(
+                f"fused inv-RoPE cos/sin cache must be bf16/fp32, got {cos_sin_cache.dtype}")
+        inv_rope = (positions, cos_sin_cache, int(head_dim), int(nope_dim), int(rope_dim))
     n = int(b.shape[0])
     _check_operand("B", b, n, k, groups)
     if not mma_view_is_canonical(sfb, n, k, 32, groups):
@@ -547,7 +567,8 @@ def dense_gemm_fused_quant_a_grouped(
         raise ValueError(f"out must be backed by physical [L, M, N] storage, got strides {out.stride()}")
     sfb_flat = sfb.view(torch.uint8) if sfb.dtype != torch.uint8 else sfb
     launch.gemm_smallm_fused_quant(_native.KIND_MXFP8, source, None, b, sfb_flat, out, None, m, n, k,
-                                   ldc=n, stream_int=cuda_stream_to_int(stream), groups=groups)
+                                   ldc=n, stream_int=cuda_stream_to_int(stream), groups=groups,
+                                   inv_rope=inv_rope)
     return out
 
 

@@ -285,11 +285,13 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
                             alpha: torch.Tensor | None, m: int, n: int, k: int, *,
                             ldc: int | None = None, sm_count: int = 0,
                             stream_int: int | None = None, bias: torch.Tensor | None = None,
-                            quantized_c: QuantizedC | None = None, groups: int = 1) -> None:
+                            quantized_c: QuantizedC | None = None, groups: int = 1,
+                            inv_rope: tuple | None = None) -> None:
     """Decode GEMM that quantizes its BF16 activation rows ``x [M, K]`` (M <= 16) inside the
     kernel; bit for bit ``quantize rows`` followed by :func:`gemm_blockscaled`. With
     ``groups > 1``: ``x [M, groups, K]``, weights / scale atoms / output group-major, one
-    launch."""
+    launch. ``inv_rope = (positions, cos_sin_cache, head_dim, nope_dim, rope_dim)`` (MXFP8
+    only) rotates the rotary part of every head back before the rows are quantized."""
     for name, t in (("x", x), ("w", w), ("sfw", sfw), ("c", c)):
         _require_cuda(name, t)
     if x.dtype != torch.bfloat16 or x.stride(-1) != 1:
@@ -311,6 +313,24 @@ def gemm_smallm_fused_quant(kind: int, x: torch.Tensor, global_scale: torch.Tens
                 f"no decode-shape plan for M={m}, N={n}, K={k}, groups={groups}")
         work = stream_workspace(need, dev, stream_int)
         row_stride, group_stride = (x.stride(0) if m > 1 else groups * k), x.stride(1)
+    if inv_rope is not None:
+        positions, cache, head_dim, nope_dim, rope_dim = inv_rope
+        _require_cuda("positions", positions)
+        _require_cuda("cos_sin_cache", cache)
+        if kind != _native.KIND_MXFP8 or ep is not None:
+            raise ValueError("the inverse-RoPE prologue exists for MXFP8 without epilogue only")
+        with torch.cuda.device(dev):
+            rc = _native.load().b12x_b200_gemm_smallm_fused_quant_grouped_inv_rope(
+                x.data_ptr(), row_stride, group_stride, positions.data_ptr(),
+                1 if positions.dtype == torch.int64 else 0, cache.data_ptr(),
+                1 if cache.dtype == torch.float32 else 0, head_dim, nope_dim, rope_dim,
+                w.data_ptr(), sfw.data_ptr(), c.data_ptr(), _DTYPE_CODE[c.dtype],
+                alpha.data_ptr() if alpha is not None else None, m, n, k,
+                ldc if ldc is not None else n, groups, work.data_ptr(), work.numel(), sm_count,
+                status_buffer(dev).data_ptr(), _stream_ptr(stream_int, dev))
+        _native.check(rc, "b12x_b200_gemm_smallm_fused_quant_grouped_inv_rope")
+        _after_launch(dev)
+        return
     with torch.cuda.device(dev):
         rc = _native.load().b12x_b200_gemm_smallm_fused_quant_grouped(
             kind, x.data_ptr(), row_stride, group_stride,

@@ -99,6 +99,12 @@ SIGNATURES = {
          _c_void_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_void_p, _c_i64, _c_epilogue_p,
          _c_int, _c_void_p, _c_void_p],
     ),
+    "b12x_b200_gemm_smallm_fused_quant_grouped_inv_rope": (
+        _c_int,
+        [_c_void_p, _c_i64, _c_i64, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_i64, _c_i64, _c_i64, _c_i64,
+         _c_i64, _c_void_p, _c_i64, _c_int, _c_void_p, _c_void_p],
+    ),
     "b12x_b200_gemm_smallm_timeline": (
         _c_int,
         [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,

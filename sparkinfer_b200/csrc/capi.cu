@@ -917,7 +917,7 @@ int plan_smallm(int kind, int64_t m, int64_t n, int64_t k, int sms, bool fused, 
   return B12X_B200_OK;
 }
 
-template <int KIND, bool FUSED, bool EPI>
+template <int KIND, bool FUSED, bool EPI, bool ROPE = false>
 int launch_smallm_impl(const CUtensorMap& map_w, const CUtensorMap& map_x, const SmallMParams& p,
                        int grid, int smem_bytes, cudaStream_t stream) {
   static std::atomic<bool> set_for[64];  // zero-initialised; setting the attribute twice is harmless
@@ -925,11 +925,11 @@ int launch_smallm_impl(const CUtensorMap& map_w, const CUtensorMap& map_x, const
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !set_for[dev]) {
     const cudaError_t attr_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND, FUSED, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        gemm_smallm_kernel<KIND, FUSED, EPI, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (attr_err != cudaSuccess) return fail_cuda(attr_err, "cudaFuncSetAttribute");
     // Largest shared-memory carve-out: the ring takes nearly all of it.
     const cudaError_t carve_err = cudaFuncSetAttribute(
-        gemm_smallm_kernel<KIND, FUSED, EPI>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        gemm_smallm_kernel<KIND, FUSED, EPI, ROPE>, cudaFuncAttributePreferredSharedMemoryCarveout,
         cudaSharedmemCarveoutMaxShared);
     if (carve_err != cudaSuccess) return fail_cuda(carve_err, "cudaFuncSetAttribute");
     set_for[dev] = true;
@@ -949,7 +949,7 @@ int launch_smallm_impl(const CUtensorMap& map_w, const CUtensorMap& map_x, const
   cfg.attrs = attr;
   cfg.numAttrs = switches().decode_overlap ? 1 : 0;
   const cudaError_t err =
-      cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND, FUSED, EPI>, map_w, map_x, p);
+      cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<KIND, FUSED, EPI, ROPE>, map_w, map_x, p);
   if (err != cudaSuccess) return fail_cuda(err, "gemm_smallm launch");
   return B12X_B200_OK;
 }
@@ -985,6 +985,11 @@ struct SmallMCall {
   const b12x_b200_epilogue_t* epilogue = nullptr;
   int64_t groups = 1;
   int64_t x_group_stride = 0;  // fused rows: elements between groups (0: group-major rows)
+  // Inverse rotary embedding in front of the fused MXFP8 quantizer (null positions: none).
+  const void* rope_positions = nullptr;
+  const void* rope_cos_sin = nullptr;
+  int rope_pos_i64 = 0, rope_cache_f32 = 0;
+  int rope_head_dim = 0, rope_nope_dim = 0, rope_dim = 0;
 };
 
 // Argument checks shared by the decode-shape entry points. On success *empty is set when there
@@ -994,6 +999,18 @@ int check_smallm(const SmallMCall& a, SmallMPlan* plan, int* sms_out, bool* empt
   const bool fused = a.x_src != nullptr;
   if (a.kind == B12X_B200_KIND_MXFP4 && fused)
     return fail(B12X_B200_ERR_UNSUPPORTED, "no activation quantizer produces MXFP4");
+  if (a.rope_positions || a.rope_cos_sin) {
+    if (!a.rope_positions || !a.rope_cos_sin)
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT, "inverse-RoPE needs both positions and cos_sin_cache");
+    if (!fused || a.kind != B12X_B200_KIND_MXFP8 || a.epilogue)
+      return fail(B12X_B200_ERR_UNSUPPORTED,
+                  "inverse-RoPE belongs to the fused MXFP8 activation quantizer without epilogue");
+    if (a.rope_head_dim <= 0 || a.rope_nope_dim < 0 || a.rope_dim <= 0 ||
+        a.rope_nope_dim + a.rope_dim != a.rope_head_dim || a.rope_head_dim % 32 != 0 ||
+        a.rope_nope_dim % 32 != 0 || a.rope_dim % 32 != 0 || a.k % a.rope_head_dim != 0)
+      return fail(B12X_B200_ERR_INVALID_ARGUMENT,
+                  "inverse-RoPE requires 32-aligned head_dim = nope_dim + rope_dim dividing K");
+  }
   if (a.kind != B12X_B200_KIND_MXFP8 && a.kind != B12X_B200_KIND_NVFP4 &&
       a.kind != B12X_B200_KIND_MXFP4)
     return fail(B12X_B200_ERR_INVALID_ARGUMENT, "unknown operand kind");
@@ -1088,6 +1105,13 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.sf_col0 = pl.sf_col0;
   p.x_gs = a.x_gs;
   p.raw_rows = pl.raw_rows;
+  p.rope_positions = a.rope_positions;
+  p.rope_cos_sin = a.rope_cos_sin;
+  p.rope_pos_i64 = a.rope_pos_i64;
+  p.rope_cache_f32 = a.rope_cache_f32;
+  p.rope_head_dim = a.rope_head_dim;
+  p.rope_nope_dim = a.rope_nope_dim;
+  p.rope_dim = a.rope_dim;
   if (a.epilogue) {
     p.bias = a.epilogue->bias;
     p.quant_values = static_cast<uint8_t*>(a.epilogue->quant_values);
@@ -1102,6 +1126,8 @@ int run_smallm(const SmallMCall& a, const SmallMPlan& pl, void* workspace,
   p.packed_store = (a.c_dtype != B12X_B200_FP32 && aligned16(a.c) && a.ldc % 8 == 0) ? 1 : 0;
   p.smem_bytes = pl.stages * pl.stage_bytes + kSmallMTailBytes;
   const int smem_bytes = pl.stages * pl.stage_bytes + kSmallMTailBytes;
+  if (a.rope_positions)   // checked: MXFP8, fused, no epilogue
+    return launch_smallm_impl<kMxfp8, true, false, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
   if (a.kind == B12X_B200_KIND_MXFP8)
     return fused ? launch_smallm<kMxfp8, true>(map_w, map_x, p, pl.grid, smem_bytes, a.stream)
                  : launch_smallm<kMxfp8, false>(map_w, map_x, p, pl.grid, smem_bytes, a.stream);
@@ -1225,6 +1251,33 @@ extern "C" int b12x_b200_gemm_smallm_fused_quant_grouped(
   a.epilogue = epilogue;
   a.groups = groups;
   a.x_group_stride = groups > 1 ? x_group_stride : 0;
+  return smallm_entry(a, workspace, workspace_bytes);
+}
+
+extern "C" int b12x_b200_gemm_smallm_fused_quant_grouped_inv_rope(
+    const void* x_bf16, int64_t ld_x, int64_t x_group_stride, const void* positions,
+    int positions_are_int64, const void* cos_sin_cache, int cache_is_fp32, int head_dim,
+    int nope_dim, int rope_dim, const void* w, const void* sf_w, void* c, int c_dtype,
+    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t groups,
+    void* workspace, int64_t workspace_bytes, int sm_count, int* status,
+    b12x_b200_stream_t stream) {
+  if (!x_bf16 || !positions || !cos_sin_cache)
+    return fail(B12X_B200_ERR_INVALID_ARGUMENT, "null pointer");
+  if (groups < 1) return fail(B12X_B200_ERR_INVALID_ARGUMENT, "groups must be positive");
+  if (groups > 1 && (x_group_stride < k || x_group_stride % 8 != 0))
+    return fail(B12X_B200_ERR_ALIGNMENT, "activation groups must be 16-byte aligned and K apart at least");
+  SmallMCall a = {B12X_B200_KIND_MXFP8, nullptr, nullptr, x_bf16, ld_x, nullptr, w, sf_w, c, c_dtype,
+                  alpha, m, n, k, ldc, sm_count, status, nullptr,
+                  reinterpret_cast<cudaStream_t>(stream)};
+  a.groups = groups;
+  a.x_group_stride = groups > 1 ? x_group_stride : 0;
+  a.rope_positions = positions;
+  a.rope_cos_sin = cos_sin_cache;
+  a.rope_pos_i64 = positions_are_int64 ? 1 : 0;
+  a.rope_cache_f32 = cache_is_fp32 ? 1 : 0;
+  a.rope_head_dim = head_dim;
+  a.rope_nope_dim = nope_dim;
+  a.rope_dim = rope_dim;
   return smallm_entry(a, workspace, workspace_bytes);
 }
 

@@ -91,6 +91,14 @@ struct SmallMParams {
   // BF16 rows (8 or 16) a stage holds behind the code tile.
   const float* x_gs;
   int raw_rows;
+  // Fused MXFP8 quantization with the inverse rotary embedding (ROPE instantiation only): row r
+  // is token r at position rope_positions[r]; in every head_dim-wide block of a group's K the
+  // trailing rope_dim elements are rotated back, interleaved pairs (even, odd), with
+  // cos = cache[pos * rope_dim + pair], sin = cache[pos * rope_dim + rope_dim / 2 + pair].
+  const void* rope_positions;   // int32 or int64 [M]
+  const void* rope_cos_sin;     // BF16 or FP32 [max_pos, rope_dim]
+  int rope_pos_i64, rope_cache_f32;
+  int rope_head_dim, rope_nope_dim, rope_dim;
   // Epilogue extras. bias: [N] values of the output dtype added to every row (null = none).
   // quant_*: MXFP8 re-quantization of the rounded output rows along N (null = off): E4M3 codes
   // [M, quant_ld], UE8M0 bytes row-major [M, quant_cols / 32] and/or in scale atoms, this GEMM's
@@ -217,9 +225,38 @@ struct FusedQuant {
 
   // Quantize the loaded rows into the stage: codes where TMA would have put them (row r at
   // r * 128, 16-byte chunk j at position j ^ (r % 8)), scale bytes into the activation atoms.
+  // Inverse rotary embedding of the lane's eight values (four interleaved pairs), in FP32
+  // before anything is rounded: even' = fma(even, cos, odd * sin), odd' = fma(odd, cos,
+  // -(even * sin)) (b12x/_lib/dense_gemm.py:3505-3530). `k` is the index of x[0] in the group's K.
+  __device__ static __forceinline__ void inverse_rope(const SmallMParams& p, int row, int k,
+                                                      float (&x)[8]) {
+    const int d = k % p.rope_head_dim;
+    if (d < p.rope_nope_dim || row >= p.m) return;
+    const long long pos = p.rope_pos_i64
+                              ? static_cast<const long long*>(p.rope_positions)[row]
+                              : static_cast<long long>(static_cast<const int*>(p.rope_positions)[row]);
+    const long long base = pos * p.rope_dim + ((d - p.rope_nope_dim) >> 1);
+    const int half = p.rope_dim >> 1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float c, sn;
+      if (p.rope_cache_f32) {
+        c = static_cast<const float*>(p.rope_cos_sin)[base + j];
+        sn = static_cast<const float*>(p.rope_cos_sin)[base + half + j];
+      } else {
+        c = __bfloat162float(static_cast<const __nv_bfloat16*>(p.rope_cos_sin)[base + j]);
+        sn = __bfloat162float(static_cast<const __nv_bfloat16*>(p.rope_cos_sin)[base + half + j]);
+      }
+      const float e = x[2 * j], o = x[2 * j + 1];
+      x[2 * j] = fmaf(e, c, __fmul_rn(o, sn));
+      x[2 * j + 1] = fmaf(o, c, -__fmul_rn(e, sn));
+    }
+  }
+
+  template <bool ROPE = false>
   __device__ static __forceinline__ void store(const SmallMParams& p, uint8_t* st, int wq, int lane,
                                                const uint4 (&buf)[kSlotsPerWarp], float gs,
-                                               float gs_rcp) {
+                                               float gs_rcp, int k0 = 0) {
     using T = SmallMTile<KIND>;
     uint8_t* x_tile = st + T::kXOffset;
     uint8_t* sf_x = st + T::kWBytes + T::kSfBytes;
@@ -230,7 +267,15 @@ struct FusedQuant {
       if (wq + s * kWarps >= ((KIND == kNvfp4) ? p.m : (p.m + 1) / 2)) continue;
       float x[8];
       unpack8<__nv_bfloat16>(buf[s], x);
-      float amax = amax8<__nv_bfloat16>(buf[s]);
+      float amax;
+      if constexpr (ROPE) {
+        inverse_rope(p, row, k0 + elem_of(lane), x);
+        amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+      } else {
+        amax = amax8<__nv_bfloat16>(buf[s]);
+      }
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       if (KIND == kNvfp4) {
         const float sc = __fmul_rn(gs, __fdiv_rn(amax, 6.0f));
@@ -357,7 +402,7 @@ __device__ __forceinline__ void store_rows8_packed(const SmallMParams& p, uint16
   }
 }
 
-template <int KIND, bool FUSED, bool EPI>
+template <int KIND, bool FUSED, bool EPI, bool ROPE = false>
 __global__ void __launch_bounds__(FUSED ? 512 : 256, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_x, const SmallMParams p) {
@@ -553,8 +598,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         gs = *p.x_gs;
         gs_rcp = (gs == 0.0f) ? 0.0f : __frcp_rn(gs);
       }
+      if constexpr (ROPE) grid_dependency_wait();  // positions may come from the previous grid
       int stage = 0;
       uint32_t phase = 0;
+      int kt_q = u_begin % p.k_tiles;   // k-tile of the unit (used by the ROPE variant)
       for (int u = u_begin; u < u_end; ++u) {
         // Weights and raw rows of the unit have landed (which also means the tensor core is
         // done with whatever the stage held before).
@@ -566,7 +613,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w,
         uint8_t* st = smem + stage * p.stage_bytes;
         uint4 raw[Q::kSlotsPerWarp];
         Q::load(p, st, wq, lane, raw);
-        Q::store(p, st, wq, lane, raw, gs, gs_rcp);
+        Q::template store<ROPE>(p, st, wq, lane, raw, gs, gs_rcp, kt_q * T::kElemsPerStage);
+        if (++kt_q == p.k_tiles) kt_q = 0;
         // The tensor core reads the stage through the async proxy.
         fence_proxy_async_smem();
         __syncwarp();

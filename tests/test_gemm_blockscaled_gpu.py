@@ -669,12 +669,77 @@ def test_mm_fused_quant_a_grouped_equals_the_groups_one_by_one(m, n, k, groups, 
         # associate differently: equal to within one rounding of the output.
         diff = float((alone[:, :, 0].float() - out[:, :, g].float()).abs().max())
         assert diff <= 2.0 ** -8 * float(np.abs(refs[g]).max()), (g, diff)
-    with pytest.raises(NotImplementedError, match="inverse-RoPE"):
+    with pytest.raises(ValueError, match="both positions and cos_sin_cache"):
         blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups,
-                                             positions=torch.zeros(m, dtype=torch.int64, device=DEV),
-                                             cos_sin_cache=torch.zeros((4, 64), device=DEV))
+                                             positions=torch.zeros(m, dtype=torch.int64, device=DEV))
     with pytest.raises(ValueError, match="source groups"):
         blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups + 1)
+    from sparkinfer_b200._lib.launch import check_kernel_status
+    check_kernel_status(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,groups,head,nope,rope,cache_dtype,pos_dtype", [
+    (3, 128, 512, 2, 128, 96, 32, torch.float32, torch.int64),
+    (3, 128, 512, 2, 128, 96, 32, torch.bfloat16, torch.int64),
+    (8, 1024, 2048, 4, 512, 448, 64, torch.float32, torch.int32),
+    (1, 256, 1024, 1, 256, 192, 64, torch.bfloat16, torch.int32),
+])
+def test_mm_fused_quant_a_grouped_inverse_rope(m, n, k, groups, head, nope, rope, cache_dtype, pos_dtype):
+    """The inverse-RoPE prologue of the grouped fused quantizer, as the reference tests it
+    (tests/gemm/test_gemm_wo_projection.py:340-372, 983-1040): an identity rotation reproduces
+    the plain fused call bit for bit; a real rotation equals rotating (oracle, FP32), quantizing
+    (oracle) and multiplying the codes with the ordinary grouped GEMM."""
+    from gpu_util import DEV, assert_gemm_close, to_dev
+    from sparkinfer_b200._lib import layout
+    from sparkinfer_b200.gemm import blockscaled
+
+    source = torch.stack([seeded_bf16(900 + g + m, (m, k), 0.125) for g in range(groups)], dim=1).contiguous()
+    b_vals, b_sw, b_deq = [], [], []
+    for g in range(groups):
+        bv, bsr = O.quantize_mxfp8_rows(seeded_bf16(950 + g + n, (n, k), 0.03).float().numpy())
+        b_vals.append(bv); b_sw.append(O.swizzle_scales(bsr, 127)); b_deq.append(O.dequantize_mxfp8(bv, bsr))
+    src_dev = source.to(DEV)
+    b_t = to_dev(np.stack(b_vals)).view(torch.float8_e4m3fn).as_strided((n, k, groups), (k, 1, n * k))
+    sfb = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(b_sw)), n, k, groups, 32)
+    max_pos = 64
+    positions = (torch.arange(7, 7 + m) % max_pos).to(pos_dtype)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rope, 2, dtype=torch.float32) / rope))
+    freqs = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv_freq)
+    cache = torch.cat([freqs.cos(), freqs.sin()], dim=-1).to(cache_dtype)
+    kw = dict(groups=groups, head_dim=head, nope_dim=nope, rope_dim=rope)
+
+    identity = torch.zeros((max_pos, rope), dtype=cache_dtype)
+    identity[:, : rope // 2] = 1
+    plain = blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, groups=groups)
+    same = blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, positions=positions.to(DEV),
+                                                cos_sin_cache=identity.to(DEV), **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(plain, same)
+
+    got = blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, positions=positions.to(DEV),
+                                               cos_sin_cache=cache.to(DEV), **kw)
+    torch.cuda.synchronize()
+    assert not torch.equal(got, plain)
+    a_vals, a_sw = [], []
+    for g in range(groups):
+        rotated = O.inverse_rope_rows(source[:, g].float().numpy(), positions.numpy(),
+                                      cache.float().numpy(), head, nope, rope)
+        av, asr = O.quantize_mxfp8_rows(rotated)
+        a_vals.append(av); a_sw.append(O.swizzle_scales(asr, 127))
+        assert_gemm_close(got[:, :, g], O.dequantize_mxfp8(av, asr) @ b_deq[g].T)
+    a_t = to_dev(np.stack(a_vals)).view(torch.float8_e4m3fn).as_strided((m, k, groups), (k, 1, m * k))
+    sfa = layout.convert_sf_to_mma_layout(to_dev(np.concatenate(a_sw)), m, k, groups, 32)
+    unfused = blockscaled.mm((a_t, sfa), (b_t, sfb), ab_dtype="float8_e4m3fn",
+                             sf_dtype="float8_e8m0fnu", sf_vec_size=32, c_dtype="bfloat16")
+    torch.cuda.synchronize()
+    # Same codes and scales (the kernel's rotation and the oracle's agree to the bit); the two
+    # launches may split K differently, so equal to within one rounding of the output.
+    diff = float((unfused.float() - got.float()).abs().max())
+    assert diff <= 2.0 ** -8 * float(got.float().abs().max()), diff
+    with pytest.raises(ValueError, match="32-aligned head_dim"):
+        blockscaled.mm_fused_quant_a_grouped(src_dev, b_t, sfb, positions=positions.to(DEV),
+                                             cos_sin_cache=cache.to(DEV), groups=groups,
+                                             head_dim=head, nope_dim=nope - 16, rope_dim=rope)
     from sparkinfer_b200._lib.launch import check_kernel_status
     check_kernel_status(DEV)
 

@@ -286,6 +286,25 @@ def test_grouped_fused_quant_host_checks_fire_before_any_launch():
             torch.zeros((4, groups, 2 * k), dtype=torch.bfloat16)[:, :, :k], b, sfb, groups=groups)
     with pytest.raises(ValueError, match=r"B must have shape \[N,256,3\]"):
         blockscaled.mm_fused_quant_a_grouped(src, b[:, :128], sfb, groups=groups)
-    with pytest.raises(NotImplementedError, match="inverse-RoPE"):
+    positions = torch.zeros(4, dtype=torch.int64)
+    with pytest.raises(ValueError, match="needs both positions and cos_sin_cache"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions)
+    rope = dict(head_dim=128, nope_dim=96, rope_dim=32)
+    with pytest.raises(ValueError, match=r"positions must have shape \(4,\)"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions[:3],
+                                             cos_sin_cache=torch.zeros((8, 32)), **rope)
+    with pytest.raises(ValueError, match=r"cos_sin_cache must have shape \[max_pos, 32\]"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions,
+                                             cos_sin_cache=torch.zeros((8, 64)), **rope)
+    with pytest.raises(ValueError, match="32-aligned head_dim = nope_dim \+ rope_dim"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions,
+                                             cos_sin_cache=torch.zeros((8, 32)), head_dim=128,
+                                             nope_dim=80, rope_dim=32)
+    with pytest.raises(ValueError, match="positions must be int32/int64"):
         blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups,
-                                             positions=torch.zeros(4, dtype=torch.int64))
+                                             positions=positions.float(),
+                                             cos_sin_cache=torch.zeros((8, 32)), **rope)
+    with pytest.raises(ValueError, match="cache must be bf16/fp32"):
+        blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions,
+                                             cos_sin_cache=torch.zeros((8, 32), dtype=torch.float16),
+                                             **rope)

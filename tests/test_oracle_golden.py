@@ -165,3 +165,23 @@ def test_bmm_oracle_scale_byte_255_is_nan():
     scales = np.array([[[255], [127]]], dtype=np.uint8)
     deq = O.dequantize_rowwise_mxfp8_bf16(values, scales)
     assert np.isnan(deq[0, 0]).all() and (deq[0, 1] == 1.0).all()
+
+
+def test_inverse_rope_oracle_identity_and_formula():
+    """cos = 1 / sin = 0 leaves the rows untouched (the case the reference's own test pins,
+    tests/gemm/test_gemm_wo_projection.py:340-372); a real rotation touches only the rotary part
+    of every head and follows even*cos + odd*sin, odd*cos - even*sin."""
+    rng = np.random.RandomState(0)
+    x = O.bf16_round(rng.randn(3, 512).astype(np.float32))
+    identity = np.zeros((8, 32), np.float32)
+    identity[:, :16] = 1
+    assert np.array_equal(O.inverse_rope_rows(x, [0, 1, 2], identity, 128, 96, 32), x)
+    theta = rng.rand(8, 16).astype(np.float32)
+    cache = np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)
+    y = O.inverse_rope_rows(x, [3, 4, 5], cache, 128, 96, 32).reshape(3, 4, 128)
+    xr = x.reshape(3, 4, 128)
+    assert np.array_equal(y[:, :, :96], xr[:, :, :96])
+    c, s = cache[[3, 4, 5], :16][:, None, :], cache[[3, 4, 5], 16:][:, None, :]
+    e, o = xr[:, :, 96::2], xr[:, :, 97::2]
+    np.testing.assert_allclose(y[:, :, 96::2], e * c + o * s, atol=1e-6)
+    np.testing.assert_allclose(y[:, :, 97::2], o * c - e * s, atol=1e-6)
