@@ -1,44 +1,41 @@
-"""GEMM op group.
+"""The ``gemm`` group.
 
-- ``mm``: block-scaled dense matrix multiplication over ``[M, K, L]`` stacks (the function
-  behind ``blockscaled.mm``).
-- ``bmm`` (+ ``prewarm_bmm``, ``can_implement_bmm``, ``is_bmm_supported``): dtype-dispatched
-  batched matrix multiplication, BF16 x rowwise-MXFP8.
-- ``blockscaled``, ``mxfp8_linear``, ``block_fp8_linear``, ``tensor_fp8_linear``: op packages.
-
-Same flat names as b12x/gemm/__init__.py:18-50; everything resolves lazily.
+Op packages: ``blockscaled``, ``block_fp8_linear``, ``mxfp8_linear``, ``tensor_fp8_linear``.
+Plain functions of the group: ``mm`` (what ``blockscaled.mm`` is), ``bmm`` and its helpers
+``prewarm_bmm`` / ``can_implement_bmm`` / ``is_bmm_supported`` (a batched BF16 x MXFP8 product;
+implementation under the private package ``_bmm`` because a function and a child package
+cannot share one name). The group's layout follows b12x/gemm/__init__.py:18-50. Nothing is
+imported until a name is first used, so ``import sparkinfer_b200.gemm`` pulls in neither torch
+nor the CUDA library.
 """
 
 from __future__ import annotations
 
-import importlib
-from typing import Any
+from importlib import import_module
 
-_OP_MODULES = ("blockscaled", "block_fp8_linear", "mxfp8_linear", "tensor_fp8_linear")
-_FUNCTIONS = {
-    "mm": (".._lib.dense_gemm", "dense_gemm"),
-    "bmm": ("._bmm.api", "bmm"),
-    "prewarm_bmm": ("._bmm.api", "prewarm_bmm"),
-    "can_implement_bmm": ("._bmm.api", "can_implement_bmm"),
-    "is_bmm_supported": ("._bmm.api", "is_bmm_supported"),
+_PACKAGES = frozenset({"blockscaled", "block_fp8_linear", "mxfp8_linear", "tensor_fp8_linear"})
+
+# public name -> "module:attribute" (module relative to this package)
+_ALIASES = {
+    "mm": ".._lib.dense_gemm:dense_gemm",
+    **{name: f"._bmm.api:{name}"
+       for name in ("bmm", "prewarm_bmm", "can_implement_bmm", "is_bmm_supported")},
 }
 
-
-def __getattr__(name: str) -> Any:
-    if name in _OP_MODULES:
-        module = importlib.import_module(f".{name}", __name__)
-        globals()[name] = module
-        return module
-    if name in _FUNCTIONS:
-        module_name, attribute = _FUNCTIONS[name]
-        value = getattr(importlib.import_module(module_name, __name__), attribute)
-        globals()[name] = value
-        return value
-    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+__all__ = sorted(_PACKAGES | set(_ALIASES))
 
 
-def __dir__() -> list[str]:
-    return sorted([*_OP_MODULES, *_FUNCTIONS])
+def __getattr__(name: str):
+    if name in _PACKAGES:
+        found = import_module(f"{__name__}.{name}")
+    elif name in _ALIASES:
+        module, _, attribute = _ALIASES[name].partition(":")
+        found = getattr(import_module(module, __name__), attribute)
+    else:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    globals()[name] = found   # next access skips this hook
+    return found
 
 
-__all__ = [*_FUNCTIONS, *_OP_MODULES]
+def __dir__():
+    return list(__all__)
