@@ -21,32 +21,6 @@ CUDA graph.
         gemm.bmm(q_nope, (w_codes, w_scales), absorbed, **kind)
 """
 
-from __future__ import annotations
+from ..._lib.registry import install
 
-from typing import TYPE_CHECKING
-
-from ..._lib.meta import OpMeta, Provenance, install_lazy_api
-
-_REFERENCE = Provenance(
-    repo="local-inference-lab/sparkinfer",
-    commit="b12x-1.1.0",
-    paths=("b12x/gemm/_bmm/api.py", "b12x/gemm/_shared/mxfp8_bmm.py"),
-)
-
-META = OpMeta(
-    group="gemm",
-    name="bmm",
-    entry_points=("bmm", "prewarm_bmm", "can_implement_bmm", "is_bmm_supported"),
-    api_style="oneshot",
-    recipes=("mxfp8",),
-    dtypes=("bf16", "fp8_e4m3"),
-    provenance=_REFERENCE,
-    since="0.2.0",
-    test_path="tests/test_bmm_gpu.py",
-    notes="dtype-dispatched batched product; one backend: BF16 activations x rowwise MXFP8",
-)
-
-install_lazy_api(globals(), META)
-
-if TYPE_CHECKING:
-    from .api import bmm, can_implement_bmm, is_bmm_supported, prewarm_bmm  # noqa: F401
+install(globals(), "gemm.bmm")

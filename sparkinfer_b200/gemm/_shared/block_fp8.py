@@ -347,9 +347,16 @@ def prewarm_block_fp8_linear_mxfp8(packed_weight: BlockFP8LinearWeight,
         torch.cuda.synchronize(device)
 
 
+def bind_block_fp8_linear_scratch(plan: BlockFP8LinearScratchPlan, **kwargs) -> BlockFP8LinearBinding:
+    """``block_fp8_linear.bind``: attach the run-time tensors and the caller's scratch to a plan.
+    Only views are made (b12x/gemm/block_fp8_linear/api.py:40-44)."""
+    return plan.bind(**kwargs)
+
+
 __all__ = [
     "BlockFP8LinearBinding", "BlockFP8LinearScratchCaps", "BlockFP8LinearScratchPlan",
-    "BlockFP8LinearWeight", "build_block_fp8_linear_binding", "block_fp8_linear_mxfp8",
+    "BlockFP8LinearWeight", "bind_block_fp8_linear_scratch", "build_block_fp8_linear_binding",
+    "block_fp8_linear_mxfp8",
     "pack_block_fp8_linear_weight_mxfp8", "plan_block_fp8_linear_scratch",
     "prewarm_block_fp8_linear_mxfp8", "quantize_block_fp8_linear_input_mxfp8",
 ]

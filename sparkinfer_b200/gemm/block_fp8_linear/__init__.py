@@ -16,33 +16,6 @@ Example:
     y = bfl.run(binding=binding)
 """
 
-from __future__ import annotations
+from ..._lib.registry import install
 
-from typing import TYPE_CHECKING
-
-from ..._lib.meta import OpMeta, Provenance, install_lazy_api
-
-META = OpMeta(
-    name="block_fp8_linear",
-    group="gemm",
-    api_style="planned",
-    entry_points=("Caps", "Plan", "Binding", "Weight", "plan", "bind", "run", "pack_weight",
-                  "quantize_input", "prewarm", "is_supported"),
-    dtypes=("bf16", "fp16", "fp8_e4m3"),
-    recipes=("block_fp8", "mxfp8"),
-    provenance=Provenance(
-        repo="local-inference-lab/sparkinfer",
-        commit="b12x-1.1.0",
-        paths=("b12x/gemm/block_fp8_linear/api.py", "b12x/gemm/_shared/block_fp8.py"),
-    ),
-    test_path="tests/test_linears_gpu.py",
-    since="0.1.0",
-)
-
-if TYPE_CHECKING:
-    from .api import (  # noqa: F401
-        Binding, Caps, Plan, Weight, bind, is_supported, pack_weight, plan, prewarm,
-        quantize_input, run,
-    )
-
-install_lazy_api(globals(), META)
+install(globals(), "gemm.block_fp8_linear")

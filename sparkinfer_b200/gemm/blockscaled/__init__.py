@@ -15,31 +15,6 @@ Example:
     )
 """
 
-from __future__ import annotations
+from ..._lib.registry import install
 
-from typing import TYPE_CHECKING
-
-from ..._lib.meta import OpMeta, Provenance, install_lazy_api
-
-META = OpMeta(
-    name="blockscaled",
-    group="gemm",
-    api_style="oneshot",
-    entry_points=("mm", "mm_fused_quant_a", "mm_fused_quant_a_grouped", "mm_fused_quant_a_nvfp4",
-                  "is_supported"),
-    dtypes=("bf16", "fp16", "fp32", "fp8_e4m3", "fp4_e2m1"),
-    recipes=("nvfp4", "mxfp8", "block_fp8"),
-    provenance=Provenance(
-        repo="local-inference-lab/sparkinfer",
-        commit="b12x-1.1.0",
-        paths=("b12x/gemm/blockscaled/api.py", "b12x/_lib/dense_gemm.py"),
-    ),
-    test_path="tests/test_gemm_blockscaled_gpu.py",
-    since="0.1.0",
-)
-
-if TYPE_CHECKING:  # static analysis only; runtime resolution is lazy
-    from .api import (is_supported, mm, mm_fused_quant_a, mm_fused_quant_a_grouped,  # noqa: F401
-                      mm_fused_quant_a_nvfp4)
-
-install_lazy_api(globals(), META)
+install(globals(), "gemm.blockscaled")

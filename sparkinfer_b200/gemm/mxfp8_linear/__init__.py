@@ -12,29 +12,6 @@ Example:
     out = mxfp8_linear.mm(x, weight, expected_m=x.shape[0])
 """
 
-from __future__ import annotations
+from ..._lib.registry import install
 
-from typing import TYPE_CHECKING
-
-from ..._lib.meta import OpMeta, Provenance, install_lazy_api
-
-META = OpMeta(
-    name="mxfp8_linear",
-    group="gemm",
-    api_style="oneshot",
-    entry_points=("Weight", "mm", "pack_weight", "is_supported"),
-    dtypes=("bf16", "fp16"),
-    recipes=("mxfp8",),
-    provenance=Provenance(
-        repo="local-inference-lab/sparkinfer",
-        commit="b12x-1.1.0",
-        paths=("b12x/gemm/mxfp8_linear/api.py", "b12x/gemm/mxfp8_linear/_kernel.py"),
-    ),
-    test_path="tests/test_linears_gpu.py",
-    since="0.1.0",
-)
-
-if TYPE_CHECKING:
-    from .api import Weight, is_supported, mm, pack_weight  # noqa: F401
-
-install_lazy_api(globals(), META)
+install(globals(), "gemm.mxfp8_linear")

@@ -65,6 +65,14 @@ def is_tensor_fp8_linear_supported() -> tuple[bool, str | None]:
     return True, None
 
 
+def is_supported(device=None) -> bool:
+    """The op's capability probe: the device / library check every op makes, and the kernel's
+    own verdict (always yes here: the kernels are compiled ahead of time)."""
+    from ..._lib.gating import default_is_supported
+
+    return default_is_supported(device) and is_tensor_fp8_linear_supported()[0]
+
+
 def _check_out_dtype(dtype: torch.dtype) -> None:
     if dtype not in LINEAR_DTYPES:
         raise ValueError(f"tensor FP8 linear output must be bf16/fp16, got {dtype}")

@@ -5,29 +5,6 @@ scales and the MMA-layout scales the block-scaled GEMM consumes). Stands in for
 ``b12x.quantization.mxfp8`` (b12x/quantization/mxfp8/api.py).
 """
 
-from __future__ import annotations
+from ..._lib.registry import install
 
-from typing import TYPE_CHECKING
-
-from ..._lib.meta import OpMeta, Provenance, install_lazy_api
-
-META = OpMeta(
-    name="mxfp8",
-    group="quantization",
-    api_style="oneshot",
-    entry_points=("quantize_rows", "is_supported"),
-    dtypes=("bf16", "fp16", "fp8_e4m3"),
-    recipes=("mxfp8",),
-    provenance=Provenance(
-        repo="local-inference-lab/sparkinfer",
-        commit="b12x-1.1.0",
-        paths=("b12x/quantization/mxfp8/api.py", "b12x/_lib/quant/mxfp8_rows.py"),
-    ),
-    test_path="tests/test_quantizers_gpu.py",
-    since="0.1.0",
-)
-
-if TYPE_CHECKING:
-    from .api import is_supported, quantize_rows  # noqa: F401
-
-install_lazy_api(globals(), META)
+install(globals(), "quantization.mxfp8")
