@@ -296,7 +296,7 @@ def test_grouped_fused_quant_host_checks_fire_before_any_launch():
     with pytest.raises(ValueError, match=r"cos_sin_cache must have shape \[max_pos, 32\]"):
         blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions,
                                              cos_sin_cache=torch.zeros((8, 64)), **rope)
-    with pytest.raises(ValueError, match="32-aligned head_dim = nope_dim \+ rope_dim"):
+    with pytest.raises(ValueError, match=r"32-aligned head_dim = nope_dim \+ rope_dim"):
         blockscaled.mm_fused_quant_a_grouped(src, b, sfb, groups=groups, positions=positions,
                                              cos_sin_cache=torch.zeros((8, 32)), head_dim=128,
                                              nope_dim=80, rope_dim=32)
