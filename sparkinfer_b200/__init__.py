@@ -18,7 +18,8 @@ import importlib
 import sys
 from typing import Any
 
-from ._lib.meta import OpMeta, Provenance
+from ._lib import registry as _registry
+from ._lib.registry import OpMeta, Provenance
 from ._lib.runtime_control import (
     KernelResolutionFrozenError,
     compilation_frozen,
@@ -31,11 +32,13 @@ from ._lib.runtime_control import (
 
 __version__ = "0.1.0"
 
-# group -> op names; one directory per op, checked by tests/test_registry.py.
-_OPS: dict[str, tuple[str, ...]] = {
-    "gemm": ("blockscaled", "mxfp8_linear", "block_fp8_linear", "tensor_fp8_linear", "bmm"),
-    "quantization": ("nvfp4", "mxfp8"),
-}
+# group -> op names, read off the op table; one directory per op, checked by
+# tests/test_registry.py.
+_OPS: dict[str, tuple[str, ...]] = {}
+for _qualname in _registry.OPS:
+    _group, _, _name = _qualname.partition(".")
+    _OPS[_group] = (*_OPS.get(_group, ()), _name)
+del _qualname, _group, _name
 
 # A group-level function cannot share its name with a child module: ``gemm.bmm`` is a function,
 # its metadata and implementation live in a private package (b12x/__init__.py:64-72).
